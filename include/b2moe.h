@@ -1,0 +1,178 @@
+/* b2moe — C ABI of the B200 (sm_100a) mixture-of-experts layer path.
+ *
+ * Drop-in boundary for tqLLM's expert-layer interface. tqLLM calls this path through the C++ virtual
+ * tqllm::WeightFormat (src/formats/weight/weight_format.hpp:33-110) and the free functions of namespace tqllm_cuda
+ * (src/experts/moe_kernels.cuh:7-82, src/experts/moe_common.cuh:11-22); its C plugin ABI (include/tqllm/plugin.h:36-75)
+ * carries only dequant and dense matvec and forwards every expert_* call to the built-in, so the seam is this C ABI
+ * plus the C++ adapter in tqllm_b200/adapter/ that implements the reference's virtuals on top of it.
+ *
+ * Conventions (identical to the reference's, src/experts/moe_kernels.cuh:29, src/formats/weight/quant_u4h.inc:445,658):
+ *   - every pointer is DEVICE memory unless a parameter says "host"; the caller owns all of it;
+ *   - stacked expert weights are [experts * rows][cols]; ids are [n][topk] int32, id -1 = skip the assignment;
+ *   - assignment a = token * topk + slot; per-assignment outputs are [n * topk][rows];
+ *   - every entry point is stream-ordered, does no host synchronisation, allocates nothing and keeps no mutable
+ *     global state: scratch comes from a caller-provided workspace (capture-safe, re-entrant across streams);
+ *   - return value: 0 = ok, otherwise a b2moe_status code (b2moe_status_string gives the text). Nothing is launched
+ *     when the arguments are rejected. There is no CPU fallback: without a CUDA device every compute entry point
+ *     returns B2MOE_ERR_CUDA.
+ */
+#ifndef B2MOE_H
+#define B2MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B2MOE_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define B2MOE_API __attribute__((visibility("default")))
+#else
+#define B2MOE_API
+#endif
+
+typedef void * b2moe_stream; /* cudaStream_t */
+
+enum b2moe_status {
+    B2MOE_OK = 0,
+    B2MOE_ERR_SHAPE = 1,     /* a dimension is out of range for the kernel (reference: std::invalid_argument) */
+    B2MOE_ERR_ALIGN = 2,     /* a pointer is not 16-byte aligned */
+    B2MOE_ERR_FORMAT = 3,    /* GGUF type id is not one of the five block formats of this path */
+    B2MOE_ERR_NULL = 4,      /* a required pointer is null */
+    B2MOE_ERR_WORKSPACE = 5, /* the workspace is smaller than b2moe_*_workspace_bytes says */
+    B2MOE_ERR_CUDA = 6,      /* a CUDA call or launch failed (reference: std::runtime_error) */
+    B2MOE_ERR_CAPACITY = 7   /* a per-expert or per-peer capacity was exceeded */
+};
+
+/* GGUF type ids of the block formats (src/core/gguf.hpp:18-37) */
+enum b2moe_type { B2MOE_Q4_K = 12, B2MOE_IQ4_NL = 20, B2MOE_IQ3_S = 21, B2MOE_IQ4_XS = 23, B2MOE_NVFP4G = 323 };
+enum b2moe_dtype { B2MOE_F32 = 0, B2MOE_F16 = 1, B2MOE_BF16 = 2 };
+/* MoeGating values, src/experts/moe.hpp:20-26 (the two the device path implements) */
+enum b2moe_gating { B2MOE_SOFTMAX = 1, B2MOE_SIGMOID = 2 };
+
+B2MOE_API const char * b2moe_status_string(int32_t status);
+B2MOE_API int32_t b2moe_abi_version(void);
+/* The 512-entry IQ3_S grid and the 16 IQ4_NL values the library was built with (host memory, for test harnesses). */
+B2MOE_API void b2moe_codebooks(uint32_t * iq3s_grid_512, int8_t * kvalues_iq4nl_16);
+
+/* ---- expert banks ---------------------------------------------------------------------------------------------
+ * A bank is one stacked expert matrix repacked from GGUF block bytes into 16-row tiles whose bytes sit in the order
+ * the kernels' lanes consume them. Replaces the loaders Q4_K::load / IQ3_S::load / IQ4_XS::load / IQ4_NL::load /
+ * NVFP4G::load (src/formats/weight/q4.cpp:807-825, 300-318, 582-600, 537-568, 500-523). */
+typedef struct b2moe_bank {
+    const void * data; /* tiles: [experts][ceil(rows/16)][cols / k_tile][tile bytes] */
+    const void * aux;  /* NVFP4G: f32 tensor scale per padded row [experts][16*ceil(rows/16)]; NULL otherwise */
+    uint32_t type;     /* b2moe_type */
+    int32_t experts, rows, cols;
+} b2moe_bank;
+
+/* bytes of `rows` x `cols` in GGUF block form (host arithmetic; 0 when the type or shape is invalid) */
+B2MOE_API size_t b2moe_raw_bytes(uint32_t type, int32_t rows, int32_t cols);
+/* bytes of one expert's matrix in bank form, and of its aux array (0 when the type has none) */
+B2MOE_API size_t b2moe_bank_bytes(uint32_t type, int32_t rows, int32_t cols);
+B2MOE_API size_t b2moe_bank_aux_bytes(uint32_t type, int32_t rows, int32_t cols);
+/* raw GGUF blocks (device, [experts*rows] rows) -> bank. `data`/`aux` are the caller's buffers of experts * the sizes above. */
+B2MOE_API int32_t b2moe_bank_load(uint32_t type, const void * raw, int32_t experts, int32_t rows, int32_t cols, void * data,
+                        void * aux, b2moe_stream stream);
+/* bank -> fp32 [experts*rows][cols], bit-identical to dequantize_host (src/formats/weight/dequant.cpp:393-606) */
+B2MOE_API int32_t b2moe_dequant_dump(const b2moe_bank * bank, float * out, b2moe_stream stream);
+
+/* ---- routing --------------------------------------------------------------------------------------------------
+ * b2moe_router replaces moe_router / moe_router_f32 (src/experts/moe.cu:17-33,237-247): logits[t][r] = W[r] . x[t] for
+ * r < experts, and column `experts` = shared_gate . x[t] when shared_gate is given. ld = row stride of logits
+ * (the reference uses experts + 1). x is [n][hidden] of x_dtype. */
+B2MOE_API int32_t b2moe_router(const float * router_w, const float * shared_gate, const void * x, int32_t x_dtype, float * logits,
+                     int32_t ld, int32_t hidden, int32_t experts, int32_t n, b2moe_stream stream);
+/* replaces moe_topk (src/experts/moe.cu:35-166,248-267): softmax over experts, top-k (larger value, then lower index),
+ * weights = p / max(sum of selected p, 6.103515625e-5) * (scale == 0 ? 1 : scale); shared_weights[t] =
+ * sigmoid(logits[t][experts]) when shared_weights is given. experts <= 4096. */
+B2MOE_API int32_t b2moe_topk_softmax(const float * logits, int32_t ld, int32_t * ids, float * weights, float * shared_weights,
+                           int32_t experts, int32_t topk, int32_t n, float scale, b2moe_stream stream);
+/* replaces moe_common::route (src/experts/moe_common.cu:18-70,197-203): p = sigmoid(logits); select top-k of p + bias
+ * (bias may be null); weights = p[selected], divided by their clamped sum when norm, times scale unless 0 or 1. */
+B2MOE_API int32_t b2moe_route_sigmoid(const float * logits, int32_t ld, const float * bias, int32_t * ids, float * weights,
+                            int32_t experts, int32_t topk, int32_t norm, float scale, int32_t n, b2moe_stream stream);
+
+/* ---- dispatch -------------------------------------------------------------------------------------------------
+ * Token -> expert dispatch: per-expert histogram, exclusive prefix sum, stable permutation (assignment indices in
+ * ascending order inside each expert). Replaces moe_group (src/experts/moe.cu:168-176,268-273, whose list order is
+ * non-deterministic), the host builder fill_pass_lists (src/models/qwen/qwen4exp/prefill_plan.hpp:62-76) and
+ * moe_dedup_maps (src/experts/moe.cu:453-483). With shared_tokens = n the always-on expert is appended as expert
+ * `experts` holding the virtual assignments n*topk .. n*topk + n - 1 (token = a - n*topk), the device form of
+ * moe_extend_ids (src/experts/moe.cu:209-222).
+ *
+ * The plan is one int32 device array of b2moe_plan_ints(experts, n * topk, shared_tokens) entries:
+ *   [0] number of active experts   [1] number of grouped assignments   [2..3] reserved
+ *   then counts[E1], offsets[E1 + 1], active[E1] (ids of experts with count > 0, ascending), perm[A + shared_tokens]
+ * with E1 = experts + 1. b2moe_plan_view gives the element offsets of the four arrays (host arithmetic). */
+typedef struct b2moe_plan_view { int64_t counts, offsets, active, perm, total; } b2moe_plan_view;
+B2MOE_API int64_t b2moe_plan_ints(int32_t experts, int32_t assignments, int32_t shared_tokens);
+B2MOE_API void b2moe_plan_view_of(int32_t experts, int32_t assignments, int32_t shared_tokens, b2moe_plan_view * view);
+/* workspace: b2moe_dispatch_workspace_bytes(experts, assignments) bytes, 16-byte aligned */
+B2MOE_API size_t b2moe_dispatch_workspace_bytes(int32_t experts, int32_t assignments);
+B2MOE_API int32_t b2moe_dispatch(const int32_t * ids, int32_t n, int32_t topk, int32_t experts, int32_t shared_tokens, int32_t * plan,
+                       void * workspace, size_t workspace_bytes, b2moe_stream stream);
+/* moe_group-compatible view of a plan (src/experts/moe_kernels.cuh:29): counts [experts], groups [experts][n] */
+B2MOE_API int32_t b2moe_plan_to_groups(const int32_t * plan, int32_t n, int32_t topk, int32_t experts, int32_t * counts,
+                             int32_t * groups, b2moe_stream stream);
+
+/* ---- expert products ------------------------------------------------------------------------------------------
+ * act[a][f] = silu(gate_e(a)[f] . x[token(a)]) * (up_e(a)[f] . x[token(a)]) for every grouped assignment a: the
+ * paired gate/up product with the SwiGLU fused (replaces expert_matvec2 / expert_matvec_dedup2 / expert_gemm_gateup +
+ * moe_swiglu: src/formats/weight/weight_format.hpp:58-73, src/formats/weight/quant.cu:167-233,384-405,
+ * src/experts/moe.cu:188-195). shared_* may be null when the plan has no shared expert. act is fp32
+ * [n*topk + shared_tokens][ff]; rows of skipped assignments are left untouched. */
+B2MOE_API int32_t b2moe_expert_gateup_swiglu(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_bank * shared_gate,
+                                   const b2moe_bank * shared_up, const void * x, int32_t x_dtype, const int32_t * plan,
+                                   int32_t n, int32_t topk, int32_t shared_tokens, float * act, b2moe_stream stream);
+/* y[a][h] = down_e(a)[h] . act[a]   (replaces expert_matvec / expert_matvec_dedup / expert_gemm with
+ * per_expert_input: src/formats/weight/weight_format.hpp:51-63, src/formats/weight/quant.cu:69-143,286-317). y fp32. */
+B2MOE_API int32_t b2moe_expert_down(const b2moe_bank * down, const b2moe_bank * shared_down, const float * act, const int32_t * plan,
+                          int32_t n, int32_t topk, int32_t shared_tokens, float * y, b2moe_stream stream);
+/* out[t] = sum_s weights[t][s] * y[t*topk + s] (slot order, skipped where ids[t][s] < 0 when ids is given)
+ *          + shared_weights[t] (1 when null) * y[n*topk + t] when shared_tokens = n.
+ * Replaces moe_sum / moe_common::moe_sum / fn_moe_combine (src/experts/moe.cu:223-234, src/experts/moe_common.cu:186-194,
+ * src/models/qwen/qwen4exp/qwen4exp.cu:846-851). out is [n][hidden] of out_dtype. */
+B2MOE_API int32_t b2moe_combine(const float * y, const int32_t * ids, const float * weights, const float * shared_weights, int32_t n,
+                      int32_t topk, int32_t hidden, int32_t shared_tokens, void * out, int32_t out_dtype,
+                      b2moe_stream stream);
+
+/* ---- whole layer ----------------------------------------------------------------------------------------------
+ * router -> top-k -> dispatch -> gate/up + SwiGLU -> down -> combine, the sequence of qwen35_forward.cpp:1121-1252,
+ * fn_layer_forward.cpp:311-336,504-522 and minimax.cpp:1083-1131, as stream-ordered launches with no host round trip. */
+typedef struct b2moe_layer {
+    int32_t hidden, experts, topk, ff;
+    int32_t gating;                /* b2moe_gating */
+    int32_t norm;                  /* sigmoid gating: normalise the selected weights (softmax gating always does) */
+    float scale;                   /* 0 and 1 both mean "no scaling" (src/experts/moe.hpp:33) */
+    int32_t has_shared;            /* 1: an always-on expert is evaluated for every token */
+    const float * router_w;        /* f32 [experts][hidden] */
+    const float * sel_bias;        /* f32 [experts] selection-only bias (sigmoid gating) or NULL */
+    const float * shared_gate_vec; /* f32 [hidden]: shared weight = sigmoid(vec . x); NULL = weight 1 */
+    b2moe_bank gate, up, down;     /* experts stacked */
+    b2moe_bank sh_gate, sh_up, sh_down; /* experts = 1; ignored unless has_shared */
+} b2moe_layer;
+
+/* byte offsets of the intermediates inside a layer workspace (so a harness can read the routing artefacts back) */
+typedef struct b2moe_layer_ws {
+    size_t logits;         /* f32 [n][experts + 1] */
+    size_t ids;            /* i32 [n][topk] */
+    size_t weights;        /* f32 [n][topk] */
+    size_t shared_weights; /* f32 [n] */
+    size_t plan;           /* i32 [b2moe_plan_ints] */
+    size_t act;            /* f32 [n*topk + shared][ff] */
+    size_t y;              /* f32 [n*topk + shared][hidden] */
+    size_t scratch;        /* dispatch scratch */
+    size_t total;          /* workspace bytes needed */
+} b2moe_layer_ws;
+B2MOE_API int32_t b2moe_layer_workspace(const b2moe_layer * layer, int32_t n, b2moe_layer_ws * ws);
+B2MOE_API int32_t b2moe_layer_forward(const b2moe_layer * layer, const void * x, int32_t x_dtype, int32_t n, void * out,
+                            int32_t out_dtype, void * workspace, size_t workspace_bytes, b2moe_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B2MOE_H */

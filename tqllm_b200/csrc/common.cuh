@@ -1,0 +1,40 @@
+// Shared host-side helpers of the C ABI: status codes, argument checks, launch checks.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b2moe.h"
+
+namespace b2 {
+
+inline int32_t launch_status() { return cudaGetLastError() == cudaSuccess ? B2MOE_OK : B2MOE_ERR_CUDA; }
+inline bool aligned16(const void * p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline cudaStream_t as_stream(b2moe_stream s) { return static_cast<cudaStream_t>(s); }
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// activation element -> float
+template <int DT> struct Elem;
+template <> struct Elem<B2MOE_F32> { using type = float; __device__ static float to_f(float v) { return v; } };
+template <> struct Elem<B2MOE_F16> { using type = __half; __device__ static float to_f(__half v) { return __half2float(v); } };
+template <> struct Elem<B2MOE_BF16> { using type = __nv_bfloat16; __device__ static float to_f(__nv_bfloat16 v) { return __bfloat162float(v); } };
+
+__device__ __forceinline__ float load_act(const void * x, int dtype, size_t i) {
+    if (dtype == B2MOE_F32) return static_cast<const float *>(x)[i];
+    if (dtype == B2MOE_BF16) return __bfloat162float(static_cast<const __nv_bfloat16 *>(x)[i]);
+    return __half2float(static_cast<const __half *>(x)[i]);
+}
+__device__ __forceinline__ void store_act(void * x, int dtype, size_t i, float v) {
+    if (dtype == B2MOE_F32) static_cast<float *>(x)[i] = v;
+    else if (dtype == B2MOE_BF16) static_cast<__nv_bfloat16 *>(x)[i] = __float2bfloat16_rn(v);
+    else static_cast<__half *>(x)[i] = __float2half_rn(v);
+}
+inline bool valid_dtype(int dt) { return dt == B2MOE_F32 || dt == B2MOE_F16 || dt == B2MOE_BF16; }
+inline size_t dtype_bytes(int dt) { return dt == B2MOE_F32 ? 4 : 2; }
+
+// plan header slots
+enum { PLAN_NACTIVE = 0, PLAN_NGROUPED = 1, PLAN_HDR = 4 };
+
+}  // namespace b2

@@ -1,0 +1,129 @@
+// C entry points of the expert products and the whole-layer sequence (router -> top-k -> dispatch -> gate/up + SwiGLU
+// -> down -> combine): the launch order of qwen35_forward.cpp:1121-1252 / fn_layer_forward.cpp:311-336,504-522 /
+// minimax.cpp:1083-1131 with every step stream-ordered on the device and no host read-back of the routing.
+#include "common.cuh"
+#include "formats.cuh"
+
+namespace b2 {
+int32_t check_bank(const b2moe_bank * b);
+int32_t generic_gateup(const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const void *, int, const int *, int,
+                       int, int, float *, cudaStream_t);
+int32_t generic_down(const b2moe_bank *, const b2moe_bank *, const float *, const int *, int, int, int, float *, cudaStream_t);
+
+namespace {
+int32_t same_shape(const b2moe_bank * a, const b2moe_bank * b, bool same_experts) {
+    if (a->type != b->type) return B2MOE_ERR_FORMAT;
+    if (a->rows != b->rows || a->cols != b->cols || (same_experts && a->experts != b->experts)) return B2MOE_ERR_SHAPE;
+    return B2MOE_OK;
+}
+}  // namespace
+}  // namespace b2
+
+using namespace b2;
+
+extern "C" B2MOE_API const char * b2moe_status_string(int32_t status) {
+    switch (status) {
+        case B2MOE_OK: return "ok";
+        case B2MOE_ERR_SHAPE: return "invalid shape";
+        case B2MOE_ERR_ALIGN: return "pointer is not 16-byte aligned";
+        case B2MOE_ERR_FORMAT: return "unsupported or mismatched block format";
+        case B2MOE_ERR_NULL: return "null pointer";
+        case B2MOE_ERR_WORKSPACE: return "workspace too small";
+        case B2MOE_ERR_CUDA: return "CUDA call failed";
+        case B2MOE_ERR_CAPACITY: return "capacity exceeded";
+    }
+    return "unknown status";
+}
+extern "C" B2MOE_API int32_t b2moe_abi_version(void) { return B2MOE_ABI_VERSION; }
+extern "C" B2MOE_API void b2moe_codebooks(uint32_t * grid, int8_t * kv) {
+    if (grid) for (int i = 0; i < 512; ++i) grid[i] = h_iq3s_grid[i];
+    if (kv) for (int i = 0; i < 16; ++i) kv[i] = h_kvalues_iq4nl[i];
+}
+
+extern "C" B2MOE_API int32_t b2moe_expert_gateup_swiglu(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_bank * shared_gate,
+                                              const b2moe_bank * shared_up, const void * x, int32_t x_dtype, const int32_t * plan,
+                                              int32_t n, int32_t topk, int32_t shared_tokens, float * act, b2moe_stream stream) {
+    if (int32_t rc = check_bank(gate)) return rc;
+    if (int32_t rc = check_bank(up)) return rc;
+    if (int32_t rc = same_shape(gate, up, true)) return rc;
+    if (n <= 0 || topk <= 0 || (shared_tokens != 0 && shared_tokens != n) || !valid_dtype(x_dtype)) return B2MOE_ERR_SHAPE;
+    if (shared_tokens) {
+        if (int32_t rc = check_bank(shared_gate)) return rc;
+        if (int32_t rc = check_bank(shared_up)) return rc;
+        if (int32_t rc = same_shape(gate, shared_gate, false)) return rc;
+        if (int32_t rc = same_shape(gate, shared_up, false)) return rc;
+    }
+    if (!x || !plan || !act) return B2MOE_ERR_NULL;
+    if (!aligned16(x) || !aligned16(act)) return B2MOE_ERR_ALIGN;
+    return generic_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, as_stream(stream));
+}
+
+extern "C" B2MOE_API int32_t b2moe_expert_down(const b2moe_bank * down, const b2moe_bank * shared_down, const float * act, const int32_t * plan,
+                                     int32_t n, int32_t topk, int32_t shared_tokens, float * y, b2moe_stream stream) {
+    if (int32_t rc = check_bank(down)) return rc;
+    if (n <= 0 || topk <= 0 || (shared_tokens != 0 && shared_tokens != n)) return B2MOE_ERR_SHAPE;
+    if (shared_tokens) {
+        if (int32_t rc = check_bank(shared_down)) return rc;
+        if (int32_t rc = same_shape(down, shared_down, false)) return rc;
+    }
+    if (!act || !plan || !y) return B2MOE_ERR_NULL;
+    if (!aligned16(act) || !aligned16(y)) return B2MOE_ERR_ALIGN;
+    return generic_down(down, shared_down, act, plan, n, topk, shared_tokens, y, as_stream(stream));
+}
+
+extern "C" B2MOE_API int32_t b2moe_layer_workspace(const b2moe_layer * L, int32_t n, b2moe_layer_ws * ws) {
+    if (!L || !ws) return B2MOE_ERR_NULL;
+    if (n <= 0 || L->hidden <= 0 || L->experts <= 0 || L->topk <= 0 || L->topk > L->experts || L->ff <= 0) return B2MOE_ERR_SHAPE;
+    if ((long long)n * L->topk > 0x3fffffffLL) return B2MOE_ERR_SHAPE;
+    const size_t A = size_t(n) * L->topk, At = A + (L->has_shared ? n : 0);
+    size_t at = 0;
+    auto take = [&](size_t bytes) { const size_t o = at; at = align_up(at + bytes, 256); return o; };
+    ws->logits = take(size_t(n) * (L->experts + 1) * sizeof(float));
+    ws->ids = take(A * sizeof(int32_t));
+    ws->weights = take(A * sizeof(float));
+    ws->shared_weights = take(size_t(n) * sizeof(float));
+    ws->plan = take(size_t(b2moe_plan_ints(L->experts, int32_t(A), L->has_shared ? n : 0)) * sizeof(int32_t));
+    ws->act = take(At * L->ff * sizeof(float));
+    ws->y = take(At * L->hidden * sizeof(float));
+    ws->scratch = take(b2moe_dispatch_workspace_bytes(L->experts, int32_t(A)));
+    ws->total = at;
+    return B2MOE_OK;
+}
+
+extern "C" B2MOE_API int32_t b2moe_layer_forward(const b2moe_layer * L, const void * x, int32_t x_dtype, int32_t n, void * out,
+                                       int32_t out_dtype, void * workspace, size_t workspace_bytes, b2moe_stream stream) {
+    b2moe_layer_ws ws;
+    if (int32_t rc = b2moe_layer_workspace(L, n, &ws)) return rc;
+    if (!x || !out || !workspace || !L->router_w) return B2MOE_ERR_NULL;
+    if (workspace_bytes < ws.total) return B2MOE_ERR_WORKSPACE;
+    if (!aligned16(workspace)) return B2MOE_ERR_ALIGN;
+    if (L->gating != B2MOE_SOFTMAX && L->gating != B2MOE_SIGMOID) return B2MOE_ERR_SHAPE;
+    if (L->gate.rows != L->ff || L->gate.cols != L->hidden || L->down.rows != L->hidden || L->down.cols != L->ff ||
+        L->gate.experts != L->experts || L->down.experts != L->experts) return B2MOE_ERR_SHAPE;
+    char * base = static_cast<char *>(workspace);
+    float * logits = reinterpret_cast<float *>(base + ws.logits);
+    int32_t * ids = reinterpret_cast<int32_t *>(base + ws.ids);
+    float * weights = reinterpret_cast<float *>(base + ws.weights);
+    float * shw = reinterpret_cast<float *>(base + ws.shared_weights);
+    int32_t * plan = reinterpret_cast<int32_t *>(base + ws.plan);
+    float * act = reinterpret_cast<float *>(base + ws.act);
+    float * y = reinterpret_cast<float *>(base + ws.y);
+    const int ld = L->experts + 1, sh = L->has_shared ? n : 0;
+    const bool gated_shared = L->has_shared && L->shared_gate_vec;
+
+    if (int32_t rc = b2moe_router(L->router_w, gated_shared ? L->shared_gate_vec : nullptr, x, x_dtype, logits, ld, L->hidden, L->experts,
+                                  n, stream)) return rc;
+    if (L->gating == B2MOE_SOFTMAX) {
+        if (int32_t rc = b2moe_topk_softmax(logits, ld, ids, weights, gated_shared ? shw : nullptr, L->experts, L->topk, n, L->scale, stream))
+            return rc;
+    } else {
+        if (gated_shared) return B2MOE_ERR_SHAPE;   // the sigmoid family adds its shared expert unscaled (moe_common.cu:191)
+        if (int32_t rc = b2moe_route_sigmoid(logits, ld, L->sel_bias, ids, weights, L->experts, L->topk, L->norm, L->scale, n, stream))
+            return rc;
+    }
+    if (int32_t rc = b2moe_dispatch(ids, n, L->topk, L->experts, sh, plan, base + ws.scratch, ws.total - ws.scratch, stream)) return rc;
+    if (int32_t rc = b2moe_expert_gateup_swiglu(&L->gate, &L->up, &L->sh_gate, &L->sh_up, x, x_dtype, plan, n, L->topk, sh, act, stream))
+        return rc;
+    if (int32_t rc = b2moe_expert_down(&L->down, &L->sh_down, act, plan, n, L->topk, sh, y, stream)) return rc;
+    return b2moe_combine(y, nullptr, weights, gated_shared ? shw : nullptr, n, L->topk, L->hidden, sh, out, out_dtype, stream);
+}
