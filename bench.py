@@ -1,0 +1,310 @@
+"""Benchmark of the MoE layer path: `python bench.py --gpus N --steps K --warmup W [--impl reference]`.
+
+Workload (N = 1): the Flash-Next-shaped decode layer — hidden 2048, 512 routed experts, softmax top-10 renormalised,
+one always-on shared expert, intermediate 512, IQ3_S expert weights quantised from N(0, 0.02), router scaled so the
+top-10 mass is about 0.6, bf16 activations N(0,1), 64 decode tokens, 4 stacked layers (each layer has its own router
+and experts and reads the step's activations). One step = one pass of the 64 tokens through the 4 layers, router to
+combine. The expert weights of the 4 layers (2.8 GB) are far larger than L2, so every step streams them from HBM.
+
+One JSON line on stdout (rank 0):
+  value      layer-tokens per second = tokens * layers / step time, inputs resident in HBM, CUDA-event timed
+  e2e        the same through host buffers: pinned-host -> device copy of the activations and device -> host copy of
+             the layer outputs inside the timed region
+  roofline   the dominant kernel (the grouped gate/up + SwiGLU product): GGUF block bytes of the gate and up matrices
+             of the experts it touched / its CUDA-event duration, against the measured HBM copy bandwidth
+  cpu_baseline  the CPU path timed on this box's host cores on a bounded sample (one layer, the same 64 tokens)
+
+`--impl reference` times the reference's CPU implementation of the path (the reference's own sources compiled in place
+under oracle/_ref when present, else the oracle restatement) on the same workload, one layer per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+TOKENS, LAYERS = 64, 4
+SEED = 20261125
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=50)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--impl", default="b200", choices=("b200", "reference"))
+    p.add_argument("--tokens", type=int, default=TOKENS)
+    p.add_argument("--layers", type=int, default=LAYERS)
+    p.add_argument("--graph", type=int, default=1, help="replay the step as a CUDA graph (1) or launch it directly (0)")
+    p.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    p.add_argument("--sweep", action="store_true", help="also time 1 / 4 / 16 tokens (extra keys, not the headline)")
+    return p.parse_args()
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs"""
+    Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.25)
+            self.proc.terminate()
+            self.t.join(timeout=2)
+
+    def summary(self):
+        sm = sorted(int(r[1]) for r in self.rows if len(r) >= 8 and r[1].isdigit())
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 8 and r[4 + i].lower().startswith("active") for r in self.rows)]
+        mx = max(int(r[2]) for r in self.rows if len(r) >= 8 and r[2].isdigit())
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": mx, "reasons": reasons, "samples": len(sm)}
+
+
+def workload_name(tokens, layers):
+    return f"c2 flash-next decode: H2048 E512 top10+1 shared F512 IQ3_S, {tokens} tokens x {layers} stacked layers"
+
+
+def make_layers(synth, shape, layers, device, experts=None):
+    scale = synth.solve_router_scale(shape, 0.6)
+    return [synth.make_layer(shape, SEED + 17 * l, device, experts=experts, router_scale=scale) for l in range(layers)], scale
+
+
+# ------------------------------------------------------------------------------------------------ CPU arm ----
+def cpu_layer_time(kind_wanted, shape, layer, x, threads):
+    """seconds for one layer forward of x on the host cores; returns (seconds, kind)"""
+    import numpy as np
+
+    import oracle
+    orc = oracle.oracle()
+    ref = oracle.reference() if kind_wanted == "reference" else None
+    xf = x.float().cpu().numpy()
+    raw = [t.cpu().numpy() for t in layer.raw]
+    sh = tuple(t.cpu().numpy() for t in layer.shared_raw) if layer.shared_raw is not None else None
+    rw = layer.router_w.cpu().numpy()
+    E = rw.shape[0]
+    t0 = time.perf_counter()
+    if ref is not None:
+        logits = orc.router_logits(rw, xf)          # the reference CPU path has no router GEMV of its own (moe.cu is CUDA)
+        ref.moe_layer(x=xf, topk=shape.topk, ff=shape.ff, gating=shape.gating, norm=shape.norm, scale=shape.scale, types=shape.types,
+                      gate=raw[0], up=raw[1], down=raw[2], experts=E, logits_in=logits, shared=sh, threads=threads)
+        kind = "reference"
+    else:
+        orc.moe_layer(x=xf, router_w=rw, topk=shape.topk, ff=shape.ff, gating=shape.gating, norm=shape.norm, scale=shape.scale,
+                      types=shape.types, gate=raw[0], up=raw[1], down=raw[2], experts=E, shared=sh, threads=threads)
+        kind = "port"
+    return time.perf_counter() - t0, kind
+
+
+def run_reference(args):
+    """the reference's CPU implementation of the path on this box's host cores; rank 0 only"""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import torch
+
+    from tqllm_b200 import synth
+    shape = synth.CONFIGS["c2"]
+    threads = os.cpu_count() or 1
+    layers, rscale = make_layers(synth, shape, 1, "cpu")
+    x = synth.make_tokens(shape, args.tokens, SEED, "cpu")
+    steps = max(1, min(args.steps, 3))
+    for _ in range(min(args.warmup, 1)):
+        cpu_layer_time("reference", shape, layers[0], x, threads)
+    times = []
+    kind = "port"
+    for _ in range(steps):
+        dt, kind = cpu_layer_time("reference", shape, layers[0], x, threads)
+        times.append(dt)
+    t = sum(times) / len(times)
+    v = args.tokens / t
+    print(json.dumps({
+        "metric": METRIC, "value": v, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1),
+        "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args.tokens, args.layers), "sample": "one layer per step", "router_scale": rscale},
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": kind,
+                         "sample": f"1 of {args.layers} layers, {args.tokens} tokens, {steps} steps"},
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm ----
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+
+    from tqllm_b200 import moe, synth
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the MoE path has no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    shape = synth.CONFIGS["c2"]
+    T, L = args.tokens, args.layers
+    synth_layers, rscale = make_layers(synth, shape, L, dev)
+    layers = [moe.MoeLayer.from_synth(sl) for sl in synth_layers]
+    host_layer0 = synth_layers[0] if rank == 0 and not args.no_cpu else None
+    if host_layer0 is not None:      # keep only the first layer's raw blocks (for the CPU baseline), on the host
+        host_layer0 = synth.Layer(shape, host_layer0.router_w.cpu(), None, tuple(t.cpu() for t in host_layer0.raw),
+                                  tuple(t.cpu() for t in host_layer0.shared_raw))
+    del synth_layers
+    torch.cuda.empty_cache()
+    x = synth.make_tokens(shape, T, SEED + rank, dev)
+    outs = [torch.empty(T, shape.hidden, dtype=torch.bfloat16, device=dev) for _ in range(L)]
+    for lay in layers:
+        lay.reserve(T)
+
+    def step():
+        for lay, o in zip(layers, outs):
+            lay.forward(x, out=o)
+
+    # pinned host buffers of the end-to-end leg
+    x_host = x.cpu().pin_memory()
+    out_host = torch.empty(L, T, shape.hidden, dtype=torch.bfloat16).pin_memory()
+
+    def step_e2e():
+        x.copy_(x_host, non_blocking=True)
+        step()
+        for l in range(L):
+            out_host[l].copy_(outs[l], non_blocking=True)
+
+    stream = torch.cuda.Stream(dev)
+    graph = None
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            step()
+        stream.synchronize()
+        if args.graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step()
+        run = graph.replay if graph is not None else step
+
+        def timed(fn, steps):
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                fn()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+            if world > 1:
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+                dist.barrier()
+            return float(ms) / steps
+
+        for _ in range(args.warmup):
+            run()
+        with ClockSampler(local) as clocks:
+            ms_step = timed(run, args.steps)
+        for _ in range(min(args.warmup, 3)):
+            step_e2e()
+        ms_e2e = timed(step_e2e, args.steps)
+
+        # dominant kernel, timed alone with events on the launching stream: the grouped gate/up + SwiGLU product
+        art = [lay.artefacts() for lay in layers]
+        plans, ids = [], []
+        for lay in layers:
+            lg = moe.router(lay.router_w, x)
+            i, w, _ = moe.topk_softmax(lg, lay.experts, shape.topk, shape.scale)
+            plans.append(moe.dispatch(i, lay.experts, T))
+        act = torch.zeros(T * shape.topk + T, shape.ff, dtype=torch.float32, device=dev)
+        import ctypes as C
+        from tqllm_b200.capi import lib, BF16
+
+        def gateup(l):
+            lay = layers[l]
+            return lib.b2moe_expert_gateup_swiglu(C.byref(lay.gate.c), C.byref(lay.up.c), C.byref(lay.sh[0].c), C.byref(lay.sh[1].c),
+                                                  x.data_ptr(), BF16, plans[l].buf.data_ptr(), T, shape.topk, T, act.data_ptr(),
+                                                  stream.cuda_stream)
+        for l in range(L):
+            assert gateup(l) == 0
+        reps = max(3, min(args.steps, 20))
+        evs = []
+        for _ in range(reps):
+            for l in range(L):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream); gateup(l); b.record(stream)
+                evs.append((a, b))
+        torch.cuda.synchronize()
+        k_ms = sum(a.elapsed_time(b) for a, b in evs) / len(evs)
+    n_active = sum(p.n_active for p in plans) / L            # includes the shared expert
+    gu_bytes = 2 * synth.raw_bytes(shape.types[0], shape.ff, shape.hidden)
+    peak, peak_kind = peaks()
+    achieved = n_active * gu_bytes / (k_ms * 1e-3) / 1e9
+    weight_bytes_step = sum(p.n_active for p in plans) * shape.expert_bytes()
+    value = world * T * L / (ms_step * 1e-3)
+    e2e = world * T * L / (ms_e2e * 1e-3)
+
+    cpu = None
+    if host_layer0 is not None:
+        threads = os.cpu_count() or 1
+        dt, kind = cpu_layer_time("port", shape, host_layer0, x.cpu(), threads)
+        cpu = {"value": T / dt, "unit": UNIT, "cores": threads, "kind": kind, "sample": f"1 of {L} layers, {T} tokens, 1 pass ({dt:.1f} s)"}
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload_name(T, L), "tokens": T, "layers": L, "router_scale": rscale,
+                       "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
+                       "l2": "per-step expert weights (GBs) exceed the 126 MB L2; no flush needed", "cuda_graph": bool(args.graph),
+                       "activations": "bf16 in, bf16 out, fp32 intermediates"},
+            "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": x_host.numel() * 2,
+                    "d2h_bytes_per_step": out_host.numel() * 2},
+            "gpu_launches": args.steps * L * 6,
+            "roofline": {"bound": "hbm", "kernel": "grouped gate/up + SwiGLU", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None, "kernel_ms": k_ms,
+                         "active_experts_per_launch": n_active, "bytes_per_expert": gu_bytes},
+            "expert_weight_gbs": weight_bytes_step / (ms_step * 1e-3) / 1e9,
+            "expert_weight_frac_of_8tbs": weight_bytes_step / (ms_step * 1e-3) / 8e12,
+            "cpu_baseline": cpu, "clocks": clocks.summary(),
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    a = parse()
+    run_reference(a) if a.impl == "reference" else run_b200(a)
