@@ -253,11 +253,14 @@ def run_b200(args):
         import ctypes as C
         from tqllm_b200.capi import lib, BF16
 
+        wsb = lib.b2moe_expert_workspace_bytes(shape.types[0], T, shape.hidden, BF16)
+        ews = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+
         def gateup(l):
             lay = layers[l]
             return lib.b2moe_expert_gateup_swiglu(C.byref(lay.gate.c), C.byref(lay.up.c), C.byref(lay.sh[0].c), C.byref(lay.sh[1].c),
                                                   x.data_ptr(), BF16, plans[l].buf.data_ptr(), T, shape.topk, T, act.data_ptr(),
-                                                  stream.cuda_stream)
+                                                  ews.data_ptr(), ews.numel(), stream.cuda_stream)
         for l in range(L):
             assert gateup(l) == 0
         reps = max(3, min(args.steps, 20))

@@ -120,18 +120,25 @@ B2MOE_API int32_t b2moe_plan_to_groups(const int32_t * plan, int32_t n, int32_t 
                              int32_t * groups, b2moe_stream stream);
 
 /* ---- expert products ------------------------------------------------------------------------------------------
- * act[a][f] = silu(gate_e(a)[f] . x[token(a)]) * (up_e(a)[f] . x[token(a)]) for every grouped assignment a: the
+ * Scratch: the tuned kernels of a format first split the activation rows into tensor-core operand form inside a
+ * caller-provided workspace of b2moe_expert_workspace_bytes(type, rows_x, k, x_dtype) bytes (16-byte aligned), where
+ * rows_x = n for the gate/up product (k = hidden) and n*topk + shared_tokens for the down product (k = ff, x_dtype
+ * B2MOE_F32). The size is 0 for formats that take no scratch; the workspace may then be NULL. */
+B2MOE_API size_t b2moe_expert_workspace_bytes(uint32_t type, int32_t rows_x, int32_t k, int32_t x_dtype);
+/* act[a][f] = silu(gate_e(a)[f] . x[token(a)]) * (up_e(a)[f] . x[token(a)]) for every grouped assignment a: the
  * paired gate/up product with the SwiGLU fused (replaces expert_matvec2 / expert_matvec_dedup2 / expert_gemm_gateup +
  * moe_swiglu: src/formats/weight/weight_format.hpp:58-73, src/formats/weight/quant.cu:167-233,384-405,
  * src/experts/moe.cu:188-195). shared_* may be null when the plan has no shared expert. act is fp32
  * [n*topk + shared_tokens][ff]; rows of skipped assignments are left untouched. */
 B2MOE_API int32_t b2moe_expert_gateup_swiglu(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_bank * shared_gate,
                                    const b2moe_bank * shared_up, const void * x, int32_t x_dtype, const int32_t * plan,
-                                   int32_t n, int32_t topk, int32_t shared_tokens, float * act, b2moe_stream stream);
+                                   int32_t n, int32_t topk, int32_t shared_tokens, float * act, void * workspace,
+                                   size_t workspace_bytes, b2moe_stream stream);
 /* y[a][h] = down_e(a)[h] . act[a]   (replaces expert_matvec / expert_matvec_dedup / expert_gemm with
  * per_expert_input: src/formats/weight/weight_format.hpp:51-63, src/formats/weight/quant.cu:69-143,286-317). y fp32. */
 B2MOE_API int32_t b2moe_expert_down(const b2moe_bank * down, const b2moe_bank * shared_down, const float * act, const int32_t * plan,
-                          int32_t n, int32_t topk, int32_t shared_tokens, float * y, b2moe_stream stream);
+                          int32_t n, int32_t topk, int32_t shared_tokens, float * y, void * workspace, size_t workspace_bytes,
+                          b2moe_stream stream);
 /* out[t] = sum_s weights[t][s] * y[t*topk + s] (slot order, skipped where ids[t][s] < 0 when ids is given)
  *          + shared_weights[t] (1 when null) * y[n*topk + t] when shared_tokens = n.
  * Replaces moe_sum / moe_common::moe_sum / fn_moe_combine (src/experts/moe.cu:223-234, src/experts/moe_common.cu:186-194,
@@ -166,6 +173,7 @@ typedef struct b2moe_layer_ws {
     size_t act;            /* f32 [n*topk + shared][ff] */
     size_t y;              /* f32 [n*topk + shared][hidden] */
     size_t scratch;        /* dispatch scratch */
+    size_t expert_scratch; /* scratch of the expert products */
     size_t total;          /* workspace bytes needed */
 } b2moe_layer_ws;
 B2MOE_API int32_t b2moe_layer_workspace(const b2moe_layer * layer, int32_t n, b2moe_layer_ws * ws);

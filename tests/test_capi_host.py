@@ -87,7 +87,12 @@ def test_arguments_are_rejected_before_any_launch():
     assert lib.b2moe_dequant_dump(C.byref(bank), None, None) == capi.ERR_NULL
     assert lib.b2moe_dequant_dump(C.byref(bad), 16, None) == capi.ERR_ALIGN
     up_other = capi.Bank(16, None, 21, 4, 32, 256)
-    assert lib.b2moe_expert_gateup_swiglu(C.byref(bank), C.byref(up_other), None, None, 16, capi.BF16, 16, 2, 2, 0, 16, None) == capi.ERR_FORMAT
+    assert lib.b2moe_expert_gateup_swiglu(C.byref(bank), C.byref(up_other), None, None, 16, capi.BF16, 16, 2, 2, 0, 16, None, 0, None) == capi.ERR_FORMAT
+    iq = capi.Bank(16, None, 21, 4, 32, 256)
+    assert lib.b2moe_expert_workspace_bytes(21, 64, 2048, capi.BF16) >= 64 * 2048 * 2 + 64 * 4
+    assert lib.b2moe_expert_workspace_bytes(12, 64, 2048, capi.BF16) == 0
+    assert lib.b2moe_expert_down(C.byref(iq), None, 16, 16, 2, 2, 0, 16, None, 0, None) == capi.ERR_NULL        # needs scratch
+    assert lib.b2moe_expert_down(C.byref(iq), None, 16, 16, 2, 2, 0, 16, 32, 64, None) == capi.ERR_WORKSPACE
     assert lib.b2moe_combine(16, None, 16, None, 2, 2, 30, 0, 16, capi.F32, None) == capi.ERR_SHAPE
     with pytest.raises(capi.B2moeError):
         capi.check(capi.ERR_WORKSPACE, "x")

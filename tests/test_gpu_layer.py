@@ -132,3 +132,32 @@ def test_errors_reach_the_caller():
     assert rc == capi.ERR_WORKSPACE
     with pytest.raises(capi.B2moeError):
         moe.DeviceBank(12, torch.zeros(10, dtype=torch.uint8, device="cuda"), 1, 16, 256)
+
+
+@pytest.mark.parametrize("act_dtype,experts,tokens,topk", (("f32", 4, 40, 2), ("bf16", 4, 70, 3), ("bf16", 24, 3, 8), ("f32", 16, 1, 4)))
+def test_iq3s_tensor_core_path(orc, act_dtype, experts, tokens, topk):
+    """the IQ3_S decode kernels: fp32 and bf16 activations (4- and 2-term splits), experts holding many more tokens
+    than one pass takes, experts holding one token, a shared expert"""
+    shape = synth.LayerShape("iq3s-mma", 512, experts, topk, 256, shared=True, types=(21, 21, 21), act_dtype=act_dtype)
+    err = run_case(orc, shape, experts, tokens, 4242 + tokens)
+    assert err < 2e-3
+
+
+def test_iq3s_activation_scale_invariance(orc):
+    """activation rows of very different magnitude go through the per-row power-of-two scaling unchanged"""
+    from tqllm_b200 import moe
+    shape = synth.LayerShape("iq3s-scale", 512, 8, 2, 256, shared=True, types=(21, 21, 21))
+    layer, x = layer_inputs(shape, 8, 6, 99)
+    x = x.float()
+    x[0] *= 1e-4
+    x[1] *= 3e3
+    x[2] = 0
+    x = x.to(torch.bfloat16)
+    dev = moe.MoeLayer.from_synth(layer, experts=8)
+    out = dev.forward(x.cuda()).cpu().numpy()
+    logits = dev.artefacts()["logits"].cpu().numpy()[:, :8].copy()
+    res = oracle_layer(orc, shape, 8, layer, x, logits)
+    for t in range(6):
+        ref = res["out"][t].astype(np.float64)
+        rms = max(np.sqrt((ref ** 2).mean()), 1e-30)
+        assert np.abs(out[t] - ref).max() / rms <= (0 if t == 2 else TOL)

@@ -41,7 +41,7 @@ class Layer(C.Structure):
 
 
 class LayerWs(C.Structure):
-    _fields_ = [(n, C.c_size_t) for n in ("logits", "ids", "weights", "shared_weights", "plan", "act", "y", "scratch", "total")]
+    _fields_ = [(n, C.c_size_t) for n in ("logits", "ids", "weights", "shared_weights", "plan", "act", "y", "scratch", "expert_scratch", "total")]
 
 
 # name -> (restype, argtypes): every symbol include/b2moe.h declares
@@ -63,8 +63,9 @@ SIGNATURES = {
     "b2moe_dispatch_workspace_bytes": (_sz, [_i32, _i32]),
     "b2moe_dispatch": (_i32, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
     "b2moe_plan_to_groups": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp, _vp]),
-    "b2moe_expert_gateup_swiglu": (_i32, [C.POINTER(Bank)] * 4 + [_vp, _i32, _vp, _i32, _i32, _i32, _vp, _vp]),
-    "b2moe_expert_down": (_i32, [C.POINTER(Bank)] * 2 + [_vp, _vp, _i32, _i32, _i32, _vp, _vp]),
+    "b2moe_expert_workspace_bytes": (_sz, [_u32, _i32, _i32, _i32]),
+    "b2moe_expert_gateup_swiglu": (_i32, [C.POINTER(Bank)] * 4 + [_vp, _i32, _vp, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
+    "b2moe_expert_down": (_i32, [C.POINTER(Bank)] * 2 + [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
     "b2moe_combine": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _i32, _vp]),
     "b2moe_layer_workspace": (_i32, [C.POINTER(Layer), _i32, C.POINTER(LayerWs)]),
     "b2moe_layer_forward": (_i32, [C.POINTER(Layer), _vp, _i32, _i32, _vp, _i32, _vp, _sz, _vp]),

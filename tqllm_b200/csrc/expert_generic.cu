@@ -103,7 +103,7 @@ int32_t launch(uint32_t type, const GroupArgs & g, const void * x, int x_dtype, 
 }  // namespace
 
 // the number of (expert) work slots a launch must cover: experts that can be active, plus the shared one
-inline int max_active_of(int experts, int n, int topk, int shared_tokens) {
+static inline int max_active_of_generic(int experts, int n, int topk, int shared_tokens) {
     const long long a = (long long)n * topk;
     return int(a < experts ? a : experts) + (shared_tokens ? 1 : 0);
 }
@@ -122,7 +122,7 @@ int32_t generic_gateup(const b2moe_bank * gate, const b2moe_bank * up, const b2m
     g.bank_bytes = b2moe_bank_bytes(gate->type, gate->rows, gate->cols);
     g.rows = gate->rows; g.cols = gate->cols; g.experts = gate->experts; g.topk = topk; g.A = n * topk;
     g.k_tiles = gate->cols / f.kt; g.units = f.units;
-    return launch<0>(gate->type, g, x, x_dtype, plan, act, max_active_of(gate->experts, n, topk, shared_tokens), s);
+    return launch<0>(gate->type, g, x, x_dtype, plan, act, max_active_of_generic(gate->experts, n, topk, shared_tokens), s);
 }
 
 int32_t generic_down(const b2moe_bank * down, const b2moe_bank * sd, const float * act, const int * plan, int n, int topk,
@@ -136,7 +136,7 @@ int32_t generic_down(const b2moe_bank * down, const b2moe_bank * sd, const float
     g.bank_bytes = b2moe_bank_bytes(down->type, down->rows, down->cols);
     g.rows = down->rows; g.cols = down->cols; g.experts = down->experts; g.topk = topk; g.A = n * topk;
     g.k_tiles = down->cols / f.kt; g.units = f.units;
-    return launch<1>(down->type, g, act, B2MOE_F32, plan, y, max_active_of(down->experts, n, topk, shared_tokens), s);
+    return launch<1>(down->type, g, act, B2MOE_F32, plan, y, max_active_of_generic(down->experts, n, topk, shared_tokens), s);
 }
 
 }  // namespace b2

@@ -9,6 +9,10 @@ int32_t check_bank(const b2moe_bank * b);
 int32_t generic_gateup(const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const void *, int, const int *, int,
                        int, int, float *, cudaStream_t);
 int32_t generic_down(const b2moe_bank *, const b2moe_bank *, const float *, const int *, int, int, int, float *, cudaStream_t);
+size_t iq3s_workspace_bytes(int rows_x, int k, int dtype);
+int32_t iq3s_gateup(const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const void *, int, const int *, int,
+                    int, int, float *, void *, int, cudaStream_t);
+int32_t iq3s_down(const b2moe_bank *, const b2moe_bank *, const float *, const int *, int, int, int, float *, void *, int, cudaStream_t);
 
 namespace {
 int32_t same_shape(const b2moe_bank * a, const b2moe_bank * b, bool same_experts) {
@@ -16,6 +20,12 @@ int32_t same_shape(const b2moe_bank * a, const b2moe_bank * b, bool same_experts
     if (a->rows != b->rows || a->cols != b->cols || (same_experts && a->experts != b->experts)) return B2MOE_ERR_SHAPE;
     return B2MOE_OK;
 }
+// experts that can be active in one launch, plus the shared one: the grid's second dimension
+int max_active_of(int experts, int n, int topk, int shared_tokens) {
+    const long long a = (long long)n * topk;
+    return int(a < experts ? a : experts) + (shared_tokens ? 1 : 0);
+}
+bool tuned(uint32_t type) { return type == T_IQ3_S; }
 }  // namespace
 }  // namespace b2
 
@@ -40,9 +50,15 @@ extern "C" B2MOE_API void b2moe_codebooks(uint32_t * grid, int8_t * kv) {
     if (kv) for (int i = 0; i < 16; ++i) kv[i] = h_kvalues_iq4nl[i];
 }
 
+extern "C" B2MOE_API size_t b2moe_expert_workspace_bytes(uint32_t type, int32_t rows_x, int32_t k, int32_t x_dtype) {
+    if (!tuned(type) || rows_x <= 0 || k <= 0 || !valid_dtype(x_dtype)) return 0;
+    return iq3s_workspace_bytes(rows_x, k, x_dtype);
+}
+
 extern "C" B2MOE_API int32_t b2moe_expert_gateup_swiglu(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_bank * shared_gate,
                                               const b2moe_bank * shared_up, const void * x, int32_t x_dtype, const int32_t * plan,
-                                              int32_t n, int32_t topk, int32_t shared_tokens, float * act, b2moe_stream stream) {
+                                              int32_t n, int32_t topk, int32_t shared_tokens, float * act, void * workspace,
+                                              size_t workspace_bytes, b2moe_stream stream) {
     if (int32_t rc = check_bank(gate)) return rc;
     if (int32_t rc = check_bank(up)) return rc;
     if (int32_t rc = same_shape(gate, up, true)) return rc;
@@ -55,11 +71,19 @@ extern "C" B2MOE_API int32_t b2moe_expert_gateup_swiglu(const b2moe_bank * gate,
     }
     if (!x || !plan || !act) return B2MOE_ERR_NULL;
     if (!aligned16(x) || !aligned16(act)) return B2MOE_ERR_ALIGN;
+    if (tuned(gate->type)) {
+        if (!workspace) return B2MOE_ERR_NULL;
+        if (!aligned16(workspace)) return B2MOE_ERR_ALIGN;
+        if (workspace_bytes < b2moe_expert_workspace_bytes(gate->type, n, gate->cols, x_dtype)) return B2MOE_ERR_WORKSPACE;
+        return iq3s_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, workspace,
+                           max_active_of(gate->experts, n, topk, shared_tokens), as_stream(stream));
+    }
     return generic_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, as_stream(stream));
 }
 
 extern "C" B2MOE_API int32_t b2moe_expert_down(const b2moe_bank * down, const b2moe_bank * shared_down, const float * act, const int32_t * plan,
-                                     int32_t n, int32_t topk, int32_t shared_tokens, float * y, b2moe_stream stream) {
+                                     int32_t n, int32_t topk, int32_t shared_tokens, float * y, void * workspace,
+                                     size_t workspace_bytes, b2moe_stream stream) {
     if (int32_t rc = check_bank(down)) return rc;
     if (n <= 0 || topk <= 0 || (shared_tokens != 0 && shared_tokens != n)) return B2MOE_ERR_SHAPE;
     if (shared_tokens) {
@@ -68,6 +92,14 @@ extern "C" B2MOE_API int32_t b2moe_expert_down(const b2moe_bank * down, const b2
     }
     if (!act || !plan || !y) return B2MOE_ERR_NULL;
     if (!aligned16(act) || !aligned16(y)) return B2MOE_ERR_ALIGN;
+    if (tuned(down->type)) {
+        const int rows_x = n * topk + shared_tokens;
+        if (!workspace) return B2MOE_ERR_NULL;
+        if (!aligned16(workspace)) return B2MOE_ERR_ALIGN;
+        if (workspace_bytes < b2moe_expert_workspace_bytes(down->type, rows_x, down->cols, B2MOE_F32)) return B2MOE_ERR_WORKSPACE;
+        return iq3s_down(down, shared_down, act, plan, n, topk, shared_tokens, y, workspace,
+                         max_active_of(down->experts, n, topk, shared_tokens), as_stream(stream));
+    }
     return generic_down(down, shared_down, act, plan, n, topk, shared_tokens, y, as_stream(stream));
 }
 
@@ -86,6 +118,9 @@ extern "C" B2MOE_API int32_t b2moe_layer_workspace(const b2moe_layer * L, int32_
     ws->act = take(At * L->ff * sizeof(float));
     ws->y = take(At * L->hidden * sizeof(float));
     ws->scratch = take(b2moe_dispatch_workspace_bytes(L->experts, int32_t(A)));
+    const size_t eg = b2moe_expert_workspace_bytes(L->gate.type, n, L->hidden, B2MOE_F32);
+    const size_t ed = b2moe_expert_workspace_bytes(L->down.type, int32_t(At), L->ff, B2MOE_F32);
+    ws->expert_scratch = take(eg > ed ? eg : ed);
     ws->total = at;
     return B2MOE_OK;
 }
@@ -121,9 +156,12 @@ extern "C" B2MOE_API int32_t b2moe_layer_forward(const b2moe_layer * L, const vo
         if (int32_t rc = b2moe_route_sigmoid(logits, ld, L->sel_bias, ids, weights, L->experts, L->topk, L->norm, L->scale, n, stream))
             return rc;
     }
-    if (int32_t rc = b2moe_dispatch(ids, n, L->topk, L->experts, sh, plan, base + ws.scratch, ws.total - ws.scratch, stream)) return rc;
-    if (int32_t rc = b2moe_expert_gateup_swiglu(&L->gate, &L->up, &L->sh_gate, &L->sh_up, x, x_dtype, plan, n, L->topk, sh, act, stream))
+    void * es = base + ws.expert_scratch;
+    const size_t es_bytes = ws.total - ws.expert_scratch;
+    if (int32_t rc = b2moe_dispatch(ids, n, L->topk, L->experts, sh, plan, base + ws.scratch, ws.expert_scratch - ws.scratch, stream))
         return rc;
-    if (int32_t rc = b2moe_expert_down(&L->down, &L->sh_down, act, plan, n, L->topk, sh, y, stream)) return rc;
+    if (int32_t rc = b2moe_expert_gateup_swiglu(&L->gate, &L->up, &L->sh_gate, &L->sh_up, x, x_dtype, plan, n, L->topk, sh, act, es,
+                                                es_bytes, stream)) return rc;
+    if (int32_t rc = b2moe_expert_down(&L->down, &L->sh_down, act, plan, n, L->topk, sh, y, es, es_bytes, stream)) return rc;
     return b2moe_combine(y, nullptr, weights, gated_shared ? shw : nullptr, n, L->topk, L->hidden, sh, out, out_dtype, stream);
 }

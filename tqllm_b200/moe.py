@@ -114,6 +114,10 @@ def plan_to_groups(plan: Plan):
     return counts, groups
 
 
+def _scratch(nbytes: int, device):
+    return torch.empty(nbytes, dtype=torch.uint8, device=device) if nbytes else None
+
+
 def _bref(b: DeviceBank | None):
     return C.byref(b.c) if b is not None else None
 
@@ -121,16 +125,19 @@ def _bref(b: DeviceBank | None):
 def expert_gateup_swiglu(gate, up, x, plan: Plan, sh_gate=None, sh_up=None):
     total = plan.n * plan.topk + plan.shared_tokens
     act = torch.zeros(total, gate.rows, dtype=torch.float32, device=x.device)
+    ws = _scratch(lib.b2moe_expert_workspace_bytes(gate.type, plan.n, gate.cols, _DT[x.dtype]), x.device)
     check(lib.b2moe_expert_gateup_swiglu(_bref(gate), _bref(up), _bref(sh_gate), _bref(sh_up), x.data_ptr(), _DT[x.dtype],
-                                         plan.buf.data_ptr(), plan.n, plan.topk, plan.shared_tokens, act.data_ptr(), _stream()),
-          "b2moe_expert_gateup_swiglu")
+                                         plan.buf.data_ptr(), plan.n, plan.topk, plan.shared_tokens, act.data_ptr(),
+                                         _ptr(ws), 0 if ws is None else ws.numel(), _stream()), "b2moe_expert_gateup_swiglu")
     return act
 
 
 def expert_down(down, act, plan: Plan, sh_down=None):
     y = torch.zeros(act.shape[0], down.rows, dtype=torch.float32, device=act.device)
+    ws = _scratch(lib.b2moe_expert_workspace_bytes(down.type, act.shape[0], down.cols, capi.F32), act.device)
     check(lib.b2moe_expert_down(_bref(down), _bref(sh_down), act.data_ptr(), plan.buf.data_ptr(), plan.n, plan.topk,
-                                plan.shared_tokens, y.data_ptr(), _stream()), "b2moe_expert_down")
+                                plan.shared_tokens, y.data_ptr(), _ptr(ws), 0 if ws is None else ws.numel(), _stream()),
+          "b2moe_expert_down")
     return y
 
 
