@@ -105,10 +105,13 @@ B2MOE_API int32_t b2moe_route_sigmoid(const float * logits, int32_t ld, const fl
  * moe_extend_ids (src/experts/moe.cu:209-222).
  *
  * The plan is one int32 device array of b2moe_plan_ints(experts, n * topk, shared_tokens) entries:
- *   [0] number of active experts   [1] number of grouped assignments   [2..3] reserved
- *   then counts[E1], offsets[E1 + 1], active[E1] (ids of experts with count > 0, ascending), perm[A + shared_tokens]
- * with E1 = experts + 1. b2moe_plan_view gives the element offsets of the four arrays (host arithmetic). */
-typedef struct b2moe_plan_view { int64_t counts, offsets, active, perm, total; } b2moe_plan_view;
+ *   [0] number of active experts   [1] number of grouped assignments   [2] number of passes   [3] kernel status word
+ *   then counts[E1], offsets[E1 + 1], active[E1] (ids of experts with count > 0, ascending), perm[A + shared_tokens],
+ *   passes[E1 + 1] (work list of the decode kernels: the active experts taken from the last to the first, each cut
+ *   into passes of 8 tokens; passes[i] = passes before the i-th expert of that order)
+ * with E1 = experts + 1. b2moe_plan_view gives the element offsets of the arrays (host arithmetic). Word [3] stays 0
+ * unless a kernel gave up a bounded wait (it then holds a nonzero code and that launch's outputs are invalid). */
+typedef struct b2moe_plan_view { int64_t counts, offsets, active, perm, passes, total; } b2moe_plan_view;
 B2MOE_API int64_t b2moe_plan_ints(int32_t experts, int32_t assignments, int32_t shared_tokens);
 B2MOE_API void b2moe_plan_view_of(int32_t experts, int32_t assignments, int32_t shared_tokens, b2moe_plan_view * view);
 /* workspace: b2moe_dispatch_workspace_bytes(experts, assignments) bytes, 16-byte aligned */

@@ -48,8 +48,8 @@ def test_sizes():
 def test_plan_layout():
     v = capi.PlanView()
     lib.b2moe_plan_view_of(8, 20, 5, C.byref(v))
-    assert (v.counts, v.offsets, v.active, v.perm, v.total) == (4, 13, 23, 32, 57)
-    assert lib.b2moe_plan_ints(8, 20, 5) == 57 and lib.b2moe_plan_ints(0, 20, 5) == 0
+    assert (v.counts, v.offsets, v.active, v.perm, v.passes, v.total) == (4, 13, 23, 32, 57, 67)
+    assert lib.b2moe_plan_ints(8, 20, 5) == 67 and lib.b2moe_plan_ints(0, 20, 5) == 0
 
 
 def test_codebooks_match_the_table_source():

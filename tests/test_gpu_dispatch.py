@@ -26,6 +26,10 @@ def check(orc, ids, experts, shared):
     act = np.flatnonzero(got_counts > 0)
     assert plan.n_active == act.size and np.array_equal(plan.active.cpu().numpy()[:act.size], act)
     assert int(plan.buf[1]) == grouped + (n if shared else 0)
+    # pass list: active experts from last to first, ceil(count / 8) passes each
+    per = [-(-int(got_counts[e]) // 8) for e in act[::-1]]
+    want = np.concatenate([[0], np.cumsum(per)]).astype(np.int32)
+    assert np.array_equal(plan.passes.cpu().numpy()[:act.size + 1], want) and int(plan.buf[2]) == want[-1] and int(plan.buf[3]) == 0
     return plan
 
 

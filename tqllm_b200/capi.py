@@ -30,7 +30,7 @@ class Bank(C.Structure):
 
 
 class PlanView(C.Structure):
-    _fields_ = [(n, C.c_int64) for n in ("counts", "offsets", "active", "perm", "total")]
+    _fields_ = [(n, C.c_int64) for n in ("counts", "offsets", "active", "perm", "passes", "total")]
 
 
 class Layer(C.Structure):

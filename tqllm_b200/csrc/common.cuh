@@ -35,6 +35,8 @@ inline bool valid_dtype(int dt) { return dt == B2MOE_F32 || dt == B2MOE_F16 || d
 inline size_t dtype_bytes(int dt) { return dt == B2MOE_F32 ? 4 : 2; }
 
 // plan header slots
-enum { PLAN_NACTIVE = 0, PLAN_NGROUPED = 1, PLAN_HDR = 4 };
+enum { PLAN_NACTIVE = 0, PLAN_NGROUPED = 1, PLAN_NPASS = 2, PLAN_STATUS = 3, PLAN_HDR = 4 };
+// tokens of one expert that one pass of the decode kernels takes; the plan's pass list is cut in these units
+constexpr int PASS_TOKENS = 8;
 
 }  // namespace b2

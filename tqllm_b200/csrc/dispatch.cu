@@ -23,7 +23,7 @@ __device__ __forceinline__ int valid_id(const int * ids, int a, int A, int e) {
 }
 
 // counts[0..e1) -> offsets[0..e1], active list and the two header words; one warp, each lane a contiguous span
-__device__ void finish_plan(int * plan, int * counts, int * offsets, int * active, int e1, int lane) {
+__device__ void finish_plan(int * plan, int * counts, int * offsets, int * active, int * passes, int e1, int lane) {
     const int span = (e1 + 31) / 32, lo = lane * span, hi = min(e1, lo + span);
     int sum = 0, act = 0;
     for (int i = lo; i < hi; ++i) { sum += counts[i]; act += counts[i] > 0; }
@@ -38,7 +38,22 @@ __device__ void finish_plan(int * plan, int * counts, int * offsets, int * activ
         if (counts[i] > 0) active[ra++] = i;
         run += counts[i];
     }
-    if (lane == 31) { offsets[e1] = ps; plan[PLAN_NGROUPED] = ps; plan[PLAN_NACTIVE] = pa; plan[2] = 0; plan[3] = 0; }
+    if (lane == 31) { offsets[e1] = ps; plan[PLAN_NGROUPED] = ps; plan[PLAN_NACTIVE] = pa; plan[PLAN_STATUS] = 0; }
+    // pass list: active experts from the last (the shared expert, the heaviest) to the first, cut into passes of
+    // PASS_TOKENS tokens; passes[i] = number of passes before the i-th expert of that order
+    const int na = __shfl_sync(0xffffffffu, pa, 31);
+    __syncwarp();
+    const int sp = (na + 31) / 32, l2 = lane * sp, h2 = min(na, l2 + sp);
+    int mine = 0;
+    for (int i = l2; i < h2; ++i) mine += (counts[active[na - 1 - i]] + PASS_TOKENS - 1) / PASS_TOKENS;
+    int pp = mine;
+    for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, pp, d);
+        if (lane >= d) pp += o;
+    }
+    int rp = pp - mine;
+    for (int i = l2; i < h2; ++i) { passes[i] = rp; rp += (counts[active[na - 1 - i]] + PASS_TOKENS - 1) / PASS_TOKENS; }
+    if (lane == 31) { passes[na] = pp; plan[PLAN_NPASS] = pp; }
 }
 
 // ---- single block: every phase in shared memory (decode-sized batches) ----
@@ -64,7 +79,7 @@ __global__ void dispatch_small_k(const int * __restrict__ ids, int A, int e, int
     }
     if (threadIdx.x == 0) counts[e] = shared_tokens;
     __syncthreads();
-    if (warp == 0) finish_plan(plan, counts, offsets, active, e1, lane);
+    if (warp == 0) finish_plan(plan, counts, offsets, active, perm + A + shared_tokens, e1, lane);
     __syncthreads();
     for (int a = a0 + lane; a - lane < min(A, a0 + chunk); a += 32) {
         const int id = valid_id(ids, a, A, e);
@@ -93,7 +108,7 @@ __global__ void dispatch_hist_k(const int * __restrict__ ids, int A, int e, int 
         __syncwarp();
     }
 }
-__global__ void dispatch_scan_k(int * __restrict__ hist, int chunks, int e, int shared_tokens, int * __restrict__ plan) {
+__global__ void dispatch_scan_k(int * __restrict__ hist, int chunks, int e, int A, int shared_tokens, int * __restrict__ plan) {
     const int e1 = e + 1;
     int * counts = plan + PLAN_HDR, * offsets = counts + e1, * active = offsets + e1 + 1;
     for (int x = threadIdx.x; x < e; x += blockDim.x) {
@@ -103,7 +118,7 @@ __global__ void dispatch_scan_k(int * __restrict__ hist, int chunks, int e, int 
     }
     if (threadIdx.x == 0) counts[e] = shared_tokens;
     __syncthreads();
-    if (threadIdx.x < 32) finish_plan(plan, counts, offsets, active, e1, threadIdx.x);
+    if (threadIdx.x < 32) finish_plan(plan, counts, offsets, active, active + e1 + A + shared_tokens, e1, threadIdx.x);
 }
 __global__ void dispatch_scatter_k(const int * __restrict__ ids, int A, int e, int shared_tokens, int * __restrict__ hist,
                                    int * __restrict__ plan) {
@@ -144,7 +159,7 @@ using namespace b2;
 extern "C" B2MOE_API int64_t b2moe_plan_ints(int32_t experts, int32_t assignments, int32_t shared_tokens) {
     if (experts <= 0 || assignments < 0 || shared_tokens < 0) return 0;
     const int64_t e1 = int64_t(experts) + 1;
-    return PLAN_HDR + e1 + (e1 + 1) + e1 + assignments + shared_tokens;
+    return PLAN_HDR + e1 + (e1 + 1) + e1 + assignments + shared_tokens + (e1 + 1);
 }
 extern "C" B2MOE_API void b2moe_plan_view_of(int32_t experts, int32_t assignments, int32_t shared_tokens, b2moe_plan_view * v) {
     const int64_t e1 = int64_t(experts) + 1;
@@ -152,7 +167,8 @@ extern "C" B2MOE_API void b2moe_plan_view_of(int32_t experts, int32_t assignment
     v->offsets = v->counts + e1;
     v->active = v->offsets + e1 + 1;
     v->perm = v->active + e1;
-    v->total = v->perm + assignments + shared_tokens;
+    v->passes = v->perm + assignments + shared_tokens;
+    v->total = v->passes + e1 + 1;
 }
 extern "C" B2MOE_API size_t b2moe_dispatch_workspace_bytes(int32_t experts, int32_t assignments) {
     if (experts <= 0 || assignments < 0) return 0;
@@ -178,7 +194,7 @@ extern "C" B2MOE_API int32_t b2moe_dispatch(const int32_t * ids, int32_t n, int3
     const int chunks = ceil_div(A, CHUNK);
     if (cudaMemsetAsync(hist, 0, size_t(chunks) * experts * sizeof(int), s) != cudaSuccess) return B2MOE_ERR_CUDA;
     dispatch_hist_k<<<ceil_div(chunks, 8), 256, 0, s>>>(ids, A, experts, hist);
-    dispatch_scan_k<<<1, 1024, 0, s>>>(hist, chunks, experts, shared_tokens, plan);
+    dispatch_scan_k<<<1, 1024, 0, s>>>(hist, chunks, experts, A, shared_tokens, plan);
     dispatch_scatter_k<<<ceil_div(chunks, 8), 256, 0, s>>>(ids, A, experts, shared_tokens, hist, plan);
     return launch_status();
 }

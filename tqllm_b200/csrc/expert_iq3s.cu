@@ -23,7 +23,6 @@ namespace b2 {
 namespace {
 
 constexpr int TILE = 1760;          // bytes of one 16 x 256 IQ3_S tile
-constexpr int WARPS = 8;
 
 // ---------------------------------------------------------------------------------------------------------------
 // Activation split: rows [R][K] -> E4M3 terms [R][K / 32][NTERM][32 bytes] (natural k order) + 1 / scale per row.
@@ -112,9 +111,63 @@ __device__ __forceinline__ void mma_e4m3(float (&c)[4], uint32_t a0, uint32_t a1
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// The grouped kernel. Block = 8 warps = 8 consecutive 16-row tiles of one active expert; a warp walks all column
-// tiles of its row tile (both matrices when MODE = gate/up), the next tile's registers in flight while it decodes
-// the current one. Tokens of the expert are taken NCH * (8 / NTERM) at a time (NCH MMAs per decoded sub-block).
+// Bulk-copy ring: each warp owns STAGES tile slots in shared memory and one mbarrier per slot. Lane 0 posts the
+// expected byte count and issues one cp.async.bulk (the 1-D bulk copy of the tensor memory accelerator, no
+// multicast) per 1760-byte tile; the warp waits on the slot's mbarrier phase, copies its 17 words to registers and
+// hands the slot straight back. Every wait is bounded: a warp that gives up writes PLAN_STATUS and stops.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int STAGES = 4;
+constexpr int CTA_WARPS = 16;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_addr(const void * p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void * src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait on one phase; false = gave up
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_test(bar, parity)) return true;
+        if (i > 64) __nanosleep(32);
+    }
+    return false;
+}
+
+// tile words of this lane from a shared-memory tile slot
+__device__ __forceinline__ void read_tile(TileRegs & r, const uint8_t * tile, int lane) {
+    const uint4 p0 = reinterpret_cast<const uint4 *>(tile)[lane];
+    const uint4 p1 = reinterpret_cast<const uint4 *>(tile + 512)[lane];
+    const uint4 p2 = reinterpret_cast<const uint4 *>(tile + 1024)[lane];
+    r.w[12] = reinterpret_cast<const uint32_t *>(tile + 1536)[lane];
+    const int g = lane >> 2;
+    r.sc0 = reinterpret_cast<const uint32_t *>(tile + 1664)[g];
+    r.sc8 = reinterpret_cast<const uint32_t *>(tile + 1664)[g + 8];
+    r.d0 = __half2float(reinterpret_cast<const __half *>(tile + 1728)[g]);
+    r.d8 = __half2float(reinterpret_cast<const __half *>(tile + 1728)[g + 8]);
+    r.w[0] = p0.x; r.w[1] = p0.y; r.w[2] = p0.z; r.w[3] = p0.w;
+    r.w[4] = p1.x; r.w[5] = p1.y; r.w[6] = p1.z; r.w[7] = p1.w;
+    r.w[8] = p2.x; r.w[9] = p2.y; r.w[10] = p2.z; r.w[11] = p2.w;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// The grouped kernel: one resident block of 16 warps per SM. A work item = (pass, 16-row tile): a pass is up to 8
+// tokens of one active expert (the plan's pass list, heaviest expert first); the warp streams every column tile of
+// its row tile (gate and up tiles alternating when MODE = 0) through its ring and issues NCH MMAs per decoded
+// sub-block (NCH * 8 / NTERM = 8 tokens). Items are dealt round-robin over all warps of the grid.
+// The grid lives in shared memory 32 times, copy L in bank L, so the 32 lanes' random lookups never conflict.
 // MODE 0: out = act[a][row] = silu(gate . x) * (up . x);   MODE 1: out = y[a][row] = down . act[a]
 // ---------------------------------------------------------------------------------------------------------------
 struct Iq3sArgs {
@@ -122,46 +175,70 @@ struct Iq3sArgs {
     size_t bank_bytes;
     const uint8_t * terms;                   // E4M3 activation terms [rows_x][k / 32][NTERM][32]
     const float * inv_scale;                 // [rows_x]
-    const int * plan;
+    int * plan;
     float * out;                             // [A + shared][rows]
     int rows, k_tiles, experts, topk, A;
 };
 
-template <int MODE, int NTERM, int NCH>
-__global__ void __launch_bounds__(WARPS * 32) iq3s_grouped_k(Iq3sArgs p) {
-    constexpr int NMAT = MODE == 0 ? 2 : 1, TPM = 8 / NTERM, TOK = NCH * TPM;
-    __shared__ uint32_t grid8[512];          // the IQ3_S grid re-encoded as E4M3 bytes
+constexpr size_t IQ3S_SMEM = 512 * 32 * 4 + size_t(CTA_WARPS) * STAGES * TILE + CTA_WARPS * STAGES * 8;
+
+template <int MODE, int NTERM>
+__global__ void __launch_bounds__(CTA_WARPS * 32, 1) iq3s_grouped_k(Iq3sArgs p) {
+    constexpr int NMAT = MODE == 0 ? 2 : 1, NCH = NTERM, TPM = 8 / NTERM;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint32_t * grid32 = reinterpret_cast<uint32_t *>(smem);                    // [512][32]: entry i of lane L at i * 32 + L
+    uint8_t * ring = smem + 512 * 32 * 4;                                       // [warp][stage][TILE]
+    uint64_t * bars = reinterpret_cast<uint64_t *>(ring + size_t(CTA_WARPS) * STAGES * TILE);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int e1 = p.experts + 1;
     const int * counts = p.plan + PLAN_HDR, * offsets = counts + e1, * active = offsets + e1 + 1, * perm = active + e1;
-    if (int(blockIdx.y) >= p.plan[PLAN_NACTIVE]) return;
-    for (int i = threadIdx.x; i < 512; i += blockDim.x) {
+    const int * passes = perm + p.A + counts[p.experts];
+    const int na = p.plan[PLAN_NACTIVE], row_tiles = (p.rows + 15) >> 4;
+    const int n_items = p.plan[PLAN_NPASS] * row_tiles;
+
+    for (int j = 0; j < 32; ++j) {
+        const int i = (threadIdx.x >> 5) + CTA_WARPS * j;
         const uint32_t m = c_iq3s_grid[i];   // odd magnitudes 1..15 -> E4M3 codes 0x38 0x44 0x4A 0x4E 0x51 0x53 0x55 0x57
         uint32_t v = 0;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) v |= uint32_t((0x575553514E4A4438ull >> (8 * (((m >> (8 * j)) & 15u) >> 1))) & 255u) << (8 * j);
-        grid8[i] = v;
+        for (int b = 0; b < 4; ++b) v |= uint32_t((0x575553514E4A4438ull >> (8 * (((m >> (8 * b)) & 15u) >> 1))) & 255u) << (8 * b);
+        grid32[i * 32 + lane] = v;
+    }
+    uint8_t * my_ring = ring + size_t(warp) * STAGES * TILE;
+    const uint32_t bar0 = smem_addr(bars + warp * STAGES), ring0 = smem_addr(my_ring);
+    if (lane == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init(bar0 + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    const int row_tiles = (p.rows + 15) >> 4, rt = blockIdx.x * WARPS + warp;
-    if (rt >= row_tiles) return;
-    const int e = active[blockIdx.y], cnt = counts[e], off = offsets[e];
-    const bool shared = e == p.experts;
-    const uint8_t * base[NMAT];
-    base[0] = (shared ? p.s0 : p.w0 + size_t(e) * p.bank_bytes) + size_t(rt) * p.k_tiles * TILE;
-    if (NMAT == 2) base[NMAT - 1] = (shared ? p.s1 : p.w1 + size_t(e) * p.bank_bytes) + size_t(rt) * p.k_tiles * TILE;
+    const uint32_t * my_grid = grid32 + lane;
     const size_t row_bytes = size_t(p.k_tiles) * 8 * NTERM * 32;
+    const int ntiles = p.k_tiles * NMAT;
+    uint32_t filled = 0, drained = 0;      // tiles issued into / taken out of this warp's ring since launch
+    bool alive = true;
 
-    for (int c0 = 0; c0 < cnt; c0 += TOK) {
-        // the activation rows of this lane's B columns: column g = (token slot g / NTERM, term g % NTERM)
+    for (int it = warp * gridDim.x + blockIdx.x; it < n_items && alive; it += CTA_WARPS * gridDim.x) {
+        const int w = it / row_tiles, rt = it - w * row_tiles;
+        int lo = 0, hi = na - 1;             // largest i with passes[i] <= w
+        while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (passes[mid] <= w) lo = mid; else hi = mid - 1; }
+        const int e = active[na - 1 - lo], cnt = counts[e], off = offsets[e], c0 = (w - passes[lo]) * PASS_TOKENS;
+        const bool shared = e == p.experts;
+        const uint8_t * base0 = (shared ? p.s0 : p.w0 + size_t(e) * p.bank_bytes) + size_t(rt) * p.k_tiles * TILE;
+        const uint8_t * base1 = NMAT == 2 ? (shared ? p.s1 : p.w1 + size_t(e) * p.bank_bytes) + size_t(rt) * p.k_tiles * TILE : base0;
+        auto issue = [&](int j) {            // tile j of this item -> the next ring slot (lane 0 only)
+            const uint32_t s = filled % STAGES;
+            const uint8_t * src = ((NMAT == 2 && (j & 1)) ? base1 : base0) + size_t(NMAT == 2 ? j >> 1 : j) * TILE;
+            mbar_expect_tx(bar0 + 8 * s, TILE);
+            bulk_g2s(ring0 + s * TILE, src, TILE, bar0 + 8 * s);
+        };
+        for (int j = 0; j < STAGES && j < ntiles; ++j) { if (lane == 0) issue(j); ++filled; }
+
         const uint8_t * bptr[NCH];
-        int arow[NCH];
 #pragma unroll
-        for (int c = 0; c < NCH; ++c) {
-            const int slot = c0 + c * TPM + g / NTERM;
-            const int a = perm[off + min(slot, cnt - 1)];
-            arow[c] = MODE == 0 ? (a < p.A ? a / p.topk : a - p.A) : a;
-            bptr[c] = p.terms + size_t(arow[c]) * row_bytes + (g % NTERM) * 32 + t * 8;
+        for (int c = 0; c < NCH; ++c) {      // column g of chunk c = (token slot g / NTERM, term g % NTERM)
+            const int a = perm[off + min(c0 + c * TPM + g / NTERM, cnt - 1)];
+            const int xr = MODE == 0 ? (a < p.A ? a / p.topk : a - p.A) : a;
+            bptr[c] = p.terms + size_t(xr) * row_bytes + (g % NTERM) * 32 + t * 8;
         }
         const int nch = min(NCH, (cnt - c0 + TPM - 1) / TPM);
         float acc[NMAT][NCH][4];
@@ -172,23 +249,26 @@ __global__ void __launch_bounds__(WARPS * 32) iq3s_grouped_k(Iq3sArgs p) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[m][c][i] = 0.f;
 
-        TileRegs cur, nxt;
-        load_tile(nxt, base[0], lane);
-        for (int kt = 0; kt < p.k_tiles; ++kt) {
+        for (int kt = 0; kt < p.k_tiles && alive; ++kt) {
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
-                cur = nxt;
-                if (m + 1 < NMAT) load_tile(nxt, base[NMAT - 1] + size_t(kt) * TILE, lane);
-                else if (kt + 1 < p.k_tiles) load_tile(nxt, base[0] + size_t(kt + 1) * TILE, lane);
+                const uint32_t s = drained % STAGES;
+                if (!__all_sync(0xffffffffu, mbar_wait(bar0 + 8 * s, (drained / STAGES) & 1u))) { alive = false; break; }
+                TileRegs cur;
+                read_tile(cur, my_ring + s * TILE, lane);
+                ++drained;
+                __syncwarp();                 // every lane has its words: the slot can be refilled
+                const int jn = kt * NMAT + m + STAGES;
+                if (jn < ntiles) { if (lane == 0) issue(jn); ++filled; }
                 const float dn0 = cur.d0 * -8388608.f, dn8 = cur.d8 * -8388608.f;
 #pragma unroll
                 for (int ib = 0; ib < 8; ++ib) {
                     const uint32_t s0 = cur.w[9 + (ib >> 2)], s8 = cur.w[11 + (ib >> 2)];
                     const int R = 2 * (ib & 3);
-                    const uint32_t a0 = grid8[grid_index(cur, 2 * ib)] ^ ((s0 << (7 - R)) & 0x80808080u);
-                    const uint32_t a2 = grid8[grid_index(cur, 2 * ib + 1)] ^ ((s0 << (6 - R)) & 0x80808080u);
-                    const uint32_t a1 = grid8[grid_index(cur, 16 + 2 * ib)] ^ ((s8 << (7 - R)) & 0x80808080u);
-                    const uint32_t a3 = grid8[grid_index(cur, 17 + 2 * ib)] ^ ((s8 << (6 - R)) & 0x80808080u);
+                    const uint32_t a0 = my_grid[grid_index(cur, 2 * ib) * 32] ^ ((s0 << (7 - R)) & 0x80808080u);
+                    const uint32_t a2 = my_grid[grid_index(cur, 2 * ib + 1) * 32] ^ ((s0 << (6 - R)) & 0x80808080u);
+                    const uint32_t a1 = my_grid[grid_index(cur, 16 + 2 * ib) * 32] ^ ((s8 << (7 - R)) & 0x80808080u);
+                    const uint32_t a3 = my_grid[grid_index(cur, 17 + 2 * ib) * 32] ^ ((s8 << (6 - R)) & 0x80808080u);
                     const float db0 = sub_scale(cur.sc0, cur.d0, dn0, ib), db8 = sub_scale(cur.sc8, cur.d8, dn8, ib);
 #pragma unroll
                     for (int c = 0; c < NCH; ++c) {
@@ -203,14 +283,15 @@ __global__ void __launch_bounds__(WARPS * 32) iq3s_grouped_k(Iq3sArgs p) {
                 }
             }
         }
-        // epilogue: lane holds rows g, g + 8 x columns 2t, 2t + 1 of every chunk; recombine the terms of a token
+        if (!alive) break;
+        // epilogue: the lane holds rows g, g + 8 x columns 2t, 2t + 1 of every chunk; recombine the terms of a token
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
-            float v[NMAT][2];                 // [matrix][row g / g + 8]
+            float v[NMAT][2];                 // [matrix][row g / row g + 8]
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
                 float lo0 = acc[m][c][0] + acc[m][c][1] * 0.0625f, lo8 = acc[m][c][2] + acc[m][c][3] * 0.0625f;
-                if (NTERM == 4) {             // columns 4s..4s+3 of a token sit in lanes t = 2s (terms 0,1) and 2s + 1 (terms 2,3)
+                if (NTERM == 4) {             // a token's columns 4s..4s+3 sit in lanes t = 2s (terms 0, 1) and 2s + 1 (terms 2, 3)
                     const float o0 = __shfl_xor_sync(0xffffffffu, lo0, 1), o8 = __shfl_xor_sync(0xffffffffu, lo8, 1);
                     lo0 = (t & 1) ? o0 + lo0 * 0.00390625f : lo0 + o0 * 0.00390625f;
                     lo8 = (t & 1) ? o8 + lo8 * 0.00390625f : lo8 + o8 * 0.00390625f;
@@ -219,10 +300,8 @@ __global__ void __launch_bounds__(WARPS * 32) iq3s_grouped_k(Iq3sArgs p) {
             }
             const int slot = c0 + c * TPM + (NTERM == 2 ? t : t >> 1);
             const bool writer = slot < cnt && (NTERM == 2 || (t & 1) == 0) && c < nch;
-            // the token of this lane's OUTPUT columns differs from the token of its B column: look it up again
-            const int a = perm[off + min(slot, cnt - 1)];
-            const int xr = MODE == 0 ? (a < p.A ? a / p.topk : a - p.A) : a;
-            const float is = p.inv_scale[xr];
+            const int a = perm[off + min(slot, cnt - 1)];          // the token of this lane's OUTPUT columns
+            const float is = p.inv_scale[MODE == 0 ? (a < p.A ? a / p.topk : a - p.A) : a];
             if (writer) {
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
@@ -241,14 +320,29 @@ __global__ void __launch_bounds__(WARPS * 32) iq3s_grouped_k(Iq3sArgs p) {
             }
         }
     }
+    if (!alive) {                             // a wait ran out: report it and let the copies in flight land before leaving
+        if (lane == 0) atomicExch(p.plan + PLAN_STATUS, 1);
+        for (; drained < filled; ++drained) mbar_wait(bar0 + 8 * (drained % STAGES), (drained / STAGES) & 1u);
+    }
 }
 
 inline int nterm_of(int dtype) { return dtype == B2MOE_BF16 ? 2 : 4; }
 
-template <int MODE, int NTERM, int NCH>
-int32_t launch_grouped(const Iq3sArgs & a, int max_active, cudaStream_t s) {
-    const dim3 grid(ceil_div(ceil_div(a.rows, 16), WARPS), max_active);
-    iq3s_grouped_k<MODE, NTERM, NCH><<<grid, WARPS * 32, 0, s>>>(a);
+int sm_count() {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    return sms;
+}
+
+// max_items: an upper bound of passes * row tiles (the true count is read from the plan on the device)
+template <int MODE, int NTERM>
+int32_t launch_grouped(const Iq3sArgs & a, long long max_items, cudaStream_t s) {
+    const int sms = sm_count();
+    if (sms <= 0) return B2MOE_ERR_CUDA;
+    if (cudaFuncSetAttribute(iq3s_grouped_k<MODE, NTERM>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(IQ3S_SMEM)) != cudaSuccess)
+        return B2MOE_ERR_CUDA;
+    const int blocks = int(std::min<long long>(sms, std::max<long long>(1, max_items)));
+    iq3s_grouped_k<MODE, NTERM><<<blocks, CTA_WARPS * 32, IQ3S_SMEM, s>>>(a);
     return launch_status();
 }
 
@@ -277,9 +371,10 @@ int32_t iq3s_gateup(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_
     a.w0 = static_cast<const uint8_t *>(gate->data); a.w1 = static_cast<const uint8_t *>(up->data);
     if (shared_tokens) { a.s0 = static_cast<const uint8_t *>(sg->data); a.s1 = static_cast<const uint8_t *>(su->data); }
     a.bank_bytes = b2moe_bank_bytes(gate->type, gate->rows, gate->cols);
-    a.terms = terms; a.inv_scale = inv; a.plan = plan; a.out = act;
+    a.terms = terms; a.inv_scale = inv; a.plan = const_cast<int *>(plan); a.out = act;
     a.rows = gate->rows; a.k_tiles = k / 256; a.experts = gate->experts; a.topk = topk; a.A = n * topk;
-    return nterm == 2 ? launch_grouped<0, 2, 2>(a, max_active, s) : launch_grouped<0, 4, 2>(a, max_active, s);
+    const long long items = (long long)(max_active + (n * topk + shared_tokens) / PASS_TOKENS) * ceil_div(gate->rows, 16);
+    return nterm == 2 ? launch_grouped<0, 2>(a, items, s) : launch_grouped<0, 4>(a, items, s);
 }
 
 int32_t iq3s_down(const b2moe_bank * down, const b2moe_bank * sd, const float * act, const int * plan, int n, int topk,
@@ -292,9 +387,9 @@ int32_t iq3s_down(const b2moe_bank * down, const b2moe_bank * sd, const float * 
     a.w0 = static_cast<const uint8_t *>(down->data);
     if (shared_tokens) a.s0 = static_cast<const uint8_t *>(sd->data);
     a.bank_bytes = b2moe_bank_bytes(down->type, down->rows, down->cols);
-    a.terms = terms; a.inv_scale = inv; a.plan = plan; a.out = y;
+    a.terms = terms; a.inv_scale = inv; a.plan = const_cast<int *>(plan); a.out = y;
     a.rows = down->rows; a.k_tiles = k / 256; a.experts = down->experts; a.topk = topk; a.A = n * topk;
-    return launch_grouped<1, 4, 4>(a, max_active, s);
+    return launch_grouped<1, 4>(a, (long long)(max_active + rows_x / PASS_TOKENS) * ceil_div(down->rows, 16), s);
 }
 
 }  // namespace b2

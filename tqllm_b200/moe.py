@@ -93,7 +93,9 @@ class Plan:
     @property
     def active(self): return self.buf[self.view.active:self.view.active + self.experts + 1]
     @property
-    def perm(self): return self.buf[self.view.perm:self.view.total]
+    def perm(self): return self.buf[self.view.perm:self.view.passes]
+    @property
+    def passes(self): return self.buf[self.view.passes:self.view.total]
 
 
 def dispatch(ids: torch.Tensor, experts: int, shared_tokens: int = 0) -> Plan:
@@ -216,7 +218,8 @@ class MoeLayer:
             shared_weights=view(v.shared_weights, n, torch.float32),
             n_active=int(plan[0]),
             counts=plan[pv.counts:pv.counts + E + 1], offsets=plan[pv.offsets:pv.offsets + E + 2],
-            active=plan[pv.active:pv.active + E + 1], perm=plan[pv.perm:pv.total],
+            active=plan[pv.active:pv.active + E + 1], perm=plan[pv.perm:pv.passes], passes=plan[pv.passes:pv.total],
+            status=int(plan[3]),
             act=view(v.act, (n * k + sh) * self.shape.ff, torch.float32).reshape(n * k + sh, self.shape.ff),
             y=view(v.y, (n * k + sh) * self.shape.hidden, torch.float32).reshape(n * k + sh, self.shape.hidden),
         )
