@@ -10,6 +10,7 @@ int32_t generic_gateup(const b2moe_bank *, const b2moe_bank *, const b2moe_bank 
                        int, int, float *, cudaStream_t);
 int32_t generic_down(const b2moe_bank *, const b2moe_bank *, const float *, const int *, int, int, int, float *, cudaStream_t);
 size_t iq3s_workspace_bytes(int rows_x, int k, int dtype);
+bool iq3s_supported(int k, int dtype);
 int32_t iq3s_gateup(const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const void *, int, const int *, int,
                     int, int, float *, void *, int, cudaStream_t);
 int32_t iq3s_down(const b2moe_bank *, const b2moe_bank *, const float *, const int *, int, int, int, float *, void *, int, cudaStream_t);
@@ -25,7 +26,7 @@ int max_active_of(int experts, int n, int topk, int shared_tokens) {
     const long long a = (long long)n * topk;
     return int(a < experts ? a : experts) + (shared_tokens ? 1 : 0);
 }
-bool tuned(uint32_t type) { return type == T_IQ3_S; }
+bool tuned(uint32_t type, int k, int dtype) { return type == T_IQ3_S && iq3s_supported(k, dtype); }
 }  // namespace
 }  // namespace b2
 
@@ -51,7 +52,7 @@ extern "C" B2MOE_API void b2moe_codebooks(uint32_t * grid, int8_t * kv) {
 }
 
 extern "C" B2MOE_API size_t b2moe_expert_workspace_bytes(uint32_t type, int32_t rows_x, int32_t k, int32_t x_dtype) {
-    if (!tuned(type) || rows_x <= 0 || k <= 0 || !valid_dtype(x_dtype)) return 0;
+    if (rows_x <= 0 || k <= 0 || !valid_dtype(x_dtype) || !tuned(type, k, x_dtype)) return 0;
     return iq3s_workspace_bytes(rows_x, k, x_dtype);
 }
 
@@ -71,10 +72,11 @@ extern "C" B2MOE_API int32_t b2moe_expert_gateup_swiglu(const b2moe_bank * gate,
     }
     if (!x || !plan || !act) return B2MOE_ERR_NULL;
     if (!aligned16(x) || !aligned16(act)) return B2MOE_ERR_ALIGN;
-    if (tuned(gate->type)) {
-        if (!workspace) return B2MOE_ERR_NULL;
-        if (!aligned16(workspace)) return B2MOE_ERR_ALIGN;
-        if (workspace_bytes < b2moe_expert_workspace_bytes(gate->type, n, gate->cols, x_dtype)) return B2MOE_ERR_WORKSPACE;
+    if (tuned(gate->type, gate->cols, x_dtype)) {
+        const size_t need = b2moe_expert_workspace_bytes(gate->type, n, gate->cols, x_dtype);
+        if (need && !workspace) return B2MOE_ERR_NULL;
+        if (need && !aligned16(workspace)) return B2MOE_ERR_ALIGN;
+        if (workspace_bytes < need) return B2MOE_ERR_WORKSPACE;
         return iq3s_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, workspace,
                            max_active_of(gate->experts, n, topk, shared_tokens), as_stream(stream));
     }
@@ -92,7 +94,7 @@ extern "C" B2MOE_API int32_t b2moe_expert_down(const b2moe_bank * down, const b2
     }
     if (!act || !plan || !y) return B2MOE_ERR_NULL;
     if (!aligned16(act) || !aligned16(y)) return B2MOE_ERR_ALIGN;
-    if (tuned(down->type)) {
+    if (tuned(down->type, down->cols, B2MOE_F32)) {
         const int rows_x = n * topk + shared_tokens;
         if (!workspace) return B2MOE_ERR_NULL;
         if (!aligned16(workspace)) return B2MOE_ERR_ALIGN;
