@@ -142,6 +142,20 @@ B2MOE_API int32_t b2moe_expert_gateup_swiglu(const b2moe_bank * gate, const b2mo
 B2MOE_API int32_t b2moe_expert_down(const b2moe_bank * down, const b2moe_bank * shared_down, const float * act, const int32_t * plan,
                           int32_t n, int32_t topk, int32_t shared_tokens, float * y, void * workspace, size_t workspace_bytes,
                           b2moe_stream stream);
+/* The down product without a workspace argument and without any allocation, for callers that cannot provide
+ * scratch (an engine plugin that owns no device memory; code inside a stream capture or another region where
+ * cudaMalloc is not allowed). It has no counterpart in the reference. The scratch b2moe_expert_down would take from
+ * the caller lives in a fixed B2MOE_STATIC_SCRATCH_BYTES array inside the library's device image: every GPU that
+ * loads the library holds that array until the process exits. Limits: the bf16 split of the activation rows,
+ * (n*topk + shared_tokens) * cols * 4 bytes, must fit the array, else B2MOE_ERR_CAPACITY and nothing is launched;
+ * all calls on a device share the array, so calls that overlap on the GPU (different streams) race on it. The first
+ * call on each device looks the array's device address up (with that device current) and should come before any
+ * stream capture; later calls only launch. Results are those of b2moe_expert_down. */
+#define B2MOE_STATIC_SCRATCH_BYTES (16u << 20)
+B2MOE_API size_t b2moe_static_scratch_bytes(void);
+B2MOE_API int32_t b2moe_expert_down_static(const b2moe_bank * down, const b2moe_bank * shared_down, const float * act,
+                                 const int32_t * plan, int32_t n, int32_t topk, int32_t shared_tokens, float * y,
+                                 b2moe_stream stream);
 /* out[t] = sum_s weights[t][s] * y[t*topk + s] (slot order, skipped where ids[t][s] < 0 when ids is given)
  *          + shared_weights[t] (1 when null) * y[n*topk + t] when shared_tokens = n.
  * Replaces moe_sum / moe_common::moe_sum / fn_moe_combine (src/experts/moe.cu:223-234, src/experts/moe_common.cu:186-194,
