@@ -263,15 +263,46 @@ def run_b200(args):
                                                   ews.data_ptr(), ews.numel(), stream.cuda_stream)
         for l in range(L):
             assert gateup(l) == 0
-        reps = max(3, min(args.steps, 20))
-        evs = []
-        for _ in range(reps):
+
+        def time_stage(fn):
+            """mean microseconds of fn(layer) over the layers, each launch bracketed by events on the launching stream"""
             for l in range(L):
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record(stream); gateup(l); b.record(stream)
-                evs.append((a, b))
-        torch.cuda.synchronize()
-        k_ms = sum(a.elapsed_time(b) for a, b in evs) / len(evs)
+                assert fn(l) == 0
+            evs = []
+            for _ in range(max(3, min(args.steps, 20))):
+                for l in range(L):
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(stream); fn(l); b.record(stream)
+                    evs.append((a, b))
+            torch.cuda.synchronize()
+            return 1e3 * sum(a.elapsed_time(b) for a, b in evs) / len(evs)
+
+        k_ms = time_stage(gateup) * 1e-3
+        # the other stages, the same way (reported as stage_us; they explain ms_per_step)
+        F32 = 0
+        st = stream.cuda_stream
+        A = T * shape.topk
+        logits = torch.zeros(T, shape.experts + 1, dtype=torch.float32, device=dev)
+        idb = torch.zeros(T, shape.topk, dtype=torch.int32, device=dev)
+        wts = torch.zeros(T, shape.topk, dtype=torch.float32, device=dev)
+        yb = torch.zeros(A + T, shape.hidden, dtype=torch.float32, device=dev)
+        ob = torch.zeros(T, shape.hidden, dtype=torch.bfloat16, device=dev)
+        dws = torch.empty(max(lib.b2moe_expert_workspace_bytes(shape.types[2], A + T, shape.ff, F32), 16), dtype=torch.uint8, device=dev)
+        plan2 = moe.Plan(shape.experts, T, shape.topk, T, dev)
+        stage_us = {
+            "router": time_stage(lambda l: lib.b2moe_router(layers[l].router_w.data_ptr(), None, x.data_ptr(), BF16, logits.data_ptr(),
+                                                            shape.experts + 1, shape.hidden, shape.experts, T, st)),
+            "topk": time_stage(lambda l: lib.b2moe_topk_softmax(logits.data_ptr(), shape.experts + 1, idb.data_ptr(), wts.data_ptr(), None,
+                                                                shape.experts, shape.topk, T, shape.scale, st)),
+            "dispatch": time_stage(lambda l: lib.b2moe_dispatch(idb.data_ptr(), T, shape.topk, shape.experts, T, plan2.buf.data_ptr(),
+                                                                None, 0, st)),
+            "gateup_swiglu": k_ms * 1e3,
+            "down": time_stage(lambda l: lib.b2moe_expert_down(C.byref(layers[l].down.c), C.byref(layers[l].sh[2].c), act.data_ptr(),
+                                                               plans[l].buf.data_ptr(), T, shape.topk, T, yb.data_ptr(), dws.data_ptr(),
+                                                               dws.numel(), st)),
+            "combine": time_stage(lambda l: lib.b2moe_combine(yb.data_ptr(), None, wts.data_ptr(), None, T, shape.topk, shape.hidden, T,
+                                                              ob.data_ptr(), BF16, st)),
+        }
     n_active = sum(p.n_active for p in plans) / L            # includes the shared expert
     gu_bytes = 2 * synth.raw_bytes(shape.types[0], shape.ff, shape.hidden)
     peak, peak_kind = peaks()
@@ -302,7 +333,7 @@ def run_b200(args):
                          "active_experts_per_launch": n_active, "bytes_per_expert": gu_bytes},
             "expert_weight_gbs": weight_bytes_step / (ms_step * 1e-3) / 1e9,
             "expert_weight_frac_of_8tbs": weight_bytes_step / (ms_step * 1e-3) / 8e12,
-            "cpu_baseline": cpu, "clocks": clocks.summary(),
+            "stage_us": stage_us, "cpu_baseline": cpu, "clocks": clocks.summary(),
         }))
     if world > 1:
         dist.destroy_process_group()
