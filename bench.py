@@ -179,9 +179,28 @@ def run_b200(args):
         dist.init_process_group("nccl", device_id=dev)
     shape = synth.CONFIGS["c2"]
     T, L = args.tokens, args.layers
-    synth_layers, rscale = make_layers(synth, shape, L, dev)
-    layers = [moe.MoeLayer.from_synth(sl) for sl in synth_layers]
-    host_layer0 = synth_layers[0] if rank == 0 and not args.no_cpu else None
+    router_all = None
+    if world > 1:
+        # expert parallel: every rank draws the same layer (same seed), keeps the banks of its own expert block only
+        from tqllm_b200 import ep
+        first, count = ep.expert_range(shape.experts, world, rank)
+        rscale = synth.solve_router_scale(shape, 0.6)
+        layers, router_all = [], []
+        H, F = shape.hidden, shape.ff
+        for l in range(L):
+            sl = synth.make_layer(shape, SEED + 17 * l, dev, router_scale=rscale)
+            cut = lambda raw, i: raw[first * synth.raw_bytes(shape.types[i], (F, F, H)[i], (H, H, F)[i]):
+                                     (first + count) * synth.raw_bytes(shape.types[i], (F, F, H)[i], (H, H, F)[i])].clone()
+            layers.append(moe.MoeLayer(shape, sl.router_w[first:first + count], tuple(cut(sl.raw[i], i) for i in range(3)), sl.shared_raw,
+                                       experts=count, device=dev))
+            router_all.append(sl.router_w.contiguous())
+            del sl
+            torch.cuda.empty_cache()
+        synth_layers = []
+    else:
+        synth_layers, rscale = make_layers(synth, shape, L, dev)
+        layers = [moe.MoeLayer.from_synth(sl, device=dev) for sl in synth_layers]
+    host_layer0 = synth_layers[0] if rank == 0 and not args.no_cpu and world == 1 else None
     if host_layer0 is not None:      # keep only the first layer's raw blocks (for the CPU baseline), on the host
         host_layer0 = synth.Layer(shape, host_layer0.router_w.cpu(), None, tuple(t.cpu() for t in host_layer0.raw),
                                   tuple(t.cpu() for t in host_layer0.shared_raw))
@@ -189,12 +208,23 @@ def run_b200(args):
     torch.cuda.empty_cache()
     x = synth.make_tokens(shape, T, SEED + rank, dev)
     outs = [torch.empty(T, shape.hidden, dtype=torch.bfloat16, device=dev) for _ in range(L)]
-    for lay in layers:
-        lay.reserve(T)
+    if world == 1:
+        for lay in layers:
+            lay.reserve(T)
 
-    def step():
-        for lay, o in zip(layers, outs):
-            lay.forward(x, out=o)
+    if world > 1:
+        from tqllm_b200 import ep
+        comm = ep.TorchComm()
+        H, F = shape.hidden, shape.ff
+        eps = [ep.CudaEpLayer(lay, rw, shape.experts, world, rank) for lay, rw in zip(layers, router_all)]
+
+        def step():
+            for l, e in enumerate(eps):
+                outs[l] = ep.ep_forward(e, comm, x)
+    else:
+        def step():
+            for lay, o in zip(layers, outs):
+                lay.forward(x, out=o)
 
     # pinned host buffers of the end-to-end leg
     x_host = x.cpu().pin_memory()
@@ -212,7 +242,7 @@ def run_b200(args):
         for _ in range(max(args.warmup, 3)):
             step()
         stream.synchronize()
-        if args.graph:
+        if args.graph and (world == 1 or args.graph > 1):
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 step()
@@ -242,72 +272,86 @@ def run_b200(args):
             step_e2e()
         ms_e2e = timed(step_e2e, args.steps)
 
-        # dominant kernel, timed alone with events on the launching stream: the grouped gate/up + SwiGLU product
-        art = [lay.artefacts() for lay in layers]
-        plans, ids = [], []
-        for lay in layers:
-            lg = moe.router(lay.router_w, x)
-            i, w, _ = moe.topk_softmax(lg, lay.experts, shape.topk, shape.scale)
-            plans.append(moe.dispatch(i, lay.experts, T))
-        act = torch.zeros(T * shape.topk + T, shape.ff, dtype=torch.float32, device=dev)
-        import ctypes as C
-        from tqllm_b200.capi import lib, BF16
+        if world == 1:
+            # dominant kernel, timed alone with events on the launching stream: the grouped gate/up + SwiGLU product
+            art = [lay.artefacts() for lay in layers]
+            plans, ids = [], []
+            for lay in layers:
+                lg = moe.router(lay.router_w, x)
+                i, w, _ = moe.topk_softmax(lg, lay.experts, shape.topk, shape.scale)
+                plans.append(moe.dispatch(i, lay.experts, T))
+            act = torch.zeros(T * shape.topk + T, shape.ff, dtype=torch.float32, device=dev)
+            import ctypes as C
+            from tqllm_b200.capi import lib, BF16
 
-        wsb = lib.b2moe_expert_workspace_bytes(shape.types[0], T, shape.hidden, BF16)
-        ews = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+            wsb = lib.b2moe_expert_workspace_bytes(shape.types[0], T, shape.hidden, BF16)
+            ews = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
 
-        def gateup(l):
-            lay = layers[l]
-            return lib.b2moe_expert_gateup_swiglu(C.byref(lay.gate.c), C.byref(lay.up.c), C.byref(lay.sh[0].c), C.byref(lay.sh[1].c),
-                                                  x.data_ptr(), BF16, plans[l].buf.data_ptr(), T, shape.topk, T, act.data_ptr(),
-                                                  ews.data_ptr(), ews.numel(), stream.cuda_stream)
-        for l in range(L):
-            assert gateup(l) == 0
-
-        def time_stage(fn):
-            """mean microseconds of fn(layer) over the layers, each launch bracketed by events on the launching stream"""
+            def gateup(l):
+                lay = layers[l]
+                return lib.b2moe_expert_gateup_swiglu(C.byref(lay.gate.c), C.byref(lay.up.c), C.byref(lay.sh[0].c), C.byref(lay.sh[1].c),
+                                                      x.data_ptr(), BF16, plans[l].buf.data_ptr(), T, shape.topk, T, act.data_ptr(),
+                                                      ews.data_ptr(), ews.numel(), stream.cuda_stream)
             for l in range(L):
-                assert fn(l) == 0
-            evs = []
-            for _ in range(max(3, min(args.steps, 20))):
-                for l in range(L):
-                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    a.record(stream); fn(l); b.record(stream)
-                    evs.append((a, b))
-            torch.cuda.synchronize()
-            return 1e3 * sum(a.elapsed_time(b) for a, b in evs) / len(evs)
+                assert gateup(l) == 0
 
-        k_ms = time_stage(gateup) * 1e-3
-        # the other stages, the same way (reported as stage_us; they explain ms_per_step)
-        F32 = 0
-        st = stream.cuda_stream
-        A = T * shape.topk
-        logits = torch.zeros(T, shape.experts + 1, dtype=torch.float32, device=dev)
-        idb = torch.zeros(T, shape.topk, dtype=torch.int32, device=dev)
-        wts = torch.zeros(T, shape.topk, dtype=torch.float32, device=dev)
-        yb = torch.zeros(A + T, shape.hidden, dtype=torch.float32, device=dev)
-        ob = torch.zeros(T, shape.hidden, dtype=torch.bfloat16, device=dev)
-        dws = torch.empty(max(lib.b2moe_expert_workspace_bytes(shape.types[2], A + T, shape.ff, F32), 16), dtype=torch.uint8, device=dev)
-        plan2 = moe.Plan(shape.experts, T, shape.topk, T, dev)
-        stage_us = {
-            "router": time_stage(lambda l: lib.b2moe_router(layers[l].router_w.data_ptr(), None, x.data_ptr(), BF16, logits.data_ptr(),
-                                                            shape.experts + 1, shape.hidden, shape.experts, T, st)),
-            "topk": time_stage(lambda l: lib.b2moe_topk_softmax(logits.data_ptr(), shape.experts + 1, idb.data_ptr(), wts.data_ptr(), None,
-                                                                shape.experts, shape.topk, T, shape.scale, st)),
-            "dispatch": time_stage(lambda l: lib.b2moe_dispatch(idb.data_ptr(), T, shape.topk, shape.experts, T, plan2.buf.data_ptr(),
-                                                                None, 0, st)),
-            "gateup_swiglu": k_ms * 1e3,
-            "down": time_stage(lambda l: lib.b2moe_expert_down(C.byref(layers[l].down.c), C.byref(layers[l].sh[2].c), act.data_ptr(),
-                                                               plans[l].buf.data_ptr(), T, shape.topk, T, yb.data_ptr(), dws.data_ptr(),
-                                                               dws.numel(), st)),
-            "combine": time_stage(lambda l: lib.b2moe_combine(yb.data_ptr(), None, wts.data_ptr(), None, T, shape.topk, shape.hidden, T,
-                                                              ob.data_ptr(), BF16, st)),
-        }
-    n_active = sum(p.n_active for p in plans) / L            # includes the shared expert
+            def time_stage(fn):
+                """mean microseconds of fn(layer) over the layers, each launch bracketed by events on the launching stream"""
+                for l in range(L):
+                    assert fn(l) == 0
+                evs = []
+                for _ in range(max(3, min(args.steps, 20))):
+                    for l in range(L):
+                        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        a.record(stream); fn(l); b.record(stream)
+                        evs.append((a, b))
+                torch.cuda.synchronize()
+                return 1e3 * sum(a.elapsed_time(b) for a, b in evs) / len(evs)
+
+            k_ms = time_stage(gateup) * 1e-3
+            # the other stages, the same way (reported as stage_us; they explain ms_per_step)
+            F32 = 0
+            st = stream.cuda_stream
+            A = T * shape.topk
+            logits = torch.zeros(T, shape.experts + 1, dtype=torch.float32, device=dev)
+            idb = torch.zeros(T, shape.topk, dtype=torch.int32, device=dev)
+            wts = torch.zeros(T, shape.topk, dtype=torch.float32, device=dev)
+            yb = torch.zeros(A + T, shape.hidden, dtype=torch.float32, device=dev)
+            ob = torch.zeros(T, shape.hidden, dtype=torch.bfloat16, device=dev)
+            dws = torch.empty(max(lib.b2moe_expert_workspace_bytes(shape.types[2], A + T, shape.ff, F32), 16), dtype=torch.uint8, device=dev)
+            plan2 = moe.Plan(shape.experts, T, shape.topk, T, dev)
+            stage_us = {
+                "router": time_stage(lambda l: lib.b2moe_router(layers[l].router_w.data_ptr(), None, x.data_ptr(), BF16, logits.data_ptr(),
+                                                                shape.experts + 1, shape.hidden, shape.experts, T, st)),
+                "topk": time_stage(lambda l: lib.b2moe_topk_softmax(logits.data_ptr(), shape.experts + 1, idb.data_ptr(), wts.data_ptr(), None,
+                                                                    shape.experts, shape.topk, T, shape.scale, st)),
+                "dispatch": time_stage(lambda l: lib.b2moe_dispatch(idb.data_ptr(), T, shape.topk, shape.experts, T, plan2.buf.data_ptr(),
+                                                                    None, 0, st)),
+                "gateup_swiglu": k_ms * 1e3,
+                "down": time_stage(lambda l: lib.b2moe_expert_down(C.byref(layers[l].down.c), C.byref(layers[l].sh[2].c), act.data_ptr(),
+                                                                   plans[l].buf.data_ptr(), T, shape.topk, T, yb.data_ptr(), dws.data_ptr(),
+                                                                   dws.numel(), st)),
+                "combine": time_stage(lambda l: lib.b2moe_combine(yb.data_ptr(), None, wts.data_ptr(), None, T, shape.topk, shape.hidden, T,
+                                                                  ob.data_ptr(), BF16, st)),
+            }
+        else:
+            torch.cuda.synchronize()
+            plans, stage_us, k_ms = None, None, None
+            n_active_rank = sum(int(e.buf["plan"][0]) for e in eps) / L      # this rank's active experts per layer (with the shared one)
     gu_bytes = 2 * synth.raw_bytes(shape.types[0], shape.ff, shape.hidden)
     peak, peak_kind = peaks()
-    achieved = n_active * gu_bytes / (k_ms * 1e-3) / 1e9
-    weight_bytes_step = sum(p.n_active for p in plans) * shape.expert_bytes()
+    if world == 1:
+        n_active = sum(p.n_active for p in plans) / L            # includes the shared expert
+        achieved = n_active * gu_bytes / (k_ms * 1e-3) / 1e9
+        weight_bytes_step = sum(p.n_active for p in plans) * shape.expert_bytes()
+        roof_kernel = "grouped gate/up + SwiGLU"
+    else:
+        # per-GPU view: the whole layer (exchanges included) against this GPU's HBM: expert bytes it streamed / step time
+        n_active = n_active_rank
+        weight_bytes_step = n_active_rank * L * shape.expert_bytes()
+        achieved = weight_bytes_step / (ms_step * 1e-3) / 1e9
+        k_ms = ms_step / L
+        roof_kernel = "whole expert-parallel layer on rank 0 (dispatch + combine exchanges included)"
     value = world * T * L / (ms_step * 1e-3)
     e2e = world * T * L / (ms_e2e * 1e-3)
 
@@ -322,13 +366,14 @@ def run_b200(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": workload_name(T, L), "tokens": T, "layers": L, "router_scale": rscale,
-                       "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
-                       "l2": "per-step expert weights (GBs) exceed the 126 MB L2; no flush needed", "cuda_graph": bool(args.graph),
+                       "parallelism": "single GPU" if world == 1 else f"ep{world}: {shape.experts // world} experts per GPU, {T} tokens per GPU, "
+                                      "NCCL all-gather dispatch + all-to-all combine",
+                       "l2": "per-step expert weights (GBs) exceed the 126 MB L2; no flush needed", "cuda_graph": graph is not None,
                        "activations": "bf16 in, bf16 out, fp32 intermediates"},
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": x_host.numel() * 2,
                     "d2h_bytes_per_step": out_host.numel() * 2},
-            "gpu_launches": args.steps * L * 6,
-            "roofline": {"bound": "hbm", "kernel": "grouped gate/up + SwiGLU", "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "gpu_launches": args.steps * L * (7 if world == 1 else 9),
+            "roofline": {"bound": "hbm", "kernel": roof_kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None, "kernel_ms": k_ms,
                          "active_experts_per_launch": n_active, "bytes_per_expert": gu_bytes},
             "expert_weight_gbs": weight_bytes_step / (ms_step * 1e-3) / 1e9,

@@ -118,6 +118,12 @@ B2MOE_API void b2moe_plan_view_of(int32_t experts, int32_t assignments, int32_t 
 B2MOE_API size_t b2moe_dispatch_workspace_bytes(int32_t experts, int32_t assignments);
 B2MOE_API int32_t b2moe_dispatch(const int32_t * ids, int32_t n, int32_t topk, int32_t experts, int32_t shared_tokens, int32_t * plan,
                        void * workspace, size_t workspace_bytes, b2moe_stream stream);
+/* The same with the always-on expert evaluated for the token range [shared_first, shared_first + shared_count) only
+ * (expert parallelism: a rank routes every rank's tokens but owns the shared expert of its own). The plan is sized
+ * with shared_tokens = shared_count; the shared rows of act / y still sit at n*topk + token. */
+B2MOE_API int32_t b2moe_dispatch_range(const int32_t * ids, int32_t n, int32_t topk, int32_t experts, int32_t shared_first,
+                             int32_t shared_count, int32_t * plan, void * workspace, size_t workspace_bytes,
+                             b2moe_stream stream);
 /* moe_group-compatible view of a plan (src/experts/moe_kernels.cuh:29): counts [experts], groups [experts][n] */
 B2MOE_API int32_t b2moe_plan_to_groups(const int32_t * plan, int32_t n, int32_t topk, int32_t experts, int32_t * counts,
                              int32_t * groups, b2moe_stream stream);
@@ -163,6 +169,21 @@ B2MOE_API int32_t b2moe_expert_down_static(const b2moe_bank * down, const b2moe_
 B2MOE_API int32_t b2moe_combine(const float * y, const int32_t * ids, const float * weights, const float * shared_weights, int32_t n,
                       int32_t topk, int32_t hidden, int32_t shared_tokens, void * out, int32_t out_dtype,
                       b2moe_stream stream);
+
+/* ---- expert parallelism --------------------------------------------------------------------------------------
+ * Rank r of G owns the contiguous experts [first_expert, first_expert + local_experts); tokens are data-parallel and
+ * router weights replicated. Per layer: all ranks exchange their activation rows and routed ids (NCCL, host-driven),
+ * each rank maps the ids onto its own experts (b2moe_ep_local_ids: others become -1 and are skipped), runs dispatch /
+ * gate-up / down on them, forms per-token partial sums with b2moe_combine (ids = the local ids), returns them to the
+ * tokens' home ranks (NCCL all-to-all) and the home rank adds the partial sums in ascending rank order plus its own
+ * shared expert (b2moe_ep_reduce). Generalises the reference's two-rank ep_local_ids / ep_gather / ep_scatter
+ * (src/experts/moe.cu:496-541, src/experts/moe_kernels.cuh:40-50) to G ranks without a result cap. */
+B2MOE_API int32_t b2moe_ep_local_ids(const int32_t * ids, int32_t * local_ids, int32_t count, int32_t first_expert,
+                           int32_t local_experts, b2moe_stream stream);
+/* parts: fp32 [ranks][n][hidden] (slice r = rank r's partial sums for this rank's n tokens); shared_y fp32 [n][hidden]
+ * and shared_weights [n] may be NULL (no shared expert / weight 1). out [n][hidden] of out_dtype. */
+B2MOE_API int32_t b2moe_ep_reduce(const float * parts, int32_t ranks, const float * shared_y, const float * shared_weights,
+                        int32_t n, int32_t hidden, void * out, int32_t out_dtype, b2moe_stream stream);
 
 /* ---- whole layer ----------------------------------------------------------------------------------------------
  * router -> top-k -> dispatch -> gate/up + SwiGLU -> down -> combine, the sequence of qwen35_forward.cpp:1121-1252,

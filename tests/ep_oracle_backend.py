@@ -1,0 +1,62 @@
+"""CPU stand-in for the three compute phases of tqllm_b200.ep (route_local / partial_sums / finish), built on the
+oracle: it lets the gloo tests run the real expert-parallel orchestration and exchanges without a GPU. Test code."""
+import numpy as np
+import torch
+
+import oracle
+from tqllm_b200 import ep, synth
+
+
+def slice_raw(raw, type_id, rows, cols, first, count):
+    b = synth.raw_bytes(type_id, rows, cols)
+    return raw[first * b:(first + count) * b]
+
+
+class OracleEpBackend:
+    def __init__(self, shape, layer, experts_total, world, rank):
+        self.orc = oracle.oracle()
+        self.shape, self.layer, self.E, self.world, self.rank = shape, layer, experts_total, world, rank
+        self.first, self.count = ep.expert_range(experts_total, world, rank)
+        H, F = shape.hidden, shape.ff
+        tg, tu, td = shape.types
+        self.w = []
+        for e in range(self.first, self.first + self.count):
+            g = self.orc.dequant(tg, slice_raw(layer.raw[0], tg, F, H, e, 1).numpy(), F * H).reshape(F, H)
+            u = self.orc.dequant(tu, slice_raw(layer.raw[1], tu, F, H, e, 1).numpy(), F * H).reshape(F, H)
+            d = self.orc.dequant(td, slice_raw(layer.raw[2], td, H, F, e, 1).numpy(), H * F).reshape(H, F)
+            self.w.append((g, u, d))
+        self.sh = None
+        if layer.shared_raw is not None:
+            self.sh = (self.orc.dequant(tg, layer.shared_raw[0].numpy(), F * H).reshape(F, H),
+                       self.orc.dequant(tu, layer.shared_raw[1].numpy(), F * H).reshape(F, H),
+                       self.orc.dequant(td, layer.shared_raw[2].numpy(), H * F).reshape(H, F))
+
+    def route_local(self, x):
+        logits = self.orc.router_logits(self.layer.router_w.numpy(), x.float().numpy())
+        bias = None if self.layer.sel_bias is None else self.layer.sel_bias.numpy()
+        ids, w = self.orc.route(self.shape.gating, logits, self.shape.topk, self.shape.norm, self.shape.scale, bias)
+        return torch.from_numpy(ids), torch.from_numpy(w)
+
+    def partial_sums(self, x_all, ids_all, w_all):
+        xs, ids, w = x_all.float().numpy(), ids_all.numpy(), w_all.numpy()
+        N, k = ids.shape
+        T = N // self.world
+        parts = np.zeros((N, self.shape.hidden), np.float32)
+        for t in range(N):
+            for s in range(k):
+                e = ids[t, s] - self.first
+                if 0 <= e < self.count:
+                    parts[t] += w[t, s] * self.orc.expert_ffn(xs[t], *self.w[e])
+        shared = None
+        if self.sh is not None:
+            shared = np.stack([self.orc.expert_ffn(xs[self.rank * T + t], *self.sh) for t in range(T)])
+            shared = torch.from_numpy(shared)
+        return torch.from_numpy(parts), shared
+
+    def finish(self, recv, shared):
+        out = torch.zeros_like(recv[0])
+        for r in range(recv.shape[0]):
+            out += recv[r]
+        if shared is not None:
+            out += shared
+        return out

@@ -1,0 +1,60 @@
+"""GPU: the expert-parallel compute phases (C ABI: b2moe_ep_local_ids, b2moe_dispatch_range, the grouped kernels,
+b2moe_combine over local ids, b2moe_ep_reduce) with all ranks emulated on one device and the exchanges done by tensor
+copies — how the reference tests its two-rank split (tests/ep_split.cu:87-151). The split result must equal the
+unsplit layer: ids exactly, outputs up to the order of the fp32 partial sums."""
+import numpy as np
+import pytest
+import torch
+
+from ep_oracle_backend import slice_raw
+from make_golden import layer_inputs
+from tqllm_b200 import synth
+from util import rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def run_split(shape, E, T, world, seed):
+    from tqllm_b200 import ep, moe
+    layer, x = layer_inputs(shape, E, T * world, seed)
+    full = moe.MoeLayer.from_synth(layer, experts=E)
+    xd = x.cuda()
+    want = full.forward(xd).cpu().numpy()
+    want_ids = full.artefacts()["ids"].cpu().numpy()
+    H, F = shape.hidden, shape.ff
+    ranks = []
+    for r in range(world):
+        first, count = ep.expert_range(E, world, r)
+        raw = tuple(slice_raw(layer.raw[i], shape.types[i], (F, F, H)[i], (H, H, F)[i], first, count) for i in range(3))
+        loc = moe.MoeLayer(shape, layer.router_w[first:first + count], raw, layer.shared_raw, experts=count)
+        ranks.append(ep.CudaEpLayer(loc, layer.router_w.cuda(), E, world, r, out_dtype=torch.float32,
+                                    sel_bias_all=None if layer.sel_bias is None else layer.sel_bias.cuda()))
+    routed = [rk.route_local(xd[r * T:(r + 1) * T]) for r, rk in enumerate(ranks)]
+    ids_all = torch.cat([i for i, _ in routed]).contiguous()
+    w_all = torch.cat([w for _, w in routed]).contiguous()
+    assert np.array_equal(ids_all.cpu().numpy(), want_ids)
+    parts = [rk.partial_sums(xd, ids_all, w_all) for rk in ranks]
+    outs = []
+    for h, rk in enumerate(ranks):
+        recv = torch.stack([parts[r][0][h * T:(h + 1) * T] for r in range(world)]).contiguous()
+        outs.append(rk.finish(recv, parts[h][1]).cpu().numpy())
+    return np.concatenate(outs), want
+
+
+@pytest.mark.parametrize("world", (2, 4))
+@pytest.mark.parametrize("types,gating,shared", (((21, 21, 21), 1, True), ((12, 12, 12), 2, False), ((23, 23, 20), 1, True)))
+def test_split_equals_unsplit(world, types, gating, shared):
+    ff = 256 if types[2] != 20 else 96
+    shape = synth.LayerShape("ep-gpu", 512, 16, 4, ff, gating=gating, sel_bias=gating == 2, shared=shared, types=types)
+    got, want = run_split(shape, 16, 6, world, 50 + world)
+    assert rel_err(got, want) <= 1e-5
+
+
+def test_uneven_blocks_and_idle_rank():
+    """7 experts over 4 ranks (blocks of 2, 2, 2, 1), and a rank whose experts nobody routed to"""
+    shape = synth.LayerShape("ep-uneven", 512, 7, 2, 256, shared=True, types=(21, 21, 21))
+    got, want = run_split(shape, 7, 3, 4, 9)
+    assert rel_err(got, want) <= 1e-5
+    shape = synth.LayerShape("ep-idle", 512, 16, 1, 256, types=(21, 21, 21))
+    got, want = run_split(shape, 16, 1, 4, 10)          # one token, one expert: three ranks have nothing to do
+    assert rel_err(got, want) <= 1e-5

@@ -57,7 +57,7 @@ __device__ void finish_plan(int * plan, int * counts, int * offsets, int * activ
 }
 
 // ---- single block: every phase in shared memory (decode-sized batches) ----
-__global__ void dispatch_small_k(const int * __restrict__ ids, int A, int e, int shared_tokens, int * __restrict__ plan) {
+__global__ void dispatch_small_k(const int * __restrict__ ids, int A, int e, int shared_first, int shared_tokens, int * __restrict__ plan) {
     extern __shared__ unsigned short hist[];       // [32 warps][e]
     const int e1 = e + 1;
     int * counts = plan + PLAN_HDR, * offsets = counts + e1, * active = offsets + e1 + 1, * perm = active + e1;
@@ -92,7 +92,7 @@ __global__ void dispatch_small_k(const int * __restrict__ ids, int A, int e, int
         if (id >= 0 && lane == __ffs(peers) - 1) hist[warp * e + id] += (unsigned short)__popc(peers);
         __syncwarp();
     }
-    for (int t = threadIdx.x; t < shared_tokens; t += blockDim.x) perm[offsets[e] + t] = A + t;
+    for (int t = threadIdx.x; t < shared_tokens; t += blockDim.x) perm[offsets[e] + t] = A + shared_first + t;
 }
 
 // ---- multi-block path: chunk counters in global scratch [chunks][e] ----
@@ -120,7 +120,7 @@ __global__ void dispatch_scan_k(int * __restrict__ hist, int chunks, int e, int 
     __syncthreads();
     if (threadIdx.x < 32) finish_plan(plan, counts, offsets, active, active + e1 + A + shared_tokens, e1, threadIdx.x);
 }
-__global__ void dispatch_scatter_k(const int * __restrict__ ids, int A, int e, int shared_tokens, int * __restrict__ hist,
+__global__ void dispatch_scatter_k(const int * __restrict__ ids, int A, int e, int shared_first, int shared_tokens, int * __restrict__ hist,
                                    int * __restrict__ plan) {
     const int e1 = e + 1;
     const int * offsets = plan + PLAN_HDR + e1;
@@ -128,7 +128,7 @@ __global__ void dispatch_scatter_k(const int * __restrict__ ids, int A, int e, i
     const int lane = threadIdx.x & 31, chunk = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int a0 = chunk * CHUNK;
     if (blockIdx.x == 0)
-        for (int t = threadIdx.x; t < shared_tokens; t += blockDim.x) perm[offsets[e] + t] = A + t;
+        for (int t = threadIdx.x; t < shared_tokens; t += blockDim.x) perm[offsets[e] + t] = A + shared_first + t;
     if (a0 >= A) return;
     int * h = hist + size_t(chunk) * e;
     for (int a = a0 + lane; a - lane < min(A, a0 + CHUNK); a += 32) {
@@ -176,15 +176,16 @@ extern "C" B2MOE_API size_t b2moe_dispatch_workspace_bytes(int32_t experts, int3
     return align_up(size_t(ceil_div(assignments, CHUNK)) * experts * sizeof(int), 16);
 }
 
-extern "C" B2MOE_API int32_t b2moe_dispatch(const int32_t * ids, int32_t n, int32_t topk, int32_t experts, int32_t shared_tokens,
-                                  int32_t * plan, void * workspace, size_t workspace_bytes, b2moe_stream stream) {
-    if (n <= 0 || topk <= 0 || experts <= 0 || (shared_tokens != 0 && shared_tokens != n)) return B2MOE_ERR_SHAPE;
+extern "C" B2MOE_API int32_t b2moe_dispatch_range(const int32_t * ids, int32_t n, int32_t topk, int32_t experts, int32_t shared_first,
+                                        int32_t shared_count, int32_t * plan, void * workspace, size_t workspace_bytes,
+                                        b2moe_stream stream) {
+    if (n <= 0 || topk <= 0 || experts <= 0 || shared_first < 0 || shared_count < 0 || shared_first + shared_count > n) return B2MOE_ERR_SHAPE;
     if ((long long)n * topk > 0x3fffffffLL) return B2MOE_ERR_SHAPE;
     if (!ids || !plan) return B2MOE_ERR_NULL;
     const int A = n * topk;
     cudaStream_t s = as_stream(stream);
     if (small_path(experts, A)) {
-        dispatch_small_k<<<1, 1024, size_t(32) * experts * sizeof(unsigned short), s>>>(ids, A, experts, shared_tokens, plan);
+        dispatch_small_k<<<1, 1024, size_t(32) * experts * sizeof(unsigned short), s>>>(ids, A, experts, shared_first, shared_count, plan);
         return launch_status();
     }
     const size_t need = b2moe_dispatch_workspace_bytes(experts, A);
@@ -194,9 +195,15 @@ extern "C" B2MOE_API int32_t b2moe_dispatch(const int32_t * ids, int32_t n, int3
     const int chunks = ceil_div(A, CHUNK);
     if (cudaMemsetAsync(hist, 0, size_t(chunks) * experts * sizeof(int), s) != cudaSuccess) return B2MOE_ERR_CUDA;
     dispatch_hist_k<<<ceil_div(chunks, 8), 256, 0, s>>>(ids, A, experts, hist);
-    dispatch_scan_k<<<1, 1024, 0, s>>>(hist, chunks, experts, A, shared_tokens, plan);
-    dispatch_scatter_k<<<ceil_div(chunks, 8), 256, 0, s>>>(ids, A, experts, shared_tokens, hist, plan);
+    dispatch_scan_k<<<1, 1024, 0, s>>>(hist, chunks, experts, A, shared_count, plan);
+    dispatch_scatter_k<<<ceil_div(chunks, 8), 256, 0, s>>>(ids, A, experts, shared_first, shared_count, hist, plan);
     return launch_status();
+}
+
+extern "C" B2MOE_API int32_t b2moe_dispatch(const int32_t * ids, int32_t n, int32_t topk, int32_t experts, int32_t shared_tokens,
+                                  int32_t * plan, void * workspace, size_t workspace_bytes, b2moe_stream stream) {
+    if (shared_tokens != 0 && shared_tokens != n) return B2MOE_ERR_SHAPE;
+    return b2moe_dispatch_range(ids, n, topk, experts, 0, shared_tokens, plan, workspace, workspace_bytes, stream);
 }
 
 extern "C" B2MOE_API int32_t b2moe_plan_to_groups(const int32_t * plan, int32_t n, int32_t topk, int32_t experts, int32_t * counts,

@@ -1,0 +1,171 @@
+"""Expert parallelism over the GPUs of one box: rank r of G owns a contiguous block of experts, tokens stay
+data-parallel, router weights and the shared expert are replicated.
+
+Per layer (the G-rank generalisation of the reference's two-rank `--split experts` path, fn_layer_forward.cpp:475-503,
+924-976, with NCCL all-gather / all-to-all in place of its grouped send / recv, tp_comm.cpp:94-101):
+
+  1. route      every rank routes its own T tokens (router + top-k);
+  2. dispatch   exchange: all ranks gather every rank's activation rows, routed ids and weights (with top-k spread
+                over G ranks nearly every token has an expert on every rank, so the dispatch all-to-all at fixed
+                capacity T is an all-gather);
+  3. experts    ids outside the rank's block become -1; the usual dispatch -> gate/up + SwiGLU -> down runs on the
+                G*T tokens for the local experts, the shared expert only for the rank's own tokens; a combine over
+                the local assignments (slot order) leaves one fp32 partial sum per token;
+  4. combine    exchange: all-to-all returns slice h of the partial sums to home rank h, which adds the G slices in
+                ascending rank order (deterministic) plus its shared expert.
+
+The orchestration below is backend-agnostic (phases + a communicator) so that the same code runs on NCCL, on gloo
+with a CPU backend in the tests, and in-process with all ranks on one GPU (the reference tests EP the same way,
+tests/ep_split.cu:87-151). The CUDA backend calls the C ABI only.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+
+def expert_range(experts: int, world: int, rank: int) -> tuple[int, int]:
+    """(first, count) of the contiguous expert block rank `rank` owns; blocks differ by at most one expert"""
+    base, extra = divmod(experts, world)
+    first = rank * base + min(rank, extra)
+    return first, base + (1 if rank < extra else 0)
+
+
+class TorchComm:
+    """all-gather / all-to-all over a torch.distributed process group (NCCL on GPUs, gloo on CPU)"""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+
+    def all_gather(self, t: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """[n, ...] per rank -> [world * n, ...] in rank order"""
+        if out is None:
+            out = torch.empty((self.world * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        try:
+            dist.all_gather_into_tensor(out, t.contiguous(), group=self.group)
+        except (RuntimeError, NotImplementedError):
+            parts = list(out.chunk(self.world))
+            dist.all_gather(parts, t.contiguous(), group=self.group)
+        return out
+
+    def all_to_all(self, t: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """[world, ...]: slice r goes to rank r; returns [world, ...] with slice r received from rank r"""
+        if out is None:
+            out = torch.empty_like(t)
+        try:
+            dist.all_to_all_single(out, t.contiguous(), group=self.group)
+        except (RuntimeError, NotImplementedError):
+            reqs = []
+            for r in range(self.world):
+                if r == self.rank:
+                    out[r].copy_(t[r])
+                else:
+                    reqs.append(dist.isend(t[r].contiguous(), r, group=self.group))
+                    reqs.append(dist.irecv(out[r], r, group=self.group))
+            for q in reqs:
+                q.wait()
+        return out
+
+
+def ep_forward(backend, comm, x_local: torch.Tensor) -> torch.Tensor:
+    """one expert-parallel layer forward for this rank's tokens; `backend` supplies the three compute phases"""
+    ids, weights = backend.route_local(x_local)
+    x_all = comm.all_gather(x_local)
+    ids_all = comm.all_gather(ids)
+    w_all = comm.all_gather(weights)
+    parts, shared = backend.partial_sums(x_all, ids_all, w_all)
+    recv = comm.all_to_all(parts.view(comm.world, x_local.shape[0], -1))
+    return backend.finish(recv, shared)
+
+
+class CudaEpLayer:
+    """The three compute phases of one rank on the device, through the C ABI. `layer` holds ONLY this rank's experts
+    (a tqllm_b200.moe.MoeLayer built from the rank's slice of the stacked banks) plus the replicated router weight
+    over ALL experts."""
+
+    def __init__(self, layer, router_w_all: torch.Tensor, experts_total: int, world: int, rank: int, out_dtype=torch.bfloat16,
+                 sel_bias_all: torch.Tensor | None = None):
+        from . import capi
+        self.capi, self.lib = capi, capi.lib
+        self.layer, self.shape = layer, layer.shape
+        self.router_w, self.sel_bias = router_w_all, sel_bias_all
+        self.E, self.world, self.rank = experts_total, world, rank
+        self.first, self.count = expert_range(experts_total, world, rank)
+        assert layer.experts == self.count
+        self.out_dtype = out_dtype
+        self.buf = {}
+
+    def _b(self, name, shape, dtype):
+        t = self.buf.get(name)
+        if t is None or tuple(t.shape) != tuple(shape) or t.dtype != dtype:
+            t = torch.zeros(shape, dtype=dtype, device=self.router_w.device)
+            self.buf[name] = t
+        return t
+
+    def _st(self):
+        return torch.cuda.current_stream().cuda_stream
+
+    def route_local(self, x):
+        from . import moe
+        lib, sh = self.lib, self.shape
+        n = x.shape[0]
+        logits = self._b("logits", (n, self.E + 1), torch.float32)
+        ids = self._b("ids", (n, sh.topk), torch.int32)
+        w = self._b("w", (n, sh.topk), torch.float32)
+        dt = moe._DT[x.dtype]
+        self.capi.check(lib.b2moe_router(self.router_w.data_ptr(), None, x.data_ptr(), dt, logits.data_ptr(), self.E + 1, sh.hidden,
+                                         self.E, n, self._st()), "b2moe_router")
+        if sh.gating == self.capi.SOFTMAX:
+            self.capi.check(lib.b2moe_topk_softmax(logits.data_ptr(), self.E + 1, ids.data_ptr(), w.data_ptr(), None, self.E, sh.topk, n,
+                                                   sh.scale, self._st()), "b2moe_topk_softmax")
+        else:
+            bias = None if self.sel_bias is None else self.sel_bias.data_ptr()
+            self.capi.check(lib.b2moe_route_sigmoid(logits.data_ptr(), self.E + 1, bias, ids.data_ptr(), w.data_ptr(), self.E, sh.topk,
+                                                    int(sh.norm), sh.scale, n, self._st()), "b2moe_route_sigmoid")
+        return ids, w
+
+    def partial_sums(self, x_all, ids_all, w_all):
+        from . import moe
+        lib, sh, L = self.lib, self.shape, self.layer
+        N, k = ids_all.shape
+        T = N // self.world
+        A = N * k
+        has_sh = L.sh is not None
+        shared_n = N if has_sh else 0                      # buffer rows for the shared expert (token-indexed)
+        local = self._b("local", (N, k), torch.int32)
+        self.capi.check(lib.b2moe_ep_local_ids(ids_all.data_ptr(), local.data_ptr(), A, self.first, self.count, self._st()), "ep_local_ids")
+        pv = self.capi.PlanView()
+        lib.b2moe_plan_view_of(self.count, A, T if has_sh else 0, C.byref(pv))
+        plan = self._b("plan", (pv.total,), torch.int32)
+        dws = self._b("dws", (max(lib.b2moe_dispatch_workspace_bytes(self.count, A), 16),), torch.uint8)
+        self.capi.check(lib.b2moe_dispatch_range(local.data_ptr(), N, k, self.count, self.rank * T, T if has_sh else 0, plan.data_ptr(),
+                                                 dws.data_ptr(), dws.numel(), self._st()), "b2moe_dispatch_range")
+        act = self._b("act", (A + shared_n, sh.ff), torch.float32)
+        y = self._b("y", (A + shared_n, sh.hidden), torch.float32)
+        dt = moe._DT[x_all.dtype]
+        eg = lib.b2moe_expert_workspace_bytes(L.gate.type, N, sh.hidden, dt)
+        ed = lib.b2moe_expert_workspace_bytes(L.down.type, A + shared_n, sh.ff, self.capi.F32)
+        ews = self._b("ews", (max(eg, ed, 16),), torch.uint8)
+        br = lambda b: C.byref(b.c)
+        shg, shu, shd = (br(L.sh[0]), br(L.sh[1]), br(L.sh[2])) if has_sh else (None, None, None)
+        self.capi.check(lib.b2moe_expert_gateup_swiglu(br(L.gate), br(L.up), shg, shu, x_all.data_ptr(), dt, plan.data_ptr(), N, k,
+                                                       shared_n, act.data_ptr(), ews.data_ptr(), ews.numel(), self._st()), "gateup")
+        self.capi.check(lib.b2moe_expert_down(br(L.down), shd, act.data_ptr(), plan.data_ptr(), N, k, shared_n, y.data_ptr(),
+                                              ews.data_ptr(), ews.numel(), self._st()), "down")
+        parts = self._b("parts", (N, sh.hidden), torch.float32)
+        self.capi.check(lib.b2moe_combine(y.data_ptr(), local.data_ptr(), w_all.data_ptr(), None, N, k, sh.hidden, 0, parts.data_ptr(),
+                                          self.capi.F32, self._st()), "b2moe_combine")
+        shared = y[A + self.rank * T:A + (self.rank + 1) * T] if has_sh else None
+        return parts, shared
+
+    def finish(self, recv, shared):
+        G, T, H = recv.shape
+        out = self._b("out", (T, H), self.out_dtype)
+        from . import moe
+        self.capi.check(self.lib.b2moe_ep_reduce(recv.data_ptr(), G, None if shared is None else shared.data_ptr(), None, T, H,
+                                                 out.data_ptr(), moe._DT[self.out_dtype], self._st()), "b2moe_ep_reduce")
+        return out
