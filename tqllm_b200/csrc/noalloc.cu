@@ -3,7 +3,7 @@
 // Some hosts of this library cannot allocate device memory themselves: a plugin loaded into an engine whose memory
 // is fully owned and pre-partitioned by that engine (the engine hands the plugin input and output pointers and
 // nothing else), or code running inside a region where cudaMalloc is forbidden, such as a stream capture or a
-// callback on a latency-critical serving thread. b2moe_expert_down needs scratch for the two-term bf16 split of the
+// callback on a latency-critical serving thread. b2moe_expert_down needs scratch for the tensor-core operand form of the
 // activation rows when the bank has a tensor-core kernel; this entry point keeps that scratch in a fixed array inside
 // the library's own device image instead, so the call allocates nothing and takes no workspace argument.
 //
@@ -19,10 +19,6 @@
 
 namespace b2 {
 int32_t check_bank(const b2moe_bank * b);
-size_t iq3s_workspace_bytes(int rows_x, int k, int dtype);
-bool iq3s_supported(int k, int dtype);
-int32_t iq3s_down(const b2moe_bank *, const b2moe_bank *, const float *, const int *, int, int, int, float *, void *, int, cudaStream_t);
-int32_t generic_down(const b2moe_bank *, const b2moe_bank *, const float *, const int *, int, int, int, float *, cudaStream_t);
 
 namespace {
 
@@ -67,15 +63,12 @@ extern "C" B2MOE_API int32_t b2moe_expert_down_static(const b2moe_bank * down, c
     }
     if (!act || !plan || !y) return B2MOE_ERR_NULL;
     if (!aligned16(act) || !aligned16(y)) return B2MOE_ERR_ALIGN;
-    const int rows_x = n * topk + shared_tokens;
-    const long long a = (long long)n * topk;
-    const int max_active = int(a < down->experts ? a : down->experts) + (shared_tokens ? 1 : 0);
-    cudaStream_t s = as_stream(stream);
-    if (down->type == T_IQ3_S && iq3s_supported(down->cols, B2MOE_F32)) {
-        if (iq3s_workspace_bytes(rows_x, down->cols, B2MOE_F32) > B2MOE_STATIC_SCRATCH_BYTES) return B2MOE_ERR_CAPACITY;
-        void * scratch = nullptr;
+    // the same kernels as b2moe_expert_down, with the library's own array as their workspace
+    const size_t need = b2moe_expert_workspace_bytes(down->type, n * topk + shared_tokens, down->cols, B2MOE_F32);
+    if (need > B2MOE_STATIC_SCRATCH_BYTES) return B2MOE_ERR_CAPACITY;
+    void * scratch = nullptr;
+    if (need) {
         if (int32_t rc = static_scratch(&scratch)) return rc;
-        return iq3s_down(down, shared_down, act, plan, n, topk, shared_tokens, y, scratch, max_active, s);
     }
-    return generic_down(down, shared_down, act, plan, n, topk, shared_tokens, y, s);   // takes no scratch at all
+    return b2moe_expert_down(down, shared_down, act, plan, n, topk, shared_tokens, y, scratch, need ? B2MOE_STATIC_SCRATCH_BYTES : 0, stream);
 }

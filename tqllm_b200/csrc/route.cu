@@ -78,6 +78,7 @@ __global__ void __launch_bounds__(RM_WARPS * 32) router_mma_k(const float * __re
         for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
     const int kper = (h / 16 + RM_WARPS - 1) / RM_WARPS * 16;           // columns per warp, a multiple of 16
     const int k_lo = warp * kper, k_hi = min(h, k_lo + kper);
+#pragma unroll 4
     for (int k0 = k_lo; k0 < k_hi; k0 += 16) {
         uint32_t hi[4], mid[4], lo[4];
         split3(*reinterpret_cast<const float2 *>(wa + k0 + 2 * t), hi[0], mid[0], lo[0]);
