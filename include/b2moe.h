@@ -124,6 +124,13 @@ B2MOE_API int32_t b2moe_dispatch(const int32_t * ids, int32_t n, int32_t topk, i
 B2MOE_API int32_t b2moe_dispatch_range(const int32_t * ids, int32_t n, int32_t topk, int32_t experts, int32_t shared_first,
                              int32_t shared_count, int32_t * plan, void * workspace, size_t workspace_bytes,
                              b2moe_stream stream);
+/* Routing and dispatch together (b2moe_topk_softmax or b2moe_route_sigmoid, then b2moe_dispatch_range): one launch for
+ * decode-sized batches, the separate launches otherwise; outputs and bits are those of the separate calls. gating is a
+ * b2moe_gating value; bias / norm apply to the sigmoid family, shared_weights to the softmax family. */
+B2MOE_API int32_t b2moe_route_dispatch(int32_t gating, const float * logits, int32_t ld, const float * bias, int32_t * ids,
+                             float * weights, float * shared_weights, int32_t experts, int32_t topk, int32_t norm, float scale,
+                             int32_t n, int32_t shared_first, int32_t shared_count, int32_t * plan, void * workspace,
+                             size_t workspace_bytes, b2moe_stream stream);
 /* moe_group-compatible view of a plan (src/experts/moe_kernels.cuh:29): counts [experts], groups [experts][n] */
 B2MOE_API int32_t b2moe_plan_to_groups(const int32_t * plan, int32_t n, int32_t topk, int32_t experts, int32_t * counts,
                              int32_t * groups, b2moe_stream stream);

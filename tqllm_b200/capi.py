@@ -65,6 +65,7 @@ SIGNATURES = {
     "b2moe_dispatch_range": (_i32, [_vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
     "b2moe_ep_local_ids": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp]),
     "b2moe_ep_reduce": (_i32, [_vp, _i32, _vp, _vp, _i32, _i32, _vp, _i32, _vp]),
+    "b2moe_route_dispatch": (_i32, [_i32, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _f32, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
     "b2moe_plan_to_groups": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp, _vp]),
     "b2moe_expert_workspace_bytes": (_sz, [_u32, _i32, _i32, _i32]),
     "b2moe_expert_gateup_swiglu": (_i32, [C.POINTER(Bank)] * 4 + [_vp, _i32, _vp, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),

@@ -173,17 +173,11 @@ extern "C" B2MOE_API int32_t b2moe_layer_forward(const b2moe_layer * L, const vo
 
     if (int32_t rc = b2moe_router(L->router_w, gated_shared ? L->shared_gate_vec : nullptr, x, x_dtype, logits, ld, L->hidden, L->experts,
                                   n, stream)) return rc;
-    if (L->gating == B2MOE_SOFTMAX) {
-        if (int32_t rc = b2moe_topk_softmax(logits, ld, ids, weights, gated_shared ? shw : nullptr, L->experts, L->topk, n, L->scale, stream))
-            return rc;
-    } else {
-        if (gated_shared) return B2MOE_ERR_SHAPE;   // the sigmoid family adds its shared expert unscaled (moe_common.cu:191)
-        if (int32_t rc = b2moe_route_sigmoid(logits, ld, L->sel_bias, ids, weights, L->experts, L->topk, L->norm, L->scale, n, stream))
-            return rc;
-    }
+    if (L->gating == B2MOE_SIGMOID && gated_shared) return B2MOE_ERR_SHAPE;   // the sigmoid family adds its shared expert unscaled (moe_common.cu:191)
     void * es = base + ws.expert_scratch;
     const size_t es_bytes = ws.total - ws.expert_scratch;
-    if (int32_t rc = b2moe_dispatch(ids, n, L->topk, L->experts, sh, plan, base + ws.scratch, ws.expert_scratch - ws.scratch, stream))
+    if (int32_t rc = b2moe_route_dispatch(L->gating, logits, ld, L->sel_bias, ids, weights, gated_shared ? shw : nullptr, L->experts, L->topk,
+                                          L->norm, L->scale, n, 0, sh, plan, base + ws.scratch, ws.expert_scratch - ws.scratch, stream))
         return rc;
     if (int32_t rc = b2moe_expert_gateup_swiglu(&L->gate, &L->up, &L->sh_gate, &L->sh_up, x, x_dtype, plan, n, L->topk, sh, act, es,
                                                 es_bytes, stream)) return rc;

@@ -6,6 +6,7 @@
 #include <math_constants.h>
 
 #include "common.cuh"
+#include "dispatch.cuh"
 
 namespace b2 {
 namespace {
@@ -117,15 +118,11 @@ __device__ __forceinline__ void argmax_merge(float & v, int & i, float ov, int o
 }
 
 // One warp per token. p[] = unbiased probabilities, key[] = selection keys (p, or p + bias), both in shared memory.
+// routes one token with one warp; p / key: e floats each of shared memory owned by the warp
 template <int GATING>
-__global__ void route_k(const float * __restrict__ logits, int ld, const float * __restrict__ bias, int * __restrict__ ids,
-                        float * __restrict__ weights, float * __restrict__ shared_weights, int e, int k, int norm, float scale, int n) {
-    extern __shared__ float smem[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-    const int token = blockIdx.x * warps + warp;
-    if (token >= n) return;
-    float * p = smem + size_t(warp) * 2 * e;
-    float * key = p + e;
+__device__ __forceinline__ void route_token(const float * __restrict__ logits, int ld, const float * __restrict__ bias, int * __restrict__ ids,
+                                            float * __restrict__ weights, float * __restrict__ shared_weights, int e, int k, int norm,
+                                            float scale, int token, int lane, float * p, float * key) {
     const float * x = logits + size_t(token) * ld;
     if (GATING == B2MOE_SOFTMAX) {
         float m = -CUDART_INF_F;
@@ -171,6 +168,35 @@ __global__ void route_k(const float * __restrict__ logits, int ld, const float *
         if (scale != 0.f && scale != 1.f) for (int r = 0; r < k; ++r) w[r] *= scale;
         if (shared_weights) shared_weights[token] = 1.f / (1.f + expf(-x[e]));
     }
+}
+
+template <int GATING>
+__global__ void route_k(const float * __restrict__ logits, int ld, const float * __restrict__ bias, int * __restrict__ ids,
+                        float * __restrict__ weights, float * __restrict__ shared_weights, int e, int k, int norm, float scale, int n) {
+    extern __shared__ float smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int token = blockIdx.x * warps + warp;
+    if (token >= n) return;
+    float * p = smem + size_t(warp) * 2 * e;
+    route_token<GATING>(logits, ld, bias, ids, weights, shared_weights, e, k, norm, scale, token, lane, p, p + e);
+}
+
+// Top-k routing and dispatch in one launch for decode-sized batches: the block's 32 warps route the tokens (round
+// robin), then the same block builds the plan from the ids it just wrote. Saves a launch and a device-wide drain.
+template <int GATING>
+__global__ void __launch_bounds__(1024) route_dispatch_k(const float * __restrict__ logits, int ld, const float * __restrict__ bias,
+                                                         int * __restrict__ ids, float * __restrict__ weights,
+                                                         float * __restrict__ shared_weights, int e, int k, int norm, float scale, int n,
+                                                         int shared_first, int shared_count, int * __restrict__ plan) {
+    extern __shared__ float smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float * p = smem + size_t(warp) * 2 * e;
+    for (int token = warp; token < n; token += 32) {
+        route_token<GATING>(logits, ld, bias, ids, weights, shared_weights, e, k, norm, scale, token, lane, p, p + e);
+        __syncwarp();
+    }
+    __syncthreads();                              // the ids are written and the routing scratch is dead
+    dispatch_small_body(ids, n * k, e, shared_first, shared_count, plan, reinterpret_cast<unsigned short *>(smem));
 }
 
 template <int GATING>
@@ -221,4 +247,33 @@ extern "C" B2MOE_API int32_t b2moe_route_sigmoid(const float * logits, int32_t l
     if (experts <= 0 || experts > 4096 || topk <= 0 || topk > experts || n <= 0 || ld < experts) return B2MOE_ERR_SHAPE;
     if (!logits || !ids || !weights) return B2MOE_ERR_NULL;
     return route_launch<B2MOE_SIGMOID>(logits, ld, bias, ids, weights, nullptr, experts, topk, norm, scale, n, as_stream(stream));
+}
+
+// b2moe_topk_softmax / b2moe_route_sigmoid followed by b2moe_dispatch_range, as one launch when the batch is
+// decode-sized (otherwise the separate launches); same outputs, same bits.
+extern "C" B2MOE_API int32_t b2moe_route_dispatch(int32_t gating, const float * logits, int32_t ld, const float * bias, int32_t * ids,
+                                                  float * weights, float * shared_weights, int32_t experts, int32_t topk, int32_t norm,
+                                                  float scale, int32_t n, int32_t shared_first, int32_t shared_count, int32_t * plan,
+                                                  void * workspace, size_t workspace_bytes, b2moe_stream stream) {
+    if (gating != B2MOE_SOFTMAX && gating != B2MOE_SIGMOID) return B2MOE_ERR_SHAPE;
+    if (experts <= 0 || experts > 4096 || topk <= 0 || topk > experts || n <= 0 || ld < experts + (shared_weights ? 1 : 0)) return B2MOE_ERR_SHAPE;
+    if (shared_first < 0 || shared_count < 0 || shared_first + shared_count > n || (long long)n * topk > 0x3fffffffLL) return B2MOE_ERR_SHAPE;
+    if (!logits || !ids || !weights || !plan) return B2MOE_ERR_NULL;
+    const size_t smem = size_t(32) * 2 * experts * sizeof(float);
+    if (dispatch_small_path(experts, n * topk) && smem <= 160 * 1024) {
+        cudaStream_t s = as_stream(stream);
+        if (gating == B2MOE_SOFTMAX) {
+            if (cudaFuncSetAttribute(route_dispatch_k<B2MOE_SOFTMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
+            route_dispatch_k<B2MOE_SOFTMAX><<<1, 1024, smem, s>>>(logits, ld, nullptr, ids, weights, shared_weights, experts, topk, 1, scale, n,
+                                                                  shared_first, shared_count, plan);
+        } else {
+            if (cudaFuncSetAttribute(route_dispatch_k<B2MOE_SIGMOID>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
+            route_dispatch_k<B2MOE_SIGMOID><<<1, 1024, smem, s>>>(logits, ld, bias, ids, weights, nullptr, experts, topk, norm, scale, n,
+                                                                  shared_first, shared_count, plan);
+        }
+        return launch_status();
+    }
+    if (int32_t rc = gating == B2MOE_SOFTMAX ? b2moe_topk_softmax(logits, ld, ids, weights, shared_weights, experts, topk, n, scale, stream)
+                                             : b2moe_route_sigmoid(logits, ld, bias, ids, weights, experts, topk, norm, scale, n, stream)) return rc;
+    return b2moe_dispatch_range(ids, n, topk, experts, shared_first, shared_count, plan, workspace, workspace_bytes, stream);
 }
