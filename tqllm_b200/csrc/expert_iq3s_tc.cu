@@ -187,8 +187,12 @@ __device__ __forceinline__ uint32_t entry_e4m3(const uint8_t * tab, const TileRe
 
 constexpr size_t TC_TABLE = 512 * 32 * 4, TC_RING = size_t(RAW_SLOTS) * RAW_SLOT_BYTES, TC_AOP = 2 * size_t(A_BUF), TC_SCALES = 4 * ROWS * 8;
 __host__ __device__ inline size_t tc_b_bytes(int k, int ncol) { return size_t(k) * ncol; }          // k / 32 sub-blocks x (2 cores x ncol x 16 bytes)
-__host__ __device__ inline size_t tc_b_area(int k, int ncol) { return tc_b_bytes(k, ncol) > size_t(32 * ROWS * 4) ? tc_b_bytes(k, ncol) : size_t(32 * ROWS * 4); }
-inline size_t tc_smem_bytes(int k, int ncol) { return TC_TABLE + TC_RING + TC_AOP + TC_SCALES + tc_b_area(k, ncol) + 256; }
+// the B operand's area doubles as the exchange buffer of the row finish: nmat * ncol floats per row
+__host__ __device__ inline size_t tc_b_area(int k, int ncol, int nmat) {
+    const size_t exch = size_t(nmat) * ncol * ROWS * 4;
+    return tc_b_bytes(k, ncol) > exch ? tc_b_bytes(k, ncol) : exch;
+}
+inline size_t tc_smem_bytes(int k, int ncol, int nmat) { return TC_TABLE + TC_RING + TC_AOP + TC_SCALES + tc_b_area(k, ncol, nmat) + 256; }
 
 template <int MODE, int NTERM>
 __global__ void __launch_bounds__(TC_THREADS, 1) iq3s_tc_k(TcArgs p) {
@@ -200,7 +204,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) iq3s_tc_k(TcArgs p) {
     uint2 * scales = reinterpret_cast<uint2 *>(aop + TC_AOP); // [4][128] (sub-block scale nibbles, d as fp32 bits), step & 3
     uint8_t * bop = reinterpret_cast<uint8_t *>(scales) + TC_SCALES;   // [k / 32][2 k cores][NCOL / 8][8][16]; also the exchange area
     const int K = p.k_tiles * 256;
-    uint64_t * bars = reinterpret_cast<uint64_t *>(bop + tc_b_area(K, NCOL));
+    uint64_t * bars = reinterpret_cast<uint64_t *>(bop + tc_b_area(K, NCOL, NMAT));
     // bars: raw_full[3], raw_empty[3], op_full[2], mma_done[2]; then tmem base and the abort flag
     uint32_t * tmem_slot = reinterpret_cast<uint32_t *>(bars + 12);
     volatile int * abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -445,7 +449,7 @@ template <int MODE, int NTERM>
 int32_t tc_launch(const TcArgs & a, long long max_items, cudaStream_t s) {
     const int sms = tc_sm_count();
     if (sms <= 0) return B2MOE_ERR_CUDA;
-    const size_t smem = tc_smem_bytes(a.k_tiles * 256, 8 * NTERM);
+    const size_t smem = tc_smem_bytes(a.k_tiles * 256, 8 * NTERM, MODE == 0 ? 2 : 1);
     if (smem > TC_SMEM_LIMIT) return B2MOE_ERR_SHAPE;
     if (cudaFuncSetAttribute(iq3s_tc_k<MODE, NTERM>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
     const int blocks = int(std::min<long long>(sms, std::max<long long>(1, max_items)));
@@ -455,8 +459,9 @@ int32_t tc_launch(const TcArgs & a, long long max_items, cudaStream_t s) {
 
 }  // namespace
 
-// true when the tcgen05 kernels take activation rows of length k in `dtype` (operands must fit shared memory)
-bool iq3s_tc_supported(int k, int dtype) { return k % 256 == 0 && tc_smem_bytes(k, 8 * tc_nterm(dtype)) <= TC_SMEM_LIMIT; }
+// true when the tcgen05 kernels take activation rows of length k in `dtype` for a product over nmat matrices (2 = gate/up,
+// 1 = down): the operands must fit shared memory
+bool iq3s_tc_supported(int k, int dtype, int nmat) { return k % 256 == 0 && tc_smem_bytes(k, 8 * tc_nterm(dtype), nmat) <= TC_SMEM_LIMIT; }
 // scratch: the E4M3 terms of `rows_x` activation rows of length k and one float per row
 size_t iq3s_tc_workspace_bytes(int rows_x, int k, int dtype) {
     return align_up(size_t(rows_x) * k * tc_nterm(dtype), 256) + align_up(size_t(rows_x) * sizeof(float), 256);

@@ -13,7 +13,7 @@ int32_t generic_gateup(const b2moe_bank *, const b2moe_bank *, const b2moe_bank 
 int32_t generic_down(const b2moe_bank *, const b2moe_bank *, const float *, const int *, int, int, int, float *, cudaStream_t);
 size_t iq3s_workspace_bytes(int rows_x, int k, int dtype);
 bool iq3s_supported(int k, int dtype);
-bool iq3s_tc_supported(int k, int dtype);
+bool iq3s_tc_supported(int k, int dtype, int nmat);
 size_t iq3s_tc_workspace_bytes(int rows_x, int k, int dtype);
 int32_t iq3s_tc_gateup(const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const void *, int, const int *, int,
                        int, int, float *, void *, int, cudaStream_t);
@@ -35,15 +35,15 @@ int max_active_of(int experts, int n, int topk, int shared_tokens) {
 }
 // Which kernel family serves an IQ3_S product: 2 = tcgen05 (tensor-memory accumulators), 1 = mma.sync, 0 = the generic path.
 // B2MOE_IQ3S_PATH=mma|generic forces a lower one (for A/B measurements); other formats always take the generic path.
-int iq3s_path(uint32_t type, int k, int dtype) {
+int iq3s_path(uint32_t type, int k, int dtype, int nmat) {
     if (type != T_IQ3_S) return 0;
     const char * v = std::getenv("B2MOE_IQ3S_PATH");
     const int cap = !v ? 2 : (v[0] == 'g' ? 0 : v[0] == 'm' ? 1 : 2);
-    if (cap >= 2 && iq3s_tc_supported(k, dtype)) return 2;
+    if (cap >= 2 && iq3s_tc_supported(k, dtype, nmat)) return 2;
     if (cap >= 1 && iq3s_supported(k, dtype)) return 1;
     return 0;
 }
-bool tuned(uint32_t type, int k, int dtype) { return iq3s_path(type, k, dtype) > 0; }
+bool tuned(uint32_t type, int k, int dtype, int nmat) { return iq3s_path(type, k, dtype, nmat) > 0; }
 }  // namespace
 }  // namespace b2
 
@@ -69,8 +69,14 @@ extern "C" B2MOE_API void b2moe_codebooks(uint32_t * grid, int8_t * kv) {
 }
 
 extern "C" B2MOE_API size_t b2moe_expert_workspace_bytes(uint32_t type, int32_t rows_x, int32_t k, int32_t x_dtype) {
-    if (rows_x <= 0 || k <= 0 || !valid_dtype(x_dtype) || !tuned(type, k, x_dtype)) return 0;
-    return iq3s_path(type, k, x_dtype) == 2 ? iq3s_tc_workspace_bytes(rows_x, k, x_dtype) : iq3s_workspace_bytes(rows_x, k, x_dtype);
+    if (rows_x <= 0 || k <= 0 || !valid_dtype(x_dtype)) return 0;
+    size_t need = 0;                       // the larger of what the gate/up (2 matrices) and the down (1) product would take
+    for (int nmat = 1; nmat <= 2; ++nmat) {
+        const int path = iq3s_path(type, k, x_dtype, nmat);
+        const size_t b = path == 2 ? iq3s_tc_workspace_bytes(rows_x, k, x_dtype) : path == 1 ? iq3s_workspace_bytes(rows_x, k, x_dtype) : 0;
+        need = b > need ? b : need;
+    }
+    return need;
 }
 
 extern "C" B2MOE_API int32_t b2moe_expert_gateup_swiglu(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_bank * shared_gate,
@@ -89,12 +95,12 @@ extern "C" B2MOE_API int32_t b2moe_expert_gateup_swiglu(const b2moe_bank * gate,
     }
     if (!x || !plan || !act) return B2MOE_ERR_NULL;
     if (!aligned16(x) || !aligned16(act)) return B2MOE_ERR_ALIGN;
-    if (tuned(gate->type, gate->cols, x_dtype)) {
+    if (tuned(gate->type, gate->cols, x_dtype, 2)) {
         const size_t need = b2moe_expert_workspace_bytes(gate->type, n, gate->cols, x_dtype);
         if (need && !workspace) return B2MOE_ERR_NULL;
         if (need && !aligned16(workspace)) return B2MOE_ERR_ALIGN;
         if (workspace_bytes < need) return B2MOE_ERR_WORKSPACE;
-        if (iq3s_path(gate->type, gate->cols, x_dtype) == 2)
+        if (iq3s_path(gate->type, gate->cols, x_dtype, 2) == 2)
             return iq3s_tc_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, workspace,
                                   max_active_of(gate->experts, n, topk, shared_tokens), as_stream(stream));
         return iq3s_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, workspace,
@@ -114,12 +120,12 @@ extern "C" B2MOE_API int32_t b2moe_expert_down(const b2moe_bank * down, const b2
     }
     if (!act || !plan || !y) return B2MOE_ERR_NULL;
     if (!aligned16(act) || !aligned16(y)) return B2MOE_ERR_ALIGN;
-    if (tuned(down->type, down->cols, B2MOE_F32)) {
+    if (tuned(down->type, down->cols, B2MOE_F32, 1)) {
         const int rows_x = n * topk + shared_tokens;
         if (!workspace) return B2MOE_ERR_NULL;
         if (!aligned16(workspace)) return B2MOE_ERR_ALIGN;
         if (workspace_bytes < b2moe_expert_workspace_bytes(down->type, rows_x, down->cols, B2MOE_F32)) return B2MOE_ERR_WORKSPACE;
-        if (iq3s_path(down->type, down->cols, B2MOE_F32) == 2)
+        if (iq3s_path(down->type, down->cols, B2MOE_F32, 1) == 2)
             return iq3s_tc_down(down, shared_down, act, plan, n, topk, shared_tokens, y, workspace,
                                 max_active_of(down->experts, n, topk, shared_tokens), as_stream(stream));
         return iq3s_down(down, shared_down, act, plan, n, topk, shared_tokens, y, workspace,
