@@ -251,16 +251,16 @@ __global__ void __launch_bounds__(CTA_WARPS * 32, 1) iq3s_grouped_k(Iq3sArgs p) 
 #pragma unroll
                     for (int ib = 0; ib < 8; ++ib) {
                         const uint32_t s0 = cur.w[9 + (ib >> 2)], s8 = cur.w[11 + (ib >> 2)];
-                        const int Q = 4 * (ib & 3);
+                        const int R = 2 * (ib & 3);
                         const uint2 e0 = *reinterpret_cast<const uint2 *>(tab + grid_offset(cur, 2 * ib));
                         const uint2 e1 = *reinterpret_cast<const uint2 *>(tab + grid_offset(cur, 16 + 2 * ib));
                         const uint2 e2 = *reinterpret_cast<const uint2 *>(tab + grid_offset(cur, 2 * ib + 1));
                         const uint2 e3 = *reinterpret_cast<const uint2 *>(tab + grid_offset(cur, 17 + 2 * ib));
                         // first MMA: grid entry 2t (weights 8t .. 8t+3); second: entry 2t + 1 (weights 8t+4 .. 8t+7)
-                        const uint32_t a0 = e0.x ^ ((s0 << (15 - Q)) & 0x80008000u), a2 = e0.y ^ ((s0 << (14 - Q)) & 0x80008000u);
-                        const uint32_t a1 = e1.x ^ ((s8 << (15 - Q)) & 0x80008000u), a3 = e1.y ^ ((s8 << (14 - Q)) & 0x80008000u);
-                        const uint32_t c0r = e2.x ^ ((s0 << (13 - Q)) & 0x80008000u), c2r = e2.y ^ ((s0 << (12 - Q)) & 0x80008000u);
-                        const uint32_t c1r = e3.x ^ ((s8 << (13 - Q)) & 0x80008000u), c3r = e3.y ^ ((s8 << (12 - Q)) & 0x80008000u);
+                        const uint32_t a0 = e0.x ^ ((s0 << (15 - R)) & 0x80008000u), a2 = e0.y ^ ((s0 << (7 - R)) & 0x80008000u);
+                        const uint32_t a1 = e1.x ^ ((s8 << (15 - R)) & 0x80008000u), a3 = e1.y ^ ((s8 << (7 - R)) & 0x80008000u);
+                        const uint32_t c0r = e2.x ^ ((s0 << (14 - R)) & 0x80008000u), c2r = e2.y ^ ((s0 << (6 - R)) & 0x80008000u);
+                        const uint32_t c1r = e3.x ^ ((s8 << (14 - R)) & 0x80008000u), c3r = e3.y ^ ((s8 << (6 - R)) & 0x80008000u);
                         const float db0 = sub_scale(cur.sc0, cur.d0, dn0, ib), db8 = sub_scale(cur.sc8, cur.d8, dn8, ib);
 #pragma unroll
                         for (int c = 0; c < NCH; ++c) {

@@ -38,7 +38,7 @@ constexpr int A_LBO = 2048 + 64;            // bytes between the two 16-byte k c
 constexpr int A_IB = 2 * A_LBO;             // bytes of one sub-block operand (128 rows x 32 k)
 constexpr int A_BUF = 8 * A_IB;             // one step's A operand (128 rows x 256 k)
 constexpr int TC_THREADS = 320;
-constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 18;
 
 __device__ __forceinline__ uint32_t saddr(const void * p) { return uint32_t(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
@@ -54,16 +54,13 @@ __device__ __forceinline__ void bulk_copy(uint32_t dst, const void * src, uint32
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(bar) : "memory");
 }
-__device__ __forceinline__ bool bar_test(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) {    // false = gave up
+// waits on one phase with the hardware's suspending try_wait (up to about a microsecond per try); false = gave up
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
-        if (bar_test(bar, parity)) return true;
-        if (i > 32) __nanosleep(32);
+        uint32_t ok;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
+        if (ok) return true;
     }
     return false;
 }
@@ -88,6 +85,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
                    "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                  : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -177,12 +182,11 @@ __device__ __forceinline__ uint32_t grid_offset(const TileRegs & r, int n) {
     else v = __funnelshift_r(r.w[q], r.w[q + 1], sh - 7);
     return v & (511u << 7);
 }
-__device__ __forceinline__ uint32_t shift_by(uint32_t v, int n) { return n >= 0 ? v << n : v >> -n; }
 // one grid entry as four E4M3 bytes with the signs applied. The A-operand word holds the entry's weights in the
-// order 0, 2, 1, 3; the bank keeps the sign of weight i of sign register Q at bit Q + (i >> 1) + 16 (i & 1).
-__device__ __forceinline__ uint32_t entry_e4m3(const uint8_t * tab, const TileRegs & r, int n, uint32_t signs, int Q) {
+// order 0, 2, 1, 3, and so do the sign bits of sign register R of the bank's sign word (bits R, R + 8, R + 16, R + 24).
+__device__ __forceinline__ uint32_t entry_e4m3(const uint8_t * tab, const TileRegs & r, int n, uint32_t signs, int R) {
     const uint32_t e = *reinterpret_cast<const uint32_t *>(tab + grid_offset(r, n));
-    return e ^ (shift_by(signs, 7 - Q) & 0x00800080u) ^ (shift_by(signs, 14 - Q) & 0x80008000u);
+    return e ^ ((signs << (7 - R)) & 0x80808080u);
 }
 
 constexpr size_t TC_TABLE = 512 * 32 * 4, TC_RING = size_t(RAW_SLOTS) * RAW_SLOT_BYTES, TC_AOP = 2 * size_t(A_BUF), TC_SCALES = 4 * ROWS * 8;
@@ -306,6 +310,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) iq3s_tc_k(TcArgs p) {
 
         // scaled accumulation of step `g_step`'s results (matrix m): acc[m][c] += d (1 + 2 s) * D[row][c]
         float acc[NMAT][NCOL];
+        int ncols = NCOL;                     // valid B columns of the current pass (tokens x terms)
         auto read_back = [&](uint32_t g_step, auto mtag) {
             constexpr int m = decltype(mtag)::value;
             const uint32_t buf = g_step & 1u;
@@ -318,13 +323,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1) iq3s_tc_k(TcArgs p) {
                 const int ib = ib0 + q;
                 // d * (1 + 2 s): 0x4B000001 | 2 s is the float 2^23 + 1 + 2 s
                 const float db = fmaf(d, __uint_as_float(((sd.x >> (4 * ib) << 1) & 0x1Eu) | 0x4B000001u), dneg);
-#pragma unroll
-                for (int h = 0; h < NCOL / 16; ++h) {
-                    uint32_t r[16];
-                    tmem_ld16(tmem + (uint32_t(32 * (w & 3)) << 16) + buf * 8 * NCOL + ib * NCOL + 16 * h, r);
+                const uint32_t taddr = tmem + (uint32_t(32 * (w & 3)) << 16) + buf * 8 * NCOL + ib * NCOL;
+                uint32_t r[16];
+                if (ncols <= 4) {                 // one or two tokens: the common pass when few tokens share an expert
+                    tmem_ld4(taddr, r);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) acc[m][16 * h + c] = fmaf(db, __uint_as_float(r[c]), acc[m][16 * h + c]);
+                    for (int c = 0; c < 4; ++c) acc[m][c] = fmaf(db, __uint_as_float(r[c]), acc[m][c]);
+                } else if (ncols <= 8) {
+                    tmem_ld8(taddr, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) acc[m][c] = fmaf(db, __uint_as_float(r[c]), acc[m][c]);
+                } else {
+#pragma unroll
+                    for (int h = 0; h < NCOL / 16; ++h) {
+                        if (16 * h < ncols) {
+                            tmem_ld16(taddr + 16 * h, r);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int c = 0; c < 16; ++c) acc[m][16 * h + c] = fmaf(db, __uint_as_float(r[c]), acc[m][16 * h + c]);
+                        }
+                    }
                 }
             }
             tc_fence_before();
@@ -335,6 +355,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) iq3s_tc_k(TcArgs p) {
             locate(it / row_blocks, e, c0);
             const int rb = it % row_blocks, rt0 = rb * 8, nt = min(8, row_tiles - rt0);
             const int cnt = counts[e], off = offsets[e], nv = min(PASS_TOKENS, cnt - c0);
+            ncols = nv * NTERM;
             // stage the B operand: 16-byte pieces of the pass's token rows into core-matrix order
             {
                 const int cores = K / 16, per_slot = cores * NTERM;
@@ -364,10 +385,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) iq3s_tc_k(TcArgs p) {
 #pragma unroll
                         for (int ib = 0; ib < 8; ++ib) {
                             const uint32_t s0 = cur.w[9 + (ib >> 2)], s8 = cur.w[11 + (ib >> 2)];
-                            const int Q = 4 * (ib & 3);
+                            const int R = 2 * (ib & 3);
                             uint2 lo, hi;
-                            lo.x = entry_e4m3(tab, cur, 2 * ib, s0, Q);       lo.y = entry_e4m3(tab, cur, 2 * ib + 1, s0, Q + 2);
-                            hi.x = entry_e4m3(tab, cur, 16 + 2 * ib, s8, Q);  hi.y = entry_e4m3(tab, cur, 17 + 2 * ib, s8, Q + 2);
+                            lo.x = entry_e4m3(tab, cur, 2 * ib, s0, R);       lo.y = entry_e4m3(tab, cur, 2 * ib + 1, s0, R + 1);
+                            hi.x = entry_e4m3(tab, cur, 16 + 2 * ib, s8, R);  hi.y = entry_e4m3(tab, cur, 17 + 2 * ib, s8, R + 1);
                             *reinterpret_cast<uint2 *>(dst + ib * A_IB) = lo;          // row g
                             *reinterpret_cast<uint2 *>(dst + ib * A_IB + 128) = hi;    // row g + 8
                         }

@@ -129,10 +129,11 @@ template <> struct Fmt<T_Q4_K> {
 template <> struct Fmt<T_IQ3_S> {
     // Per lane 13 words. Words 0..8: thirty-two 9-bit grid indices, entry n = 16 r + 2 ib + j at bits [9n, 9n + 9)
     // (r = 0: row g, 1: row g + 8; sub-block ib; j selects grid entry w = 2 t + j of the sub-block's eight).
-    // Words 9..12: sign bits, word 9 + 2 r + (ib >> 2) covers sub-blocks 4 (ib >> 2) .. +3 of row g + 8 r. A grid entry's
-    // four weights fill two tensor-core A registers of two bf16 each (weights 0,1 and 2,3); register
-    // Q = 4 (ib & 3) + 2 j + (i >> 1) of the word (j: entry 2 t + j, i: weight) keeps the sign of its low half at bit Q
-    // and of its high half at bit Q + 16, so (word << (15 - Q)) & 0x80008000 is the register's sign mask.
+    // Words 9..12: sign bits, word 9 + 2 r + (ib >> 2) covers sub-blocks 4 (ib >> 2) .. +3 of row g + 8 r. The signs of
+    // grid entry 2 t + j of sub-block ib (R = 2 (ib & 3) + j) sit at bits R (weight 0), R + 8 (weight 2), R + 16
+    // (weight 1), R + 24 (weight 3): one shift gives the sign mask of either tensor-core operand form —
+    // (word << (7 - R)) & 0x80808080 for the entry as four E4M3 bytes in the order 0, 2, 1, 3, and
+    // (word << (15 - R)) & 0x80008000 / (word << (7 - R)) & 0x80008000 for the bf16 pairs (0, 1) / (2, 3).
     // Words 4q'..4q'+3 (q' = 0..2) form plane q' at 512 q' + 16 L; word 12 at 1536 + 4 L.
     // 1664 + 4 row: the four scale bytes (nibble ib = 4-bit sub-block scale); 1728 + 2 row: d (fp16).
     static constexpr int KT = 256, TILE = 1760, RAW = 110;
@@ -163,7 +164,7 @@ template <> struct Fmt<T_IQ3_S> {
             for (int b = 0; b < 4; ++b) {
                 const uint32_t sb = blk[74 + 4 * (4 * half + b) + t];      // raw sign byte: bit 4 j + i = weight i of entry 2t + j
                 for (int j = 0; j < 2; ++j)
-                    for (int i = 0; i < 4; ++i) v |= ((sb >> (4 * j + i)) & 1u) << (4 * b + 2 * j + (i >> 1) + 16 * (i & 1));
+                    for (int i = 0; i < 4; ++i) v |= ((sb >> (4 * j + i)) & 1u) << (2 * b + j + 8 * ((i >> 1) + 2 * (i & 1)));
             }
             return v;
         }
@@ -188,7 +189,7 @@ template <> struct Fmt<T_IQ3_S> {
         uint64_t two = lane_word(tile, L, q);
         if (sh > 23) two |= uint64_t(lane_word(tile, L, q + 1)) << 32;
         const uint32_t idx = uint32_t(two >> sh) & 511u;
-        const uint32_t sg = lane_word(tile, L, 9 + 2 * r + (ib >> 2)) >> (4 * (ib & 3) + 2 * j);   // weight i at bit (i >> 1) + 16 (i & 1)
+        const uint32_t sg = lane_word(tile, L, 9 + 2 * r + (ib >> 2)) >> (2 * (ib & 3) + j);   // weight i at bit 8 ((i >> 1) + 2 (i & 1))
         const uint32_t sc = *reinterpret_cast<const uint32_t *>(tile + 1664 + 4 * row);
         const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(tile + 1728 + 2 * row));
         const float db = d * float(1 + 2 * int((sc >> (4 * ib)) & 15u));
@@ -197,7 +198,7 @@ template <> struct Fmt<T_IQ3_S> {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float mag = db * float((grid >> (8 * i)) & 255u);
-            o[i] = ((sg >> ((i >> 1) + 16 * (i & 1))) & 1u) ? -mag : mag;
+            o[i] = ((sg >> (8 * ((i >> 1) + 2 * (i & 1)))) & 1u) ? -mag : mag;
         }
     }
 };

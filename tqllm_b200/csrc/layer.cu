@@ -34,11 +34,12 @@ int max_active_of(int experts, int n, int topk, int shared_tokens) {
     return int(a < experts ? a : experts) + (shared_tokens ? 1 : 0);
 }
 // Which kernel family serves an IQ3_S product: 2 = tcgen05 (tensor-memory accumulators), 1 = mma.sync, 0 = the generic path.
-// B2MOE_IQ3S_PATH=mma|generic forces a lower one (for A/B measurements); other formats always take the generic path.
+// Default: mma.sync. B2MOE_IQ3S_PATH=tc selects the tcgen05 kernels, =generic the generic path (A/B measurements);
+// other formats always take the generic path.
 int iq3s_path(uint32_t type, int k, int dtype, int nmat) {
     if (type != T_IQ3_S) return 0;
     const char * v = std::getenv("B2MOE_IQ3S_PATH");
-    const int cap = !v ? 2 : (v[0] == 'g' ? 0 : v[0] == 'm' ? 1 : 2);
+    const int cap = !v ? 1 : (v[0] == 'g' ? 0 : v[0] == 'm' ? 1 : 2);
     if (cap >= 2 && iq3s_tc_supported(k, dtype, nmat)) return 2;
     if (cap >= 1 && iq3s_supported(k, dtype)) return 1;
     return 0;
