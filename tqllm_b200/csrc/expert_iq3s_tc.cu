@@ -12,13 +12,14 @@
 // result is read back from tensor memory. Activations are split exactly into E4M3 terms (x 2^e = h0 + h1/16 + ...),
 // the terms of a token being adjacent columns of the B operand.
 //
-// Block = 10 warps, one block per SM, persistent over items (pass of <= 8 tokens of one expert, 128-row block):
-//   warp 9      lane 0 streams the raw 1760-byte tiles of the next steps into a ring with cp.async.bulk + mbarrier;
-//   warps 0..7  decode: warp w turns row tile w of the step (16 rows x 256 columns) into the A operand (canonical
-//               K-major core-matrix layout, no swizzle), then — one step later — read the step's eight fp32 results
-//               from tensor memory and accumulate them, scaled, in registers (thread = row, half of the sub-blocks);
-//   warp 8      lane 0 issues the eight MMAs of a step when all decode warps have arrived, and commits them to the
-//               mbarrier the read-back waits on.
+// Block = 18 warps, one block per SM, persistent over items (pass of <= 8 tokens of one expert, 128-row block):
+//   warp 17      lane 0 streams the raw 1760-byte tiles of the next steps into a ring with cp.async.bulk + mbarrier;
+//   warps 0..15  decode: warps w and w + 8 turn row tile w of the step (16 rows x 256 columns, four sub-blocks each)
+//                into the A operand (canonical K-major core-matrix layout, no swizzle), then — one step later — read
+//                the step's fp32 results from tensor memory and accumulate them, scaled, in registers (thread = row,
+//                two of the eight sub-blocks);
+//   warp 16      lane 0 issues the eight MMAs of a step when all decode warps have arrived, and commits them to the
+//                mbarrier the read-back waits on.
 // Every wait is bounded; a wait that runs out sets the plan's status word and the block drains and leaves.
 #include <cuda_fp8.h>
 
@@ -37,7 +38,9 @@ constexpr int RAW_SLOT_BYTES = 8 * TILE;
 constexpr int A_LBO = 2048 + 64;            // bytes between the two 16-byte k cores of a sub-block (+64: bank spread)
 constexpr int A_IB = 2 * A_LBO;             // bytes of one sub-block operand (128 rows x 32 k)
 constexpr int A_BUF = 8 * A_IB;             // one step's A operand (128 rows x 256 k)
-constexpr int TC_THREADS = 320;
+constexpr int DEC_WARPS = 16;                // decode / read-back warps: two per row tile (four sub-blocks each)
+constexpr int MMA_WARP = DEC_WARPS, TMA_WARP = DEC_WARPS + 1;
+constexpr int TC_THREADS = (DEC_WARPS + 2) * 32;
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 18;
 
 __device__ __forceinline__ uint32_t saddr(const void * p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -191,11 +194,7 @@ __device__ __forceinline__ uint32_t entry_e4m3(const uint8_t * tab, const TileRe
 
 constexpr size_t TC_TABLE = 512 * 32 * 4, TC_RING = size_t(RAW_SLOTS) * RAW_SLOT_BYTES, TC_AOP = 2 * size_t(A_BUF), TC_SCALES = 4 * ROWS * 8;
 __host__ __device__ inline size_t tc_b_bytes(int k, int ncol) { return size_t(k) * ncol; }          // k / 32 sub-blocks x (2 cores x ncol x 16 bytes)
-// the B operand's area doubles as the exchange buffer of the row finish: nmat * ncol floats per row
-__host__ __device__ inline size_t tc_b_area(int k, int ncol, int nmat) {
-    const size_t exch = size_t(nmat) * ncol * ROWS * 4;
-    return tc_b_bytes(k, ncol) > exch ? tc_b_bytes(k, ncol) : exch;
-}
+__host__ __device__ inline size_t tc_b_area(int k, int ncol, int) { return tc_b_bytes(k, ncol) < 1024 ? 1024 : tc_b_bytes(k, ncol); }
 inline size_t tc_smem_bytes(int k, int ncol, int nmat) { return TC_TABLE + TC_RING + TC_AOP + TC_SCALES + tc_b_area(k, ncol, nmat) + 256; }
 
 template <int MODE, int NTERM>
@@ -228,12 +227,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) iq3s_tc_k(TcArgs p) {
         reinterpret_cast<uint32_t *>(table)[i] = b[0] | (b[2] << 8) | (b[1] << 16) | (b[3] << 24);   // weights 0, 2, 1, 3
     }
     if (threadIdx.x == 0) {
-        for (int s = 0; s < 3; ++s) { bar_init(raw_full + 8 * s, 1); bar_init(raw_empty + 8 * s, 8); }
-        for (int s = 0; s < 2; ++s) { bar_init(op_full + 8 * s, 8); bar_init(mma_done + 8 * s, 1); }
+        for (int s = 0; s < 3; ++s) { bar_init(raw_full + 8 * s, 1); bar_init(raw_empty + 8 * s, DEC_WARPS); }
+        for (int s = 0; s < 2; ++s) { bar_init(op_full + 8 * s, DEC_WARPS); bar_init(mma_done + 8 * s, 1); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 8) {
+    if (warp == MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -251,7 +250,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) iq3s_tc_k(TcArgs p) {
     };
     auto give_up = [&]() { *abort_flag = 1; atomicExch(p.plan + PLAN_STATUS, 2); };
 
-    if (warp == 9) {
+    if (warp == TMA_WARP) {
         // ---- producer: raw tiles of every step, RAW_SLOTS steps ahead ----
         uint32_t gs = 0;
         for (int it = blockIdx.x; it < n_items && !*abort_flag; it += gridDim.x) {
@@ -276,7 +275,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) iq3s_tc_k(TcArgs p) {
                 if (*abort_flag) break;
             }
         }
-    } else if (warp == 8) {
+    } else if (warp == MMA_WARP) {
         // ---- MMA issuer ----
         const uint32_t idesc = (1u << 4) | (uint32_t(NCOL >> 3) << 17) | (8u << 24);   // fp32 D, E4M3 x E4M3, K-major, N, M = 128
         uint32_t gs = 0;
@@ -300,11 +299,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) iq3s_tc_k(TcArgs p) {
             }
         }
     } else {
-        // ---- decode + read-back warps: warp w owns row tile w of the 128-row block ----
-        const int g = lane >> 2, t = lane & 3, w = warp;
+        // ---- decode + read-back warps: warps w and w + 8 share row tile w & 7 (sub-blocks 0..3 / 4..7) ----
+        const int g = lane >> 2, t = lane & 3, w = warp, tw = w & 7, half = w >> 3;
         const uint8_t * tab = table + lane * 4;
-        const int my_row = 32 * (w & 3) + lane, ib0 = (w >> 2) * 4;          // read-back: this thread's row and sub-blocks
-        const int tid = threadIdx.x;                                          // 0..255
+        const int my_row = 32 * (w & 3) + lane, ib0 = (w >> 2) * 2;          // read-back: this thread's row and its two sub-blocks
+        const int tid = threadIdx.x;                                          // 0..511
         uint32_t gs = 0;
         bool alive = true;
 
@@ -319,7 +318,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) iq3s_tc_k(TcArgs p) {
             const uint2 sd = scales[(g_step & 3u) * ROWS + my_row];
             const float d = __uint_as_float(sd.y), dneg = d * -8388608.f;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
+            for (int q = 0; q < 2; ++q) {
                 const int ib = ib0 + q;
                 // d * (1 + 2 s): 0x4B000001 | 2 s is the float 2^23 + 1 + 2 s
                 const float db = fmaf(d, __uint_as_float(((sd.x >> (4 * ib) << 1) & 0x1Eu) | 0x4B000001u), dneg);
@@ -359,7 +358,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) iq3s_tc_k(TcArgs p) {
             // stage the B operand: 16-byte pieces of the pass's token rows into core-matrix order
             {
                 const int cores = K / 16, per_slot = cores * NTERM;
-                for (int pi = tid; pi < nv * per_slot; pi += 256) {
+                for (int pi = tid; pi < nv * per_slot; pi += DEC_WARPS * 32) {
                     const int slot = pi / per_slot, rem = pi - slot * per_slot, c = rem / NTERM, term = rem - c * NTERM;
                     const int a = perm[off + c0 + slot];
                     const size_t row = MODE == 0 ? size_t(a < p.A ? a / p.topk : a - p.A) : size_t(a);
@@ -378,23 +377,32 @@ __global__ void __launch_bounds__(TC_THREADS, 1) iq3s_tc_k(TcArgs p) {
                     if (!alive) return;
                     const uint32_t buf = gs & 1u, slot = gs % RAW_SLOTS;
                     if (!__all_sync(0xffffffffu, bar_wait(raw_full + 8 * slot, (gs / RAW_SLOTS) & 1u))) { alive = false; return; }
-                    if (w < nt) {
+                    if (tw < nt) {
                         TileRegs cur;
-                        read_tile(cur, ring + slot * RAW_SLOT_BYTES + w * TILE, lane);
-                        uint8_t * dst = aop + buf * A_BUF + (t >> 1) * A_LBO + (2 * w) * 128 + g * 16 + (t & 1) * 8;
+                        read_tile(cur, ring + slot * RAW_SLOT_BYTES + tw * TILE, lane);
+                        uint8_t * dst = aop + buf * A_BUF + (t >> 1) * A_LBO + (2 * tw) * 128 + g * 16 + (t & 1) * 8;
+                        auto decode_half = [&](auto htag) {
+                            constexpr int H = decltype(htag)::value;
+                            const uint32_t s0 = cur.w[9 + H], s8 = cur.w[11 + H];
 #pragma unroll
-                        for (int ib = 0; ib < 8; ++ib) {
-                            const uint32_t s0 = cur.w[9 + (ib >> 2)], s8 = cur.w[11 + (ib >> 2)];
-                            const int R = 2 * (ib & 3);
-                            uint2 lo, hi;
-                            lo.x = entry_e4m3(tab, cur, 2 * ib, s0, R);       lo.y = entry_e4m3(tab, cur, 2 * ib + 1, s0, R + 1);
-                            hi.x = entry_e4m3(tab, cur, 16 + 2 * ib, s8, R);  hi.y = entry_e4m3(tab, cur, 17 + 2 * ib, s8, R + 1);
-                            *reinterpret_cast<uint2 *>(dst + ib * A_IB) = lo;          // row g
-                            *reinterpret_cast<uint2 *>(dst + ib * A_IB + 128) = hi;    // row g + 8
-                        }
-                        if (t == 0) {
-                            scales[(gs & 3u) * ROWS + 16 * w + g] = make_uint2(cur.sc0, cur.d0);
-                            scales[(gs & 3u) * ROWS + 16 * w + g + 8] = make_uint2(cur.sc8, cur.d8);
+                            for (int q = 0; q < 4; ++q) {
+                                constexpr int dummy = 0; (void)dummy;
+                                const int ib = 4 * H + q, R = 2 * q;
+                                uint2 lo, hi;
+                                lo.x = entry_e4m3(tab, cur, 2 * ib, s0, R);       lo.y = entry_e4m3(tab, cur, 2 * ib + 1, s0, R + 1);
+                                hi.x = entry_e4m3(tab, cur, 16 + 2 * ib, s8, R);  hi.y = entry_e4m3(tab, cur, 17 + 2 * ib, s8, R + 1);
+                                *reinterpret_cast<uint2 *>(dst + ib * A_IB) = lo;          // row g
+                                *reinterpret_cast<uint2 *>(dst + ib * A_IB + 128) = hi;    // row g + 8
+                            }
+                        };
+                        if (half == 0) {
+                            decode_half(std::integral_constant<int, 0>{});
+                            if (t == 0) {
+                                scales[(gs & 3u) * ROWS + 16 * tw + g] = make_uint2(cur.sc0, cur.d0);
+                                scales[(gs & 3u) * ROWS + 16 * tw + g + 8] = make_uint2(cur.sc8, cur.d8);
+                            }
+                        } else {
+                            decode_half(std::integral_constant<int, 1>{});
                         }
                     }
                     fence_async_smem();       // the operand bytes (and the B pieces) must be visible to the tensor core
@@ -412,17 +420,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) iq3s_tc_k(TcArgs p) {
             if (alive) read_back(gs - 1, std::integral_constant<int, NMAT - 1>{});
             if (!alive && lane == 0) give_up();
 
-            // the two warp groups hold different sub-blocks of the same rows: add them through shared memory
-            // (the B operand's area: every MMA of the item has completed), then finish the rows in warps 0..3
-            float * exch = reinterpret_cast<float *>(bop);
-            if (w >= 4) {
+            // four warps hold different sub-blocks of the same rows: three park their sums in shared memory (the A operand
+            // area: every MMA of the item has completed), the fourth adds them and finishes the rows
+            float * exch = reinterpret_cast<float *>(aop);
+            const int grp = w >> 2;
+            if (grp > 0) {
 #pragma unroll
                 for (int m = 0; m < NMAT; ++m)
 #pragma unroll
-                    for (int c = 0; c < NCOL; ++c) exch[(m * NCOL + c) * ROWS + my_row] = acc[m][c];
+                    for (int c = 0; c < NCOL; ++c) exch[(((grp - 1) * NMAT + m) * NCOL + c) * ROWS + my_row] = acc[m][c];
             }
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            if (w < 4) {
+            asm volatile("bar.sync 1, 512;" ::: "memory");
+            if (grp == 0) {
                 const int row = rb * ROWS + my_row;
 #pragma unroll
                 for (int slot = 0; slot < PASS_TOKENS; ++slot) {
@@ -436,7 +445,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) iq3s_tc_k(TcArgs p) {
 #pragma unroll
                             for (int term = 0; term < NTERM; ++term) {
                                 const int c = slot * NTERM + term;
-                                sum = fmaf(acc[m][c] + exch[(m * NCOL + c) * ROWS + my_row], wgt, sum);
+                                float part = acc[m][c];
+#pragma unroll
+                                for (int q = 0; q < 3; ++q) part += exch[((q * NMAT + m) * NCOL + c) * ROWS + my_row];
+                                sum = fmaf(part, wgt, sum);
                                 wgt *= 0.0625f;
                             }
                             v[m] = sum * is;
@@ -445,12 +457,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) iq3s_tc_k(TcArgs p) {
                     }
                 }
             }
-            asm volatile("bar.sync 1, 256;" ::: "memory");
+            asm volatile("bar.sync 1, 512;" ::: "memory");
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 8) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    if (warp == MMA_WARP) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
 }
 
 constexpr size_t TC_SMEM_LIMIT = 232448 - 1024;
@@ -482,7 +494,10 @@ int32_t tc_launch(const TcArgs & a, long long max_items, cudaStream_t s) {
 
 // true when the tcgen05 kernels take activation rows of length k in `dtype` for a product over nmat matrices (2 = gate/up,
 // 1 = down): the operands must fit shared memory
-bool iq3s_tc_supported(int k, int dtype, int nmat) { return k % 256 == 0 && tc_smem_bytes(k, 8 * tc_nterm(dtype), nmat) <= TC_SMEM_LIMIT; }
+bool iq3s_tc_supported(int k, int dtype, int nmat) {
+    if (nmat == 2 && tc_nterm(dtype) == 4) return false;      // 64 accumulators per thread do not fit 18 warps' registers
+    return k % 256 == 0 && tc_smem_bytes(k, 8 * tc_nterm(dtype), nmat) <= TC_SMEM_LIMIT;
+}
 // scratch: the E4M3 terms of `rows_x` activation rows of length k and one float per row
 size_t iq3s_tc_workspace_bytes(int rows_x, int k, int dtype) {
     return align_up(size_t(rows_x) * k * tc_nterm(dtype), 256) + align_up(size_t(rows_x) * sizeof(float), 256);

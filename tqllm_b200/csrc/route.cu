@@ -117,12 +117,81 @@ __device__ __forceinline__ void argmax_merge(float & v, int & i, float ov, int o
     if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
 }
 
+// ---- register-resident routing of one token by one warp (experts <= 32 R) ----
+// Lane l keeps experts l, l + 32, ... in registers; a round is a local scan, one warp-wide max of an order-preserving
+// integer image of the key and one warp-wide min over the indices that hold it (ties -> lowest index), so the ten
+// rounds of a top-10 cost about a microsecond instead of a chain of shared-memory scans and shuffle ladders.
+__device__ __forceinline__ uint32_t ordered_bits(float v) {          // monotonic float -> uint (taken entries use 0)
+    const uint32_t u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+template <int GATING, int R>
+__device__ __forceinline__ void route_token_regs(const float * __restrict__ logits, int ld, const float * __restrict__ bias,
+                                                 int * __restrict__ ids, float * __restrict__ weights, float * __restrict__ shared_weights,
+                                                 int e, int k, int norm, float scale, int token, int lane) {
+    const float * x = logits + size_t(token) * ld;
+    float p[R];
+    uint32_t key[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) p[r] = lane + 32 * r < e ? x[lane + 32 * r] : -CUDART_INF_F;
+    if (GATING == B2MOE_SOFTMAX) {
+        float m = -CUDART_INF_F;
+#pragma unroll
+        for (int r = 0; r < R; ++r) m = fmaxf(m, p[r]);
+        for (int d = 16; d; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+        float sum = 0.f;
+#pragma unroll
+        for (int r = 0; r < R; ++r) if (lane + 32 * r < e) { p[r] = expf(p[r] - m); sum += p[r]; }
+        for (int d = 16; d; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+#pragma unroll
+        for (int r = 0; r < R; ++r) { p[r] = p[r] / sum; key[r] = lane + 32 * r < e ? ordered_bits(p[r]) : 0u; }
+    } else {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const bool in = lane + 32 * r < e;
+            p[r] = 1.f / (1.f + expf(-p[r]));
+            key[r] = in ? ordered_bits(bias ? p[r] + bias[lane + 32 * r] : p[r]) : 0u;
+        }
+    }
+    float sel_sum = 0.f;
+    for (int q = 0; q < k; ++q) {
+        uint32_t best = 0;
+        int br = 0;
+#pragma unroll
+        for (int r = 0; r < R; ++r) if (key[r] > best) { best = key[r]; br = r; }     // ascending r: the lowest index keeps a tie
+        const uint32_t top = __reduce_max_sync(0xffffffffu, best);
+        const int idx = int(__reduce_min_sync(0xffffffffu, (best == top && best != 0u) ? uint32_t(lane + 32 * br) : 0x7fffffffu));
+        const int owner = idx & 31, orow = idx >> 5;
+        float pv = 0.f;
+#pragma unroll
+        for (int r = 0; r < R; ++r) if (r == orow) { pv = p[r]; if (lane == owner) key[r] = 0u; }
+        pv = __shfl_sync(0xffffffffu, pv, owner);
+        if (lane == 0) {
+            ids[size_t(token) * k + q] = idx == 0x7fffffff ? 0 : idx;
+            weights[size_t(token) * k + q] = pv;
+        }
+        sel_sum += pv;
+    }
+    if (lane == 0) {
+        float * w = weights + size_t(token) * k;
+        if (norm) {
+            const float total = fmaxf(sel_sum, 6.103515625e-5f);
+            for (int r = 0; r < k; ++r) w[r] = w[r] / total;
+        }
+        if (scale != 0.f && scale != 1.f) for (int r = 0; r < k; ++r) w[r] *= scale;
+        if (shared_weights) shared_weights[token] = 1.f / (1.f + expf(-x[e]));
+    }
+}
+
 // One warp per token. p[] = unbiased probabilities, key[] = selection keys (p, or p + bias), both in shared memory.
 // routes one token with one warp; p / key: e floats each of shared memory owned by the warp
 template <int GATING>
 __device__ __forceinline__ void route_token(const float * __restrict__ logits, int ld, const float * __restrict__ bias, int * __restrict__ ids,
                                             float * __restrict__ weights, float * __restrict__ shared_weights, int e, int k, int norm,
                                             float scale, int token, int lane, float * p, float * key) {
+    if (e <= 128) return route_token_regs<GATING, 4>(logits, ld, bias, ids, weights, shared_weights, e, k, norm, scale, token, lane);
+    if (e <= 256) return route_token_regs<GATING, 8>(logits, ld, bias, ids, weights, shared_weights, e, k, norm, scale, token, lane);
+    if (e <= 512) return route_token_regs<GATING, 16>(logits, ld, bias, ids, weights, shared_weights, e, k, norm, scale, token, lane);
     const float * x = logits + size_t(token) * ld;
     if (GATING == B2MOE_SOFTMAX) {
         float m = -CUDART_INF_F;
