@@ -28,7 +28,7 @@ static void run(const uint8_t * raw, int rows, int cols, uint8_t * bank, float *
                 aux16[r] = 0.f;
                 if (T == T_NVFP4G && row < rows) std::memcpy(&aux16[r], raw + size_t(row) * k_tiles * 76, 4);
             }
-            for (int u = 0; u < f.units; ++u) Fmt<T>::decode_unit(tile, aux16, u, w.data(), f.kt);
+            for (int u = 0; u < f.units; ++u) decode_unit<T>(tile, aux16, u, w.data(), f.kt);
             for (int r = 0; r < 16 && 16 * rt + r < rows; ++r)
                 std::memcpy(out + size_t(16 * rt + r) * cols + size_t(kt) * f.kt, &w[size_t(r) * f.kt], sizeof(float) * f.kt);
         }

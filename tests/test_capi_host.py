@@ -91,8 +91,10 @@ def test_arguments_are_rejected_before_any_launch():
     iq = capi.Bank(16, None, 21, 4, 32, 256)
     assert lib.b2moe_expert_workspace_bytes(21, 64, 2048, capi.BF16) >= 64 * 2048 * 2    # two E4M3 terms per bf16 value
     assert lib.b2moe_expert_workspace_bytes(21, 64, 2048, capi.F32) >= 64 * 2 * 2048 * 2
-    assert lib.b2moe_expert_workspace_bytes(21, 64, 16384, capi.F32) == 0          # too long to stage: generic path
-    assert lib.b2moe_expert_workspace_bytes(12, 64, 2048, capi.BF16) == 0
+    # every format: at least the scaled fp16 copy of the rows + one float per row that the tensor-core GEMM takes
+    for t in (12, 20, 21, 23, 323):
+        assert lib.b2moe_expert_workspace_bytes(t, 64, 16384, capi.F32) >= 64 * 16384 * 2 + 64 * 4
+    assert lib.b2moe_expert_workspace_bytes(12, 0, 2048, capi.BF16) == 0
     assert lib.b2moe_expert_down(C.byref(iq), None, 16, 16, 2, 2, 0, 16, None, 0, None) == capi.ERR_NULL        # needs scratch
     assert lib.b2moe_expert_down(C.byref(iq), None, 16, 16, 2, 2, 0, 16, 32, 64, None) == capi.ERR_WORKSPACE
     assert lib.b2moe_combine(16, None, 16, None, 2, 2, 30, 0, 16, capi.F32, None) == capi.ERR_SHAPE

@@ -1,0 +1,87 @@
+"""GPU: the tcgen05 grouped GEMM (every bank format, experts holding many tokens) against the exact fp32 generic path
+of the same library and, end to end, against the oracle.
+
+The GEMM rounds the decoded weights and the activations to bf16 and sums in fp32; the generic path is exact fp32
+(src/experts/moe.cpp:115-155 order). Tolerance: max |err| / RMS(reference) <= 1e-2, the bound of the layer tests;
+observed values are about 3e-3."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from make_golden import layer_inputs
+from test_gpu_layer import run_case
+from tqllm_b200 import synth
+from util import rel_err
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+class forced_path:
+    """B2MOE_EXPERT_PATH for the calls inside the block (the library reads it at every call)"""
+
+    def __init__(self, name):
+        self.name = name
+
+    def __enter__(self):
+        self.old = os.environ.get("B2MOE_EXPERT_PATH")
+        os.environ["B2MOE_EXPERT_PATH"] = self.name
+
+    def __exit__(self, *a):
+        if self.old is None:
+            del os.environ["B2MOE_EXPERT_PATH"]
+        else:
+            os.environ["B2MOE_EXPERT_PATH"] = self.old
+
+
+def products(shape, experts, tokens, seed, path):
+    from tqllm_b200 import moe
+    layer, x = layer_inputs(shape, experts, tokens, seed)
+    dev = moe.MoeLayer.from_synth(layer, experts=experts)
+    xd = x.cuda()
+    logits = moe.router(dev.router_w, xd)
+    ids, w, _ = moe.topk_softmax(logits, experts, shape.topk, shape.scale)
+    plan = moe.dispatch(ids, experts, tokens if shape.shared else 0)
+    sh = dev.sh if shape.shared else (None, None, None)
+    with forced_path(path):
+        act = moe.expert_gateup_swiglu(dev.gate, dev.up, xd, plan, sh[0], sh[1])
+        y = moe.expert_down(dev.down, act, plan, sh[2])
+    torch.cuda.synchronize()
+    assert int(plan.buf[3]) == 0, "a bounded wait ran out"
+    return act.cpu().numpy(), y.cpu().numpy()
+
+
+# (types, hidden, ff, experts, topk, tokens, shared, act dtype): token tiles of 128 + a ragged rest, partial row blocks
+# (ff = 320: 20 row tiles = 2.5 blocks), a 64-column tail chunk (IQ4_NL down with K = 320), a shared expert
+GEMM_CASES = (
+    ((12, 12, 12), 512, 256, 4, 2, 300, True, "bf16"),
+    ((21, 21, 21), 512, 256, 4, 2, 150, True, "f32"),
+    ((23, 23, 20), 512, 320, 3, 2, 200, False, "bf16"),
+    ((20, 20, 20), 256, 192, 2, 1, 270, True, "bf16"),
+    ((323, 323, 323), 512, 256, 4, 3, 130, True, "bf16"),
+    ((12, 12, 12), 256, 256, 8, 2, 5, True, "f32"),
+)
+
+
+@pytest.mark.parametrize("case", GEMM_CASES, ids=[f"{c[0][0]}-{c[0][2]}-t{c[5]}" for c in GEMM_CASES])
+def test_gemm_matches_exact_path(case):
+    types, hidden, ff, experts, topk, tokens, shared, dt = case
+    shape = synth.LayerShape("gemm", hidden, experts, topk, ff, shared=shared, types=types, act_dtype=dt)
+    act_g, y_g = products(shape, experts, tokens, 7, "gemm")
+    act_x, y_x = products(shape, experts, tokens, 7, "generic")
+    assert rel_err(act_g, act_x) <= TOL
+    assert rel_err(y_g, y_x) <= TOL
+    # the same call again: the same bits
+    act_2, y_2 = products(shape, experts, tokens, 7, "gemm")
+    assert np.array_equal(act_g.view(np.uint32), act_2.view(np.uint32)) and np.array_equal(y_g.view(np.uint32), y_2.view(np.uint32))
+
+
+@pytest.mark.parametrize("types", ((12, 12, 12), (21, 21, 21), (23, 23, 20), (323, 323, 323)), ids=("q4k", "iq3s", "iq4xs-nl", "nvfp4"))
+def test_gemm_layer_against_oracle(orc, types):
+    """whole layer with the GEMM forced, 40 tokens per expert on average"""
+    shape = synth.LayerShape("gemm-layer", 512, 8, 2, 256, shared=True, types=types)
+    with forced_path("gemm"):
+        err = run_case(orc, shape, 8, 160, 31)
+    assert err <= TOL

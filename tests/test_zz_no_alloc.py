@@ -47,7 +47,7 @@ def test_static_scratch_down_matches_workspace_down_twice():
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32))   # in fact the same kernel: the same bits
 
 
-def test_static_scratch_rejects_oversize_and_other_formats_need_none():
+def test_static_scratch_rejects_oversize_and_serves_other_formats():
     from tqllm_b200 import capi
     from tqllm_b200.capi import lib
     assert lib.b2moe_static_scratch_bytes() == 16 << 20
@@ -56,7 +56,7 @@ def test_static_scratch_rejects_oversize_and_other_formats_need_none():
     rc = lib.b2moe_expert_down_static(C.byref(bank), None, 256, 256, 7000, 10, 0, 256, None)
     assert rc == capi.ERR_CAPACITY
     assert lib.b2moe_expert_down_static(C.byref(bank), None, None, 256, 4, 2, 0, 256, None) == capi.ERR_NULL
-    # a Q4_K bank takes the scratch-free path and matches the ordinary entry point
+    # a Q4_K bank (tensor-core GEMM: its fp16 rows go to the same array) matches the ordinary entry point
     shape = synth.LayerShape("noalloc-q4k", 256, 8, 2, 256, shared=True, types=(12, 12, 12))
     got, want = down_both_ways(shape, 8, 6, 4)
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))

@@ -1,0 +1,411 @@
+// Grouped expert GEMM on the 5th-generation tensor cores for every bank format: the path for batches where an expert
+// sees many tokens (prefill) and the tensor-core path of the formats that have no hand-tuned decode kernel.
+// Replaces the grouped prefill kernels u4h_gemm_k / k_expert_gemm / k_expert_gemm_gateup
+// (src/formats/weight/quant_u4h.inc:609-774, src/formats/weight/quant.cu:286-405) with their fused SwiGLU epilogue
+// (quant_u4h.inc:756-759): per expert Y_e = W_e . X_e^T over the expert's gathered token rows.
+//
+// One persistent block per SM; an item is (expert, tile of <= 128 of its tokens, block of 128 weight rows):
+//   D[128 rows][N tokens] (fp32, tensor memory) = sum over K of A[128][K] (fp16) . B[N][K] (fp16)
+//   A: the weight rows, decoded from the bank's block format to fp16 in shared memory by the CUDA cores, 64 columns per
+//      step (canonical K-major core-matrix layout, no swizzle); the raw blocks arrive through a per-warp ring of bulk
+//      copies (cp.async.bulk + mbarrier), 256 columns per copy;
+//   B: the tokens' activation rows (fp16, each row scaled by a power of two), gathered through the dispatch permutation with 16-byte cp.async;
+//   the gate and the up matrix share B and have an accumulator each; two accumulator sets alternate between items, so
+//   the epilogue of one item (SwiGLU, stores) overlaps the products of the next.
+// Warps: 0 issues tcgen05.mma (one lane); 1..4 epilogue (tcgen05.ld, one TMEM lane quarter each); 5..8 load B;
+// 9..16 decode A (warp w owns row tile w of the block). Every wait is bounded; a wait that runs out sets the plan's
+// status word, and the block drains and leaves.
+//
+// Numerics: weights are rounded to fp16 after the exact fp32 decode (relative error <= 2^-11 per weight; bf16 operands
+// gave 3e-2 of the output RMS as the largest error, fp16 stays below the layer tolerance). An activation row is
+// multiplied by 2^e so that its largest magnitude lies in [2^14, 2^15) and rounded to fp16: exact for bf16 inputs down
+// to 2^-29 of the row maximum; the epilogue multiplies the sums (fp32) by 2^-e.
+#include "common.cuh"
+#include "formats.cuh"
+#include "tc_ptx.cuh"
+
+namespace b2 {
+namespace {
+using namespace tc;
+
+constexpr int G_ROWS = 128;                 // weight rows per item = M
+constexpr int G_NT = 128;                   // tokens per item (N <= 128, a multiple of 16)
+constexpr int G_KS = 64;                    // columns per pipeline step (four MMAs of K = 16 per matrix)
+constexpr int A_STAGES = 2, B_STAGES = 4, RAW_SLOTS = 2, B_LAG = 2;
+constexpr int A_LBO = 2048 + 64;            // bytes between k cores of A (+64 spreads the decode stores over the banks)
+constexpr int A_MAT = 8 * A_LBO;            // one matrix of one A stage: 128 rows x 64 columns
+constexpr int B_LBO = G_NT * 16;            // bytes between k cores of B
+constexpr int B_STAGE = 8 * B_LBO;          // 128 tokens x 64 columns
+constexpr int MMA_WARP = 0, EPI_WARP0 = 1, LOAD_WARP0 = 5, DEC_WARP0 = 9;
+constexpr int G_THREADS = 17 * 32;
+constexpr int N_BARS = 8 * RAW_SLOTS + 2 * A_STAGES + 2 * B_STAGES + 4;
+
+struct GemmArgs {
+    const uint8_t * w0, * w1;               // stacked banks (gate, up) or (down, -)
+    const uint8_t * s0, * s1;               // the shared expert's banks (may be null)
+    const float * aux0, * aux1, * saux0, * saux1;
+    size_t bank_bytes;
+    const __half * xb;                      // activation rows, fp16, row stride k, row r scaled by 1 / inv_scale[r]
+    const float * inv_scale;
+    int * plan;
+    float * out;
+    int rows, k, experts, topk, A;
+};
+
+template <uint32_t T> constexpr int chunk_tiles() { return 256 / Fmt<T>::KT; }
+template <uint32_t T> constexpr int chunk_bytes() { return chunk_tiles<T>() * Fmt<T>::TILE; }
+
+template <uint32_t T, int NMAT>
+constexpr size_t gemm_smem(int experts) {
+    return size_t(A_STAGES) * NMAT * A_MAT + size_t(B_STAGES) * B_STAGE + size_t(8) * RAW_SLOTS * NMAT * chunk_bytes<T>() +
+           (T == T_IQ3_S ? 2048 : 0) + size_t(experts + 3) * 4 + 16 + size_t(N_BARS) * 8 + 16;
+}
+
+// any activation dtype -> fp16 rows scaled by a power of two per row (one warp per row) + the inverse scales
+__global__ void rows_to_f16_k(const void * __restrict__ x, int dtype, int rows, int k, __half * __restrict__ out, float * __restrict__ inv_scale) {
+    const int lane = threadIdx.x & 31, row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    float mx = 0.f;
+    for (int j = lane; j < k; j += 32) mx = fmaxf(mx, fabsf(load_act(x, dtype, size_t(row) * k + j)));
+    for (int d = 16; d; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+    int ex = int((__float_as_uint(mx) >> 23) & 255u) - 127;              // floor(log2(mx)) for a normal mx
+    ex = (mx > 0.f && mx < 3e38f) ? max(-100, min(100, ex)) : 14;
+    const float scale = __uint_as_float(uint32_t(127 + 14 - ex) << 23);  // 2^(14 - ex)
+    if (lane == 0) inv_scale[row] = __uint_as_float(uint32_t(127 - 14 + ex) << 23);
+    for (int j = lane; j < k; j += 32) out[size_t(row) * k + j] = __float2half_rn(load_act(x, dtype, size_t(row) * k + j) * scale);
+}
+
+__device__ __forceinline__ uint32_t pack_f16(float a, float b) {
+    const __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+
+// MODE 0: act[a][r] = silu(gate_r . x_tok(a)) * (up_r . x_tok(a));  MODE 1: y[a][r] = down_r . act[a]
+template <uint32_t T, int MODE>
+__global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
+    constexpr int NMAT = MODE == 0 ? 2 : 1;
+    constexpr int KT = Fmt<T>::KT, TILE = Fmt<T>::TILE, CT = chunk_tiles<T>(), CB = chunk_bytes<T>();
+    constexpr uint32_t TMEM_COLS = 512;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t * a_st = smem;                                            // [A_STAGES][NMAT][A_MAT]
+    uint8_t * b_st = a_st + A_STAGES * NMAT * A_MAT;                  // [B_STAGES][B_STAGE]
+    uint8_t * raw = b_st + B_STAGES * B_STAGE;                        // [8 warps][RAW_SLOTS][NMAT][CB]
+    uint32_t * grid_tab = reinterpret_cast<uint32_t *>(raw + 8 * RAW_SLOTS * NMAT * CB);
+    int * cum = reinterpret_cast<int *>(reinterpret_cast<uint8_t *>(grid_tab) + (T == T_IQ3_S ? 2048 : 0));   // [na + 1]
+    uint64_t * bars = reinterpret_cast<uint64_t *>((reinterpret_cast<uintptr_t>(cum + p.experts + 3) + 15) & ~uintptr_t(15));
+    uint32_t * tmem_slot = reinterpret_cast<uint32_t *>(bars + N_BARS);
+    volatile int * abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const uint32_t raw_full = saddr(bars), a_full = raw_full + 8 * 8 * RAW_SLOTS, a_empty = a_full + 8 * A_STAGES,
+                   b_full = a_empty + 8 * A_STAGES, b_empty = b_full + 8 * B_STAGES, acc_full = b_empty + 8 * B_STAGES,
+                   acc_empty = acc_full + 16;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int e1 = p.experts + 1;
+    const int * counts = p.plan + PLAN_HDR, * offsets = counts + e1, * active = offsets + e1 + 1, * perm = active + e1;
+    const int na = p.plan[PLAN_NACTIVE], row_tiles = (p.rows + 15) >> 4, row_blocks = (row_tiles + 7) >> 3;
+    const int k_tiles = p.k / KT, ksteps = p.k / G_KS, nchunks = (k_tiles + CT - 1) / CT;
+
+    if (T == T_IQ3_S) for (int i = threadIdx.x; i < 512; i += G_THREADS) grid_tab[i] = c_iq3s_grid[i];
+    if (warp == 1) {                                                  // items before active expert i: cum[i]
+        int carry = 0;
+        for (int base = 0; base < na; base += 32) {
+            const int i = base + lane;
+            int v = i < na ? ((counts[active[i]] + G_NT - 1) / G_NT) * row_blocks : 0;
+            for (int d = 1; d < 32; d <<= 1) { const int o = __shfl_up_sync(0xffffffffu, v, d); if (lane >= d) v += o; }
+            if (i < na) cum[i + 1] = carry + v;
+            carry += __shfl_sync(0xffffffffu, v, 31);
+        }
+        if (lane == 0) cum[0] = 0;
+    }
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 8 * RAW_SLOTS; ++i) bar_init(raw_full + 8 * i, 1);
+        for (int i = 0; i < A_STAGES; ++i) { bar_init(a_full + 8 * i, 8); bar_init(a_empty + 8 * i, 1); }
+        for (int i = 0; i < B_STAGES; ++i) { bar_init(b_full + 8 * i, 4); bar_init(b_empty + 8 * i, 1); }
+        for (int i = 0; i < 2; ++i) { bar_init(acc_full + 8 * i, 1); bar_init(acc_empty + 8 * i, 4); }
+        *abort_flag = 0;
+        bar_init_fence();
+    }
+    if (warp == MMA_WARP) tmem_alloc(saddr(tmem_slot), TMEM_COLS);
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const int n_items = cum[na];
+
+    // item -> expert, first token slot, token count, row block
+    struct Item { int e, off, c0, nv, rb; };
+    auto locate = [&](int it) {
+        int lo = 0, hi = na - 1;
+        while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (cum[mid] <= it) lo = mid; else hi = mid - 1; }
+        Item r;
+        r.e = active[lo];
+        const int cnt = counts[r.e], nt = (cnt + G_NT - 1) / G_NT, local = it - cum[lo];
+        r.off = offsets[r.e];
+        r.rb = local / nt;
+        r.c0 = (local - r.rb * nt) * G_NT;
+        r.nv = min(G_NT, cnt - r.c0);
+        return r;
+    };
+    auto give_up = [&]() { *abort_flag = 1; atomicExch(p.plan + PLAN_STATUS, 2); };
+
+    if (warp == MMA_WARP) {
+        // ---- MMA issuer ----
+        uint32_t gk = 0, ic = 0;
+        for (int it = blockIdx.x; it < n_items && !*abort_flag; it += gridDim.x, ++ic) {
+            const Item im = locate(it);
+            const uint32_t npad = uint32_t(im.nv + 15) & ~15u, id = idesc(G_ROWS, npad, 0), ab = ic & 1u;
+            if (lane == 0) {
+                if (ic >= 2 && !bar_wait(acc_empty + 8 * ab, ((ic >> 1) - 1) & 1u)) give_up();
+                fence_after();
+                for (int ks = 0; ks < ksteps && !*abort_flag; ++ks, ++gk) {
+                    const uint32_t sa = gk % A_STAGES, sb = gk % B_STAGES;
+                    if (!bar_wait(a_full + 8 * sa, (gk / A_STAGES) & 1u) || !bar_wait(b_full + 8 * sb, (gk / B_STAGES) & 1u)) { give_up(); break; }
+                    fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint64_t bd = smem_desc(saddr(b_st) + sb * B_STAGE + 2 * kk * B_LBO, B_LBO, 128);
+#pragma unroll
+                        for (int m = 0; m < NMAT; ++m)
+                            mma_f16(tmem + ab * (NMAT * G_NT) + m * G_NT,
+                                    smem_desc(saddr(a_st) + (sa * NMAT + m) * A_MAT + 2 * kk * A_LBO, A_LBO, 128), bd, id, (ks | kk) != 0);
+                    }
+                    mma_commit(a_empty + 8 * sa);
+                    mma_commit(b_empty + 8 * sb);
+                }
+                mma_commit(acc_full + 8 * ab);
+            }
+            __syncwarp();
+        }
+    } else if (warp < LOAD_WARP0) {
+        // ---- epilogue: warp q reads TMEM lanes [32 q, 32 q + 32) = rows of the block ----
+        const int q = warp & 3;
+        uint32_t ic = 0;
+        for (int it = blockIdx.x; it < n_items && !*abort_flag; it += gridDim.x, ++ic) {
+            const Item im = locate(it);
+            const uint32_t ab = ic & 1u;
+            if (!__all_sync(0xffffffffu, bar_wait(acc_full + 8 * ab, (ic >> 1) & 1u))) { if (lane == 0) give_up(); break; }
+            fence_after();
+            const int row = im.rb * G_ROWS + 32 * q + lane;
+            const uint32_t taddr = tmem + (uint32_t(32 * q) << 16) + ab * (NMAT * G_NT);
+            for (int c = 0; c < im.nv; c += 16) {
+                uint32_t g[16], u[16];
+                tmem_ld16(taddr + c, g);
+                if (NMAT == 2) tmem_ld16(taddr + G_NT + c, u);
+                tmem_ld_wait();
+                if (row < p.rows) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (c + j < im.nv) {
+                            const int a = perm[im.off + im.c0 + c + j];
+                            const float is = p.inv_scale[MODE == 0 ? (a < p.A ? a / p.topk : a - p.A) : a];
+                            const float gv = __uint_as_float(g[j]) * is;
+                            p.out[size_t(a) * p.rows + row] = MODE == 0 ? (gv / (1.f + expf(-gv))) * (__uint_as_float(u[j]) * is) : gv;
+                        }
+                    }
+                }
+            }
+            fence_before();
+            __syncwarp();
+            if (lane == 0) bar_arrive(acc_empty + 8 * ab);
+        }
+    } else if (warp < DEC_WARP0) {
+        // ---- B loader: thread n copies the 128 bytes of token row n of every step, B_LAG steps in flight ----
+        const int n = threadIdx.x - LOAD_WARP0 * 32;
+        uint32_t gk = 0, arrived = 0;
+        bool ok = true;
+        auto arrive_next = [&]() {
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) bar_arrive(b_full + 8 * (arrived % B_STAGES));
+            ++arrived;
+        };
+        for (int it = blockIdx.x; it < n_items && ok && !*abort_flag; it += gridDim.x) {
+            const Item im = locate(it);
+            const int npad = (im.nv + 15) & ~15;
+            const __half * src = p.xb;
+            uint32_t src_bytes = 0;
+            if (n < im.nv) {
+                const int a = perm[im.off + im.c0 + n];
+                src = p.xb + size_t(MODE == 0 ? (a < p.A ? a / p.topk : a - p.A) : a) * p.k;
+                src_bytes = 16;
+            }
+            const uint32_t dst0 = saddr(b_st) + (n >> 3) * 128 + (n & 7) * 16;
+            for (int ks = 0; ks < ksteps; ++ks, ++gk) {
+                const uint32_t sb = gk % B_STAGES;
+                if (gk >= B_STAGES && !__all_sync(0xffffffffu, bar_wait(b_empty + 8 * sb, ((gk / B_STAGES) - 1) & 1u))) { ok = false; break; }
+                if (n < npad) {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) cp_async16(dst0 + sb * B_STAGE + c * B_LBO, src + (src_bytes ? ks * G_KS + c * 8 : 0), src_bytes);
+                }
+                cp_async_commit();
+                if (gk - arrived >= B_LAG) { cp_async_wait<B_LAG>(); arrive_next(); }
+            }
+        }
+        cp_async_wait<0>();
+        while (arrived < gk) arrive_next();
+        if (!ok && lane == 0) give_up();
+    } else {
+        // ---- A decoder: warp dw owns row tile dw of the block: raw chunks (256 columns) -> fp16 operand, 64 columns a step ----
+        const int dw = warp - DEC_WARP0;
+        uint8_t * my_raw = raw + dw * RAW_SLOTS * NMAT * CB;
+        const uint32_t my_full = raw_full + 8 * dw * RAW_SLOTS;
+        uint32_t gk = 0, gc = 0;
+        bool ok = true;
+        for (int it = blockIdx.x; it < n_items && ok && !*abort_flag; it += gridDim.x) {
+            const Item im = locate(it);
+            const int rt = im.rb * 8 + dw;
+            const bool live = rt < row_tiles, shared = im.e == p.experts;
+            const uint8_t * base[NMAT];
+            const float * aux[NMAT];
+            base[0] = (shared ? p.s0 : p.w0 + size_t(im.e) * p.bank_bytes) + size_t(rt) * k_tiles * TILE;
+            aux[0] = shared ? p.saux0 : p.aux0;
+            if (NMAT == 2) {
+                base[NMAT - 1] = (shared ? p.s1 : p.w1 + size_t(im.e) * p.bank_bytes) + size_t(rt) * k_tiles * TILE;
+                aux[NMAT - 1] = shared ? p.saux1 : p.aux1;
+            }
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m)
+                if (aux[m]) aux[m] += (size_t(shared ? 0 : im.e) * row_tiles + rt) * 16;
+            auto issue = [&](int c, uint32_t slot) {                   // chunk c of this row tile -> ring slot (lane 0)
+                const int tiles = min(CT, k_tiles - c * CT);
+                const uint32_t bytes = uint32_t(tiles) * TILE, bar = my_full + 8 * slot;
+                bar_expect_tx(bar, bytes * NMAT);
+#pragma unroll
+                for (int m = 0; m < NMAT; ++m)
+                    bulk_copy(saddr(my_raw) + (slot * NMAT + m) * CB, base[m] + size_t(c) * CT * TILE, bytes, bar);
+            };
+            if (live && lane == 0)
+                for (int c = 0; c < RAW_SLOTS && c < nchunks; ++c) issue(c, (gc + c) % RAW_SLOTS);
+            for (int c = 0; c < nchunks && ok; ++c, gc += live ? 1u : 0u) {     // a dead row tile (past the last row) uses no slot
+                const uint32_t slot = gc % RAW_SLOTS;
+                if (live && !__all_sync(0xffffffffu, bar_wait(my_full + 8 * slot, (gc / RAW_SLOTS) & 1u))) { ok = false; break; }
+                const int steps = min(4, ksteps - 4 * c);
+                for (int j = 0; j < steps; ++j, ++gk) {
+                    const uint32_t sa = gk % A_STAGES;
+                    if (gk >= A_STAGES && !__all_sync(0xffffffffu, bar_wait(a_empty + 8 * sa, ((gk / A_STAGES) - 1) & 1u))) { ok = false; break; }
+                    if (live) {
+#pragma unroll
+                        for (int m = 0; m < NMAT; ++m) {
+                            const uint8_t * chunk = my_raw + (slot * NMAT + m) * CB;
+                            uint8_t * dst = a_st + (sa * NMAT + m) * A_MAT + 2 * dw * 128;
+#pragma unroll 4
+                            for (int i = lane; i < Fmt<T>::STEP_UNITS; i += 32) {
+                                int tl, u, row, k0, k1;
+                                float v[8];
+                                Fmt<T>::step_unit(j, i, tl, u);
+                                Fmt<T>::unit_vals(chunk + tl * TILE, aux[m], u, v, row, k0, k1, T == T_IQ3_S ? grid_tab : nullptr);
+                                const int kk0 = tl * KT + k0 - 64 * j;
+                                uint8_t * d0 = dst + (kk0 >> 3) * A_LBO + (row >> 3) * 128 + (row & 7) * 16 + (kk0 & 7) * 2;
+                                *reinterpret_cast<uint2 *>(d0) = make_uint2(pack_f16(v[0], v[1]), pack_f16(v[2], v[3]));
+                                if (k1 >= 0) {
+                                    const int kk1 = tl * KT + k1 - 64 * j;
+                                    uint8_t * d1 = dst + (kk1 >> 3) * A_LBO + (row >> 3) * 128 + (row & 7) * 16 + (kk1 & 7) * 2;
+                                    *reinterpret_cast<uint2 *>(d1) = make_uint2(pack_f16(v[4], v[5]), pack_f16(v[6], v[7]));
+                                }
+                            }
+                        }
+                    }
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) bar_arrive(a_full + 8 * sa);
+                }
+                __syncwarp();                                          // every lane is done with the slot: refill it
+                if (live && lane == 0 && c + RAW_SLOTS < nchunks) issue(c + RAW_SLOTS, slot);
+            }
+        }
+        if (!ok && lane == 0) give_up();
+    }
+    fence_before();
+    __syncthreads();
+    if (warp == MMA_WARP) tmem_free(tmem, TMEM_COLS);
+}
+
+int gemm_sm_count() {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    return sms;
+}
+constexpr size_t GEMM_SMEM_LIMIT = 232448 - 1024;
+
+template <uint32_t T, int MODE>
+int32_t gemm_launch_t(const GemmArgs & a, cudaStream_t s) {
+    const int sms = gemm_sm_count();
+    if (sms <= 0) return B2MOE_ERR_CUDA;
+    const size_t smem = gemm_smem<T, MODE == 0 ? 2 : 1>(a.experts);
+    if (smem > GEMM_SMEM_LIMIT) return B2MOE_ERR_SHAPE;
+    if (cudaFuncSetAttribute(gemm_tc_k<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
+    gemm_tc_k<T, MODE><<<sms, G_THREADS, smem, s>>>(a);
+    return launch_status();
+}
+template <int MODE>
+int32_t gemm_launch(uint32_t type, const GemmArgs & a, cudaStream_t s) {
+    switch (type) {
+        case T_Q4_K: return gemm_launch_t<T_Q4_K, MODE>(a, s);
+        case T_IQ3_S: return gemm_launch_t<T_IQ3_S, MODE>(a, s);
+        case T_IQ4_XS: return gemm_launch_t<T_IQ4_XS, MODE>(a, s);
+        case T_IQ4_NL: return gemm_launch_t<T_IQ4_NL, MODE>(a, s);
+        case T_NVFP4G: return gemm_launch_t<T_NVFP4G, MODE>(a, s);
+    }
+    return B2MOE_ERR_FORMAT;
+}
+size_t gemm_smem_of(uint32_t type, int nmat, int experts) {
+    switch (type) {
+        case T_Q4_K: return nmat == 2 ? gemm_smem<T_Q4_K, 2>(experts) : gemm_smem<T_Q4_K, 1>(experts);
+        case T_IQ3_S: return nmat == 2 ? gemm_smem<T_IQ3_S, 2>(experts) : gemm_smem<T_IQ3_S, 1>(experts);
+        case T_IQ4_XS: return nmat == 2 ? gemm_smem<T_IQ4_XS, 2>(experts) : gemm_smem<T_IQ4_XS, 1>(experts);
+        case T_IQ4_NL: return nmat == 2 ? gemm_smem<T_IQ4_NL, 2>(experts) : gemm_smem<T_IQ4_NL, 1>(experts);
+        case T_NVFP4G: return nmat == 2 ? gemm_smem<T_NVFP4G, 2>(experts) : gemm_smem<T_NVFP4G, 1>(experts);
+    }
+    return ~size_t(0);
+}
+int32_t convert_rows(const void * x, int dtype, int rows, int k, __half * out, float * inv, cudaStream_t s) {
+    rows_to_f16_k<<<ceil_div(rows, 8), 256, 0, s>>>(x, dtype, rows, k, out, inv);
+    return launch_status();
+}
+
+}  // namespace
+
+// true when the tensor-core GEMM takes banks of this type with rows of length k (nmat: 2 = gate/up, 1 = down)
+bool gemm_tc_supported(uint32_t type, int k, int nmat, int experts) {
+    return k >= G_KS && k % G_KS == 0 && gemm_smem_of(type, nmat, experts) <= GEMM_SMEM_LIMIT;
+}
+// scratch: the scaled fp16 copy of `rows_x` activation rows of length k and one float per row
+size_t gemm_tc_workspace_bytes(int rows_x, int k) {
+    return align_up(size_t(rows_x) * k * 2, 256) + align_up(size_t(rows_x) * sizeof(float), 256);
+}
+
+int32_t gemm_tc_gateup(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_bank * sg, const b2moe_bank * su, const void * x,
+                       int x_dtype, const int * plan, int n, int topk, int shared_tokens, float * act, void * ws, cudaStream_t s) {
+    const int k = gate->cols;
+    __half * xb = static_cast<__half *>(ws);
+    float * inv = reinterpret_cast<float *>(static_cast<uint8_t *>(ws) + align_up(size_t(n) * k * 2, 256));
+    if (int32_t rc = convert_rows(x, x_dtype, n, k, xb, inv, s)) return rc;
+    GemmArgs a{};
+    a.w0 = static_cast<const uint8_t *>(gate->data); a.w1 = static_cast<const uint8_t *>(up->data);
+    a.aux0 = static_cast<const float *>(gate->aux); a.aux1 = static_cast<const float *>(up->aux);
+    if (shared_tokens) {
+        a.s0 = static_cast<const uint8_t *>(sg->data); a.s1 = static_cast<const uint8_t *>(su->data);
+        a.saux0 = static_cast<const float *>(sg->aux); a.saux1 = static_cast<const float *>(su->aux);
+    }
+    a.bank_bytes = b2moe_bank_bytes(gate->type, gate->rows, gate->cols);
+    a.xb = xb; a.inv_scale = inv; a.plan = const_cast<int *>(plan); a.out = act;
+    a.rows = gate->rows; a.k = k; a.experts = gate->experts; a.topk = topk; a.A = n * topk;
+    return gemm_launch<0>(gate->type, a, s);
+}
+
+int32_t gemm_tc_down(const b2moe_bank * down, const b2moe_bank * sd, const float * act, const int * plan, int n, int topk,
+                     int shared_tokens, float * y, void * ws, cudaStream_t s) {
+    const int rows_x = n * topk + shared_tokens, k = down->cols;
+    __half * xb = static_cast<__half *>(ws);
+    float * inv = reinterpret_cast<float *>(static_cast<uint8_t *>(ws) + align_up(size_t(rows_x) * k * 2, 256));
+    if (int32_t rc = convert_rows(act, B2MOE_F32, rows_x, k, xb, inv, s)) return rc;
+    GemmArgs a{};
+    a.w0 = static_cast<const uint8_t *>(down->data);
+    a.aux0 = static_cast<const float *>(down->aux);
+    if (shared_tokens) { a.s0 = static_cast<const uint8_t *>(sd->data); a.saux0 = static_cast<const float *>(sd->aux); }
+    a.bank_bytes = b2moe_bank_bytes(down->type, down->rows, down->cols);
+    a.xb = xb; a.inv_scale = inv; a.plan = const_cast<int *>(plan); a.out = y;
+    a.rows = down->rows; a.k = k; a.experts = down->experts; a.topk = topk; a.A = n * topk;
+    return gemm_launch<1>(down->type, a, s);
+}
+
+}  // namespace b2

@@ -84,7 +84,8 @@ __host__ __device__ __forceinline__ void k4_scale_min(int j, const uint8_t * s, 
 // ---------------------------------------------------------------------------------------------------------------
 // pack_word: value of 32-bit word `wi` of the tile (row tile rt, column tile kt) of one expert's matrix, gathered from
 // the GGUF blocks `raw` of that expert ([rows][nblk][raw_bytes]). Rows >= rows decode to zero weights.
-// decode_unit: unit u of a tile -> its weights as fp32 into out[row * ld + k] (k inside the tile).
+// unit_vals: unit u of a tile -> its weights as fp32: v[0..3] are columns k0.. of row `row`, v[4..7] columns k1.. (k1 < 0: the
+// unit has four weights). step_unit enumerates the units of one 64-column step for the tensor-core GEMM path.
 // ---------------------------------------------------------------------------------------------------------------
 template <uint32_t T> struct Fmt;
 
@@ -106,8 +107,10 @@ template <> struct Fmt<T_Q4_K> {
         if (row >= rows) return 0u;
         return ld_u32_bytes(raw + (size_t(row) * nblk + kt) * RAW + off);
     }
-    __host__ __device__ static void decode_unit(const uint8_t * tile, const float *, int u, float * out, int ld) {
-        const int row = u >> 5, p = (u >> 3) & 3, m = u & 7;
+    __host__ __device__ static void unit_vals(const uint8_t * tile, const float *, int u, float (&v)[8], int & row, int & k0, int & k1,
+                                              const uint32_t * = nullptr) {
+        row = u >> 5;
+        const int p = (u >> 3) & 3, m = u & 7;
         const int L = 4 * (row & 7) + (m & 3);
         const uint32_t w = *reinterpret_cast<const uint32_t *>(tile + 512 * p + 16 * L + 8 * (row >> 3) + 4 * (m >> 2));
         const uint8_t * h = tile + 2048 + 16 * row;
@@ -117,13 +120,17 @@ template <> struct Fmt<T_Q4_K> {
         const float d1 = d * float(sc), m1 = dmin * float(mn);
         k4_scale_min(2 * p + 1, h + 4, sc, mn);
         const float d2 = d * float(sc), m2 = dmin * float(mn);
-        float * o = out + row * ld + 64 * p + 4 * m;
+        k0 = 64 * p + 4 * m;
+        k1 = k0 + 32;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            o[i] = d1 * float((w >> (8 * i)) & 15u) - m1;
-            o[32 + i] = d2 * float((w >> (8 * i + 4)) & 15u) - m2;
+            v[i] = d1 * float((w >> (8 * i)) & 15u) - m1;
+            v[4 + i] = d2 * float((w >> (8 * i + 4)) & 15u) - m2;
         }
     }
+    // unit i (of STEP_UNITS) of the 64 columns [64 j, 64 j + 64) of a 256-column chunk: tile inside the chunk, unit id
+    static constexpr int STEP_UNITS = 128;
+    __host__ __device__ static void step_unit(int j, int i, int & tl, int & u) { tl = 0; u = (i >> 3) * 32 + j * 8 + (i & 7); }
 };
 
 template <> struct Fmt<T_IQ3_S> {
@@ -182,8 +189,10 @@ template <> struct Fmt<T_IQ3_S> {
     __host__ __device__ __forceinline__ static uint32_t lane_word(const uint8_t * tile, int L, int q) {
         return *reinterpret_cast<const uint32_t *>(q < 12 ? tile + 512 * (q >> 2) + 16 * L + 4 * (q & 3) : tile + 1536 + 4 * L);
     }
-    __host__ __device__ static void decode_unit(const uint8_t * tile, const float *, int u, float * out, int ld) {
-        const int row = u >> 6, ib = (u >> 3) & 7, w = u & 7;
+    __host__ __device__ static void unit_vals(const uint8_t * tile, const float *, int u, float (&v)[8], int & row, int & k0, int & k1,
+                                              const uint32_t * grid_tab = nullptr) {
+        row = u >> 6;
+        const int ib = (u >> 3) & 7, w = u & 7;
         const int g = row & 7, r = row >> 3, t = w >> 1, j = w & 1, L = 4 * g + t;
         const int bit = 9 * (16 * r + 2 * ib + j), q = bit >> 5, sh = bit & 31;
         uint64_t two = lane_word(tile, L, q);
@@ -193,14 +202,18 @@ template <> struct Fmt<T_IQ3_S> {
         const uint32_t sc = *reinterpret_cast<const uint32_t *>(tile + 1664 + 4 * row);
         const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(tile + 1728 + 2 * row));
         const float db = d * float(1 + 2 * int((sc >> (4 * ib)) & 15u));
-        const uint32_t grid = B2_GRID(idx);
-        float * o = out + row * ld + 32 * ib + 4 * w;
+        const uint32_t grid = grid_tab ? grid_tab[idx] : B2_GRID(idx);
+        k0 = 32 * ib + 4 * w;
+        k1 = -1;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float mag = db * float((grid >> (8 * i)) & 255u);
-            o[i] = ((sg >> (8 * ((i >> 1) + 2 * (i & 1)))) & 1u) ? -mag : mag;
+            v[i] = ((sg >> (8 * ((i >> 1) + 2 * (i & 1)))) & 1u) ? -mag : mag;
+            v[4 + i] = 0.f;
         }
     }
+    static constexpr int STEP_UNITS = 256;
+    __host__ __device__ static void step_unit(int j, int i, int & tl, int & u) { tl = 0; u = (i >> 4) * 64 + (2 * j + ((i >> 3) & 1)) * 8 + (i & 7); }
 };
 
 template <> struct Fmt<T_IQ4_XS> {
@@ -221,8 +234,10 @@ template <> struct Fmt<T_IQ4_XS> {
         if (row >= rows) return 0u;
         return ld_u32_bytes(raw + (size_t(row) * nblk + kt) * RAW + off);
     }
-    __host__ __device__ static void decode_unit(const uint8_t * tile, const float *, int u, float * out, int ld) {
-        const int row = u >> 5, ib = (u >> 2) & 7, m = u & 3;
+    __host__ __device__ static void unit_vals(const uint8_t * tile, const float *, int u, float (&v)[8], int & row, int & k0, int & k1,
+                                              const uint32_t * = nullptr) {
+        row = u >> 5;
+        const int ib = (u >> 2) & 7, m = u & 3;
         const int L = 4 * (row & 7) + m;
         const uint32_t w = *reinterpret_cast<const uint32_t *>(tile + 512 * (ib >> 1) + 16 * L + 8 * (row >> 3) + 4 * (ib & 1));
         const uint8_t * h = tile + 2048 + 8 * row;
@@ -230,13 +245,16 @@ template <> struct Fmt<T_IQ4_XS> {
         const uint32_t sh = ld_u16_bytes(h + 2);
         const int ls = int((h[4 + (ib >> 1)] >> (4 * (ib & 1))) & 15) | int(((sh >> (2 * ib)) & 3u) << 4);
         const float dl = d * float(ls - 32);
-        float * o = out + row * ld + 32 * ib + 4 * m;
+        k0 = 32 * ib + 4 * m;
+        k1 = k0 + 16;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            o[i] = dl * float(B2_KV((w >> (8 * i)) & 15u));
-            o[16 + i] = dl * float(B2_KV((w >> (8 * i + 4)) & 15u));
+            v[i] = dl * float(B2_KV((w >> (8 * i)) & 15u));
+            v[4 + i] = dl * float(B2_KV((w >> (8 * i + 4)) & 15u));
         }
     }
+    static constexpr int STEP_UNITS = 128;
+    __host__ __device__ static void step_unit(int j, int i, int & tl, int & u) { tl = 0; u = (i >> 3) * 32 + (2 * j + ((i >> 2) & 1)) * 4 + (i & 3); }
 };
 
 template <> struct Fmt<T_IQ4_NL> {
@@ -254,17 +272,22 @@ template <> struct Fmt<T_IQ4_NL> {
         }
         return v;
     }
-    __host__ __device__ static void decode_unit(const uint8_t * tile, const float *, int u, float * out, int ld) {
-        const int row = u >> 2, m = u & 3, L = 4 * (row & 7) + m;
+    __host__ __device__ static void unit_vals(const uint8_t * tile, const float *, int u, float (&v)[8], int & row, int & k0, int & k1,
+                                              const uint32_t * = nullptr) {
+        row = u >> 2;
+        const int m = u & 3, L = 4 * (row & 7) + m;
         const uint32_t w = *reinterpret_cast<const uint32_t *>(tile + 8 * L + 4 * (row >> 3));
         const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(tile + 256 + 2 * row));
-        float * o = out + row * ld + 4 * m;
+        k0 = 4 * m;
+        k1 = k0 + 16;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            o[i] = d * float(B2_KV((w >> (8 * i)) & 15u));
-            o[16 + i] = d * float(B2_KV((w >> (8 * i + 4)) & 15u));
+            v[i] = d * float(B2_KV((w >> (8 * i)) & 15u));
+            v[4 + i] = d * float(B2_KV((w >> (8 * i + 4)) & 15u));
         }
     }
+    static constexpr int STEP_UNITS = 128;
+    __host__ __device__ static void step_unit(int j, int i, int & tl, int & u) { tl = 2 * j + (i >> 6); u = i & 63; }
 };
 
 template <> struct Fmt<T_NVFP4G> {
@@ -285,25 +308,44 @@ template <> struct Fmt<T_NVFP4G> {
         if (row >= rows) return 0u;
         return ld_u32_bytes(raw + (size_t(row) * nblk + kt) * RAW + off);
     }
-    __host__ __device__ static void decode_unit(const uint8_t * tile, const float * aux16, int u, float * out, int ld) {
+    __host__ __device__ static void unit_vals(const uint8_t * tile, const float * aux16, int u, float (&v)[8], int & row, int & k0, int & k1,
+                                              const uint32_t * = nullptr) {
         const float lut[16] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f, -0.f, -0.5f, -1.f, -1.5f, -2.f, -3.f, -4.f, -6.f};
-        const int row = u >> 4, s = (u >> 2) & 3, m = u & 3, L = 4 * (row & 7) + m;
+        row = u >> 4;
+        const int s = (u >> 2) & 3, m = u & 3, L = 4 * (row & 7) + m;
         const uint32_t w = *reinterpret_cast<const uint32_t *>(tile + 512 * (s >> 1) + 16 * L + 8 * (row >> 3) + 4 * (s & 1));
         const float d = e4m3_to_float(tile[1024 + 8 * row + 2 * s + (m >> 1)]) * aux16[row];
-        float * o = out + row * ld + 32 * s + 8 * m;
+        k0 = 32 * s + 8 * m;
+        k1 = k0 + 4;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            o[2 * i] = lut[(w >> (8 * i)) & 15u] * d;
-            o[2 * i + 1] = lut[(w >> (8 * i + 4)) & 15u] * d;
+            v[2 * i] = lut[(w >> (8 * i)) & 15u] * d;
+            v[2 * i + 1] = lut[(w >> (8 * i + 4)) & 15u] * d;
         }
     }
+    static constexpr int STEP_UNITS = 128;
+    __host__ __device__ static void step_unit(int j, int i, int & tl, int & u) { tl = j >> 1; u = (i >> 3) * 16 + (2 * (j & 1) + ((i >> 2) & 1)) * 4 + (i & 3); }
 };
+
+// unit u of a tile -> out[row * ld + k]
+template <uint32_t T>
+__host__ __device__ __forceinline__ void decode_unit(const uint8_t * tile, const float * aux16, int u, float * out, int ld) {
+    float v[8];
+    int row, k0, k1;
+    Fmt<T>::unit_vals(tile, aux16, u, v, row, k0, k1);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) out[row * ld + k0 + i] = v[i];
+    if (k1 >= 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out[row * ld + k1 + i] = v[4 + i];
+    }
+}
 
 // decode a whole tile (16 x KT fp32, row stride ld) with the calling block's threads
 template <uint32_t T>
 __host__ __device__ __forceinline__ void decode_tile(const uint8_t * tile, const float * aux16, float * out, int ld, int tid, int nthreads,
                                             int units) {
-    for (int u = tid; u < units; u += nthreads) Fmt<T>::decode_unit(tile, aux16, u, out, ld);
+    for (int u = tid; u < units; u += nthreads) decode_unit<T>(tile, aux16, u, out, ld);
 }
 
 }  // namespace b2

@@ -21,6 +21,11 @@ int32_t iq3s_tc_down(const b2moe_bank *, const b2moe_bank *, const float *, cons
 int32_t iq3s_gateup(const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const void *, int, const int *, int,
                     int, int, float *, void *, int, cudaStream_t);
 int32_t iq3s_down(const b2moe_bank *, const b2moe_bank *, const float *, const int *, int, int, int, float *, void *, int, cudaStream_t);
+bool gemm_tc_supported(uint32_t type, int k, int nmat, int experts);
+size_t gemm_tc_workspace_bytes(int rows_x, int k);
+int32_t gemm_tc_gateup(const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const void *, int, const int *, int,
+                       int, int, float *, void *, cudaStream_t);
+int32_t gemm_tc_down(const b2moe_bank *, const b2moe_bank *, const float *, const int *, int, int, int, float *, void *, cudaStream_t);
 
 namespace {
 int32_t same_shape(const b2moe_bank * a, const b2moe_bank * b, bool same_experts) {
@@ -33,9 +38,8 @@ int max_active_of(int experts, int n, int topk, int shared_tokens) {
     const long long a = (long long)n * topk;
     return int(a < experts ? a : experts) + (shared_tokens ? 1 : 0);
 }
-// Which kernel family serves an IQ3_S product: 2 = tcgen05 (tensor-memory accumulators), 1 = mma.sync, 0 = the generic path.
-// Default: mma.sync. B2MOE_IQ3S_PATH=tc selects the tcgen05 kernels, =generic the generic path (A/B measurements);
-// other formats always take the generic path.
+// Which IQ3_S decode kernel: 2 = tcgen05 (tensor-memory accumulators), 1 = mma.sync, 0 = none.
+// Default: mma.sync. B2MOE_IQ3S_PATH=tc selects the tcgen05 kernels, =generic none (A/B measurements).
 int iq3s_path(uint32_t type, int k, int dtype, int nmat) {
     if (type != T_IQ3_S) return 0;
     const char * v = std::getenv("B2MOE_IQ3S_PATH");
@@ -44,7 +48,24 @@ int iq3s_path(uint32_t type, int k, int dtype, int nmat) {
     if (cap >= 1 && iq3s_supported(k, dtype)) return 1;
     return 0;
 }
-bool tuned(uint32_t type, int k, int dtype, int nmat) { return iq3s_path(type, k, dtype, nmat) > 0; }
+// The kernel family of one expert product.
+//   PATH_DECODE  the IQ3_S decode kernels: every expert sees a few tokens, the product is bound by streaming the weights;
+//   PATH_GEMM    the tcgen05 grouped GEMM (all formats): the weights of an expert are decoded once per 128 tokens;
+//   PATH_GENERIC exact fp32 CUDA-core path: every shape, the floor under the other two.
+// Default: IQ3_S takes the decode kernels while the batch averages fewer than GEMM_MIN_PER assignments per expert, everything
+// else the GEMM. B2MOE_EXPERT_PATH=generic|decode|gemm forces a family where it supports the shape.
+enum { PATH_GENERIC = 0, PATH_DECODE = 1, PATH_GEMM = 3 };
+constexpr int GEMM_MIN_PER = 16;
+int expert_path(uint32_t type, int k, int dtype, int nmat, int experts, long long assignments) {
+    const char * v = std::getenv("B2MOE_EXPERT_PATH");
+    const char f = v ? v[0] : 'a';
+    if (f == 'g' && v[1] == 'e' && v[2] == 'n') return PATH_GENERIC;
+    const bool dec = iq3s_path(type, k, dtype, nmat) > 0, gemm = gemm_tc_supported(type, k, nmat, experts);
+    if (f == 'd') return dec ? PATH_DECODE : PATH_GENERIC;
+    if (f == 'g') return gemm ? PATH_GEMM : dec ? PATH_DECODE : PATH_GENERIC;
+    if (dec && (!gemm || assignments < (long long)GEMM_MIN_PER * experts)) return PATH_DECODE;
+    return gemm ? PATH_GEMM : PATH_GENERIC;
+}
 }  // namespace
 }  // namespace b2
 
@@ -75,7 +96,9 @@ extern "C" B2MOE_API size_t b2moe_expert_workspace_bytes(uint32_t type, int32_t 
     for (int nmat = 1; nmat <= 2; ++nmat) {
         const int path = iq3s_path(type, k, x_dtype, nmat);
         const size_t b = path == 2 ? iq3s_tc_workspace_bytes(rows_x, k, x_dtype) : path == 1 ? iq3s_workspace_bytes(rows_x, k, x_dtype) : 0;
+        const size_t g = gemm_tc_workspace_bytes(rows_x, k);
         need = b > need ? b : need;
+        need = g > need ? g : need;
     }
     return need;
 }
@@ -96,11 +119,14 @@ extern "C" B2MOE_API int32_t b2moe_expert_gateup_swiglu(const b2moe_bank * gate,
     }
     if (!x || !plan || !act) return B2MOE_ERR_NULL;
     if (!aligned16(x) || !aligned16(act)) return B2MOE_ERR_ALIGN;
-    if (tuned(gate->type, gate->cols, x_dtype, 2)) {
+    const int path = expert_path(gate->type, gate->cols, x_dtype, 2, gate->experts, (long long)n * topk);
+    if (path != PATH_GENERIC) {
         const size_t need = b2moe_expert_workspace_bytes(gate->type, n, gate->cols, x_dtype);
         if (need && !workspace) return B2MOE_ERR_NULL;
         if (need && !aligned16(workspace)) return B2MOE_ERR_ALIGN;
         if (workspace_bytes < need) return B2MOE_ERR_WORKSPACE;
+        if (path == PATH_GEMM)
+            return gemm_tc_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, workspace, as_stream(stream));
         if (iq3s_path(gate->type, gate->cols, x_dtype, 2) == 2)
             return iq3s_tc_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, workspace,
                                   max_active_of(gate->experts, n, topk, shared_tokens), as_stream(stream));
@@ -121,11 +147,14 @@ extern "C" B2MOE_API int32_t b2moe_expert_down(const b2moe_bank * down, const b2
     }
     if (!act || !plan || !y) return B2MOE_ERR_NULL;
     if (!aligned16(act) || !aligned16(y)) return B2MOE_ERR_ALIGN;
-    if (tuned(down->type, down->cols, B2MOE_F32, 1)) {
+    const int path = expert_path(down->type, down->cols, B2MOE_F32, 1, down->experts, (long long)n * topk);
+    if (path != PATH_GENERIC) {
         const int rows_x = n * topk + shared_tokens;
         if (!workspace) return B2MOE_ERR_NULL;
         if (!aligned16(workspace)) return B2MOE_ERR_ALIGN;
         if (workspace_bytes < b2moe_expert_workspace_bytes(down->type, rows_x, down->cols, B2MOE_F32)) return B2MOE_ERR_WORKSPACE;
+        if (path == PATH_GEMM)
+            return gemm_tc_down(down, shared_down, act, plan, n, topk, shared_tokens, y, workspace, as_stream(stream));
         if (iq3s_path(down->type, down->cols, B2MOE_F32, 1) == 2)
             return iq3s_tc_down(down, shared_down, act, plan, n, topk, shared_tokens, y, workspace,
                                 max_active_of(down->experts, n, topk, shared_tokens), as_stream(stream));
