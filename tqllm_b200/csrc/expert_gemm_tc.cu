@@ -12,8 +12,8 @@
 //   B: the tokens' activation rows (fp16, each row scaled by a power of two), gathered through the dispatch permutation with 16-byte cp.async;
 //   the gate and the up matrix share B and have an accumulator each; two accumulator sets alternate between items, so
 //   the epilogue of one item (SwiGLU, stores) overlaps the products of the next.
-// Warps: 0 issues tcgen05.mma (one lane); 1..4 epilogue (tcgen05.ld, one TMEM lane quarter each); 5..8 load B;
-// 9..16 decode A (warp w owns row tile w of the block). Every wait is bounded; a wait that runs out sets the plan's
+// Warps: 0 issues tcgen05.mma (one lane); 1..4 epilogue (tcgen05.ld, one TMEM lane quarter each); 5..6 load B;
+// 7..22 decode A (two warps per row tile of the block: rows g and rows g + 8 of the lane-major tile). Every wait is bounded; a wait that runs out sets the plan's
 // status word, and the block drains and leaves.
 //
 // Numerics: weights are rounded to fp16 after the exact fp32 decode (relative error <= 2^-11 per weight; bf16 operands
@@ -22,6 +22,7 @@
 // to 2^-29 of the row maximum; the epilogue multiplies the sums (fp32) by 2^-e.
 #include "common.cuh"
 #include "formats.cuh"
+#include "gemm_decode.cuh"
 #include "tc_ptx.cuh"
 
 namespace b2 {
@@ -32,13 +33,13 @@ constexpr int G_ROWS = 128;                 // weight rows per item = M
 constexpr int G_NT = 128;                   // tokens per item (N <= 128, a multiple of 16)
 constexpr int G_KS = 64;                    // columns per pipeline step (four MMAs of K = 16 per matrix)
 constexpr int A_STAGES = 2, B_STAGES = 4, RAW_SLOTS = 2, B_LAG = 2;
-constexpr int A_LBO = 2048 + 64;            // bytes between k cores of A (+64 spreads the decode stores over the banks)
+constexpr int A_LBO = gdec::A_LBO;          // bytes between k cores of A
 constexpr int A_MAT = 8 * A_LBO;            // one matrix of one A stage: 128 rows x 64 columns
 constexpr int B_LBO = G_NT * 16;            // bytes between k cores of B
 constexpr int B_STAGE = 8 * B_LBO;          // 128 tokens x 64 columns
-constexpr int MMA_WARP = 0, EPI_WARP0 = 1, LOAD_WARP0 = 5, DEC_WARP0 = 9;
-constexpr int G_THREADS = 17 * 32;
-constexpr int N_BARS = 8 * RAW_SLOTS + 2 * A_STAGES + 2 * B_STAGES + 4;
+constexpr int MMA_WARP = 0, LOAD_WARP0 = 5, LOAD_WARPS = 2, DEC_WARP0 = 7, DEC_WARPS = 16;   // warps 1..4: epilogue
+constexpr int G_THREADS = (DEC_WARP0 + DEC_WARPS) * 32;
+constexpr int N_BARS = 2 * 8 * RAW_SLOTS + 2 * A_STAGES + 2 * B_STAGES + 4;
 
 struct GemmArgs {
     const uint8_t * w0, * w1;               // stacked banks (gate, up) or (down, -)
@@ -58,10 +59,12 @@ template <uint32_t T> constexpr int chunk_bytes() { return chunk_tiles<T>() * Fm
 template <uint32_t T, int NMAT>
 constexpr size_t gemm_smem(int experts) {
     return size_t(A_STAGES) * NMAT * A_MAT + size_t(B_STAGES) * B_STAGE + size_t(8) * RAW_SLOTS * NMAT * chunk_bytes<T>() +
-           (T == T_IQ3_S ? 2048 : 0) + size_t(experts + 3) * 4 + 16 + size_t(N_BARS) * 8 + 16;
+           gdec::Dec<T>::TAB_BYTES + size_t(experts + 3) * 4 + 16 + size_t(N_BARS) * 8 + 16;
 }
 
-// any activation dtype -> fp16 rows scaled by a power of two per row (one warp per row) + the inverse scales
+// any activation dtype -> fp16 rows scaled by a power of two per row (one warp per row) + the inverse scales; inside every
+// 64-column step the columns are stored in the order of the format's A operand (gdec::colmap)
+template <uint32_t T>
 __global__ void rows_to_f16_k(const void * __restrict__ x, int dtype, int rows, int k, __half * __restrict__ out, float * __restrict__ inv_scale) {
     const int lane = threadIdx.x & 31, row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -72,13 +75,20 @@ __global__ void rows_to_f16_k(const void * __restrict__ x, int dtype, int rows, 
     ex = (mx > 0.f && mx < 3e38f) ? max(-100, min(100, ex)) : 14;
     const float scale = __uint_as_float(uint32_t(127 + 14 - ex) << 23);  // 2^(14 - ex)
     if (lane == 0) inv_scale[row] = __uint_as_float(uint32_t(127 - 14 + ex) << 23);
-    for (int j = lane; j < k; j += 32) out[size_t(row) * k + j] = __float2half_rn(load_act(x, dtype, size_t(row) * k + j) * scale);
+    for (int j = lane; j < k; j += 32)
+        out[size_t(row) * k + j] = __float2half_rn(load_act(x, dtype, size_t(row) * k + (j & ~63) + gdec::colmap<T>(j & 63)) * scale);
 }
 
-__device__ __forceinline__ uint32_t pack_f16(float a, float b) {
-    const __half2 v = __floats2half2_rn(a, b);
-    return *reinterpret_cast<const uint32_t *>(&v);
-}
+#ifdef B2_GEMM_PROF
+__device__ unsigned long long g_gemm_prof[8];
+#define GP_DECL long long gp_acc[8] = {}, gp_last = clock64()
+#define GP_LAP(i) do { const long long _n = clock64(); gp_acc[i] += _n - gp_last; gp_last = _n; } while (0)
+#define GP_FLUSH(base, n) do { for (int _i = 0; _i < n; ++_i) atomicAdd(&g_gemm_prof[base + _i], (unsigned long long)gp_acc[_i]); } while (0)
+#else
+#define GP_DECL
+#define GP_LAP(i)
+#define GP_FLUSH(base, n)
+#endif
 
 // MODE 0: act[a][r] = silu(gate_r . x_tok(a)) * (up_r . x_tok(a));  MODE 1: y[a][r] = down_r . act[a]
 template <uint32_t T, int MODE>
@@ -90,12 +100,12 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
     uint8_t * a_st = smem;                                            // [A_STAGES][NMAT][A_MAT]
     uint8_t * b_st = a_st + A_STAGES * NMAT * A_MAT;                  // [B_STAGES][B_STAGE]
     uint8_t * raw = b_st + B_STAGES * B_STAGE;                        // [8 warps][RAW_SLOTS][NMAT][CB]
-    uint32_t * grid_tab = reinterpret_cast<uint32_t *>(raw + 8 * RAW_SLOTS * NMAT * CB);
-    int * cum = reinterpret_cast<int *>(reinterpret_cast<uint8_t *>(grid_tab) + (T == T_IQ3_S ? 2048 : 0));   // [na + 1]
+    uint8_t * dec_tab = raw + 8 * RAW_SLOTS * NMAT * CB;             // the decoder's lookup table
+    int * cum = reinterpret_cast<int *>(dec_tab + gdec::Dec<T>::TAB_BYTES);                                   // [na + 1]
     uint64_t * bars = reinterpret_cast<uint64_t *>((reinterpret_cast<uintptr_t>(cum + p.experts + 3) + 15) & ~uintptr_t(15));
     uint32_t * tmem_slot = reinterpret_cast<uint32_t *>(bars + N_BARS);
     volatile int * abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-    const uint32_t raw_full = saddr(bars), a_full = raw_full + 8 * 8 * RAW_SLOTS, a_empty = a_full + 8 * A_STAGES,
+    const uint32_t raw_full = saddr(bars), raw_empty = raw_full + 8 * 8 * RAW_SLOTS, a_full = raw_empty + 8 * 8 * RAW_SLOTS, a_empty = a_full + 8 * A_STAGES,
                    b_full = a_empty + 8 * A_STAGES, b_empty = b_full + 8 * B_STAGES, acc_full = b_empty + 8 * B_STAGES,
                    acc_empty = acc_full + 16;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -104,7 +114,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
     const int na = p.plan[PLAN_NACTIVE], row_tiles = (p.rows + 15) >> 4, row_blocks = (row_tiles + 7) >> 3;
     const int k_tiles = p.k / KT, ksteps = p.k / G_KS, nchunks = (k_tiles + CT - 1) / CT;
 
-    if (T == T_IQ3_S) for (int i = threadIdx.x; i < 512; i += G_THREADS) grid_tab[i] = c_iq3s_grid[i];
+    gdec::Dec<T>::init(dec_tab, threadIdx.x, G_THREADS);
     if (warp == 1) {                                                  // items before active expert i: cum[i]
         int carry = 0;
         for (int base = 0; base < na; base += 32) {
@@ -117,9 +127,9 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
         if (lane == 0) cum[0] = 0;
     }
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 8 * RAW_SLOTS; ++i) bar_init(raw_full + 8 * i, 1);
-        for (int i = 0; i < A_STAGES; ++i) { bar_init(a_full + 8 * i, 8); bar_init(a_empty + 8 * i, 1); }
-        for (int i = 0; i < B_STAGES; ++i) { bar_init(b_full + 8 * i, 4); bar_init(b_empty + 8 * i, 1); }
+        for (int i = 0; i < 8 * RAW_SLOTS; ++i) { bar_init(raw_full + 8 * i, 1); bar_init(raw_empty + 8 * i, 2); }
+        for (int i = 0; i < A_STAGES; ++i) { bar_init(a_full + 8 * i, DEC_WARPS); bar_init(a_empty + 8 * i, 1); }
+        for (int i = 0; i < B_STAGES; ++i) { bar_init(b_full + 8 * i, LOAD_WARPS); bar_init(b_empty + 8 * i, 1); }
         for (int i = 0; i < 2; ++i) { bar_init(acc_full + 8 * i, 1); bar_init(acc_empty + 8 * i, 4); }
         *abort_flag = 0;
         bar_init_fence();
@@ -150,15 +160,21 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
     if (warp == MMA_WARP) {
         // ---- MMA issuer ----
         uint32_t gk = 0, ic = 0;
+        GP_DECL;
         for (int it = blockIdx.x; it < n_items && !*abort_flag; it += gridDim.x, ++ic) {
             const Item im = locate(it);
             const uint32_t npad = uint32_t(im.nv + 15) & ~15u, id = idesc(G_ROWS, npad, 0), ab = ic & 1u;
             if (lane == 0) {
+                GP_LAP(3);
                 if (ic >= 2 && !bar_wait(acc_empty + 8 * ab, ((ic >> 1) - 1) & 1u)) give_up();
                 fence_after();
+                GP_LAP(0);
                 for (int ks = 0; ks < ksteps && !*abort_flag; ++ks, ++gk) {
                     const uint32_t sa = gk % A_STAGES, sb = gk % B_STAGES;
-                    if (!bar_wait(a_full + 8 * sa, (gk / A_STAGES) & 1u) || !bar_wait(b_full + 8 * sb, (gk / B_STAGES) & 1u)) { give_up(); break; }
+                    if (!bar_wait(a_full + 8 * sa, (gk / A_STAGES) & 1u)) { give_up(); break; }
+                    GP_LAP(1);
+                    if (!bar_wait(b_full + 8 * sb, (gk / B_STAGES) & 1u)) { give_up(); break; }
+                    GP_LAP(2);
                     fence_after();
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {
@@ -170,11 +186,13 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
                     }
                     mma_commit(a_empty + 8 * sa);
                     mma_commit(b_empty + 8 * sb);
+                    GP_LAP(3);
                 }
                 mma_commit(acc_full + 8 * ab);
             }
             __syncwarp();
         }
+        if (lane == 0) GP_FLUSH(0, 4);
     } else if (warp < LOAD_WARP0) {
         // ---- epilogue: warp q reads TMEM lanes [32 q, 32 q + 32) = rows of the block ----
         const int q = warp & 3;
@@ -185,6 +203,14 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
             if (!__all_sync(0xffffffffu, bar_wait(acc_full + 8 * ab, (ic >> 1) & 1u))) { if (lane == 0) give_up(); break; }
             fence_after();
             const int row = im.rb * G_ROWS + 32 * q + lane;
+            float rs[NMAT];                                            // fp32 row scales of the bank (NVFP4G), else 1
+            {
+                const bool shared = im.e == p.experts;
+                const size_t ai = size_t(shared ? 0 : im.e) * row_tiles * 16 + row;
+                const float * a0 = shared ? p.saux0 : p.aux0, * a1 = shared ? p.saux1 : p.aux1;
+                rs[0] = (a0 && row < p.rows) ? a0[ai] : 1.f;
+                if (NMAT == 2) rs[NMAT - 1] = (a1 && row < p.rows) ? a1[ai] : 1.f;
+            }
             const uint32_t taddr = tmem + (uint32_t(32 * q) << 16) + ab * (NMAT * G_NT);
             for (int c = 0; c < im.nv; c += 16) {
                 uint32_t g[16], u[16];
@@ -197,8 +223,8 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
                         if (c + j < im.nv) {
                             const int a = perm[im.off + im.c0 + c + j];
                             const float is = p.inv_scale[MODE == 0 ? (a < p.A ? a / p.topk : a - p.A) : a];
-                            const float gv = __uint_as_float(g[j]) * is;
-                            p.out[size_t(a) * p.rows + row] = MODE == 0 ? (gv / (1.f + expf(-gv))) * (__uint_as_float(u[j]) * is) : gv;
+                            const float gv = __uint_as_float(g[j]) * (is * rs[0]);
+                            p.out[size_t(a) * p.rows + row] = MODE == 0 ? (gv / (1.f + expf(-gv))) * (__uint_as_float(u[j]) * (is * rs[NMAT - 1])) : gv;
                         }
                     }
                 }
@@ -208,7 +234,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
             if (lane == 0) bar_arrive(acc_empty + 8 * ab);
         }
     } else if (warp < DEC_WARP0) {
-        // ---- B loader: thread n copies the 128 bytes of token row n of every step, B_LAG steps in flight ----
+        // ---- B loader: thread n copies the 128 bytes of token rows n and n + 64 of every step, B_LAG steps in flight ----
         const int n = threadIdx.x - LOAD_WARP0 * 32;
         uint32_t gk = 0, arrived = 0;
         bool ok = true;
@@ -221,20 +247,27 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
         for (int it = blockIdx.x; it < n_items && ok && !*abort_flag; it += gridDim.x) {
             const Item im = locate(it);
             const int npad = (im.nv + 15) & ~15;
-            const __half * src = p.xb;
-            uint32_t src_bytes = 0;
-            if (n < im.nv) {
-                const int a = perm[im.off + im.c0 + n];
-                src = p.xb + size_t(MODE == 0 ? (a < p.A ? a / p.topk : a - p.A) : a) * p.k;
-                src_bytes = 16;
+            const __half * src[2] = {p.xb, p.xb};
+            uint32_t src_bytes[2] = {0, 0};
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (n + 64 * h < im.nv) {
+                    const int a = perm[im.off + im.c0 + n + 64 * h];
+                    src[h] = p.xb + size_t(MODE == 0 ? (a < p.A ? a / p.topk : a - p.A) : a) * p.k;
+                    src_bytes[h] = 16;
+                }
             }
             const uint32_t dst0 = saddr(b_st) + (n >> 3) * 128 + (n & 7) * 16;
             for (int ks = 0; ks < ksteps; ++ks, ++gk) {
                 const uint32_t sb = gk % B_STAGES;
                 if (gk >= B_STAGES && !__all_sync(0xffffffffu, bar_wait(b_empty + 8 * sb, ((gk / B_STAGES) - 1) & 1u))) { ok = false; break; }
-                if (n < npad) {
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) cp_async16(dst0 + sb * B_STAGE + c * B_LBO, src + (src_bytes ? ks * G_KS + c * 8 : 0), src_bytes);
+                for (int h = 0; h < 2; ++h) {
+                    if (n + 64 * h < npad) {
+#pragma unroll
+                        for (int c = 0; c < 8; ++c)
+                            cp_async16(dst0 + sb * B_STAGE + c * B_LBO + h * 1024, src[h] + (src_bytes[h] ? ks * G_KS + c * 8 : 0), src_bytes[h]);
+                    }
                 }
                 cp_async_commit();
                 if (gk - arrived >= B_LAG) { cp_async_wait<B_LAG>(); arrive_next(); }
@@ -244,75 +277,76 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
         while (arrived < gk) arrive_next();
         if (!ok && lane == 0) give_up();
     } else {
-        // ---- A decoder: warp dw owns row tile dw of the block: raw chunks (256 columns) -> fp16 operand, 64 columns a step ----
-        const int dw = warp - DEC_WARP0;
-        uint8_t * my_raw = raw + dw * RAW_SLOTS * NMAT * CB;
-        const uint32_t my_full = raw_full + 8 * dw * RAW_SLOTS;
+        // ---- A decoder: warps tw and tw + 8 own row tile tw of the block (rows g / rows g + 8 of the tile): raw chunks
+        // (256 columns) -> fp16 operand, 64 columns a step; the first warp of the pair streams the chunks ----
+        const int dwi = warp - DEC_WARP0, tw = dwi & 7, half = dwi >> 3;
+        uint8_t * my_raw = raw + tw * RAW_SLOTS * NMAT * CB;
+        const uint32_t my_full = raw_full + 8 * tw * RAW_SLOTS, my_empty = raw_empty + 8 * tw * RAW_SLOTS;
         uint32_t gk = 0, gc = 0;
         bool ok = true;
+        GP_DECL;
         for (int it = blockIdx.x; it < n_items && ok && !*abort_flag; it += gridDim.x) {
             const Item im = locate(it);
-            const int rt = im.rb * 8 + dw;
+            const int rt = im.rb * 8 + tw;
             const bool live = rt < row_tiles, shared = im.e == p.experts;
             const uint8_t * base[NMAT];
-            const float * aux[NMAT];
             base[0] = (shared ? p.s0 : p.w0 + size_t(im.e) * p.bank_bytes) + size_t(rt) * k_tiles * TILE;
-            aux[0] = shared ? p.saux0 : p.aux0;
-            if (NMAT == 2) {
-                base[NMAT - 1] = (shared ? p.s1 : p.w1 + size_t(im.e) * p.bank_bytes) + size_t(rt) * k_tiles * TILE;
-                aux[NMAT - 1] = shared ? p.saux1 : p.aux1;
-            }
-#pragma unroll
-            for (int m = 0; m < NMAT; ++m)
-                if (aux[m]) aux[m] += (size_t(shared ? 0 : im.e) * row_tiles + rt) * 16;
-            auto issue = [&](int c, uint32_t slot) {                   // chunk c of this row tile -> ring slot (lane 0)
+            if (NMAT == 2) base[NMAT - 1] = (shared ? p.s1 : p.w1 + size_t(im.e) * p.bank_bytes) + size_t(rt) * k_tiles * TILE;
+            // chunk c of this row tile -> the ring slot of use number u (lane 0 of the pair's first warp); false = gave up
+            auto issue = [&](int c, uint32_t u) {
+                const uint32_t slot = u % RAW_SLOTS;
+                if (u >= RAW_SLOTS && !bar_wait(my_empty + 8 * slot, ((u / RAW_SLOTS) - 1) & 1u)) return false;   // both warps are done with it
                 const int tiles = min(CT, k_tiles - c * CT);
                 const uint32_t bytes = uint32_t(tiles) * TILE, bar = my_full + 8 * slot;
                 bar_expect_tx(bar, bytes * NMAT);
 #pragma unroll
                 for (int m = 0; m < NMAT; ++m)
                     bulk_copy(saddr(my_raw) + (slot * NMAT + m) * CB, base[m] + size_t(c) * CT * TILE, bytes, bar);
+                return true;
             };
-            if (live && lane == 0)
-                for (int c = 0; c < RAW_SLOTS && c < nchunks; ++c) issue(c, (gc + c) % RAW_SLOTS);
+            if (live && half == 0 && lane == 0)
+                for (int c = 0; c < RAW_SLOTS && c < nchunks; ++c)
+                    if (!issue(c, gc + c)) { give_up(); break; }
             for (int c = 0; c < nchunks && ok; ++c, gc += live ? 1u : 0u) {     // a dead row tile (past the last row) uses no slot
                 const uint32_t slot = gc % RAW_SLOTS;
+                GP_LAP(3);
                 if (live && !__all_sync(0xffffffffu, bar_wait(my_full + 8 * slot, (gc / RAW_SLOTS) & 1u))) { ok = false; break; }
+                GP_LAP(0);
                 const int steps = min(4, ksteps - 4 * c);
                 for (int j = 0; j < steps; ++j, ++gk) {
                     const uint32_t sa = gk % A_STAGES;
                     if (gk >= A_STAGES && !__all_sync(0xffffffffu, bar_wait(a_empty + 8 * sa, ((gk / A_STAGES) - 1) & 1u))) { ok = false; break; }
+                    GP_LAP(1);
+#ifndef B2_GEMM_SKIP_DECODE
                     if (live) {
 #pragma unroll
                         for (int m = 0; m < NMAT; ++m) {
                             const uint8_t * chunk = my_raw + (slot * NMAT + m) * CB;
-                            uint8_t * dst = a_st + (sa * NMAT + m) * A_MAT + 2 * dw * 128;
-#pragma unroll 4
-                            for (int i = lane; i < Fmt<T>::STEP_UNITS; i += 32) {
-                                int tl, u, row, k0, k1;
-                                float v[8];
-                                Fmt<T>::step_unit(j, i, tl, u);
-                                Fmt<T>::unit_vals(chunk + tl * TILE, aux[m], u, v, row, k0, k1, T == T_IQ3_S ? grid_tab : nullptr);
-                                const int kk0 = tl * KT + k0 - 64 * j;
-                                uint8_t * d0 = dst + (kk0 >> 3) * A_LBO + (row >> 3) * 128 + (row & 7) * 16 + (kk0 & 7) * 2;
-                                *reinterpret_cast<uint2 *>(d0) = make_uint2(pack_f16(v[0], v[1]), pack_f16(v[2], v[3]));
-                                if (k1 >= 0) {
-                                    const int kk1 = tl * KT + k1 - 64 * j;
-                                    uint8_t * d1 = dst + (kk1 >> 3) * A_LBO + (row >> 3) * 128 + (row & 7) * 16 + (kk1 & 7) * 2;
-                                    *reinterpret_cast<uint2 *>(d1) = make_uint2(pack_f16(v[4], v[5]), pack_f16(v[6], v[7]));
-                                }
+                            uint8_t * dst = a_st + (sa * NMAT + m) * A_MAT + 2 * tw * 128;
+                            switch (j) {
+                                case 0: gdec::Dec<T>::template step<0>(chunk, lane, dst, dec_tab, half); break;
+                                case 1: gdec::Dec<T>::template step<1>(chunk, lane, dst, dec_tab, half); break;
+                                case 2: gdec::Dec<T>::template step<2>(chunk, lane, dst, dec_tab, half); break;
+                                default: gdec::Dec<T>::template step<3>(chunk, lane, dst, dec_tab, half); break;
                             }
                         }
                     }
+#endif
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0) bar_arrive(a_full + 8 * sa);
+                    GP_LAP(2);
                 }
-                __syncwarp();                                          // every lane is done with the slot: refill it
-                if (live && lane == 0 && c + RAW_SLOTS < nchunks) issue(c + RAW_SLOTS, slot);
+                __syncwarp();                                          // every lane is done with the slot
+                if (live && lane == 0) {
+                    bar_arrive(my_empty + 8 * slot);
+                    if (half == 0 && c + RAW_SLOTS < nchunks && !issue(c + RAW_SLOTS, gc + RAW_SLOTS)) { give_up(); ok = false; }
+                }
+                ok = __all_sync(0xffffffffu, ok);
             }
         }
         if (!ok && lane == 0) give_up();
+        if (lane == 0 && dwi == 0) GP_FLUSH(4, 4);
     }
     fence_before();
     __syncthreads();
@@ -357,8 +391,16 @@ size_t gemm_smem_of(uint32_t type, int nmat, int experts) {
     }
     return ~size_t(0);
 }
-int32_t convert_rows(const void * x, int dtype, int rows, int k, __half * out, float * inv, cudaStream_t s) {
-    rows_to_f16_k<<<ceil_div(rows, 8), 256, 0, s>>>(x, dtype, rows, k, out, inv);
+int32_t convert_rows(uint32_t type, const void * x, int dtype, int rows, int k, __half * out, float * inv, cudaStream_t s) {
+    const int blocks = ceil_div(rows, 8);
+    switch (type) {
+        case T_Q4_K: rows_to_f16_k<T_Q4_K><<<blocks, 256, 0, s>>>(x, dtype, rows, k, out, inv); break;
+        case T_IQ3_S: rows_to_f16_k<T_IQ3_S><<<blocks, 256, 0, s>>>(x, dtype, rows, k, out, inv); break;
+        case T_IQ4_XS: rows_to_f16_k<T_IQ4_XS><<<blocks, 256, 0, s>>>(x, dtype, rows, k, out, inv); break;
+        case T_IQ4_NL: rows_to_f16_k<T_IQ4_NL><<<blocks, 256, 0, s>>>(x, dtype, rows, k, out, inv); break;
+        case T_NVFP4G: rows_to_f16_k<T_NVFP4G><<<blocks, 256, 0, s>>>(x, dtype, rows, k, out, inv); break;
+        default: return B2MOE_ERR_FORMAT;
+    }
     return launch_status();
 }
 
@@ -378,7 +420,7 @@ int32_t gemm_tc_gateup(const b2moe_bank * gate, const b2moe_bank * up, const b2m
     const int k = gate->cols;
     __half * xb = static_cast<__half *>(ws);
     float * inv = reinterpret_cast<float *>(static_cast<uint8_t *>(ws) + align_up(size_t(n) * k * 2, 256));
-    if (int32_t rc = convert_rows(x, x_dtype, n, k, xb, inv, s)) return rc;
+    if (int32_t rc = convert_rows(gate->type, x, x_dtype, n, k, xb, inv, s)) return rc;
     GemmArgs a{};
     a.w0 = static_cast<const uint8_t *>(gate->data); a.w1 = static_cast<const uint8_t *>(up->data);
     a.aux0 = static_cast<const float *>(gate->aux); a.aux1 = static_cast<const float *>(up->aux);
@@ -397,7 +439,7 @@ int32_t gemm_tc_down(const b2moe_bank * down, const b2moe_bank * sd, const float
     const int rows_x = n * topk + shared_tokens, k = down->cols;
     __half * xb = static_cast<__half *>(ws);
     float * inv = reinterpret_cast<float *>(static_cast<uint8_t *>(ws) + align_up(size_t(rows_x) * k * 2, 256));
-    if (int32_t rc = convert_rows(act, B2MOE_F32, rows_x, k, xb, inv, s)) return rc;
+    if (int32_t rc = convert_rows(down->type, act, B2MOE_F32, rows_x, k, xb, inv, s)) return rc;
     GemmArgs a{};
     a.w0 = static_cast<const uint8_t *>(down->data);
     a.aux0 = static_cast<const float *>(down->aux);
@@ -409,3 +451,12 @@ int32_t gemm_tc_down(const b2moe_bank * down, const b2moe_bank * sd, const float
 }
 
 }  // namespace b2
+
+#ifdef B2_GEMM_PROF
+// debug builds only: reads and clears the cycle counters of gemm_tc_k
+extern "C" B2MOE_API int b2moe_gemm_prof_read(unsigned long long * out8) {
+    unsigned long long zero[8] = {};
+    if (cudaMemcpyFromSymbol(out8, b2::g_gemm_prof, sizeof(zero)) != cudaSuccess) return 1;
+    return cudaMemcpyToSymbol(b2::g_gemm_prof, zero, sizeof(zero)) != cudaSuccess;
+}
+#endif

@@ -1,0 +1,239 @@
+// Weight decoders of the tensor-core grouped GEMM: one 64-column step of one 16-row bank tile -> fp16 A operand.
+//
+// Two warps own a row tile (warp half r decodes rows g + 8 r); lane L = 4 g + t holds, in the bank's lane-major
+// layout, the code words of rows g and g + 8 (formats.cuh). Every code word (or pair of IQ3_S grid entries) decodes to eight fp16 values = one 16-byte row of one
+// core matrix, so a lane writes whole core-matrix rows with 16-byte stores. Which eight columns a word covers depends
+// on the format (a Q4_K byte holds column c of two different sub-blocks, an IQ4 byte columns c and c + 16, ...): rather
+// than shuffling values between lanes, the GEMM permutes the 64 columns of a step — colmap<T>(pos) is the column stored
+// at operand position pos — and the activation rows are written in the same order (the sum over K does not care).
+//
+// Values: the fp32 formula of the format's host decoder (dequantize_host, src/formats/weight/dequant.cpp:80-99,137-150,
+// 177-192,352-360,397-409) evaluated so that the fp16 result carries one rounding: Q4_K in fp32 (d sc q - dmin m);
+// IQ3_S (odd magnitude x (1 + 2 s)) exact in fp16, then x d; IQ4_NL kvalue x d; NVFP4 e2m1 x e4m3 exact (the fp32 row
+// scale is applied to the accumulator in the epilogue). IQ4_XS multiplies the kvalue by fp16(d (ls - 32)): that factor's
+// rounding (relative 2^-12, the same for the 32 weights of a sub-block) comes on top of the single rounding.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+#include "formats.cuh"
+
+namespace b2 {
+namespace gdec {
+
+constexpr int A_LBO = 2048 + 32;            // bytes between the k cores of the A operand (+32: conflict-free 16-byte stores)
+
+// column (0..63, inside the step) held at operand position pos (0..63)
+template <uint32_t T> __host__ __device__ inline int colmap(int pos) {
+    const int c = pos >> 3, q = pos & 7;                               // core, position inside the 16-byte row
+    if (T == T_Q4_K) return q < 4 ? 4 * c + q : 32 + 4 * c + (q - 4); // word c: low nibbles = sub-block 0, high = sub-block 1
+    if (T == T_IQ4_XS || T == T_IQ4_NL) return 32 * (c >> 2) + 4 * (c & 3) + (q >> 1) + 16 * (q & 1);   // byte i: columns i, i + 16
+    return pos;                                                        // IQ3_S, NVFP4G: eight consecutive columns per word
+}
+
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+    const __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+__device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<const uint32_t *>(&v); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t v) { return *reinterpret_cast<const __half2 *>(&v); }
+// the 16-byte row of core matrix `core` for row r16 (0..15) of the warp's tile; base = the warp's first row group
+__device__ __forceinline__ uint4 * core_row(uint8_t * base, int core, int r16) {
+    return reinterpret_cast<uint4 *>(base + core * A_LBO + (r16 >> 3) * 128 + (r16 & 7) * 16);
+}
+
+// 256-entry table byte -> half2(value of the low nibble, value of the high nibble), eight interleaved copies
+// (entry b of copy c at word 8 b + c) so that the lanes of a warp spread over the banks
+constexpr int LUT_COPIES = 8, LUT_BYTES = 256 * LUT_COPIES * 4;
+template <uint32_t T> __device__ inline void build_lut(uint32_t * lut, int tid, int nthreads) {
+    for (int i = tid; i < 256 * LUT_COPIES; i += nthreads) {
+        const int b = i / LUT_COPIES;
+        float lo, hi;
+        if (T == T_NVFP4G) {
+            const float m[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+            lo = (b & 8) ? -m[b & 7] : m[b & 7];
+            hi = (b & 128) ? -m[(b >> 4) & 7] : m[(b >> 4) & 7];
+        } else {
+            lo = float(c_kvalues_iq4nl[b & 15]);
+            hi = float(c_kvalues_iq4nl[b >> 4]);
+        }
+        lut[i] = pack_h2(lo, hi);
+    }
+}
+// the four bytes of a code word -> eight values times `scale`, in byte order (low, high, low, high, ...)
+__device__ __forceinline__ uint4 lut_word(const uint32_t * lut_lane, uint32_t w, __half2 scale) {
+    uint4 o;
+    o.x = h2_bits(__hmul2(bits_h2(lut_lane[(w & 255u) * LUT_COPIES]), scale));
+    o.y = h2_bits(__hmul2(bits_h2(lut_lane[((w >> 8) & 255u) * LUT_COPIES]), scale));
+    o.z = h2_bits(__hmul2(bits_h2(lut_lane[((w >> 16) & 255u) * LUT_COPIES]), scale));
+    o.w = h2_bits(__hmul2(bits_h2(lut_lane[(w >> 24) * LUT_COPIES]), scale));
+    return o;
+}
+
+template <uint32_t T> struct Dec;
+
+// ---------------------------------------------------------------------------------------------------------------
+template <> struct Dec<T_Q4_K> {
+    static constexpr int TAB_BYTES = 0;
+    __device__ static void init(void *, int, int) {}
+    // (1 + q / 16) as a float from the nibble at bit `pos` of w, then S (1 + q / 16) + C = d sc q - dmin m with S = 16 d sc,
+    // C = -(S + dmin m): one fp32 rounding, far below the fp16 rounding that follows
+    template <int POS> __device__ __forceinline__ static float val(uint32_t w, float S, float C) {
+        const uint32_t f = ((POS <= 19 ? w << (19 - POS) : w >> (POS - 19)) & 0x00780000u) | 0x3F800000u;
+        return fmaf(__uint_as_float(f), S, C);
+    }
+    __device__ __forceinline__ static uint4 word(uint32_t w, float S1, float C1, float S2, float C2) {
+        uint4 o;
+        o.x = pack_h2(val<0>(w, S1, C1), val<8>(w, S1, C1));
+        o.y = pack_h2(val<16>(w, S1, C1), val<24>(w, S1, C1));
+        o.z = pack_h2(val<4>(w, S2, C2), val<12>(w, S2, C2));
+        o.w = pack_h2(val<20>(w, S2, C2), val<28>(w, S2, C2));
+        return o;
+    }
+    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void *, int r) {
+        const int g = lane >> 2, t = lane & 3;
+        const uint4 q4 = *reinterpret_cast<const uint4 *>(chunk + 512 * J + 16 * lane);
+        const uint32_t wr[2] = {r ? q4.z : q4.x, r ? q4.w : q4.y};             // this warp's row: g + 8 r
+        {
+            const uint4 h = *reinterpret_cast<const uint4 *>(chunk + 2048 + 16 * (g + 8 * r));
+            const uint32_t sw[3] = {h.y, h.z, h.w};
+            auto sb = [&](int i) { return (sw[i >> 2] >> (8 * (i & 3))) & 255u; };     // byte i of the 12 scale bytes
+            uint32_t sc[2], mn[2];
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                constexpr int dummy = 0; (void)dummy;
+                const int jj = 2 * J + b;
+                if (jj < 4) { sc[b] = sb(jj) & 63u; mn[b] = sb(jj + 4) & 63u; }
+                else { sc[b] = (sb(jj + 4) & 15u) | ((sb(jj - 4) >> 6) << 4); mn[b] = (sb(jj + 4) >> 4) | ((sb(jj) >> 6) << 4); }
+            }
+            const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
+            const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
+            const float S1 = 16.f * (d * float(sc[0])), C1 = -(S1 + dmin * float(mn[0]));
+            const float S2 = 16.f * (d * float(sc[1])), C2 = -(S2 + dmin * float(mn[1]));
+            *core_row(dst, t, g + 8 * r) = word(wr[0], S1, C1, S2, C2);
+            *core_row(dst, t + 4, g + 8 * r) = word(wr[1], S1, C1, S2, C2);
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------------------------------------------
+template <> struct Dec<T_IQ4_XS> {
+    static constexpr int TAB_BYTES = LUT_BYTES;
+    __device__ static void init(void * tab, int tid, int n) { build_lut<T_IQ4_XS>(static_cast<uint32_t *>(tab), tid, n); }
+    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void * tab, int r) {
+        const int g = lane >> 2, t = lane & 3;
+        const uint32_t * lut = static_cast<const uint32_t *>(tab) + (lane & (LUT_COPIES - 1));
+        const uint4 q4 = *reinterpret_cast<const uint4 *>(chunk + 512 * J + 16 * lane);
+        const uint32_t wr[2] = {r ? q4.z : q4.x, r ? q4.w : q4.y};             // this warp's row: g + 8 r
+        {
+            const uint2 h = *reinterpret_cast<const uint2 *>(chunk + 2048 + 8 * (g + 8 * r));   // d, scales_h | scales_l[4]
+            const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
+            const uint32_t sh = h.x >> 16;
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                const int ib = 2 * J + b;
+                const int ls = int((h.y >> (4 * ib)) & 15u) | int(((sh >> (2 * ib)) & 3u) << 4);
+                const __half2 dl = __float2half2_rn(d * float(ls - 32));
+                *core_row(dst, 4 * b + t, g + 8 * r) = lut_word(lut, wr[b], dl);
+            }
+        }
+    }
+};
+
+template <> struct Dec<T_IQ4_NL> {
+    static constexpr int TAB_BYTES = LUT_BYTES;
+    __device__ static void init(void * tab, int tid, int n) { build_lut<T_IQ4_NL>(static_cast<uint32_t *>(tab), tid, n); }
+    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void * tab, int r) {
+        const int g = lane >> 2, t = lane & 3;
+        const uint32_t * lut = static_cast<const uint32_t *>(tab) + (lane & (LUT_COPIES - 1));
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {                                   // the step's two 32-column tiles
+            const uint8_t * tile = chunk + (2 * J + b) * Fmt<T_IQ4_NL>::TILE;
+            const uint2 w = *reinterpret_cast<const uint2 *>(tile + 8 * lane);
+            {
+                const __half dh = __ushort_as_half(*reinterpret_cast<const unsigned short *>(tile + 256 + 2 * (g + 8 * r)));
+                *core_row(dst, 4 * b + t, g + 8 * r) = lut_word(lut, r ? w.y : w.x, __half2half2(dh));
+            }
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------------------------------------------
+template <> struct Dec<T_NVFP4G> {
+    static constexpr int TAB_BYTES = LUT_BYTES;
+    __device__ static void init(void * tab, int tid, int n) { build_lut<T_NVFP4G>(static_cast<uint32_t *>(tab), tid, n); }
+    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void * tab, int r) {
+        const int g = lane >> 2, t = lane & 3;
+        const uint32_t * lut = static_cast<const uint32_t *>(tab) + (lane & (LUT_COPIES - 1));
+        const uint8_t * tile = chunk + (J >> 1) * Fmt<T_NVFP4G>::TILE;
+        constexpr int P = J & 1;                                         // plane = sub-blocks 2 P, 2 P + 1 of the 128-column tile
+        const uint4 q4 = *reinterpret_cast<const uint4 *>(tile + 512 * P + 16 * lane);
+        const uint32_t wr[2] = {r ? q4.z : q4.x, r ? q4.w : q4.y};             // this warp's row: g + 8 r
+        {
+            const uint2 sc8 = *reinterpret_cast<const uint2 *>(tile + 1024 + 8 * (g + 8 * r));     // eight E4M3 group scales
+            const uint32_t scw = P ? sc8.y : sc8.x;                      // scales of sub-blocks 2 P (bytes 0, 1), 2 P + 1 (bytes 2, 3)
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                const uint32_t sbyte = (scw >> (16 * b + 8 * (t >> 1))) & 255u;       // the 16-weight group of word t
+                const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(sbyte | (sbyte << 8)), __NV_E4M3);
+                *core_row(dst, 4 * b + t, g + 8 * r) = lut_word(lut, wr[b], __half2(hr));
+            }
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------------------------------------------
+template <> struct Dec<T_IQ3_S> {
+    // table: grid entry -> its four odd magnitudes as fp16 (8 bytes)
+    static constexpr int TAB_BYTES = 512 * 8;
+    __device__ static void init(void * tab, int tid, int n) {
+        uint2 * t2 = static_cast<uint2 *>(tab);
+        for (int i = tid; i < 512; i += n) {
+            const uint32_t m = c_iq3s_grid[i];
+            t2[i] = make_uint2(pack_h2(float(m & 255u), float((m >> 8) & 255u)), pack_h2(float((m >> 16) & 255u), float(m >> 24)));
+        }
+    }
+    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void * tab, int r) {
+        const int g = lane >> 2, t = lane & 3;
+        const uint2 * mags = static_cast<const uint2 *>(tab);
+        uint32_t w[13];
+        {
+            const uint4 p0 = reinterpret_cast<const uint4 *>(chunk)[lane], p1 = reinterpret_cast<const uint4 *>(chunk + 512)[lane],
+                        p2 = reinterpret_cast<const uint4 *>(chunk + 1024)[lane];
+            w[0] = p0.x; w[1] = p0.y; w[2] = p0.z; w[3] = p0.w; w[4] = p1.x; w[5] = p1.y; w[6] = p1.z; w[7] = p1.w;
+            w[8] = p2.x; w[9] = p2.y; w[10] = p2.z; w[11] = p2.w;
+            w[12] = reinterpret_cast<const uint32_t *>(chunk + 1536)[lane];
+        }
+        {
+            const int row = g + 8 * r;
+            const uint32_t scales = *reinterpret_cast<const uint32_t *>(chunk + 1664 + 4 * row);
+            const __half2 d2 = __half2half2(__ushort_as_half(*reinterpret_cast<const unsigned short *>(chunk + 1728 + 2 * row)));
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                constexpr int dummy = 0; (void)dummy;
+                const int ib = 2 * J + b;
+                const __half2 s2 = __float2half2_rn(float(1 + 2 * int((scales >> (4 * ib)) & 15u)));      // 1 + 2 s: exact
+                const uint32_t sg = r ? w[11 + (ib >> 2)] : w[9 + (ib >> 2)];
+                uint32_t o[4];
+#pragma unroll
+                for (int jj = 0; jj < 2; ++jj) {
+                    // entry n = 16 r + 2 ib + jj of the lane's 9-bit stream; r = 1 starts at bit 144 = word 4, bit 16
+                    const int n0 = 2 * ib + jj;
+                    const int bitA = 9 * n0, bitB = 9 * (16 + n0);
+                    const uint32_t ia = (((bitA & 31) > 23 ? __funnelshift_r(w[bitA >> 5], w[(bitA >> 5) + 1], bitA & 31) : w[bitA >> 5] >> (bitA & 31))) & 511u;
+                    const uint32_t ibx = (((bitB & 31) > 23 ? __funnelshift_r(w[bitB >> 5], w[(bitB >> 5) + 1 > 8 ? 8 : (bitB >> 5) + 1], bitB & 31) : w[bitB >> 5] >> (bitB & 31))) & 511u;
+                    const uint32_t idx = r ? ibx : ia;
+                    const uint2 m = mags[idx];
+                    const int R = 2 * (ib & 3) + jj;
+                    // (mag x (1 + 2 s)) exact (<= 465), x d: one rounding; then the sign bits of the pairs (0, 1) and (2, 3)
+                    o[2 * jj] = h2_bits(__hmul2(__hmul2(bits_h2(m.x), s2), d2)) ^ ((sg << (15 - R)) & 0x80008000u);
+                    o[2 * jj + 1] = h2_bits(__hmul2(__hmul2(bits_h2(m.y), s2), d2)) ^ ((R <= 7 ? sg << (7 - R) : sg >> (R - 7)) & 0x80008000u);
+                }
+                *core_row(dst, 4 * b + t, row) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
+    }
+};
+
+}  // namespace gdec
+}  // namespace b2

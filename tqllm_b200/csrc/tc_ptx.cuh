@@ -23,8 +23,16 @@ __device__ __forceinline__ void bar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
         uint32_t ok;
+#if defined(B2_TC_POLL)
+        asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+#elif defined(B2_TC_NOHINT)
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+#else
         asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
                      : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
+#endif
         if (ok) return true;
     }
     return false;
