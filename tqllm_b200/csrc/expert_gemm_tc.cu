@@ -32,7 +32,15 @@ using namespace tc;
 constexpr int G_ROWS = 128;                 // weight rows per item = M
 constexpr int G_NT = 128;                   // tokens per item (N <= 128, a multiple of 16)
 constexpr int G_KS = 64;                    // columns per pipeline step (four MMAs of K = 16 per matrix)
-constexpr int A_STAGES = 2, B_STAGES = 4, RAW_SLOTS = 2, B_LAG = 2;
+#ifndef DEC_BACKOFF
+#define DEC_BACKOFF 100
+#endif
+#ifndef B2_A_STAGES
+#define B2_A_STAGES 2
+#define B2_B_STAGES 4
+#define B2_B_LAG 2
+#endif
+constexpr int A_STAGES = B2_A_STAGES, B_STAGES = B2_B_STAGES, RAW_SLOTS = 2, B_LAG = B2_B_LAG;
 constexpr int A_LBO = gdec::A_LBO;          // bytes between k cores of A
 constexpr int A_MAT = 8 * A_LBO;            // one matrix of one A stage: 128 rows x 64 columns
 constexpr int B_LBO = G_NT * 16;            // bytes between k cores of B
@@ -161,28 +169,33 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
         // ---- MMA issuer ----
         uint32_t gk = 0, ic = 0;
         GP_DECL;
+        // descriptor halves: low = address / 16 | (bytes between k cores / 16) << 16; high = (128 / 16) | the format's fixed bit 46
+        const uint32_t a_lo0 = ((saddr(a_st) & 0x3FFFFu) >> 4) | (uint32_t(A_LBO >> 4) << 16);
+        const uint32_t b_lo0 = ((saddr(b_st) & 0x3FFFFu) >> 4) | (uint32_t(B_LBO >> 4) << 16);
+        const uint32_t a_hi = (128u >> 4) | (1u << 14), b_hi = a_hi;
         for (int it = blockIdx.x; it < n_items && !*abort_flag; it += gridDim.x, ++ic) {
             const Item im = locate(it);
             const uint32_t npad = uint32_t(im.nv + 15) & ~15u, id = idesc(G_ROWS, npad, 0), ab = ic & 1u;
             if (lane == 0) {
                 GP_LAP(3);
-                if (ic >= 2 && !bar_wait(acc_empty + 8 * ab, ((ic >> 1) - 1) & 1u)) give_up();
+                if (ic >= 2 && !bar_wait(acc_empty + 8 * ab, ((ic >> 1) - 1) & 1u, 100)) give_up();
                 fence_after();
                 GP_LAP(0);
                 for (int ks = 0; ks < ksteps && !*abort_flag; ++ks, ++gk) {
                     const uint32_t sa = gk % A_STAGES, sb = gk % B_STAGES;
-                    if (!bar_wait(a_full + 8 * sa, (gk / A_STAGES) & 1u)) { give_up(); break; }
+                    if (!bar_wait(a_full + 8 * sa, (gk / A_STAGES) & 1u, 32)) { give_up(); break; }
                     GP_LAP(1);
-                    if (!bar_wait(b_full + 8 * sb, (gk / B_STAGES) & 1u)) { give_up(); break; }
+                    if (!bar_wait(b_full + 8 * sb, (gk / B_STAGES) & 1u, 32)) { give_up(); break; }
                     GP_LAP(2);
                     fence_after();
+                    const uint32_t a_lo = a_lo0 + sa * uint32_t((NMAT * A_MAT) >> 4), b_lo = b_lo0 + sb * uint32_t(B_STAGE >> 4);
+                    const uint32_t d0 = tmem + ab * (NMAT * G_NT);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {
-                        const uint64_t bd = smem_desc(saddr(b_st) + sb * B_STAGE + 2 * kk * B_LBO, B_LBO, 128);
 #pragma unroll
                         for (int m = 0; m < NMAT; ++m)
-                            mma_f16(tmem + ab * (NMAT * G_NT) + m * G_NT,
-                                    smem_desc(saddr(a_st) + (sa * NMAT + m) * A_MAT + 2 * kk * A_LBO, A_LBO, 128), bd, id, (ks | kk) != 0);
+                            mma_f16_lohi(d0 + m * G_NT, a_lo + uint32_t((m * A_MAT + 2 * kk * A_LBO) >> 4), a_hi,
+                                         b_lo + uint32_t((2 * kk * B_LBO) >> 4), b_hi, id, (ks | kk) != 0);
                     }
                     mma_commit(a_empty + 8 * sa);
                     mma_commit(b_empty + 8 * sb);
@@ -200,7 +213,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
         for (int it = blockIdx.x; it < n_items && !*abort_flag; it += gridDim.x, ++ic) {
             const Item im = locate(it);
             const uint32_t ab = ic & 1u;
-            if (!__all_sync(0xffffffffu, bar_wait(acc_full + 8 * ab, (ic >> 1) & 1u))) { if (lane == 0) give_up(); break; }
+            if (!__all_sync(0xffffffffu, bar_wait(acc_full + 8 * ab, (ic >> 1) & 1u, 400))) { if (lane == 0) give_up(); break; }
             fence_after();
             const int row = im.rb * G_ROWS + 32 * q + lane;
             float rs[NMAT];                                            // fp32 row scales of the bank (NVFP4G), else 1
@@ -260,7 +273,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
             const uint32_t dst0 = saddr(b_st) + (n >> 3) * 128 + (n & 7) * 16;
             for (int ks = 0; ks < ksteps; ++ks, ++gk) {
                 const uint32_t sb = gk % B_STAGES;
-                if (gk >= B_STAGES && !__all_sync(0xffffffffu, bar_wait(b_empty + 8 * sb, ((gk / B_STAGES) - 1) & 1u))) { ok = false; break; }
+                if (gk >= B_STAGES && !__all_sync(0xffffffffu, bar_wait(b_empty + 8 * sb, ((gk / B_STAGES) - 1) & 1u, 100))) { ok = false; break; }
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     if (n + 64 * h < npad) {
@@ -310,12 +323,17 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
             for (int c = 0; c < nchunks && ok; ++c, gc += live ? 1u : 0u) {     // a dead row tile (past the last row) uses no slot
                 const uint32_t slot = gc % RAW_SLOTS;
                 GP_LAP(3);
-                if (live && !__all_sync(0xffffffffu, bar_wait(my_full + 8 * slot, (gc / RAW_SLOTS) & 1u))) { ok = false; break; }
+                if (live && !__all_sync(0xffffffffu, bar_wait(my_full + 8 * slot, (gc / RAW_SLOTS) & 1u, DEC_BACKOFF))) { ok = false; break; }
                 GP_LAP(0);
                 const int steps = min(4, ksteps - 4 * c);
+                typename gdec::Dec<T>::Pre pre[NMAT];                  // per-chunk constants of the decoder
+                if (live) {
+#pragma unroll
+                    for (int m = 0; m < NMAT; ++m) pre[m] = gdec::Dec<T>::prep(my_raw + (slot * NMAT + m) * CB, lane, half);
+                }
                 for (int j = 0; j < steps; ++j, ++gk) {
                     const uint32_t sa = gk % A_STAGES;
-                    if (gk >= A_STAGES && !__all_sync(0xffffffffu, bar_wait(a_empty + 8 * sa, ((gk / A_STAGES) - 1) & 1u))) { ok = false; break; }
+                    if (gk >= A_STAGES && !__all_sync(0xffffffffu, bar_wait(a_empty + 8 * sa, ((gk / A_STAGES) - 1) & 1u, DEC_BACKOFF))) { ok = false; break; }
                     GP_LAP(1);
 #ifndef B2_GEMM_SKIP_DECODE
                     if (live) {
@@ -324,10 +342,10 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
                             const uint8_t * chunk = my_raw + (slot * NMAT + m) * CB;
                             uint8_t * dst = a_st + (sa * NMAT + m) * A_MAT + 2 * tw * 128;
                             switch (j) {
-                                case 0: gdec::Dec<T>::template step<0>(chunk, lane, dst, dec_tab, half); break;
-                                case 1: gdec::Dec<T>::template step<1>(chunk, lane, dst, dec_tab, half); break;
-                                case 2: gdec::Dec<T>::template step<2>(chunk, lane, dst, dec_tab, half); break;
-                                default: gdec::Dec<T>::template step<3>(chunk, lane, dst, dec_tab, half); break;
+                                case 0: gdec::Dec<T>::template step<0>(chunk, lane, dst, dec_tab, half, pre[m]); break;
+                                case 1: gdec::Dec<T>::template step<1>(chunk, lane, dst, dec_tab, half, pre[m]); break;
+                                case 2: gdec::Dec<T>::template step<2>(chunk, lane, dst, dec_tab, half, pre[m]); break;
+                                default: gdec::Dec<T>::template step<3>(chunk, lane, dst, dec_tab, half, pre[m]); break;
                             }
                         }
                     }

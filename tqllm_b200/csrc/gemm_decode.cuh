@@ -90,29 +90,42 @@ template <> struct Dec<T_Q4_K> {
         o.w = pack_h2(val<20>(w, S2, C2), val<28>(w, S2, C2));
         return o;
     }
-    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void *, int r) {
+    // Once per 256-column chunk: lane t of a row's four lanes turns the header into the constants of sub-blocks 2 t and
+    // 2 t + 1 (S = 16 d sc, C = -(S + dmin m)); a step fetches the pair it needs from lane J with shuffles.
+    struct Pre { float S[2], C[2]; };
+    __device__ __forceinline__ static Pre prep(const uint8_t * chunk, int lane, int r) {
         const int g = lane >> 2, t = lane & 3;
-        const uint4 q4 = *reinterpret_cast<const uint4 *>(chunk + 512 * J + 16 * lane);
-        const uint32_t wr[2] = {r ? q4.z : q4.x, r ? q4.w : q4.y};             // this warp's row: g + 8 r
-        {
-            const uint4 h = *reinterpret_cast<const uint4 *>(chunk + 2048 + 16 * (g + 8 * r));
-            const uint32_t sw[3] = {h.y, h.z, h.w};
-            auto sb = [&](int i) { return (sw[i >> 2] >> (8 * (i & 3))) & 255u; };     // byte i of the 12 scale bytes
-            uint32_t sc[2], mn[2];
+        const uint4 h = *reinterpret_cast<const uint4 *>(chunk + 2048 + 16 * (g + 8 * r));
+        const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
+        const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
+        // bytes of the 12-byte scale field: s[i] = byte i of (h.y, h.z, h.w)
+        const uint32_t hi = h.w;
+        Pre p;
 #pragma unroll
-            for (int b = 0; b < 2; ++b) {
-                constexpr int dummy = 0; (void)dummy;
-                const int jj = 2 * J + b;
-                if (jj < 4) { sc[b] = sb(jj) & 63u; mn[b] = sb(jj + 4) & 63u; }
-                else { sc[b] = (sb(jj + 4) & 15u) | ((sb(jj - 4) >> 6) << 4); mn[b] = (sb(jj + 4) >> 4) | ((sb(jj) >> 6) << 4); }
+        for (int b = 0; b < 2; ++b) {
+            const int jj = 2 * t + b;
+            uint32_t sc, mn;
+            if (t < 2) {                                               // jj < 4: sc = s[jj] & 63, mn = s[jj + 4] & 63
+                sc = (h.y >> (8 * jj)) & 63u;
+                mn = (h.z >> (8 * jj)) & 63u;
+            } else {                                                   // jj >= 4: high bits from s[jj - 4] / s[jj], low nibbles from s[jj + 4]
+                const uint32_t q = (hi >> (8 * (jj - 4))) & 255u;
+                sc = (q & 15u) | ((((h.y >> (8 * (jj - 4))) & 255u) >> 6) << 4);
+                mn = (q >> 4) | ((((h.z >> (8 * (jj - 4))) & 255u) >> 6) << 4);
             }
-            const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
-            const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
-            const float S1 = 16.f * (d * float(sc[0])), C1 = -(S1 + dmin * float(mn[0]));
-            const float S2 = 16.f * (d * float(sc[1])), C2 = -(S2 + dmin * float(mn[1]));
-            *core_row(dst, t, g + 8 * r) = word(wr[0], S1, C1, S2, C2);
-            *core_row(dst, t + 4, g + 8 * r) = word(wr[1], S1, C1, S2, C2);
+            p.S[b] = 16.f * (d * float(sc));
+            p.C[b] = -(p.S[b] + dmin * float(mn));
         }
+        return p;
+    }
+    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void *, int r, const Pre & pre) {
+        const int g = lane >> 2, t = lane & 3, src = (lane & ~3) | J;
+        const uint4 q4 = *reinterpret_cast<const uint4 *>(chunk + 512 * J + 16 * lane);
+        const uint32_t wa = r ? q4.z : q4.x, wb = r ? q4.w : q4.y;      // this warp's row: g + 8 r
+        const float S1 = __shfl_sync(0xffffffffu, pre.S[0], src), C1 = __shfl_sync(0xffffffffu, pre.C[0], src);
+        const float S2 = __shfl_sync(0xffffffffu, pre.S[1], src), C2 = __shfl_sync(0xffffffffu, pre.C[1], src);
+        *core_row(dst, t, g + 8 * r) = word(wa, S1, C1, S2, C2);
+        *core_row(dst, t + 4, g + 8 * r) = word(wb, S1, C1, S2, C2);
     }
 };
 
@@ -120,30 +133,38 @@ template <> struct Dec<T_Q4_K> {
 template <> struct Dec<T_IQ4_XS> {
     static constexpr int TAB_BYTES = LUT_BYTES;
     __device__ static void init(void * tab, int tid, int n) { build_lut<T_IQ4_XS>(static_cast<uint32_t *>(tab), tid, n); }
-    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void * tab, int r) {
+    // once per chunk: lane t holds fp16(d (ls - 32)) of sub-blocks 2 t and 2 t + 1 of its row
+    struct Pre { uint32_t dl[2]; };
+    __device__ __forceinline__ static Pre prep(const uint8_t * chunk, int lane, int r) {
         const int g = lane >> 2, t = lane & 3;
+        const uint2 h = *reinterpret_cast<const uint2 *>(chunk + 2048 + 8 * (g + 8 * r));       // d, scales_h | scales_l[4]
+        const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
+        const uint32_t sh = h.x >> 16;
+        Pre p;
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            const int ib = 2 * t + b;
+            const int ls = int((h.y >> (4 * ib)) & 15u) | int(((sh >> (2 * ib)) & 3u) << 4);
+            p.dl[b] = h2_bits(__float2half2_rn(d * float(ls - 32)));
+        }
+        return p;
+    }
+    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void * tab, int r, const Pre & pre) {
+        const int g = lane >> 2, t = lane & 3, src = (lane & ~3) | J;
         const uint32_t * lut = static_cast<const uint32_t *>(tab) + (lane & (LUT_COPIES - 1));
         const uint4 q4 = *reinterpret_cast<const uint4 *>(chunk + 512 * J + 16 * lane);
-        const uint32_t wr[2] = {r ? q4.z : q4.x, r ? q4.w : q4.y};             // this warp's row: g + 8 r
-        {
-            const uint2 h = *reinterpret_cast<const uint2 *>(chunk + 2048 + 8 * (g + 8 * r));   // d, scales_h | scales_l[4]
-            const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
-            const uint32_t sh = h.x >> 16;
-#pragma unroll
-            for (int b = 0; b < 2; ++b) {
-                const int ib = 2 * J + b;
-                const int ls = int((h.y >> (4 * ib)) & 15u) | int(((sh >> (2 * ib)) & 3u) << 4);
-                const __half2 dl = __float2half2_rn(d * float(ls - 32));
-                *core_row(dst, 4 * b + t, g + 8 * r) = lut_word(lut, wr[b], dl);
-            }
-        }
+        const uint32_t d0 = __shfl_sync(0xffffffffu, pre.dl[0], src), d1 = __shfl_sync(0xffffffffu, pre.dl[1], src);
+        *core_row(dst, t, g + 8 * r) = lut_word(lut, r ? q4.z : q4.x, bits_h2(d0));
+        *core_row(dst, 4 + t, g + 8 * r) = lut_word(lut, r ? q4.w : q4.y, bits_h2(d1));
     }
 };
 
 template <> struct Dec<T_IQ4_NL> {
+    struct Pre {};
+    __device__ __forceinline__ static Pre prep(const uint8_t *, int, int) { return Pre{}; }
     static constexpr int TAB_BYTES = LUT_BYTES;
     __device__ static void init(void * tab, int tid, int n) { build_lut<T_IQ4_NL>(static_cast<uint32_t *>(tab), tid, n); }
-    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void * tab, int r) {
+    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void * tab, int r, const Pre &) {
         const int g = lane >> 2, t = lane & 3;
         const uint32_t * lut = static_cast<const uint32_t *>(tab) + (lane & (LUT_COPIES - 1));
 #pragma unroll
@@ -160,9 +181,11 @@ template <> struct Dec<T_IQ4_NL> {
 
 // ---------------------------------------------------------------------------------------------------------------
 template <> struct Dec<T_NVFP4G> {
+    struct Pre {};
+    __device__ __forceinline__ static Pre prep(const uint8_t *, int, int) { return Pre{}; }
     static constexpr int TAB_BYTES = LUT_BYTES;
     __device__ static void init(void * tab, int tid, int n) { build_lut<T_NVFP4G>(static_cast<uint32_t *>(tab), tid, n); }
-    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void * tab, int r) {
+    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void * tab, int r, const Pre &) {
         const int g = lane >> 2, t = lane & 3;
         const uint32_t * lut = static_cast<const uint32_t *>(tab) + (lane & (LUT_COPIES - 1));
         const uint8_t * tile = chunk + (J >> 1) * Fmt<T_NVFP4G>::TILE;
@@ -184,6 +207,8 @@ template <> struct Dec<T_NVFP4G> {
 
 // ---------------------------------------------------------------------------------------------------------------
 template <> struct Dec<T_IQ3_S> {
+    struct Pre {};
+    __device__ __forceinline__ static Pre prep(const uint8_t *, int, int) { return Pre{}; }
     // table: grid entry -> its four odd magnitudes as fp16 (8 bytes)
     static constexpr int TAB_BYTES = 512 * 8;
     __device__ static void init(void * tab, int tid, int n) {
@@ -193,7 +218,7 @@ template <> struct Dec<T_IQ3_S> {
             t2[i] = make_uint2(pack_h2(float(m & 255u), float((m >> 8) & 255u)), pack_h2(float((m >> 16) & 255u), float(m >> 24)));
         }
     }
-    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void * tab, int r) {
+    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void * tab, int r, const Pre &) {
         const int g = lane >> 2, t = lane & 3;
         const uint2 * mags = static_cast<const uint2 *>(tab);
         uint32_t w[13];

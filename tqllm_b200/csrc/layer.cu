@@ -55,7 +55,7 @@ int iq3s_path(uint32_t type, int k, int dtype, int nmat) {
 // Default: IQ3_S takes the decode kernels while the batch averages fewer than GEMM_MIN_PER assignments per expert, everything
 // else the GEMM. B2MOE_EXPERT_PATH=generic|decode|gemm forces a family where it supports the shape.
 enum { PATH_GENERIC = 0, PATH_DECODE = 1, PATH_GEMM = 3 };
-constexpr int GEMM_MIN_PER = 16;
+constexpr int GEMM_MIN_PER = 32;
 int expert_path(uint32_t type, int k, int dtype, int nmat, int experts, long long assignments) {
     const char * v = std::getenv("B2MOE_EXPERT_PATH");
     const char f = v ? v[0] : 'a';

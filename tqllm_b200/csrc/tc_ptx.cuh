@@ -19,21 +19,15 @@ __device__ __forceinline__ void bar_arrive(uint32_t bar) {
 __device__ __forceinline__ void bar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// one phase of a barrier, with the hardware's suspending try_wait; false = gave up after WAIT_LIMIT tries
-__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) {
+// one phase of a barrier, with the hardware's suspending try_wait; between tries the thread sleeps `backoff_ns` (0 = retry at
+// once: for waits on the critical path), so that waiting warps leave the issue slots to the working ones; false = gave up
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, uint32_t backoff_ns = 0) {
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
         uint32_t ok;
-#if defined(B2_TC_POLL)
-        asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-#elif defined(B2_TC_NOHINT)
-        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-#else
         asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
                      : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
-#endif
         if (ok) return true;
+        if (backoff_ns) __nanosleep(backoff_ns);
     }
     return false;
 }
@@ -76,6 +70,14 @@ __device__ __forceinline__ uint32_t idesc(uint32_t m, uint32_t n, uint32_t ab_fo
 __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t id, uint32_t accumulate) {
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
                  ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(id), "r"(accumulate) : "memory");
+}
+// the same with the descriptors given as (low, high) 32-bit halves: the issuing thread keeps the high halves and the base low
+// halves in registers and adds small constants per MMA, so that its instruction stream (one thread feeds the tensor core) stays short
+__device__ __forceinline__ void mma_f16_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t id,
+                                             uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n .reg .b64 da, db;\n mov.b64 da, {%1, %2};\n mov.b64 db, {%3, %4};\n setp.ne.b32 p, %6, 0;\n"
+                 " tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}"
+                 ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(id), "r"(accumulate) : "memory");
 }
 // the barrier gets one arrival when every MMA this thread issued before has completed
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
