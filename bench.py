@@ -44,7 +44,7 @@ def parse():
     p.add_argument("--impl", default="b200", choices=("b200", "reference"))
     p.add_argument("--tokens", type=int, default=TOKENS)
     p.add_argument("--layers", type=int, default=LAYERS)
-    p.add_argument("--graph", type=int, default=1, help="replay the step as a CUDA graph (1) or launch it directly (0)")
+    p.add_argument("--graph", type=int, default=1, help="single GPU: replay the step as a CUDA graph (1) or launch it directly (0)")
     p.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     p.add_argument("--sweep", action="store_true", help="also time 1 / 4 / 16 tokens (extra keys, not the headline)")
     return p.parse_args()
@@ -242,7 +242,7 @@ def run_b200(args):
         for _ in range(max(args.warmup, 3)):
             step()
         stream.synchronize()
-        if args.graph and (world == 1 or args.graph > 1):
+        if args.graph and world == 1:      # the expert-parallel step (NCCL collectives between kernels) is launched directly
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 step()

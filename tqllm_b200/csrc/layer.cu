@@ -52,10 +52,10 @@ int iq3s_path(uint32_t type, int k, int dtype, int nmat) {
 //   PATH_DECODE  the IQ3_S decode kernels: every expert sees a few tokens, the product is bound by streaming the weights;
 //   PATH_GEMM    the tcgen05 grouped GEMM (all formats): the weights of an expert are decoded once per 128 tokens;
 //   PATH_GENERIC exact fp32 CUDA-core path: every shape, the floor under the other two.
-// Default: IQ3_S takes the decode kernels while the batch averages fewer than GEMM_MIN_PER assignments per expert, everything
-// else the GEMM. B2MOE_EXPERT_PATH=generic|decode|gemm forces a family where it supports the shape.
+// Default: IQ3_S takes the decode kernels while the batch averages fewer than GEMM_MIN_PER assignments per expert or the bank
+// has fewer than GEMM_MIN_EXPERTS experts (too few 128-row x 128-token items to fill the SMs), everything else the GEMM. B2MOE_EXPERT_PATH=generic|decode|gemm forces a family where it supports the shape.
 enum { PATH_GENERIC = 0, PATH_DECODE = 1, PATH_GEMM = 3 };
-constexpr int GEMM_MIN_PER = 32;
+constexpr int GEMM_MIN_PER = 32, GEMM_MIN_EXPERTS = 128;   // measured on the c2 shape: below either, the decode kernels' finer work items win
 int expert_path(uint32_t type, int k, int dtype, int nmat, int experts, long long assignments) {
     const char * v = std::getenv("B2MOE_EXPERT_PATH");
     const char f = v ? v[0] : 'a';
@@ -63,7 +63,7 @@ int expert_path(uint32_t type, int k, int dtype, int nmat, int experts, long lon
     const bool dec = iq3s_path(type, k, dtype, nmat) > 0, gemm = gemm_tc_supported(type, k, nmat, experts);
     if (f == 'd') return dec ? PATH_DECODE : PATH_GENERIC;
     if (f == 'g') return gemm ? PATH_GEMM : dec ? PATH_DECODE : PATH_GENERIC;
-    if (dec && (!gemm || assignments < (long long)GEMM_MIN_PER * experts)) return PATH_DECODE;
+    if (dec && (!gemm || assignments < (long long)GEMM_MIN_PER * experts || experts < GEMM_MIN_EXPERTS)) return PATH_DECODE;
     return gemm ? PATH_GEMM : PATH_GENERIC;
 }
 }  // namespace
