@@ -42,19 +42,22 @@ def parse():
     p.add_argument("--steps", type=int, default=50)
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--impl", default="b200", choices=("b200", "reference"))
-    p.add_argument("--tokens", type=int, default=TOKENS)
-    p.add_argument("--layers", type=int, default=LAYERS)
+    p.add_argument("--workload", default="c2", choices=("c1", "c2", "c3", "c4", "c5"),
+                   help="layer shape (tqllm_b200.synth.CONFIGS); c2 is the headline workload, the others are for profiling")
+    p.add_argument("--tokens", type=int, default=0, help="tokens per step per GPU (default: 64; 4096 / 2048 / 8192 for c3 / c4 / c5)")
+    p.add_argument("--layers", type=int, default=0, help="stacked layers per step (default: 4 for c2, else 1)")
     p.add_argument("--graph", type=int, default=1, help="single GPU: replay the step as a CUDA graph (1) or launch it directly (0)")
     p.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     p.add_argument("--sweep", action="store_true", help="also time 1 / 4 / 16 tokens (extra keys, not the headline)")
     return p.parse_args()
 
 
-def peaks():
+def peaks(key="hbm_gbs"):
+    """the roofline denominator: the pool's measured copy bandwidth (GB/s) or burst bf16 GEMM rate (TFLOP/s), else the stated fallback"""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.isfile(path):
-        return float(json.load(open(path))["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return float(json.load(open(path))[key]), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}[key], "fallback"
 
 
 class ClockSampler:
@@ -95,12 +98,25 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": mx, "reasons": reasons, "samples": len(sm)}
 
 
-def workload_name(tokens, layers):
-    return f"c2 flash-next decode: H2048 E512 top10+1 shared F512 IQ3_S, {tokens} tokens x {layers} stacked layers"
+FMT_NAMES = {12: "Q4_K", 20: "IQ4_NL", 21: "IQ3_S", 23: "IQ4_XS", 323: "NVFP4G"}
+
+
+def workload_name(shape, tokens, layers):
+    fm = "+".join(dict.fromkeys(FMT_NAMES[t] for t in shape.types))
+    kind = {"c2": "c2 flash-next decode", "c1": "c1 small", "c3": "c3 flash-next prefill", "c4": "c4 minimax", "c5": "c5 prefill"}[shape.name[:2]]
+    return (f"{kind}: H{shape.hidden} E{shape.experts} top{shape.topk}{'+1 shared' if shape.shared else ''} F{shape.ff} {fm}, "
+            f"{tokens} tokens x {layers} stacked layers")
+
+
+def defaults(args):
+    if not args.tokens:
+        args.tokens = {"c3": 4096, "c4": 2048, "c5": 8192}.get(args.workload, TOKENS)
+    if not args.layers:
+        args.layers = LAYERS if args.workload == "c2" else 1
 
 
 def make_layers(synth, shape, layers, device, experts=None):
-    scale = synth.solve_router_scale(shape, 0.6)
+    scale = synth.solve_router_scale(shape, 0.6) if shape.name.startswith("c2") else 1.0      # c2: top-10 mass about 0.6
     return [synth.make_layer(shape, SEED + 17 * l, device, experts=experts, router_scale=scale) for l in range(layers)], scale
 
 
@@ -137,7 +153,7 @@ def run_reference(args):
     import torch
 
     from tqllm_b200 import synth
-    shape = synth.CONFIGS["c2"]
+    shape = synth.CONFIGS[args.workload]
     threads = os.cpu_count() or 1
     layers, rscale = make_layers(synth, shape, 1, "cpu")
     x = synth.make_tokens(shape, args.tokens, SEED, "cpu")
@@ -154,7 +170,7 @@ def run_reference(args):
     print(json.dumps({
         "metric": METRIC, "value": v, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1),
         "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(args.tokens, args.layers), "sample": "one layer per step", "router_scale": rscale},
+        "config": {"workload": workload_name(shape, args.tokens, args.layers), "sample": "one layer per step", "router_scale": rscale},
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": kind,
                          "sample": f"1 of {args.layers} layers, {args.tokens} tokens, {steps} steps"},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -177,8 +193,10 @@ def run_b200(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    shape = synth.CONFIGS["c2"]
+    shape = synth.CONFIGS[args.workload]
     T, L = args.tokens, args.layers
+    if world > 1 and args.workload != "c2":
+        raise SystemExit("bench.py: the expert-parallel arm runs the c2 workload")
     router_all = None
     if world > 1:
         # expert parallel: every rank draws the same layer (same seed), keeps the banks of its own expert block only
@@ -200,7 +218,7 @@ def run_b200(args):
     else:
         synth_layers, rscale = make_layers(synth, shape, L, dev)
         layers = [moe.MoeLayer.from_synth(sl, device=dev) for sl in synth_layers]
-    host_layer0 = synth_layers[0] if rank == 0 and not args.no_cpu and world == 1 else None
+    host_layer0 = synth_layers[0] if rank == 0 and not args.no_cpu and world == 1 and args.workload == "c2" else None
     if host_layer0 is not None:      # keep only the first layer's raw blocks (for the CPU baseline), on the host
         host_layer0 = synth.Layer(shape, host_layer0.router_w.cpu(), None, tuple(t.cpu() for t in host_layer0.raw),
                                   tuple(t.cpu() for t in host_layer0.shared_raw))
@@ -276,21 +294,27 @@ def run_b200(args):
             # dominant kernel, timed alone with events on the launching stream: the grouped gate/up + SwiGLU product
             art = [lay.artefacts() for lay in layers]
             plans, ids = [], []
+            ST = T if shape.shared else 0                         # rows of the always-on shared expert
             for lay in layers:
                 lg = moe.router(lay.router_w, x)
-                i, w, _ = moe.topk_softmax(lg, lay.experts, shape.topk, shape.scale)
-                plans.append(moe.dispatch(i, lay.experts, T))
-            act = torch.zeros(T * shape.topk + T, shape.ff, dtype=torch.float32, device=dev)
+                if shape.gating == 1:
+                    i, w, _ = moe.topk_softmax(lg, lay.experts, shape.topk, shape.scale)
+                else:
+                    i, w = moe.route_sigmoid(lg, lay.experts, shape.topk, lay.sel_bias, shape.norm, shape.scale)
+                plans.append(moe.dispatch(i, lay.experts, ST))
+            act = torch.zeros(T * shape.topk + ST, shape.ff, dtype=torch.float32, device=dev)
+            XDT = {torch.bfloat16: 2, torch.float16: 1, torch.float32: 0}[x.dtype]
+            shp = lambda lay, i: C.byref(lay.sh[i].c) if shape.shared else None
             import ctypes as C
             from tqllm_b200.capi import lib, BF16
 
-            wsb = lib.b2moe_expert_workspace_bytes(shape.types[0], T, shape.hidden, BF16)
+            wsb = lib.b2moe_expert_workspace_bytes(shape.types[0], T, shape.hidden, XDT)
             ews = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
 
             def gateup(l):
                 lay = layers[l]
-                return lib.b2moe_expert_gateup_swiglu(C.byref(lay.gate.c), C.byref(lay.up.c), C.byref(lay.sh[0].c), C.byref(lay.sh[1].c),
-                                                      x.data_ptr(), BF16, plans[l].buf.data_ptr(), T, shape.topk, T, act.data_ptr(),
+                return lib.b2moe_expert_gateup_swiglu(C.byref(lay.gate.c), C.byref(lay.up.c), shp(lay, 0), shp(lay, 1),
+                                                      x.data_ptr(), XDT, plans[l].buf.data_ptr(), T, shape.topk, ST, act.data_ptr(),
                                                       ews.data_ptr(), ews.numel(), stream.cuda_stream)
             for l in range(L):
                 assert gateup(l) == 0
@@ -316,22 +340,26 @@ def run_b200(args):
             logits = torch.zeros(T, shape.experts + 1, dtype=torch.float32, device=dev)
             idb = torch.zeros(T, shape.topk, dtype=torch.int32, device=dev)
             wts = torch.zeros(T, shape.topk, dtype=torch.float32, device=dev)
-            yb = torch.zeros(A + T, shape.hidden, dtype=torch.float32, device=dev)
+            yb = torch.zeros(A + ST, shape.hidden, dtype=torch.float32, device=dev)
             ob = torch.zeros(T, shape.hidden, dtype=torch.bfloat16, device=dev)
-            dws = torch.empty(max(lib.b2moe_expert_workspace_bytes(shape.types[2], A + T, shape.ff, F32), 16), dtype=torch.uint8, device=dev)
-            plan2 = moe.Plan(shape.experts, T, shape.topk, T, dev)
+            dws = torch.empty(max(lib.b2moe_expert_workspace_bytes(shape.types[2], A + ST, shape.ff, F32), 16), dtype=torch.uint8, device=dev)
+            plan2 = moe.Plan(shape.experts, T, shape.topk, ST, dev)
+            dsw = torch.empty(max(lib.b2moe_dispatch_workspace_bytes(shape.experts, A), 16), dtype=torch.uint8, device=dev)
+            bias = lambda l: None if layers[l].sel_bias is None else layers[l].sel_bias.data_ptr()
             stage_us = {
-                "router": time_stage(lambda l: lib.b2moe_router(layers[l].router_w.data_ptr(), None, x.data_ptr(), BF16, logits.data_ptr(),
+                "router": time_stage(lambda l: lib.b2moe_router(layers[l].router_w.data_ptr(), None, x.data_ptr(), XDT, logits.data_ptr(),
                                                                 shape.experts + 1, shape.hidden, shape.experts, T, st)),
-                "topk": time_stage(lambda l: lib.b2moe_topk_softmax(logits.data_ptr(), shape.experts + 1, idb.data_ptr(), wts.data_ptr(), None,
-                                                                    shape.experts, shape.topk, T, shape.scale, st)),
-                "dispatch": time_stage(lambda l: lib.b2moe_dispatch(idb.data_ptr(), T, shape.topk, shape.experts, T, plan2.buf.data_ptr(),
-                                                                    None, 0, st)),
+                "topk": time_stage((lambda l: lib.b2moe_topk_softmax(logits.data_ptr(), shape.experts + 1, idb.data_ptr(), wts.data_ptr(), None,
+                                                                     shape.experts, shape.topk, T, shape.scale, st)) if shape.gating == 1 else
+                                   (lambda l: lib.b2moe_route_sigmoid(logits.data_ptr(), shape.experts + 1, bias(l), idb.data_ptr(), wts.data_ptr(),
+                                                                      shape.experts, shape.topk, int(shape.norm), shape.scale, T, st))),
+                "dispatch": time_stage(lambda l: lib.b2moe_dispatch(idb.data_ptr(), T, shape.topk, shape.experts, ST, plan2.buf.data_ptr(),
+                                                                    dsw.data_ptr(), dsw.numel(), st)),
                 "gateup_swiglu": k_ms * 1e3,
-                "down": time_stage(lambda l: lib.b2moe_expert_down(C.byref(layers[l].down.c), C.byref(layers[l].sh[2].c), act.data_ptr(),
-                                                                   plans[l].buf.data_ptr(), T, shape.topk, T, yb.data_ptr(), dws.data_ptr(),
+                "down": time_stage(lambda l: lib.b2moe_expert_down(C.byref(layers[l].down.c), shp(layers[l], 2), act.data_ptr(),
+                                                                   plans[l].buf.data_ptr(), T, shape.topk, ST, yb.data_ptr(), dws.data_ptr(),
                                                                    dws.numel(), st)),
-                "combine": time_stage(lambda l: lib.b2moe_combine(yb.data_ptr(), None, wts.data_ptr(), None, T, shape.topk, shape.hidden, T,
+                "combine": time_stage(lambda l: lib.b2moe_combine(yb.data_ptr(), None, wts.data_ptr(), None, T, shape.topk, shape.hidden, ST,
                                                                   ob.data_ptr(), BF16, st)),
             }
         else:
@@ -340,11 +368,16 @@ def run_b200(args):
             n_active_rank = sum(int(e.buf["plan"][0]) for e in eps) / L      # this rank's active experts per layer (with the shared one)
     gu_bytes = 2 * synth.raw_bytes(shape.types[0], shape.ff, shape.hidden)
     peak, peak_kind = peaks()
+    bound, roof_unit = "hbm", "GB/s"
     if world == 1:
         n_active = sum(p.n_active for p in plans) / L            # includes the shared expert
         achieved = n_active * gu_bytes / (k_ms * 1e-3) / 1e9
         weight_bytes_step = sum(p.n_active for p in plans) * shape.expert_bytes()
         roof_kernel = "grouped gate/up + SwiGLU"
+        if T * shape.topk >= 128 * shape.experts:                # >= 128 tokens per expert: the tensor cores bound the product
+            bound, roof_unit = "tensor", "TFLOP/s"
+            achieved = 4.0 * shape.hidden * shape.ff * (T * shape.topk + (T if shape.shared else 0)) / (k_ms * 1e-3) / 1e12
+            peak, peak_kind = peaks("bf16_tflops")
     else:
         # per-GPU view: the whole layer (exchanges included) against this GPU's HBM: expert bytes it streamed / step time
         n_active = n_active_rank
@@ -365,7 +398,7 @@ def run_b200(args):
         print(json.dumps({
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": workload_name(T, L), "tokens": T, "layers": L, "router_scale": rscale,
+            "config": {"workload": workload_name(shape, T, L), "tokens": T, "layers": L, "router_scale": rscale,
                        "parallelism": "single GPU" if world == 1 else f"ep{world}: {shape.experts // world} experts per GPU, {T} tokens per GPU, "
                                       "NCCL all-gather dispatch + all-to-all combine",
                        "l2": "per-step expert weights (GBs) exceed the 126 MB L2; no flush needed", "cuda_graph": graph is not None,
@@ -373,7 +406,7 @@ def run_b200(args):
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": x_host.numel() * 2,
                     "d2h_bytes_per_step": out_host.numel() * 2},
             "gpu_launches": args.steps * L * (7 if world == 1 else 9),
-            "roofline": {"bound": "hbm", "kernel": roof_kernel, "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "roofline": {"bound": bound, "kernel": roof_kernel, "achieved": achieved, "peak": peak, "unit": roof_unit,
                          "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None, "kernel_ms": k_ms,
                          "active_experts_per_launch": n_active, "bytes_per_expert": gu_bytes},
             "expert_weight_gbs": weight_bytes_step / (ms_step * 1e-3) / 1e9,
@@ -386,4 +419,5 @@ def run_b200(args):
 
 if __name__ == "__main__":
     a = parse()
+    defaults(a)
     run_reference(a) if a.impl == "reference" else run_b200(a)
