@@ -85,3 +85,33 @@ def test_gemm_layer_against_oracle(orc, types):
     with forced_path("gemm"):
         err = run_case(orc, shape, 8, 160, 31)
     assert err <= TOL
+
+
+def test_full_size_c2_gemm_agrees_with_decode_kernels():
+    """benchmark shape (512 experts, hidden 2048, IQ3_S), 512 tokens: two independent tensor-core paths, same sums"""
+    from tqllm_b200 import moe
+    shape = synth.CONFIGS["c2"]
+    layer = synth.make_layer(shape, 5, "cuda")
+    dev = moe.MoeLayer.from_synth(layer)
+    x = synth.make_tokens(shape, 512, 6, "cuda")
+    outs = {}
+    for path in ("decode", "gemm"):
+        with forced_path(path):
+            outs[path] = dev.forward(x).float().cpu().numpy()
+        assert dev.artefacts()["status"] == 0          # no bounded wait ran out
+    assert rel_err(outs["gemm"], outs["decode"]) <= TOL
+    assert np.isfinite(outs["gemm"]).all()
+
+
+def test_token_order_does_not_change_a_token():
+    """c3 shape (NVFP4G, 512 experts), 640 tokens: reversing the batch reverses the outputs bit for bit — a token's sums
+    do not depend on its column in the MMA tile or on its neighbours"""
+    from tqllm_b200 import moe
+    shape = synth.CONFIGS["c3"]
+    layer = synth.make_layer(shape, 8, "cuda")
+    dev = moe.MoeLayer.from_synth(layer)
+    x = synth.make_tokens(shape, 640, 9, "cuda")
+    with forced_path("gemm"):
+        a = dev.forward(x).float().cpu().numpy()
+        b = dev.forward(torch.flip(x, dims=(0,)).contiguous()).float().cpu().numpy()
+    assert np.array_equal(a.view(np.uint32), b[::-1].copy().view(np.uint32))

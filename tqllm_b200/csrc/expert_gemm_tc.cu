@@ -32,15 +32,8 @@ using namespace tc;
 constexpr int G_ROWS = 128;                 // weight rows per item = M
 constexpr int G_NT = 128;                   // tokens per item (N <= 128, a multiple of 16)
 constexpr int G_KS = 64;                    // columns per pipeline step (four MMAs of K = 16 per matrix)
-#ifndef DEC_BACKOFF
-#define DEC_BACKOFF 100
-#endif
-#ifndef B2_A_STAGES
-#define B2_A_STAGES 2
-#define B2_B_STAGES 4
-#define B2_B_LAG 2
-#endif
-constexpr int A_STAGES = B2_A_STAGES, B_STAGES = B2_B_STAGES, RAW_SLOTS = 2, B_LAG = B2_B_LAG;
+constexpr int A_STAGES = 2, B_STAGES = 4, RAW_SLOTS = 2, B_LAG = 2;
+constexpr uint32_t DEC_BACKOFF = 100;      // ns between tries of a decode warp's waits
 constexpr int A_LBO = gdec::A_LBO;          // bytes between k cores of A
 constexpr int A_MAT = 8 * A_LBO;            // one matrix of one A stage: 128 rows x 64 columns
 constexpr int B_LBO = G_NT * 16;            // bytes between k cores of B
@@ -335,7 +328,6 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
                     const uint32_t sa = gk % A_STAGES;
                     if (gk >= A_STAGES && !__all_sync(0xffffffffu, bar_wait(a_empty + 8 * sa, ((gk / A_STAGES) - 1) & 1u, DEC_BACKOFF))) { ok = false; break; }
                     GP_LAP(1);
-#ifndef B2_GEMM_SKIP_DECODE
                     if (live) {
 #pragma unroll
                         for (int m = 0; m < NMAT; ++m) {
@@ -349,7 +341,6 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
                             }
                         }
                     }
-#endif
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0) bar_arrive(a_full + 8 * sa);

@@ -169,3 +169,42 @@ class CudaEpLayer:
         self.capi.check(self.lib.b2moe_ep_reduce(recv.data_ptr(), G, None if shared is None else shared.data_ptr(), None, T, H,
                                                  out.data_ptr(), moe._DT[self.out_dtype], self._st()), "b2moe_ep_reduce")
         return out
+
+
+class GraphedEpForward:
+    """ep_forward for a CUDA backend with the three compute phases replayed as CUDA graphs (one launch each instead of
+    about ten) and the collectives issued between them in the ordinary way: no collective is ever captured. The input
+    tensor and every exchange buffer keep their addresses; `x_local` must be the same tensor at every call."""
+
+    def __init__(self, backend: CudaEpLayer, comm, x_local: torch.Tensor):
+        self.backend, self.comm, self.x = backend, comm, x_local
+        G, T = comm.world, x_local.shape[0]
+        dev = x_local.device
+        stream = torch.cuda.current_stream()
+        # eager pass: allocates the backend's buffers and gives the exchange buffers their shapes
+        ids, w = backend.route_local(x_local)
+        self.x_all = torch.empty((G * T,) + tuple(x_local.shape[1:]), dtype=x_local.dtype, device=dev)
+        self.ids_all = torch.empty((G * T, ids.shape[1]), dtype=ids.dtype, device=dev)
+        self.w_all = torch.empty((G * T, w.shape[1]), dtype=w.dtype, device=dev)
+        comm.all_gather(x_local, self.x_all); comm.all_gather(ids, self.ids_all); comm.all_gather(w, self.w_all)
+        parts, shared = backend.partial_sums(self.x_all, self.ids_all, self.w_all)
+        self.recv = torch.empty((G, T, parts.shape[1]), dtype=parts.dtype, device=dev)
+        comm.all_to_all(parts.view(G, T, -1), self.recv)
+        backend.finish(self.recv, shared)
+        stream.synchronize()
+        self.g_route, self.g_part, self.g_fin = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.g_route, stream=stream):
+            self.ids, self.w = backend.route_local(x_local)
+        with torch.cuda.graph(self.g_part, stream=stream):
+            self.parts, self.shared = backend.partial_sums(self.x_all, self.ids_all, self.w_all)
+        with torch.cuda.graph(self.g_fin, stream=stream):
+            self.out = backend.finish(self.recv, self.shared)
+
+    def __call__(self) -> torch.Tensor:
+        c = self.comm
+        self.g_route.replay()
+        c.all_gather(self.x, self.x_all); c.all_gather(self.ids, self.ids_all); c.all_gather(self.w, self.w_all)
+        self.g_part.replay()
+        c.all_to_all(self.parts.view(c.world, self.x.shape[0], -1), self.recv)
+        self.g_fin.replay()
+        return self.out
