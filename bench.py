@@ -394,6 +394,12 @@ def run_b200(args):
         roof_kernel = "whole expert-parallel layer on rank 0 (dispatch + combine exchanges included)"
     value = world * T * L / (ms_step * 1e-3)
     e2e = world * T * L / (ms_e2e * 1e-3)
+    # DRAM bytes per launch of the dominant kernel: one ncu capture of the c2 gate/up kernel (profiles/iq3s_grouped_decode_c2_t64.md:
+    # 317.7 MB read + 1.4 MB written with 353 experts active) scaled by the experts this launch touched; traffic grows with them
+    traffic, traffic_src = None, None
+    if world == 1 and args.workload == "c2" and T * shape.topk < 32 * shape.experts:
+        traffic = (317.7e6 + 1.4e6) / 353.0 * n_active
+        traffic_src = "ncu dram__bytes_read+write of one capture, scaled by active experts (profiles/iq3s_grouped_decode_c2_t64.md)"
 
     cpu = None
     if host_layer0 is not None:
@@ -414,7 +420,8 @@ def run_b200(args):
                     "d2h_bytes_per_step": out_host.numel() * 2},
             "gpu_launches": args.steps * L * (7 if world == 1 else 9),
             "roofline": {"bound": bound, "kernel": roof_kernel, "achieved": achieved, "peak": peak, "unit": roof_unit,
-                         "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None, "kernel_ms": k_ms,
+                         "frac": achieved / peak, "peak_kind": peak_kind, "traffic": traffic, "traffic_source": traffic_src,
+                         "kernel_ms": k_ms,
                          "active_experts_per_launch": n_active, "bytes_per_expert": gu_bytes},
             "expert_weight_gbs": weight_bytes_step / (ms_step * 1e-3) / 1e9,
             "expert_weight_frac_of_8tbs": weight_bytes_step / (ms_step * 1e-3) / 8e12,

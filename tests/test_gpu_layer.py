@@ -134,11 +134,13 @@ def test_errors_reach_the_caller():
         moe.DeviceBank(12, torch.zeros(10, dtype=torch.uint8, device="cuda"), 1, 16, 256)
 
 
+@pytest.mark.parametrize("kernel", ("mma", "tc"))
 @pytest.mark.parametrize("act_dtype,experts,tokens,topk", (("f32", 4, 40, 2), ("bf16", 4, 70, 3), ("bf16", 24, 3, 8), ("f32", 16, 1, 4)))
-def test_iq3s_tensor_core_path(orc, act_dtype, experts, tokens, topk, monkeypatch):
+def test_iq3s_tensor_core_path(orc, act_dtype, experts, tokens, topk, kernel, monkeypatch):
     """the IQ3_S decode kernels (pinned: batches this dense default to the grouped GEMM): fp32 and bf16 activations (4- and
     2-term splits), experts holding many more tokens than one pass takes, experts holding one token, a shared expert"""
     monkeypatch.setenv("B2MOE_EXPERT_PATH", "decode")
+    monkeypatch.setenv("B2MOE_IQ3S_PATH", kernel)          # mma.sync kernels (the default) / their tcgen05 variant
     shape = synth.LayerShape("iq3s-mma", 512, experts, topk, 256, shared=True, types=(21, 21, 21), act_dtype=act_dtype)
     err = run_case(orc, shape, experts, tokens, 4242 + tokens)
     assert err < 2e-3

@@ -50,7 +50,7 @@ __global__ void router_k(const float * __restrict__ w, const float * __restrict_
 // is: every product is exact in fp32 and the sums are fp32, so the result is fp32-accurate (within 3e-6 of an fp64
 // dot) at a fraction of the instructions of the scalar loop. One block = 16 router rows x 64 tokens; its 8 warps
 // split the hidden dimension and add their partial tiles in shared memory in warp order.
-constexpr int RM_WARPS = 8;
+constexpr int RM_WARPS = 16, RM_PART = 8;   // warps per block (each takes a slice of the columns); partial-sum slots in shared memory
 __device__ __forceinline__ void split3(float2 w, uint32_t & hi, uint32_t & mid, uint32_t & lo) {
     const __nv_bfloat16 h0 = __float2bfloat16_rn(w.x), h1 = __float2bfloat16_rn(w.y);
     const float r0 = w.x - __bfloat162float(h0), r1 = w.y - __bfloat162float(h1);
@@ -67,7 +67,7 @@ __device__ __forceinline__ void mma_bf16_acc(float (&c)[4], const uint32_t (&a)[
 __global__ void __launch_bounds__(RM_WARPS * 32) router_mma_k(const float * __restrict__ w, const float * __restrict__ shared,
                                                                 const __nv_bfloat16 * __restrict__ x, float * __restrict__ logits, int ld,
                                                                 int h, int e, int rows, int n) {
-    __shared__ float part[RM_WARPS][16][65];
+    __shared__ float part[RM_PART][16][65];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int r0 = blockIdx.x * 16, t0 = blockIdx.y * 64;
     const int ra = min(r0 + g, rows - 1), rb = min(r0 + g + 8, rows - 1);
@@ -96,10 +96,21 @@ __global__ void __launch_bounds__(RM_WARPS * 32) router_mma_k(const float * __re
             mma_bf16_acc(acc[j], hi, b0, b1);
         }
     }
+    // warps 8..15 park their sums, warps 0..7 add theirs on top (always in this order: the same bits every run)
+    if (warp >= RM_PART) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        part[warp][g][8 * j + 2 * t] = acc[j][0]; part[warp][g][8 * j + 2 * t + 1] = acc[j][1];
-        part[warp][g + 8][8 * j + 2 * t] = acc[j][2]; part[warp][g + 8][8 * j + 2 * t + 1] = acc[j][3];
+        for (int j = 0; j < 8; ++j) {
+            part[warp - RM_PART][g][8 * j + 2 * t] = acc[j][0]; part[warp - RM_PART][g][8 * j + 2 * t + 1] = acc[j][1];
+            part[warp - RM_PART][g + 8][8 * j + 2 * t] = acc[j][2]; part[warp - RM_PART][g + 8][8 * j + 2 * t + 1] = acc[j][3];
+        }
+    }
+    __syncthreads();
+    if (warp < RM_PART) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            part[warp][g][8 * j + 2 * t] += acc[j][0]; part[warp][g][8 * j + 2 * t + 1] += acc[j][1];
+            part[warp][g + 8][8 * j + 2 * t] += acc[j][2]; part[warp][g + 8][8 * j + 2 * t + 1] += acc[j][3];
+        }
     }
     __syncthreads();
     for (int i = threadIdx.x; i < 16 * 64; i += blockDim.x) {
@@ -107,7 +118,7 @@ __global__ void __launch_bounds__(RM_WARPS * 32) router_mma_k(const float * __re
         if (r0 + r < rows && t0 + c < n) {
             float s = 0.f;
 #pragma unroll
-            for (int q = 0; q < RM_WARPS; ++q) s += part[q][r][c];
+            for (int q = 0; q < RM_PART; ++q) s += part[q][r][c];
             logits[size_t(t0 + c) * ld + r0 + r] = s;
         }
     }
