@@ -70,3 +70,40 @@ def test_uneven_blocks_and_idle_rank(monkeypatch):
     shape = synth.LayerShape("ep-idle", 512, 16, 1, 256, types=(21, 21, 21))
     got, want = run_split(shape, 16, 1, 4, 10)          # one token, one expert: three ranks have nothing to do
     assert rel_err(got, want) <= 1e-5
+
+
+class OneRankComm:
+    """world of one: the exchanges are copies (the graphed forward must give the bits of the direct one)"""
+    world, rank = 1, 0
+
+    def all_gather(self, t, out=None):
+        if out is None:
+            return t.clone()
+        out.copy_(t)
+        return out
+
+    def all_to_all(self, t, out=None):
+        if out is None:
+            return t.clone()
+        out.copy_(t)
+        return out
+
+
+def test_graphed_compute_phases_equal_direct_launches():
+    from tqllm_b200 import ep, moe
+    shape = synth.LayerShape("ep-graph", 512, 16, 4, 256, shared=True, types=(21, 21, 21))
+    layer, x = layer_inputs(shape, 16, 24, 3)
+    loc = moe.MoeLayer.from_synth(layer, experts=16)
+    rk = ep.CudaEpLayer(loc, layer.router_w.cuda(), 16, 1, 0, out_dtype=torch.float32)
+    comm = OneRankComm()
+    xd = x.cuda()
+    want = ep.ep_forward(rk, comm, xd).clone()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        gf = ep.GraphedEpForward(rk, comm, xd)
+        got1 = gf().clone()
+        xd.copy_(torch.flip(xd, dims=(0,)))              # new contents at the same address
+        got2 = gf().clone()
+    side.synchronize()
+    assert torch.equal(got1, want)
+    assert torch.equal(got2, torch.flip(want, dims=(0,)))

@@ -33,7 +33,7 @@ constexpr int G_ROWS = 128;                 // weight rows per item = M
 constexpr int G_NT = 128;                   // tokens per item (N <= 128, a multiple of 16)
 constexpr int G_KS = 64;                    // columns per pipeline step (four MMAs of K = 16 per matrix)
 constexpr int A_STAGES = 2, B_STAGES = 4, RAW_SLOTS = 2, B_LAG = 2;
-constexpr uint32_t DEC_BACKOFF = 100;      // ns between tries of a decode warp's waits
+constexpr uint32_t DEC_BACKOFF = 60;       // ns between tries of a decode warp's waits
 constexpr int A_LBO = gdec::A_LBO;          // bytes between k cores of A
 constexpr int A_MAT = 8 * A_LBO;            // one matrix of one A stage: 128 rows x 64 columns
 constexpr int B_LBO = G_NT * 16;            // bytes between k cores of B
@@ -176,9 +176,9 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
                 GP_LAP(0);
                 for (int ks = 0; ks < ksteps && !*abort_flag; ++ks, ++gk) {
                     const uint32_t sa = gk % A_STAGES, sb = gk % B_STAGES;
-                    if (!bar_wait(a_full + 8 * sa, (gk / A_STAGES) & 1u, 32)) { give_up(); break; }
+                    if (!bar_wait(a_full + 8 * sa, (gk / A_STAGES) & 1u, 40)) { give_up(); break; }
                     GP_LAP(1);
-                    if (!bar_wait(b_full + 8 * sb, (gk / B_STAGES) & 1u, 32)) { give_up(); break; }
+                    if (!bar_wait(b_full + 8 * sb, (gk / B_STAGES) & 1u, 40)) { give_up(); break; }
                     GP_LAP(2);
                     fence_after();
                     const uint32_t a_lo = a_lo0 + sa * uint32_t((NMAT * A_MAT) >> 4), b_lo = b_lo0 + sb * uint32_t(B_STAGE >> 4);
@@ -206,7 +206,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
         for (int it = blockIdx.x; it < n_items && !*abort_flag; it += gridDim.x, ++ic) {
             const Item im = locate(it);
             const uint32_t ab = ic & 1u;
-            if (!__all_sync(0xffffffffu, bar_wait(acc_full + 8 * ab, (ic >> 1) & 1u, 400))) { if (lane == 0) give_up(); break; }
+            if (!__all_sync(0xffffffffu, bar_wait(acc_full + 8 * ab, (ic >> 1) & 1u, 1000))) { if (lane == 0) give_up(); break; }
             fence_after();
             const int row = im.rb * G_ROWS + 32 * q + lane;
             float rs[NMAT];                                            // fp32 row scales of the bank (NVFP4G), else 1
@@ -266,7 +266,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
             const uint32_t dst0 = saddr(b_st) + (n >> 3) * 128 + (n & 7) * 16;
             for (int ks = 0; ks < ksteps; ++ks, ++gk) {
                 const uint32_t sb = gk % B_STAGES;
-                if (gk >= B_STAGES && !__all_sync(0xffffffffu, bar_wait(b_empty + 8 * sb, ((gk / B_STAGES) - 1) & 1u, 100))) { ok = false; break; }
+                if (gk >= B_STAGES && !__all_sync(0xffffffffu, bar_wait(b_empty + 8 * sb, ((gk / B_STAGES) - 1) & 1u, 200))) { ok = false; break; }
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     if (n + 64 * h < npad) {

@@ -19,15 +19,25 @@ __device__ __forceinline__ void bar_arrive(uint32_t bar) {
 __device__ __forceinline__ void bar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// one phase of a barrier, with the hardware's suspending try_wait; between tries the thread sleeps `backoff_ns` (0 = retry at
-// once: for waits on the critical path), so that waiting warps leave the issue slots to the working ones; false = gave up
+// One phase of a barrier; false = gave up after WAIT_LIMIT tries.
+// backoff_ns = 0: the hardware's suspending try_wait (fast wake-up, for the waits on the critical path). The compiler
+// expands it into a polling loop, which takes issue slots and the integer pipe from the warps that work; so a wait
+// that is expected to last (an epilogue waiting for a whole item, a loader waiting for a free stage) passes a back-off
+// and polls with test_wait + nanosleep instead.
 __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, uint32_t backoff_ns = 0) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    const uint32_t limit = (backoff_ns && backoff_ns < 500) ? WAIT_LIMIT * 8 : WAIT_LIMIT;   // about a quarter of a second either way
+    for (uint32_t i = 0; i < limit; ++i) {
         uint32_t ok;
-        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
-                     : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
-        if (ok) return true;
-        if (backoff_ns) __nanosleep(backoff_ns);
+        if (backoff_ns) {
+            asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+            if (ok) return true;
+            __nanosleep(backoff_ns);
+        } else {
+            asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
+                         : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
+            if (ok) return true;
+        }
     }
     return false;
 }
