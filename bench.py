@@ -46,8 +46,8 @@ def parse():
                    help="layer shape (tqllm_b200.synth.CONFIGS); c2 is the headline workload, the others are for profiling")
     p.add_argument("--tokens", type=int, default=0, help="tokens per step per GPU (default: 64; 4096 / 2048 / 8192 for c3 / c4 / c5)")
     p.add_argument("--layers", type=int, default=0, help="stacked layers per step (default: 4 for c2, else 1)")
-    p.add_argument("--graph", type=int, default=1, help="single GPU: replay the step as a CUDA graph (1) or launch it directly (0); expert parallel: 2 replays the compute "
-                        "phases between directly issued collectives as graphs")
+    p.add_argument("--graph", type=int, default=1, help="1: replay the step as a CUDA graph (expert parallel: the compute phases only, the collectives between them are "
+                        "issued directly); 0: launch everything directly")
     p.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     p.add_argument("--sweep", action="store_true", help="also time 1 / 4 / 16 tokens (extra keys, not the headline)")
     return p.parse_args()
@@ -266,7 +266,7 @@ def run_b200(args):
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 step()
-        elif args.graph > 1:               # expert parallel, --graph 2: only the compute phases are captured, no collective is
+        elif args.graph:                   # expert parallel: only the compute phases are captured, no collective is
             graphed = [ep.GraphedEpForward(e, comm, x) for e in eps]
 
             def step():
@@ -415,7 +415,7 @@ def run_b200(args):
             "config": {"workload": workload_name(shape, T, L), "tokens": T, "layers": L, "router_scale": rscale,
                        "parallelism": "single GPU" if world == 1 else f"ep{world}: {shape.experts // world} experts per GPU, {T} tokens per GPU, "
                                       "NCCL all-gather dispatch + all-to-all combine",
-                       "l2": "per-step expert weights (GBs) exceed the 126 MB L2; no flush needed", "cuda_graph": (graph is not None) or ("compute phases only" if world > 1 and args.graph > 1 else False),
+                       "l2": "per-step expert weights (GBs) exceed the 126 MB L2; no flush needed", "cuda_graph": (graph is not None) or ("compute phases only" if world > 1 and args.graph else False),
                        "activations": "bf16 in, bf16 out, fp32 intermediates"},
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": x_host.numel() * 2,
                     "d2h_bytes_per_step": out_host.numel() * 2},
