@@ -4,12 +4,14 @@
 // (src/experts/moe.cu:188-195).
 //
 // Every expert's weights are read once per pass of up to 8 of its tokens. The arithmetic runs on the tensor cores
-// (mma.m16n8k16, bf16 x bf16 -> fp32) without losing anything:
+// (mma.m16n8k16 -> fp32):
 //   * an IQ3_S weight is  d * (1 + 2 s) * (+-m)  with m an odd magnitude 1..15 from the 512-entry grid; +-m is exact
-//     in bf16, so a grid entry re-encoded as four bf16 IS two A-fragment registers, fetched with one 8-byte
-//     shared-memory load, and its signs are one shift + one xor per register (bank layout, formats.cuh);
-//   * bf16 activations are the B fragment as they are; fp32 / fp16 activations are split into two bf16 terms
-//     hi + lo (16 significant bits) that sit in adjacent columns and are added after the loop;
+//     in bf16 and in fp16, so a grid entry re-encoded as four 16-bit floats IS two A-fragment registers, fetched with
+//     one 8-byte shared-memory load, and its signs are one shift + one xor per register (bank layout, formats.cuh);
+//   * bf16 activations are the B fragment as they are (bf16 x bf16, nothing lost); fp32 / fp16 activations (the down
+//     product's inputs among them) become one fp16 term per value after a per-row power-of-two scale (fp16 x fp16,
+//     relative rounding 2^-12 per activation: 1e-4 of the output RMS; two bf16 terms were exact to 2^-17 but doubled
+//     the MMAs, the scaling FMAs and the activation loads of the down product);
 //   * the two MMAs of one 32-weight sub-block start from zero and their fp32 result is scaled by that sub-block's
 //     d (1 + 2 s) with one FFMA per accumulator: sums stay fp32, as in the host reference (src/experts/moe.cpp:115-155).
 // Lane L = 4 g + t of a warp owns rows g, g + 8 of a 16-row tile and grid entries 2t, 2t + 1 of every sub-block,
@@ -27,16 +29,20 @@ constexpr int XPAD = 64;             // bytes added to an activation row in shar
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 // ---------------------------------------------------------------------------------------------------------------
-// fp32 / fp16 rows [R][K] -> two bf16 terms [R][2][K]: hi = bf16(x), lo = bf16(x - hi)
-// ---------------------------------------------------------------------------------------------------------------
-__global__ void act_split_k(const void * __restrict__ x, int dtype, size_t total, int k, __nv_bfloat16 * __restrict__ terms) {
-    const size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= total) return;
-    const size_t row = i / k, col = i % k;
-    const float v = load_act(x, dtype, i);
-    const __nv_bfloat16 hi = __float2bfloat16_rn(v);
-    terms[(row * 2) * k + col] = hi;
-    terms[(row * 2 + 1) * k + col] = __float2bfloat16_rn(v - __bfloat162float(hi));
+// fp32 / fp16 rows [R][K] -> one fp16 term [R][K], the row multiplied by 2^e so that its largest magnitude lies in
+// [2^14, 2^15) (relative rounding error 2^-12 per element, no overflow whatever the input range), + 2^-e per row.
+// One warp per row.
+__global__ void act_f16_k(const void * __restrict__ x, int dtype, int rows, int k, __half * __restrict__ out, float * __restrict__ inv_scale) {
+    const int lane = threadIdx.x & 31, row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    float mx = 0.f;
+    for (int j = lane; j < k; j += 32) mx = fmaxf(mx, fabsf(load_act(x, dtype, size_t(row) * k + j)));
+    for (int d = 16; d; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+    int ex = int((__float_as_uint(mx) >> 23) & 255u) - 127;              // floor(log2(mx)) for a normal mx
+    ex = (mx > 0.f && mx < 3e38f) ? max(-100, min(100, ex)) : 14;
+    const float scale = __uint_as_float(uint32_t(127 + 14 - ex) << 23);  // 2^(14 - ex)
+    if (lane == 0) inv_scale[row] = __uint_as_float(uint32_t(127 - 14 + ex) << 23);
+    for (int j = lane; j < k; j += 32) out[size_t(row) * k + j] = __float2half_rn(load_act(x, dtype, size_t(row) * k + j) * scale);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -108,6 +114,16 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_f16_zero(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+                 : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
 __device__ __forceinline__ void mma_bf16_zero(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
                  : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
@@ -126,12 +142,14 @@ __device__ __forceinline__ void mma_bf16_zero(float (&c)[4], uint32_t a0, uint32
 // The grid sits in shared memory as bf16 quadruples, 16 copies, copy c in banks 2c, 2c + 1: the 16 lanes of a
 // half-warp (one wavefront of an 8-byte load) never collide.
 // MODE 0: out = act[a][row] = silu(gate . x) * (up . x);   MODE 1: out = y[a][row] = down . act[a]
-// NTERM 1: x is bf16 [rows_x][k]; NTERM 2: x is the two-term split [rows_x][2][k].
+// NTERM terms per activation value ([rows_x][NTERM][k]; the launchers use one). OP 0: bf16 operands (bf16 activations as
+// they are); OP 1: fp16 operands (fp32 / fp16 activations as one scaled fp16 term, the sums multiplied by the row's 2^-e).
 // ---------------------------------------------------------------------------------------------------------------
 struct Iq3sArgs {
     const uint8_t * w0, * w1, * s0, * s1;   // stacked banks (gate, up | down, -) and the shared expert's
     size_t bank_bytes;
-    const __nv_bfloat16 * x;
+    const __nv_bfloat16 * x;                 // 16-bit activation terms: bf16 (OP 0) or scaled fp16 (OP 1)
+    const float * inv_scale;                 // OP 1: 2^-e of every activation row
     int * plan;
     float * out;                             // [A + shared][rows]
     int rows, k_tiles, experts, topk, A, rpw, nbuf;
@@ -140,7 +158,7 @@ struct Iq3sArgs {
 constexpr size_t TABLE_BYTES = 512 * 16 * 8, RING_BYTES = size_t(CTA_WARPS) * STAGES * TILE, BAR_BYTES = (CTA_WARPS * STAGES + 2) * 8;
 inline size_t xs_bytes(int k, int nterm, int nbuf) { return size_t(nbuf) * 8 * nterm * (size_t(k) * 2 + XPAD); }
 
-template <int MODE, int NTERM>
+template <int MODE, int NTERM, int OP>
 __global__ void __launch_bounds__(CTA_WARPS * 32, 1) iq3s_grouped_k(Iq3sArgs p) {
     constexpr int NMAT = MODE == 0 ? 2 : 1, NCH = NTERM;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -162,7 +180,8 @@ __global__ void __launch_bounds__(CTA_WARPS * 32, 1) iq3s_grouped_k(Iq3sArgs p) 
         const uint32_t m = c_iq3s_grid[i];                        // four odd magnitudes 1..15 -> bf16 bits (exact)
         uint32_t h[4];
 #pragma unroll
-        for (int b = 0; b < 4; ++b) h[b] = __float_as_uint(float((m >> (8 * b)) & 255u)) >> 16;
+        for (int b = 0; b < 4; ++b)
+            h[b] = OP == 0 ? __float_as_uint(float((m >> (8 * b)) & 255u)) >> 16 : uint32_t(__half_as_ushort(__float2half_rn(float((m >> (8 * b)) & 255u))));
         *reinterpret_cast<uint2 *>(table + i * 128 + c * 8) = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
     }
     uint8_t * my_ring = ring + size_t(warp) * STAGES * TILE;
@@ -266,8 +285,8 @@ __global__ void __launch_bounds__(CTA_WARPS * 32, 1) iq3s_grouped_k(Iq3sArgs p) 
                         for (int c = 0; c < NCH; ++c) {
                             const uint4 xv = *reinterpret_cast<const uint4 *>(xw + (8 * c + g) * xrow + (kt * 8 + ib) * 64);
                             float r[4];
-                            mma_bf16_zero(r, a0, a1, a2, a3, xv.x, xv.y);
-                            mma_bf16(r, c0r, c1r, c2r, c3r, xv.z, xv.w);
+                            if (OP == 0) { mma_bf16_zero(r, a0, a1, a2, a3, xv.x, xv.y); mma_bf16(r, c0r, c1r, c2r, c3r, xv.z, xv.w); }
+                            else { mma_f16_zero(r, a0, a1, a2, a3, xv.x, xv.y); mma_f16(r, c0r, c1r, c2r, c3r, xv.z, xv.w); }
                             acc[m][c][0] = fmaf(db0, r[0], acc[m][c][0]); acc[m][c][1] = fmaf(db0, r[1], acc[m][c][1]);
                             acc[m][c][2] = fmaf(db8, r[2], acc[m][c][2]); acc[m][c][3] = fmaf(db8, r[3], acc[m][c][3]);
                         }
@@ -284,6 +303,7 @@ __global__ void __launch_bounds__(CTA_WARPS * 32, 1) iq3s_grouped_k(Iq3sArgs p) 
                     const int slot = NTERM == 1 ? 2 * t + q : 4 * c + t;
                     if (slot >= nv) continue;
                     const int a = perm[off + c0 + slot];
+                    const float is = OP == 0 ? 1.f : p.inv_scale[MODE == 0 ? (a < p.A ? a / p.topk : a - p.A) : a];
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const int row = 16 * rt + g + 8 * h;
@@ -291,7 +311,7 @@ __global__ void __launch_bounds__(CTA_WARPS * 32, 1) iq3s_grouped_k(Iq3sArgs p) 
                         float v[NMAT];
 #pragma unroll
                         for (int m = 0; m < NMAT; ++m)
-                            v[m] = NTERM == 1 ? acc[m][c][2 * h + q] : acc[m][c][2 * h] + acc[m][c][2 * h + 1];
+                            v[m] = (NTERM == 1 ? acc[m][c][2 * h + q] : acc[m][c][2 * h] + acc[m][c][2 * h + 1]) * is;
                         p.out[size_t(a) * p.rows + row] = MODE == 0 ? (v[0] / (1.f + expf(-v[0]))) * v[NMAT - 1] : v[0];
                     }
                 }
@@ -312,7 +332,7 @@ int sm_count() {
 constexpr size_t SMEM_LIMIT = 232448 - 1024;
 
 // max_items: an upper bound of passes * groups (the true count is read from the plan on the device)
-template <int MODE, int NTERM>
+template <int MODE, int NTERM, int OP>
 int32_t launch_grouped(Iq3sArgs a, long long max_items, cudaStream_t s) {
     const int sms = sm_count(), k = a.k_tiles * 256;
     if (sms <= 0) return B2MOE_ERR_CUDA;
@@ -320,63 +340,68 @@ int32_t launch_grouped(Iq3sArgs a, long long max_items, cudaStream_t s) {
     a.nbuf = fixed + xs_bytes(k, NTERM, 2) <= SMEM_LIMIT ? 2 : 1;
     const size_t smem = fixed + xs_bytes(k, NTERM, a.nbuf);
     if (smem > SMEM_LIMIT) return B2MOE_ERR_SHAPE;
-    if (cudaFuncSetAttribute(iq3s_grouped_k<MODE, NTERM>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
+    if (cudaFuncSetAttribute(iq3s_grouped_k<MODE, NTERM, OP>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
         return B2MOE_ERR_CUDA;
     const int blocks = int(std::min<long long>(sms, std::max<long long>(1, max_items)));
-    iq3s_grouped_k<MODE, NTERM><<<blocks, CTA_WARPS * 32, smem, s>>>(a);
+    iq3s_grouped_k<MODE, NTERM, OP><<<blocks, CTA_WARPS * 32, smem, s>>>(a);
     return launch_status();
 }
 
-inline int nterm_of(int dtype) { return dtype == B2MOE_BF16 ? 1 : 2; }
+// bf16 activations are exact bf16 operands; fp32 / fp16 activations become one scaled fp16 term
+inline bool f16_path(int dtype) { return dtype != B2MOE_BF16; }
 inline int rpw_of(int rows) { return std::max(1, ceil_div(rows, 16) / (2 * CTA_WARPS)); }
+inline size_t f16_terms_bytes(int rows_x, int k) { return align_up(size_t(rows_x) * k * sizeof(__half), 256); }
+// x -> scaled fp16 rows + inverse scales in the workspace; fills a.x / a.inv_scale
+int32_t stage_f16(Iq3sArgs & a, const void * x, int dtype, int rows_x, int k, void * ws, cudaStream_t s) {
+    __half * terms = static_cast<__half *>(ws);
+    float * inv = reinterpret_cast<float *>(static_cast<uint8_t *>(ws) + f16_terms_bytes(rows_x, k));
+    act_f16_k<<<ceil_div(rows_x, 8), 256, 0, s>>>(x, dtype, rows_x, k, terms, inv);
+    a.x = reinterpret_cast<const __nv_bfloat16 *>(terms);
+    a.inv_scale = inv;
+    return launch_status();
+}
 
 }  // namespace
 
 // true when the IQ3_S kernels take an activation row of length k in `dtype` (it must fit their shared-memory staging)
 bool iq3s_supported(int k, int dtype) {
-    return k % 256 == 0 && TABLE_BYTES + RING_BYTES + BAR_BYTES + xs_bytes(k, nterm_of(dtype), 1) <= SMEM_LIMIT;
+    (void)dtype;
+    return k % 256 == 0 && TABLE_BYTES + RING_BYTES + BAR_BYTES + xs_bytes(k, 1, 1) <= SMEM_LIMIT;
 }
-// scratch: the two-term bf16 split of `rows_x` activation rows of length k (nothing for bf16 activations)
+// scratch: the scaled fp16 copy of `rows_x` activation rows of length k + one float per row (nothing for bf16 activations)
 size_t iq3s_workspace_bytes(int rows_x, int k, int dtype) {
-    return nterm_of(dtype) == 1 ? 0 : align_up(size_t(rows_x) * 2 * k * sizeof(__nv_bfloat16), 256);
+    return f16_path(dtype) ? f16_terms_bytes(rows_x, k) + align_up(size_t(rows_x) * sizeof(float), 256) : 0;
 }
 
 int32_t iq3s_gateup(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_bank * sg, const b2moe_bank * su, const void * x,
                     int x_dtype, const int * plan, int n, int topk, int shared_tokens, float * act, void * ws, int max_active,
                     cudaStream_t s) {
-    const int nterm = nterm_of(x_dtype), k = gate->cols;
+    const int k = gate->cols;
     Iq3sArgs a{};
     a.x = static_cast<const __nv_bfloat16 *>(x);
-    if (nterm == 2) {
-        const size_t total = size_t(n) * k;
-        act_split_k<<<unsigned((total + 255) / 256), 256, 0, s>>>(x, x_dtype, total, k, static_cast<__nv_bfloat16 *>(ws));
-        if (launch_status()) return B2MOE_ERR_CUDA;
-        a.x = static_cast<const __nv_bfloat16 *>(ws);
-    }
+    if (f16_path(x_dtype))
+        if (int32_t rc = stage_f16(a, x, x_dtype, n, k, ws, s)) return rc;
     a.w0 = static_cast<const uint8_t *>(gate->data); a.w1 = static_cast<const uint8_t *>(up->data);
     if (shared_tokens) { a.s0 = static_cast<const uint8_t *>(sg->data); a.s1 = static_cast<const uint8_t *>(su->data); }
     a.bank_bytes = b2moe_bank_bytes(gate->type, gate->rows, gate->cols);
     a.plan = const_cast<int *>(plan); a.out = act;
     a.rows = gate->rows; a.k_tiles = k / 256; a.experts = gate->experts; a.topk = topk; a.A = n * topk; a.rpw = rpw_of(gate->rows);
     const long long items = (long long)(max_active + (n * topk + shared_tokens) / PASS_TOKENS) * ceil_div(ceil_div(gate->rows, 16), CTA_WARPS * a.rpw);
-    return nterm == 1 ? launch_grouped<0, 1>(a, items, s) : launch_grouped<0, 2>(a, items, s);
+    return f16_path(x_dtype) ? launch_grouped<0, 1, 1>(a, items, s) : launch_grouped<0, 1, 0>(a, items, s);
 }
 
 int32_t iq3s_down(const b2moe_bank * down, const b2moe_bank * sd, const float * act, const int * plan, int n, int topk,
                   int shared_tokens, float * y, void * ws, int max_active, cudaStream_t s) {
     const int rows_x = n * topk + shared_tokens, k = down->cols;
-    const size_t total = size_t(rows_x) * k;
-    act_split_k<<<unsigned((total + 255) / 256), 256, 0, s>>>(act, B2MOE_F32, total, k, static_cast<__nv_bfloat16 *>(ws));
-    if (launch_status()) return B2MOE_ERR_CUDA;
     Iq3sArgs a{};
-    a.x = static_cast<const __nv_bfloat16 *>(ws);
+    if (int32_t rc = stage_f16(a, act, B2MOE_F32, rows_x, k, ws, s)) return rc;
     a.w0 = static_cast<const uint8_t *>(down->data);
     if (shared_tokens) a.s0 = static_cast<const uint8_t *>(sd->data);
     a.bank_bytes = b2moe_bank_bytes(down->type, down->rows, down->cols);
     a.plan = const_cast<int *>(plan); a.out = y;
     a.rows = down->rows; a.k_tiles = k / 256; a.experts = down->experts; a.topk = topk; a.A = n * topk; a.rpw = rpw_of(down->rows);
     const long long items = (long long)(max_active + rows_x / PASS_TOKENS) * ceil_div(ceil_div(down->rows, 16), CTA_WARPS * a.rpw);
-    return launch_grouped<1, 2>(a, items, s);
+    return launch_grouped<1, 1, 1>(a, items, s);
 }
 
 }  // namespace b2
