@@ -402,6 +402,42 @@ def run_b200(args):
         traffic = (317.7e6 + 1.4e6) / 353.0 * n_active
         traffic_src = "ncu dram__bytes_read+write of one capture, scaled by active experts (profiles/iq3s_grouped_decode_c2_t64.md)"
 
+    sweep = None
+    if args.sweep and world == 1:
+        # decode batches of 1 / 4 / 16 tokens: all L layers per step, replayed as a CUDA graph like the headline step, CUDA events
+        sweep = {}
+        with torch.cuda.stream(stream):
+            for ts in (1, 4, 16):
+                xs = x[:ts].contiguous()
+                os_ = [torch.empty(ts, shape.hidden, dtype=torch.bfloat16, device=dev) for _ in range(L)]
+
+                def small_step():
+                    for lay, o in zip(layers, os_):
+                        lay.forward(xs, out=o)
+                for _ in range(3):
+                    small_step()
+                stream.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    small_step()
+                for _ in range(5):
+                    g.replay()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = 50
+                stream.synchronize()
+                e0.record(stream)
+                for _ in range(reps):
+                    g.replay()
+                e1.record(stream)
+                stream.synchronize()
+                us_layer = e0.elapsed_time(e1) * 1e3 / (reps * L)
+                act_l = sum(lay.artefacts()["n_active"] for lay in layers) / L
+                sweep[str(ts)] = {"us_per_layer": us_layer, "tokens_per_s": ts / (us_layer * 1e-6), "active_experts": act_l,
+                                  "expert_weight_gbs": act_l * shape.expert_bytes() / (us_layer * 1e-6) / 1e9}
+                del g
+            for lay in layers:
+                lay.reserve(T)
+
     cpu = None
     if host_layer0 is not None:
         threads = os.cpu_count() or 1
@@ -426,7 +462,7 @@ def run_b200(args):
                          "active_experts_per_launch": n_active, "bytes_per_expert": gu_bytes},
             "expert_weight_gbs": weight_bytes_step / (ms_step * 1e-3) / 1e9,
             "expert_weight_frac_of_8tbs": weight_bytes_step / (ms_step * 1e-3) / 8e12,
-            "stage_us": stage_us, "cpu_baseline": cpu, "clocks": clocks.summary(),
+            "stage_us": stage_us, "sweep": sweep, "cpu_baseline": cpu, "clocks": clocks.summary(),
         }))
     if world > 1:
         dist.destroy_process_group()

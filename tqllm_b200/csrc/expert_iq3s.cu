@@ -349,7 +349,14 @@ int32_t launch_grouped(Iq3sArgs a, long long max_items, cudaStream_t s) {
 
 // bf16 activations are exact bf16 operands; fp32 / fp16 activations become one scaled fp16 term
 inline bool f16_path(int dtype) { return dtype != B2MOE_BF16; }
-inline int rpw_of(int rows) { return std::max(1, ceil_div(rows, 16) / (2 * CTA_WARPS)); }
+// row tiles per warp of one work item: as many as keep at least two items per SM (an item = a pass of <= 8 tokens x
+// CTA_WARPS * rpw row tiles), so that a handful of tokens still spreads over the SMs; at most row_tiles / 32
+inline int rpw_of(int rows, long long est_passes) {
+    const int row_tiles = ceil_div(rows, 16), sms = std::max(1, sm_count());
+    int rpw = std::max(1, row_tiles / (2 * CTA_WARPS));
+    while (rpw > 1 && est_passes * ceil_div(row_tiles, CTA_WARPS * rpw) < 2LL * sms) rpw >>= 1;
+    return rpw;
+}
 inline size_t f16_terms_bytes(int rows_x, int k) { return align_up(size_t(rows_x) * k * sizeof(__half), 256); }
 // x -> scaled fp16 rows + inverse scales in the workspace; fills a.x / a.inv_scale
 int32_t stage_f16(Iq3sArgs & a, const void * x, int dtype, int rows_x, int k, void * ws, cudaStream_t s) {
@@ -385,8 +392,10 @@ int32_t iq3s_gateup(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_
     if (shared_tokens) { a.s0 = static_cast<const uint8_t *>(sg->data); a.s1 = static_cast<const uint8_t *>(su->data); }
     a.bank_bytes = b2moe_bank_bytes(gate->type, gate->rows, gate->cols);
     a.plan = const_cast<int *>(plan); a.out = act;
-    a.rows = gate->rows; a.k_tiles = k / 256; a.experts = gate->experts; a.topk = topk; a.A = n * topk; a.rpw = rpw_of(gate->rows);
-    const long long items = (long long)(max_active + (n * topk + shared_tokens) / PASS_TOKENS) * ceil_div(ceil_div(gate->rows, 16), CTA_WARPS * a.rpw);
+    a.rows = gate->rows; a.k_tiles = k / 256; a.experts = gate->experts; a.topk = topk; a.A = n * topk;
+    const long long est = (long long)max_active + (n * topk + shared_tokens) / PASS_TOKENS;
+    a.rpw = rpw_of(gate->rows, est);
+    const long long items = est * ceil_div(ceil_div(gate->rows, 16), CTA_WARPS * a.rpw);
     return f16_path(x_dtype) ? launch_grouped<0, 1, 1>(a, items, s) : launch_grouped<0, 1, 0>(a, items, s);
 }
 
@@ -399,8 +408,10 @@ int32_t iq3s_down(const b2moe_bank * down, const b2moe_bank * sd, const float * 
     if (shared_tokens) a.s0 = static_cast<const uint8_t *>(sd->data);
     a.bank_bytes = b2moe_bank_bytes(down->type, down->rows, down->cols);
     a.plan = const_cast<int *>(plan); a.out = y;
-    a.rows = down->rows; a.k_tiles = k / 256; a.experts = down->experts; a.topk = topk; a.A = n * topk; a.rpw = rpw_of(down->rows);
-    const long long items = (long long)(max_active + rows_x / PASS_TOKENS) * ceil_div(ceil_div(down->rows, 16), CTA_WARPS * a.rpw);
+    a.rows = down->rows; a.k_tiles = k / 256; a.experts = down->experts; a.topk = topk; a.A = n * topk;
+    const long long est = (long long)max_active + rows_x / PASS_TOKENS;
+    a.rpw = rpw_of(down->rows, est);
+    const long long items = est * ceil_div(ceil_div(down->rows, 16), CTA_WARPS * a.rpw);
     return launch_grouped<1, 1, 1>(a, items, s);
 }
 
