@@ -455,7 +455,8 @@ def run_b200(args):
                        "activations": "bf16 in, bf16 out, fp32 intermediates"},
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": x_host.numel() * 2,
                     "d2h_bytes_per_step": out_host.numel() * 2},
-            "gpu_launches": args.steps * L * (7 if world == 1 else 9),
+            "gpu_launches": args.steps * L * (6 if world == 1 else 9),   # per layer: router, route + dispatch, gate/up, fp16 rows, down, combine
+                                                                      # (expert parallel: + top-k, local ids, rank-ordered reduce)
             "roofline": {"bound": bound, "kernel": roof_kernel, "achieved": achieved, "peak": peak, "unit": roof_unit,
                          "frac": achieved / peak, "peak_kind": peak_kind, "traffic": traffic, "traffic_source": traffic_src,
                          "kernel_ms": k_ms,
