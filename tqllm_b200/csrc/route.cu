@@ -3,6 +3,7 @@
 // Selection rule everywhere: larger key first, lower index on ties (src/experts/moe.cpp:75-78); weights come from
 // the unbiased probabilities (src/experts/moe.cpp:85-86); the renormalising sum is clamped at 6.103515625e-5
 // (src/experts/moe.hpp:38) and accumulated in selection order like the host reference (src/experts/moe.cpp:103-108).
+#include <cooperative_groups.h>
 #include <math_constants.h>
 
 #include "common.cuh"
@@ -68,6 +69,9 @@ __global__ void __launch_bounds__(RM_WARPS * 32) router_mma_k(const float * __re
                                                                 const __nv_bfloat16 * __restrict__ x, float * __restrict__ logits, int ld,
                                                                 int h, int e, int rows, int n) {
     __shared__ float part[RM_PART][16][65];
+    __shared__ float tile[16][65];                                      // this block's sums over its slice of the columns
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();                    // the gridDim.z blocks that split the hidden dimension
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int r0 = blockIdx.x * 16, t0 = blockIdx.y * 64;
     const int ra = min(r0 + g, rows - 1), rb = min(r0 + g + 8, rows - 1);
@@ -77,8 +81,9 @@ __global__ void __launch_bounds__(RM_WARPS * 32) router_mma_k(const float * __re
     for (int j = 0; j < 8; ++j)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
-    const int kper = (h / 16 + RM_WARPS - 1) / RM_WARPS * 16;           // columns per warp, a multiple of 16
-    const int k_lo = warp * kper, k_hi = min(h, k_lo + kper);
+    const int hs = h / int(gridDim.z), h_lo = int(blockIdx.z) * hs;     // this block's columns (a multiple of 16)
+    const int kper = (hs / 16 + RM_WARPS - 1) / RM_WARPS * 16;          // columns per warp, a multiple of 16
+    const int k_lo = h_lo + warp * kper, k_hi = min(h_lo + hs, k_lo + kper);
 #pragma unroll 4
     for (int k0 = k_lo; k0 < k_hi; k0 += 16) {
         uint32_t hi[4], mid[4], lo[4];
@@ -115,13 +120,25 @@ __global__ void __launch_bounds__(RM_WARPS * 32) router_mma_k(const float * __re
     __syncthreads();
     for (int i = threadIdx.x; i < 16 * 64; i += blockDim.x) {
         const int r = i & 15, c = i >> 4;
-        if (r0 + r < rows && t0 + c < n) {
-            float s = 0.f;
+        float s = 0.f;
 #pragma unroll
-            for (int q = 0; q < RM_PART; ++q) s += part[q][r][c];
-            logits[size_t(t0 + c) * ld + r0 + r] = s;
+        for (int q = 0; q < RM_PART; ++q) s += part[q][r][c];
+        tile[r][c] = s;
+    }
+    // the blocks of the cluster hold the sums of their column slices: block 0 adds them in block order through
+    // distributed shared memory (the same bits every run) and writes the logits
+    cluster.sync();
+    if (blockIdx.z == 0) {
+        for (int i = threadIdx.x; i < 16 * 64; i += blockDim.x) {
+            const int r = i & 15, c = i >> 4;
+            if (r0 + r < rows && t0 + c < n) {
+                float s = tile[r][c];
+                for (unsigned z = 1; z < gridDim.z; ++z) s += cluster.map_shared_rank(&tile[0][0], z)[r * 65 + c];
+                logits[size_t(t0 + c) * ld + r0 + r] = s;
+            }
         }
     }
+    cluster.sync();                                                     // the other blocks' tiles stay alive until block 0 has read them
 }
 
 __device__ __forceinline__ void argmax_merge(float & v, int & i, float ov, int oi) {
@@ -305,8 +322,22 @@ extern "C" B2MOE_API int32_t b2moe_router(const float * router_w, const float * 
     if (x_dtype == B2MOE_F32)
         router_k<B2MOE_F32><<<grid, 256, 0, s>>>(router_w, shared_gate, static_cast<const float *>(x), logits, ld, hidden, experts, rows, n);
     else if (x_dtype == B2MOE_BF16 && hidden % 16 == 0)
-        router_mma_k<<<dim3(ceil_div(rows, 16), ceil_div(n, 64)), RM_WARPS * 32, 0, s>>>(router_w, shared_gate, static_cast<const __nv_bfloat16 *>(x),
-                                                                                         logits, ld, hidden, experts, rows, n);
+    {
+        // split the hidden dimension over a cluster of up to 4 blocks while every block keeps at least 256 columns
+        int ks = 1;
+        while (ks < 4 && hidden % (32 * ks) == 0 && hidden / (2 * ks) >= 256) ks *= 2;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(ceil_div(rows, 16), ceil_div(n, 64), ks);
+        cfg.blockDim = dim3(RM_WARPS * 32);
+        cfg.stream = s;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 1; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = ks;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, router_mma_k, router_w, shared_gate, static_cast<const __nv_bfloat16 *>(x), logits, ld, hidden, experts,
+                               rows, n) != cudaSuccess) return B2MOE_ERR_CUDA;
+    }
     else if (x_dtype == B2MOE_BF16)
         router_k<B2MOE_BF16><<<grid, 256, 0, s>>>(router_w, shared_gate, static_cast<const __nv_bfloat16 *>(x), logits, ld, hidden, experts, rows, n);
     else
