@@ -136,10 +136,10 @@ B2MOE_API int32_t b2moe_plan_to_groups(const int32_t * plan, int32_t n, int32_t 
                              int32_t * groups, b2moe_stream stream);
 
 /* ---- expert products ------------------------------------------------------------------------------------------
- * Scratch: the tuned kernels of a format first split the activation rows into tensor-core operand form inside a
- * caller-provided workspace of b2moe_expert_workspace_bytes(type, rows_x, k, x_dtype) bytes (16-byte aligned), where
+ * Scratch: the tensor-core kernels first bring the activation rows into operand form (one fp16 term per value, the row
+ * scaled by a power of two, + that scale) inside a caller-provided workspace of b2moe_expert_workspace_bytes(type, rows_x, k, x_dtype) bytes (16-byte aligned), where
  * rows_x = n for the gate/up product (k = hidden) and n*topk + shared_tokens for the down product (k = ff, x_dtype
- * B2MOE_F32). The size is 0 for formats that take no scratch; the workspace may then be NULL. */
+ * B2MOE_F32). The workspace may be NULL only where the size is 0. */
 B2MOE_API size_t b2moe_expert_workspace_bytes(uint32_t type, int32_t rows_x, int32_t k, int32_t x_dtype);
 /* act[a][f] = silu(gate_e(a)[f] . x[token(a)]) * (up_e(a)[f] . x[token(a)]) for every grouped assignment a: the
  * paired gate/up product with the SwiGLU fused (replaces expert_matvec2 / expert_matvec_dedup2 / expert_gemm_gateup +
@@ -159,8 +159,8 @@ B2MOE_API int32_t b2moe_expert_down(const b2moe_bank * down, const b2moe_bank * 
  * scratch (an engine plugin that owns no device memory; code inside a stream capture or another region where
  * cudaMalloc is not allowed). It has no counterpart in the reference. The scratch b2moe_expert_down would take from
  * the caller lives in a fixed B2MOE_STATIC_SCRATCH_BYTES array inside the library's device image: every GPU that
- * loads the library holds that array until the process exits. Limits: the bf16 split of the activation rows,
- * (n*topk + shared_tokens) * cols * 4 bytes, must fit the array, else B2MOE_ERR_CAPACITY and nothing is launched;
+ * loads the library holds that array until the process exits. Limits: the operand form of the activation rows,
+ * b2moe_expert_workspace_bytes(type, n*topk + shared_tokens, cols, B2MOE_F32) bytes (about 2 bytes per value), must fit the array, else B2MOE_ERR_CAPACITY and nothing is launched;
  * all calls on a device share the array, so calls that overlap on the GPU (different streams) race on it. The first
  * call on each device looks the array's device address up (with that device current) and should come before any
  * stream capture; later calls only launch. Results are those of b2moe_expert_down. */

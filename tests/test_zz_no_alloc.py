@@ -51,7 +51,7 @@ def test_static_scratch_rejects_oversize_and_serves_other_formats():
     from tqllm_b200 import capi
     from tqllm_b200.capi import lib
     assert lib.b2moe_static_scratch_bytes() == 16 << 20
-    # 70,000 assignments x 256 columns x 4 bytes > 16 MiB: refused before anything is launched
+    # 70,000 assignments x 256 columns x 2 bytes (fp16 operand rows) > 16 MiB: refused before anything is launched
     bank = capi.Bank(256, None, 21, 4, 32, 256)
     rc = lib.b2moe_expert_down_static(C.byref(bank), None, 256, 256, 7000, 10, 0, 256, None)
     assert rc == capi.ERR_CAPACITY
