@@ -115,3 +115,11 @@ def test_token_order_does_not_change_a_token():
         a = dev.forward(x).float().cpu().numpy()
         b = dev.forward(torch.flip(x, dims=(0,)).contiguous()).float().cpu().numpy()
     assert np.array_equal(a.view(np.uint32), b[::-1].copy().view(np.uint32))
+
+
+def test_gemm_layer_sigmoid_bias_routing(orc):
+    """the c4 routing (sigmoid scores, selection bias, renormalised weights, no shared expert) over Q4_K banks, GEMM forced"""
+    shape = synth.LayerShape("gemm-c4", 768, 16, 4, 512, gating=2, sel_bias=True, types=(12, 12, 12))
+    with forced_path("gemm"):
+        err = run_case(orc, shape, 16, 200, 77)
+    assert err <= TOL
