@@ -123,3 +123,15 @@ def test_gemm_layer_sigmoid_bias_routing(orc):
     with forced_path("gemm"):
         err = run_case(orc, shape, 16, 200, 77)
     assert err <= TOL
+
+
+@pytest.mark.parametrize("case", (GEMM_CASES[0], GEMM_CASES[2], GEMM_CASES[4]), ids=("q4k", "iq4xs-nl", "nvfp4"))
+def test_gemm_256_token_items_match_exact_path(case, monkeypatch):
+    """the 256-token item variant (one accumulator set, two B stages), forced: token tiles of 256 + a ragged rest"""
+    monkeypatch.setenv("B2MOE_GEMM_NT", "256")
+    types, hidden, ff, experts, topk, tokens, shared, dt = case
+    shape = synth.LayerShape("gemm-wide", hidden, experts, topk, ff, shared=shared, types=types, act_dtype=dt)
+    act_g, y_g = products(shape, experts, 3 * tokens, 11, "gemm")
+    act_x, y_x = products(shape, experts, 3 * tokens, 11, "generic")
+    assert rel_err(act_g, act_x) <= TOL
+    assert rel_err(y_g, y_x) <= TOL

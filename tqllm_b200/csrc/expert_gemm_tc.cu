@@ -20,6 +20,8 @@
 // gave 3e-2 of the output RMS as the largest error, fp16 stays below the layer tolerance). An activation row is
 // multiplied by 2^e so that its largest magnitude lies in [2^14, 2^15) and rounded to fp16: exact for bf16 inputs down
 // to 2^-29 of the row maximum; the epilogue multiplies the sums (fp32) by 2^-e.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "formats.cuh"
 #include "gemm_decode.cuh"
@@ -30,17 +32,19 @@ namespace {
 using namespace tc;
 
 constexpr int G_ROWS = 128;                 // weight rows per item = M
-constexpr int G_NT = 128;                   // tokens per item (N <= 128, a multiple of 16)
+// tokens per item: template parameter NT = 128 (two accumulator sets, four B stages; the default) or 256 (one accumulator
+// set in the gate/up product, two B stages; opt-in)
 constexpr int G_KS = 64;                    // columns per pipeline step (four MMAs of K = 16 per matrix)
-constexpr int A_STAGES = 2, B_STAGES = 4, RAW_SLOTS = 2, B_LAG = 2;
+constexpr int A_STAGES = 2, RAW_SLOTS = 2, MAX_B_STAGES = 4;
 constexpr uint32_t DEC_BACKOFF = 60;       // ns between tries of a decode warp's waits
 constexpr int A_LBO = gdec::A_LBO;          // bytes between k cores of A
 constexpr int A_MAT = 8 * A_LBO;            // one matrix of one A stage: 128 rows x 64 columns
-constexpr int B_LBO = G_NT * 16;            // bytes between k cores of B
-constexpr int B_STAGE = 8 * B_LBO;          // 128 tokens x 64 columns
-constexpr int MMA_WARP = 0, LOAD_WARP0 = 5, LOAD_WARPS = 2, DEC_WARP0 = 7, DEC_WARPS = 16;   // warps 1..4: epilogue
+#ifndef B2_LOAD_WARPS
+#define B2_LOAD_WARPS 2
+#endif
+constexpr int MMA_WARP = 0, LOAD_WARP0 = 5, LOAD_WARPS = B2_LOAD_WARPS, LOAD_THREADS = 32 * LOAD_WARPS, DEC_WARP0 = LOAD_WARP0 + LOAD_WARPS, DEC_WARPS = 16;   // warps 1..4: epilogue
 constexpr int G_THREADS = (DEC_WARP0 + DEC_WARPS) * 32;
-constexpr int N_BARS = 2 * 8 * RAW_SLOTS + 2 * A_STAGES + 2 * B_STAGES + 4;
+constexpr int N_BARS = 2 * 8 * RAW_SLOTS + 2 * A_STAGES + 2 * MAX_B_STAGES + 4;
 
 struct GemmArgs {
     const uint8_t * w0, * w1;               // stacked banks (gate, up) or (down, -)
@@ -57,9 +61,9 @@ struct GemmArgs {
 template <uint32_t T> constexpr int chunk_tiles() { return 256 / Fmt<T>::KT; }
 template <uint32_t T> constexpr int chunk_bytes() { return chunk_tiles<T>() * Fmt<T>::TILE; }
 
-template <uint32_t T, int NMAT>
+template <uint32_t T, int NMAT, int NT>
 constexpr size_t gemm_smem(int experts) {
-    return size_t(A_STAGES) * NMAT * A_MAT + size_t(B_STAGES) * B_STAGE + size_t(8) * RAW_SLOTS * NMAT * chunk_bytes<T>() +
+    return size_t(A_STAGES) * NMAT * A_MAT + size_t(NT == 128 ? 4 : 2) * (8 * NT * 16) + size_t(8) * RAW_SLOTS * NMAT * chunk_bytes<T>() +
            gdec::Dec<T>::TAB_BYTES + size_t(experts + 3) * 4 + 16 + size_t(N_BARS) * 8 + 16;
 }
 
@@ -92,9 +96,12 @@ __device__ unsigned long long g_gemm_prof[8];
 #endif
 
 // MODE 0: act[a][r] = silu(gate_r . x_tok(a)) * (up_r . x_tok(a));  MODE 1: y[a][r] = down_r . act[a]
-template <uint32_t T, int MODE>
+template <uint32_t T, int MODE, int NT>
 __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
     constexpr int NMAT = MODE == 0 ? 2 : 1;
+    constexpr int G_NT = NT, B_LBO = NT * 16, B_STAGE = 8 * B_LBO;      // B: bytes between k cores; NT tokens x 64 columns
+    constexpr int B_STAGES = NT == 128 ? 4 : 2, B_LAG = NT == 128 ? 2 : 1;
+    constexpr uint32_t ACC_SETS = NMAT * NT * 2 <= 512 ? 2 : 1;        // accumulator sets that fit the 512 tensor-memory columns
     constexpr int KT = Fmt<T>::KT, TILE = Fmt<T>::TILE, CT = chunk_tiles<T>(), CB = chunk_bytes<T>();
     constexpr uint32_t TMEM_COLS = 512;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -107,7 +114,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
     uint32_t * tmem_slot = reinterpret_cast<uint32_t *>(bars + N_BARS);
     volatile int * abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const uint32_t raw_full = saddr(bars), raw_empty = raw_full + 8 * 8 * RAW_SLOTS, a_full = raw_empty + 8 * 8 * RAW_SLOTS, a_empty = a_full + 8 * A_STAGES,
-                   b_full = a_empty + 8 * A_STAGES, b_empty = b_full + 8 * B_STAGES, acc_full = b_empty + 8 * B_STAGES,
+                   b_full = a_empty + 8 * A_STAGES, b_empty = b_full + 8 * MAX_B_STAGES, acc_full = b_empty + 8 * MAX_B_STAGES,
                    acc_empty = acc_full + 16;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int e1 = p.experts + 1;
@@ -130,7 +137,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
     if (threadIdx.x == 0) {
         for (int i = 0; i < 8 * RAW_SLOTS; ++i) { bar_init(raw_full + 8 * i, 1); bar_init(raw_empty + 8 * i, 2); }
         for (int i = 0; i < A_STAGES; ++i) { bar_init(a_full + 8 * i, DEC_WARPS); bar_init(a_empty + 8 * i, 1); }
-        for (int i = 0; i < B_STAGES; ++i) { bar_init(b_full + 8 * i, LOAD_WARPS); bar_init(b_empty + 8 * i, 1); }
+        for (int i = 0; i < MAX_B_STAGES; ++i) { bar_init(b_full + 8 * i, LOAD_WARPS); bar_init(b_empty + 8 * i, 1); }
         for (int i = 0; i < 2; ++i) { bar_init(acc_full + 8 * i, 1); bar_init(acc_empty + 8 * i, 4); }
         *abort_flag = 0;
         bar_init_fence();
@@ -168,10 +175,10 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
         const uint32_t a_hi = (128u >> 4) | (1u << 14), b_hi = a_hi;
         for (int it = blockIdx.x; it < n_items && !*abort_flag; it += gridDim.x, ++ic) {
             const Item im = locate(it);
-            const uint32_t npad = uint32_t(im.nv + 15) & ~15u, id = idesc(G_ROWS, npad, 0), ab = ic & 1u;
+            const uint32_t npad = uint32_t(im.nv + 15) & ~15u, id = idesc(G_ROWS, npad, 0), ab = ic % ACC_SETS;
             if (lane == 0) {
                 GP_LAP(3);
-                if (ic >= 2 && !bar_wait(acc_empty + 8 * ab, ((ic >> 1) - 1) & 1u, 100)) give_up();
+                if (ic >= ACC_SETS && !bar_wait(acc_empty + 8 * ab, ((ic / ACC_SETS) - 1) & 1u, 100)) give_up();
                 fence_after();
                 GP_LAP(0);
                 for (int ks = 0; ks < ksteps && !*abort_flag; ++ks, ++gk) {
@@ -205,8 +212,8 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
         uint32_t ic = 0;
         for (int it = blockIdx.x; it < n_items && !*abort_flag; it += gridDim.x, ++ic) {
             const Item im = locate(it);
-            const uint32_t ab = ic & 1u;
-            if (!__all_sync(0xffffffffu, bar_wait(acc_full + 8 * ab, (ic >> 1) & 1u, 1000))) { if (lane == 0) give_up(); break; }
+            const uint32_t ab = ic % ACC_SETS;
+            if (!__all_sync(0xffffffffu, bar_wait(acc_full + 8 * ab, (ic / ACC_SETS) & 1u, 1000))) { if (lane == 0) give_up(); break; }
             fence_after();
             const int row = im.rb * G_ROWS + 32 * q + lane;
             float rs[NMAT];                                            // fp32 row scales of the bank (NVFP4G), else 1
@@ -240,7 +247,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
             if (lane == 0) bar_arrive(acc_empty + 8 * ab);
         }
     } else if (warp < DEC_WARP0) {
-        // ---- B loader: thread n copies the 128 bytes of token rows n and n + 64 of every step, B_LAG steps in flight ----
+        // ---- B loader: thread n copies the 128 bytes of token rows n, n + 64, ... of every step, B_LAG steps in flight ----
         const int n = threadIdx.x - LOAD_WARP0 * 32;
         uint32_t gk = 0, arrived = 0;
         bool ok = true;
@@ -253,12 +260,15 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
         for (int it = blockIdx.x; it < n_items && ok && !*abort_flag; it += gridDim.x) {
             const Item im = locate(it);
             const int npad = (im.nv + 15) & ~15;
-            const __half * src[2] = {p.xb, p.xb};
-            uint32_t src_bytes[2] = {0, 0};
+            constexpr int RPT = NT / LOAD_THREADS;                      // token rows per loader thread
+            const __half * src[RPT];
+            uint32_t src_bytes[RPT];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                if (n + 64 * h < im.nv) {
-                    const int a = perm[im.off + im.c0 + n + 64 * h];
+            for (int h = 0; h < RPT; ++h) {
+                src[h] = p.xb;
+                src_bytes[h] = 0;
+                if (n + LOAD_THREADS * h < im.nv) {
+                    const int a = perm[im.off + im.c0 + n + LOAD_THREADS * h];
                     src[h] = p.xb + size_t(MODE == 0 ? (a < p.A ? a / p.topk : a - p.A) : a) * p.k;
                     src_bytes[h] = 16;
                 }
@@ -268,11 +278,11 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
                 const uint32_t sb = gk % B_STAGES;
                 if (gk >= B_STAGES && !__all_sync(0xffffffffu, bar_wait(b_empty + 8 * sb, ((gk / B_STAGES) - 1) & 1u, 200))) { ok = false; break; }
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    if (n + 64 * h < npad) {
+                for (int h = 0; h < RPT; ++h) {
+                    if (n + LOAD_THREADS * h < npad) {
 #pragma unroll
                         for (int c = 0; c < 8; ++c)
-                            cp_async16(dst0 + sb * B_STAGE + c * B_LBO + h * 1024, src[h] + (src_bytes[h] ? ks * G_KS + c * 8 : 0), src_bytes[h]);
+                            cp_async16(dst0 + sb * B_STAGE + c * B_LBO + h * (LOAD_THREADS * 16), src[h] + (src_bytes[h] ? ks * G_KS + c * 8 : 0), src_bytes[h]);
                     }
                 }
                 cp_async_commit();
@@ -369,15 +379,25 @@ int gemm_sm_count() {
 }
 constexpr size_t GEMM_SMEM_LIMIT = 232448 - 1024;
 
+template <uint32_t T, int MODE, int NT>
+int32_t gemm_launch_nt(const GemmArgs & a, int sms, cudaStream_t s) {
+    const size_t smem = gemm_smem<T, MODE == 0 ? 2 : 1, NT>(a.experts);
+    if (smem > GEMM_SMEM_LIMIT) return B2MOE_ERR_SHAPE;
+    if (cudaFuncSetAttribute(gemm_tc_k<T, MODE, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
+    gemm_tc_k<T, MODE, NT><<<sms, G_THREADS, smem, s>>>(a);
+    return launch_status();
+}
+// 128-token items. The 256-token variant (weights decoded once per 256 tokens, but one accumulator set and two B stages) is
+// correct and slower where it was measured (c5, 512 tokens per expert: 261 against 395 TFLOP/s: the gathered B loads with one
+// step of lookahead become the limit); B2MOE_GEMM_NT=256 selects it for measurements
 template <uint32_t T, int MODE>
 int32_t gemm_launch_t(const GemmArgs & a, cudaStream_t s) {
     const int sms = gemm_sm_count();
     if (sms <= 0) return B2MOE_ERR_CUDA;
-    const size_t smem = gemm_smem<T, MODE == 0 ? 2 : 1>(a.experts);
-    if (smem > GEMM_SMEM_LIMIT) return B2MOE_ERR_SHAPE;
-    if (cudaFuncSetAttribute(gemm_tc_k<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
-    gemm_tc_k<T, MODE><<<sms, G_THREADS, smem, s>>>(a);
-    return launch_status();
+    const char * v = std::getenv("B2MOE_GEMM_NT");
+    const bool wide = v && v[0] == '2';
+    if (wide && gemm_smem<T, MODE == 0 ? 2 : 1, 256>(a.experts) <= GEMM_SMEM_LIMIT) return gemm_launch_nt<T, MODE, 256>(a, sms, s);
+    return gemm_launch_nt<T, MODE, 128>(a, sms, s);
 }
 template <int MODE>
 int32_t gemm_launch(uint32_t type, const GemmArgs & a, cudaStream_t s) {
@@ -392,11 +412,11 @@ int32_t gemm_launch(uint32_t type, const GemmArgs & a, cudaStream_t s) {
 }
 size_t gemm_smem_of(uint32_t type, int nmat, int experts) {
     switch (type) {
-        case T_Q4_K: return nmat == 2 ? gemm_smem<T_Q4_K, 2>(experts) : gemm_smem<T_Q4_K, 1>(experts);
-        case T_IQ3_S: return nmat == 2 ? gemm_smem<T_IQ3_S, 2>(experts) : gemm_smem<T_IQ3_S, 1>(experts);
-        case T_IQ4_XS: return nmat == 2 ? gemm_smem<T_IQ4_XS, 2>(experts) : gemm_smem<T_IQ4_XS, 1>(experts);
-        case T_IQ4_NL: return nmat == 2 ? gemm_smem<T_IQ4_NL, 2>(experts) : gemm_smem<T_IQ4_NL, 1>(experts);
-        case T_NVFP4G: return nmat == 2 ? gemm_smem<T_NVFP4G, 2>(experts) : gemm_smem<T_NVFP4G, 1>(experts);
+        case T_Q4_K: return nmat == 2 ? gemm_smem<T_Q4_K, 2, 128>(experts) : gemm_smem<T_Q4_K, 1, 128>(experts);
+        case T_IQ3_S: return nmat == 2 ? gemm_smem<T_IQ3_S, 2, 128>(experts) : gemm_smem<T_IQ3_S, 1, 128>(experts);
+        case T_IQ4_XS: return nmat == 2 ? gemm_smem<T_IQ4_XS, 2, 128>(experts) : gemm_smem<T_IQ4_XS, 1, 128>(experts);
+        case T_IQ4_NL: return nmat == 2 ? gemm_smem<T_IQ4_NL, 2, 128>(experts) : gemm_smem<T_IQ4_NL, 1, 128>(experts);
+        case T_NVFP4G: return nmat == 2 ? gemm_smem<T_NVFP4G, 2, 128>(experts) : gemm_smem<T_NVFP4G, 1, 128>(experts);
     }
     return ~size_t(0);
 }
