@@ -158,8 +158,8 @@ def run_reference(args):
     threads = os.cpu_count() or 1
     layers, rscale = make_layers(synth, shape, 1, "cpu")
     x = synth.make_tokens(shape, args.tokens, SEED, "cpu")
-    steps = max(1, min(args.steps, 3))
-    for _ in range(min(args.warmup, 1)):
+    steps = max(1, min(args.steps, 200))          # one layer pass (about 0.3 s on 16 cores) per step
+    for _ in range(min(args.warmup, 3)):
         cpu_layer_time("reference", shape, layers[0], x, threads)
     times = []
     kind = "port"
@@ -169,7 +169,7 @@ def run_reference(args):
     t = sum(times) / len(times)
     v = args.tokens / t
     print(json.dumps({
-        "metric": METRIC, "value": v, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1),
+        "metric": METRIC, "value": v, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 3),
         "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_name(shape, args.tokens, args.layers), "sample": "one layer per step", "router_scale": rscale},
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": kind,
