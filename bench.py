@@ -316,7 +316,7 @@ def run_b200(args):
             import ctypes as C
             from tqllm_b200.capi import lib, BF16
 
-            wsb = lib.b2moe_expert_workspace_bytes(shape.types[0], T, shape.hidden, XDT)
+            wsb = lib.b2moe_expert_workspace_bytes(layers[0].gate.type, T, shape.hidden, XDT)
             ews = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
 
             def gateup(l):
@@ -350,7 +350,7 @@ def run_b200(args):
             wts = torch.zeros(T, shape.topk, dtype=torch.float32, device=dev)
             yb = torch.zeros(A + ST, shape.hidden, dtype=torch.float32, device=dev)
             ob = torch.zeros(T, shape.hidden, dtype=torch.bfloat16, device=dev)
-            dws = torch.empty(max(lib.b2moe_expert_workspace_bytes(shape.types[2], A + ST, shape.ff, F32), 16), dtype=torch.uint8, device=dev)
+            dws = torch.empty(max(lib.b2moe_expert_workspace_bytes(layers[0].down.type, A + ST, shape.ff, F32), 16), dtype=torch.uint8, device=dev)
             plan2 = moe.Plan(shape.experts, T, shape.topk, ST, dev)
             dsw = torch.empty(max(lib.b2moe_dispatch_workspace_bytes(shape.experts, A), 16), dtype=torch.uint8, device=dev)
             bias = lambda l: None if layers[l].sel_bias is None else layers[l].sel_bias.data_ptr()

@@ -10,8 +10,10 @@
  *   - every pointer is DEVICE memory unless a parameter says "host"; the caller owns all of it;
  *   - stacked expert weights are [experts * rows][cols]; ids are [n][topk] int32, id -1 = skip the assignment;
  *   - assignment a = token * topk + slot; per-assignment outputs are [n * topk][rows];
- *   - every entry point is stream-ordered, does no host synchronisation, allocates nothing and keeps no mutable
- *     global state: scratch comes from a caller-provided workspace (capture-safe, re-entrant across streams);
+ *   - every entry point is stream-ordered, does no host synchronisation and allocates nothing: scratch comes from a
+ *     caller-provided workspace, and the library keeps no mutable state between calls (re-entrant across streams).
+ *     Two exceptions, both stated where they are declared: b2moe_expert_down_static keeps its scratch in one array
+ *     inside the library, and the b2moe_harness_* hooks set process-wide switches for tests and benchmarks;
  *   - return value: 0 = ok, otherwise a b2moe_status code (b2moe_status_string gives the text). Nothing is launched
  *     when the arguments are rejected. There is no CPU fallback: without a CUDA device every compute entry point
  *     returns B2MOE_ERR_CUDA.
@@ -48,7 +50,14 @@ enum b2moe_status {
 };
 
 /* GGUF type ids of the block formats (src/core/gguf.hpp:18-37) */
-enum b2moe_type { B2MOE_Q4_K = 12, B2MOE_IQ4_NL = 20, B2MOE_IQ3_S = 21, B2MOE_IQ4_XS = 23, B2MOE_NVFP4G = 323 };
+enum b2moe_type {
+    B2MOE_Q4_K = 12, B2MOE_IQ4_NL = 20, B2MOE_IQ3_S = 21, B2MOE_IQ4_XS = 23, B2MOE_NVFP4G = 323,
+    /* Not a GGUF type: a second bank layout for IQ3_S blocks. b2moe_bank_load takes the same raw IQ3_S blocks and
+     * stores every weight as a 4-bit code (grid lookup and sign applied once, at load time): 134 bytes per 256 weights
+     * in HBM instead of 110, the same fp32 values bit for bit, and decode kernels that need no codebook lookup. The
+     * layout to choose when HBM capacity allows (21.8 % more bytes per expert); B2MOE_IQ3_S keeps the GGUF size. */
+    B2MOE_IQ3_S_X4 = 0x1015
+};
 enum b2moe_dtype { B2MOE_F32 = 0, B2MOE_F16 = 1, B2MOE_BF16 = 2 };
 /* MoeGating values, src/experts/moe.hpp:20-26 (the two the device path implements) */
 enum b2moe_gating { B2MOE_SOFTMAX = 1, B2MOE_SIGMOID = 2 };
@@ -69,7 +78,8 @@ typedef struct b2moe_bank {
     int32_t experts, rows, cols;
 } b2moe_bank;
 
-/* bytes of `rows` x `cols` in GGUF block form (host arithmetic; 0 when the type or shape is invalid) */
+/* bytes of `rows` x `cols` in GGUF block form (host arithmetic; 0 when the type or shape is invalid; B2MOE_IQ3_S_X4
+ * loads from IQ3_S blocks and reports their size) */
 B2MOE_API size_t b2moe_raw_bytes(uint32_t type, int32_t rows, int32_t cols);
 /* bytes of one expert's matrix in bank form, and of its aux array (0 when the type has none) */
 B2MOE_API size_t b2moe_bank_bytes(uint32_t type, int32_t rows, int32_t cols);
@@ -163,7 +173,8 @@ B2MOE_API int32_t b2moe_expert_down(const b2moe_bank * down, const b2moe_bank * 
  * b2moe_expert_workspace_bytes(type, n*topk + shared_tokens, cols, B2MOE_F32) bytes (about 2 bytes per value), must fit the array, else B2MOE_ERR_CAPACITY and nothing is launched;
  * all calls on a device share the array, so calls that overlap on the GPU (different streams) race on it. The first
  * call on each device looks the array's device address up (with that device current) and should come before any
- * stream capture; later calls only launch. Results are those of b2moe_expert_down. */
+ * stream capture; later calls only launch (the cached address does not survive a cudaDeviceReset). A call that
+ * resolves to the format-generic kernels uses no scratch and is not limited. Results are those of b2moe_expert_down. */
 #define B2MOE_STATIC_SCRATCH_BYTES (16u << 20)
 B2MOE_API size_t b2moe_static_scratch_bytes(void);
 B2MOE_API int32_t b2moe_expert_down_static(const b2moe_bank * down, const b2moe_bank * shared_down, const float * act,
@@ -191,6 +202,19 @@ B2MOE_API int32_t b2moe_ep_local_ids(const int32_t * ids, int32_t * local_ids, i
  * and shared_weights [n] may be NULL (no shared expert / weight 1). out [n][hidden] of out_dtype. */
 B2MOE_API int32_t b2moe_ep_reduce(const float * parts, int32_t ranks, const float * shared_y, const float * shared_weights,
                         int32_t n, int32_t hidden, void * out, int32_t out_dtype, b2moe_stream stream);
+
+/* ---- harness hooks ---------------------------------------------------------------------------------------------
+ * For tests and benchmarks, not for engines: process-wide switches, not thread-safe, to be set while no call of this
+ * library is running. They have no counterpart in the reference.
+ * b2moe_harness_select: family = the kernel family every later expert product takes where it supports the shape
+ * (AUTO = the library's own choice by tokens per expert, the default); gemm_item_tokens = 128 (default; 0 means the
+ * same) or 256 tokens per work item of the grouped GEMM.
+ * b2moe_harness_wait_probe: the 4-bit decode kernels skip the copy of weight tile number drop_tile of every warp
+ * (-1 = none, the default) and bound each wait by wait_limit polls (0 = default), so that a test can watch a bounded
+ * wait run out: the launch then sets plan word [3] and returns, its outputs invalid. */
+enum b2moe_family { B2MOE_FAMILY_AUTO = 0, B2MOE_FAMILY_GENERIC = 1, B2MOE_FAMILY_DECODE = 2, B2MOE_FAMILY_GEMM = 3 };
+B2MOE_API void b2moe_harness_select(int32_t family, int32_t gemm_item_tokens);
+B2MOE_API void b2moe_harness_wait_probe(int32_t drop_tile, uint32_t wait_limit);
 
 /* ---- whole layer ----------------------------------------------------------------------------------------------
  * router -> top-k -> dispatch -> gate/up + SwiGLU -> down -> combine, the sequence of qwen35_forward.cpp:1121-1252,

@@ -39,6 +39,7 @@ extern "C" int host_pack_decode(uint32_t type, const uint8_t * raw, int rows, in
     switch (type) {
         case T_Q4_K: run<T_Q4_K>(raw, rows, cols, bank, out); return 0;
         case T_IQ3_S: run<T_IQ3_S>(raw, rows, cols, bank, out); return 0;
+        case T_IQ3S4: run<T_IQ3S4>(raw, rows, cols, bank, out); return 0;
         case T_IQ4_XS: run<T_IQ4_XS>(raw, rows, cols, bank, out); return 0;
         case T_IQ4_NL: run<T_IQ4_NL>(raw, rows, cols, bank, out); return 0;
         case T_NVFP4G: run<T_NVFP4G>(raw, rows, cols, bank, out); return 0;

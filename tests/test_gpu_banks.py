@@ -8,7 +8,8 @@ from tqllm_b200 import synth
 from util import same_bits
 
 pytestmark = pytest.mark.gpu
-TYPES = (12, 21, 23, 20, 323)
+TYPES = (12, 21, 23, 20, 323, 0x1015)       # 0x1015: IQ3_S blocks in the 4-bit-code bank layout
+RAW = lambda t: 21 if t == 0x1015 else t    # the GGUF type whose blocks the bank is loaded from
 
 
 @pytest.mark.parametrize("t", TYPES)
@@ -17,11 +18,11 @@ def test_dump_equals_oracle_random_blocks(orc, t, experts, rows, cols):
     from tqllm_b200 import moe
     g = torch.Generator()
     g.manual_seed(t * 31 + rows)
-    elems, _ = synth.BLOCK[t]
-    raw = synth.random_blocks(t, experts * rows * cols // elems, g, cols // elems)
+    elems, _ = synth.BLOCK[RAW(t)]
+    raw = synth.random_blocks(RAW(t), experts * rows * cols // elems, g, cols // elems)
     bank = moe.DeviceBank(t, raw.cuda(), experts, rows, cols)
     got = bank.dequant().cpu().numpy().reshape(-1)
-    assert same_bits(got, orc.dequant(t, raw.numpy(), experts * rows * cols))
+    assert same_bits(got, orc.dequant(RAW(t), raw.numpy(), experts * rows * cols))
 
 
 @pytest.mark.parametrize("t", TYPES)
@@ -30,17 +31,17 @@ def test_dump_equals_oracle_quantised_weights(orc, t):
     g = torch.Generator()
     g.manual_seed(t)
     w = torch.randn(4 * 64, 1024, generator=g) * 0.02
-    raw = synth.quantize(t, w)
+    raw = synth.quantize(RAW(t), w)
     bank = moe.DeviceBank(t, raw.cuda(), 4, 64, 1024)
-    assert same_bits(bank.dequant().cpu().numpy().reshape(-1), orc.dequant(t, raw.numpy(), w.numel()))
+    assert same_bits(bank.dequant().cpu().numpy().reshape(-1), orc.dequant(RAW(t), raw.numpy(), w.numel()))
 
 
 @pytest.mark.parametrize("t", TYPES)
 def test_committed_golden_blocks(golden, t):
     """the golden blocks (gguf-py / reference values) through the device path"""
     from tqllm_b200 import moe
-    raw, vals = golden["dequant"][f"raw_{t}"], golden["dequant"][f"vals_{t}"]
-    elems, nbytes = synth.BLOCK[t]
+    raw, vals = golden["dequant"][f"raw_{RAW(t)}"], golden["dequant"][f"vals_{RAW(t)}"]
+    elems, nbytes = synth.BLOCK[RAW(t)]
     blocks = raw.size // nbytes
     per_row = 4 if t == 323 else 1
     bank = moe.DeviceBank(t, torch.from_numpy(raw.copy()).cuda(), 1, blocks // per_row, elems * per_row)

@@ -2,7 +2,7 @@
 b2moe_combine over local ids, b2moe_ep_reduce) with all ranks emulated on one device and the exchanges done by tensor
 copies — how the reference tests its two-rank split (tests/ep_split.cu:87-151). The split result must equal the
 unsplit layer: ids exactly, outputs up to the order of the fp32 partial sums when both sides run the same kernel
-family (B2MOE_EXPERT_PATH=decode pins it: a rank with a quarter of the experts would otherwise cross the
+family (b2moe_harness_select pins it: a rank with a quarter of the experts would otherwise cross the
 tokens-per-expert threshold of the tensor-core GEMM, whose fp16 operands round differently), and within the layer
 tolerance with the default choice."""
 import numpy as np
@@ -46,11 +46,12 @@ def run_split(shape, E, T, world, seed):
 
 @pytest.mark.parametrize("world", (2, 4))
 @pytest.mark.parametrize("types,gating,shared", (((21, 21, 21), 1, True), ((12, 12, 12), 2, False), ((23, 23, 20), 1, True)))
-def test_split_equals_unsplit(world, types, gating, shared, monkeypatch):
-    monkeypatch.setenv("B2MOE_EXPERT_PATH", "decode")
+def test_split_equals_unsplit(world, types, gating, shared):
+    from tqllm_b200 import capi
     ff = 256 if types[2] != 20 else 96
     shape = synth.LayerShape("ep-gpu", 512, 16, 4, ff, gating=gating, sel_bias=gating == 2, shared=shared, types=types)
-    got, want = run_split(shape, 16, 6, world, 50 + world)
+    with capi.family("decode"):
+        got, want = run_split(shape, 16, 6, world, 50 + world)
     assert rel_err(got, want) <= 1e-5
 
 
@@ -61,15 +62,16 @@ def test_split_default_paths_within_layer_tolerance(types):
     assert rel_err(got, want) <= 1e-2
 
 
-def test_uneven_blocks_and_idle_rank(monkeypatch):
+def test_uneven_blocks_and_idle_rank():
     """7 experts over 4 ranks (blocks of 2, 2, 2, 1), and a rank whose experts nobody routed to"""
-    monkeypatch.setenv("B2MOE_EXPERT_PATH", "decode")
-    shape = synth.LayerShape("ep-uneven", 512, 7, 2, 256, shared=True, types=(21, 21, 21))
-    got, want = run_split(shape, 7, 3, 4, 9)
-    assert rel_err(got, want) <= 1e-5
-    shape = synth.LayerShape("ep-idle", 512, 16, 1, 256, types=(21, 21, 21))
-    got, want = run_split(shape, 16, 1, 4, 10)          # one token, one expert: three ranks have nothing to do
-    assert rel_err(got, want) <= 1e-5
+    from tqllm_b200 import capi
+    with capi.family("decode"):
+        shape = synth.LayerShape("ep-uneven", 512, 7, 2, 256, shared=True, types=(21, 21, 21))
+        got, want = run_split(shape, 7, 3, 4, 9)
+        assert rel_err(got, want) <= 1e-5
+        shape = synth.LayerShape("ep-idle", 512, 16, 1, 256, types=(21, 21, 21))
+        got, want = run_split(shape, 16, 1, 4, 10)          # one token, one expert: three ranks have nothing to do
+        assert rel_err(got, want) <= 1e-5
 
 
 class OneRankComm:

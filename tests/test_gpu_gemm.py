@@ -1,11 +1,9 @@
 """GPU: the tcgen05 grouped GEMM (every bank format, experts holding many tokens) against the exact fp32 generic path
 of the same library and, end to end, against the oracle.
 
-The GEMM rounds the decoded weights and the activations to bf16 and sums in fp32; the generic path is exact fp32
+The GEMM rounds the decoded weights and the activations to fp16 and sums in fp32; the generic path is exact fp32
 (src/experts/moe.cpp:115-155 order). Tolerance: max |err| / RMS(reference) <= 1e-2, the bound of the layer tests;
 observed values are about 3e-3."""
-import os
-
 import numpy as np
 import pytest
 import torch
@@ -19,33 +17,22 @@ pytestmark = pytest.mark.gpu
 TOL = 1e-2
 
 
-class forced_path:
-    """B2MOE_EXPERT_PATH for the calls inside the block (the library reads it at every call)"""
-
-    def __init__(self, name):
-        self.name = name
-
-    def __enter__(self):
-        self.old = os.environ.get("B2MOE_EXPERT_PATH")
-        os.environ["B2MOE_EXPERT_PATH"] = self.name
-
-    def __exit__(self, *a):
-        if self.old is None:
-            del os.environ["B2MOE_EXPERT_PATH"]
-        else:
-            os.environ["B2MOE_EXPERT_PATH"] = self.old
+def forced_path(name, item_tokens=0):
+    """the kernel family of every expert product inside the block (b2moe_harness_select)"""
+    from tqllm_b200 import capi
+    return capi.family(name, item_tokens)
 
 
-def products(shape, experts, tokens, seed, path):
+def products(shape, experts, tokens, seed, path, item_tokens=0, iq3s_layout="codes"):
     from tqllm_b200 import moe
     layer, x = layer_inputs(shape, experts, tokens, seed)
-    dev = moe.MoeLayer.from_synth(layer, experts=experts)
+    dev = moe.MoeLayer.from_synth(layer, experts=experts, iq3s_layout=iq3s_layout)
     xd = x.cuda()
     logits = moe.router(dev.router_w, xd)
     ids, w, _ = moe.topk_softmax(logits, experts, shape.topk, shape.scale)
     plan = moe.dispatch(ids, experts, tokens if shape.shared else 0)
     sh = dev.sh if shape.shared else (None, None, None)
-    with forced_path(path):
+    with forced_path(path, item_tokens):
         act = moe.expert_gateup_swiglu(dev.gate, dev.up, xd, plan, sh[0], sh[1])
         y = moe.expert_down(dev.down, act, plan, sh[2])
     torch.cuda.synchronize()
@@ -58,6 +45,7 @@ def products(shape, experts, tokens, seed, path):
 GEMM_CASES = (
     ((12, 12, 12), 512, 256, 4, 2, 300, True, "bf16"),
     ((21, 21, 21), 512, 256, 4, 2, 150, True, "f32"),
+    ((21, 21, 21), 512, 256, 4, 2, 140, True, "bf16", "gguf"),
     ((23, 23, 20), 512, 320, 3, 2, 200, False, "bf16"),
     ((20, 20, 20), 256, 192, 2, 1, 270, True, "bf16"),
     ((323, 323, 323), 512, 256, 4, 3, 130, True, "bf16"),
@@ -65,16 +53,17 @@ GEMM_CASES = (
 )
 
 
-@pytest.mark.parametrize("case", GEMM_CASES, ids=[f"{c[0][0]}-{c[0][2]}-t{c[5]}" for c in GEMM_CASES])
+@pytest.mark.parametrize("case", GEMM_CASES, ids=[f"{c[0][0]}-{c[0][2]}-t{c[5]}" + (f"-{c[8]}" if len(c) > 8 else "") for c in GEMM_CASES])
 def test_gemm_matches_exact_path(case):
-    types, hidden, ff, experts, topk, tokens, shared, dt = case
+    types, hidden, ff, experts, topk, tokens, shared, dt = case[:8]
+    lay = case[8] if len(case) > 8 else "codes"                  # IQ3_S banks: 4-bit codes (default) or the GGUF-sized layout
     shape = synth.LayerShape("gemm", hidden, experts, topk, ff, shared=shared, types=types, act_dtype=dt)
-    act_g, y_g = products(shape, experts, tokens, 7, "gemm")
-    act_x, y_x = products(shape, experts, tokens, 7, "generic")
+    act_g, y_g = products(shape, experts, tokens, 7, "gemm", iq3s_layout=lay)
+    act_x, y_x = products(shape, experts, tokens, 7, "generic", iq3s_layout=lay)
     assert rel_err(act_g, act_x) <= TOL
     assert rel_err(y_g, y_x) <= TOL
     # the same call again: the same bits
-    act_2, y_2 = products(shape, experts, tokens, 7, "gemm")
+    act_2, y_2 = products(shape, experts, tokens, 7, "gemm", iq3s_layout=lay)
     assert np.array_equal(act_g.view(np.uint32), act_2.view(np.uint32)) and np.array_equal(y_g.view(np.uint32), y_2.view(np.uint32))
 
 
@@ -125,13 +114,12 @@ def test_gemm_layer_sigmoid_bias_routing(orc):
     assert err <= TOL
 
 
-@pytest.mark.parametrize("case", (GEMM_CASES[0], GEMM_CASES[2], GEMM_CASES[4]), ids=("q4k", "iq4xs-nl", "nvfp4"))
-def test_gemm_256_token_items_match_exact_path(case, monkeypatch):
+@pytest.mark.parametrize("case", (GEMM_CASES[0], GEMM_CASES[3], GEMM_CASES[5]), ids=("q4k", "iq4xs-nl", "nvfp4"))
+def test_gemm_256_token_items_match_exact_path(case):
     """the 256-token item variant (one accumulator set, two B stages), forced: token tiles of 256 + a ragged rest"""
-    monkeypatch.setenv("B2MOE_GEMM_NT", "256")
-    types, hidden, ff, experts, topk, tokens, shared, dt = case
+    types, hidden, ff, experts, topk, tokens, shared, dt = case[:8]
     shape = synth.LayerShape("gemm-wide", hidden, experts, topk, ff, shared=shared, types=types, act_dtype=dt)
-    act_g, y_g = products(shape, experts, 3 * tokens, 11, "gemm")
+    act_g, y_g = products(shape, experts, 3 * tokens, 11, "gemm", item_tokens=256)
     act_x, y_x = products(shape, experts, 3 * tokens, 11, "generic")
     assert rel_err(act_g, act_x) <= TOL
     assert rel_err(y_g, y_x) <= TOL

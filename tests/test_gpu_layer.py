@@ -28,10 +28,20 @@ def oracle_layer(orc, shape, experts, layer, x, logits):
                          logits_in=logits)
 
 
-def run_case(orc, shape, experts, tokens, seed, golden=None, name=None, tol=TOL):
+def device_made_inputs(shape, tokens, seed):
+    """a full-size layer generated and quantised on the GPU (seconds instead of minutes), handed back as host tensors"""
+    import dataclasses
+    layer = synth.make_layer(shape, seed, "cuda")
+    host = lambda t: None if t is None else t.cpu()
+    layer = dataclasses.replace(layer, router_w=host(layer.router_w), sel_bias=host(layer.sel_bias), raw=tuple(host(t) for t in layer.raw),
+                                shared_raw=None if layer.shared_raw is None else tuple(host(t) for t in layer.shared_raw))
+    return layer, synth.make_tokens(shape, tokens, seed, "cuda").cpu()
+
+
+def run_case(orc, shape, experts, tokens, seed, golden=None, name=None, tol=TOL, iq3s_layout="codes", inputs=None):
     from tqllm_b200 import moe
-    layer, x = layer_inputs(shape, experts, tokens, seed)
-    dev = moe.MoeLayer.from_synth(layer, experts=experts)
+    layer, x = inputs if inputs is not None else layer_inputs(shape, experts, tokens, seed)
+    dev = moe.MoeLayer.from_synth(layer, experts=experts, iq3s_layout=iq3s_layout)
     out = dev.forward(x.cuda()).cpu().numpy()
     art = dev.artefacts()
     logits = art["logits"].cpu().numpy()[:, :experts].copy()
@@ -65,6 +75,7 @@ def run_case(orc, shape, experts, tokens, seed, golden=None, name=None, tol=TOL)
             assert rel_err(out, g[f"{name}_out"]) <= tol
     # the same input again gives the same bits
     assert np.array_equal(dev.forward(x.cuda()).cpu().numpy().view(np.uint32), out.view(np.uint32))
+    assert dev.artefacts()["status"] == 0          # no bounded wait of a kernel ran out
     return err
 
 
@@ -134,23 +145,132 @@ def test_errors_reach_the_caller():
         moe.DeviceBank(12, torch.zeros(10, dtype=torch.uint8, device="cuda"), 1, 16, 256)
 
 
-@pytest.mark.parametrize("kernel", ("mma", "tc"))
+@pytest.mark.parametrize("layout", ("codes", "gguf"))
 @pytest.mark.parametrize("act_dtype,experts,tokens,topk", (("f32", 4, 40, 2), ("bf16", 4, 70, 3), ("bf16", 24, 3, 8), ("f32", 16, 1, 4)))
-def test_iq3s_tensor_core_path(orc, act_dtype, experts, tokens, topk, kernel, monkeypatch):
-    """the IQ3_S decode kernels (pinned: batches this dense default to the grouped GEMM): fp32 and bf16 activations (4- and
-    2-term splits), experts holding many more tokens than one pass takes, experts holding one token, a shared expert"""
-    monkeypatch.setenv("B2MOE_EXPERT_PATH", "decode")
-    monkeypatch.setenv("B2MOE_IQ3S_PATH", kernel)          # mma.sync kernels (the default) / their tcgen05 variant
-    shape = synth.LayerShape("iq3s-mma", 512, experts, topk, 256, shared=True, types=(21, 21, 21), act_dtype=act_dtype)
-    err = run_case(orc, shape, experts, tokens, 4242 + tokens)
+def test_iq3s_decode_kernels(orc, act_dtype, experts, tokens, topk, layout):
+    """the IQ3_S decode kernels of both bank layouts (pinned: batches this dense default to the grouped GEMM): fp32 and
+    bf16 activations, experts holding many more tokens than one pass takes, experts holding one token, a shared expert"""
+    from tqllm_b200 import capi
+    shape = synth.LayerShape("iq3s-dec", 512, experts, topk, 256, shared=True, types=(21, 21, 21), act_dtype=act_dtype)
+    with capi.family("decode"):
+        err = run_case(orc, shape, experts, tokens, 4242 + tokens, iq3s_layout=layout)
     assert err < 2e-3
+
+
+@pytest.mark.parametrize("gating,shared,hidden,ff,experts,tokens,topk", ((2, False, 768, 512, 16, 16, 4), (1, True, 512, 256, 4, 70, 2),
+                                                                           (1, True, 256, 1024, 24, 3, 8), (1, False, 1024, 288, 8, 9, 3)))
+def test_q4k_decode_kernels(orc, gating, shared, hidden, ff, experts, tokens, topk):
+    """the 4-bit decode kernels over Q4_K banks, pinned: sigmoid + bias routing (the c4 family), a shared expert, experts
+    with more tokens than a pass takes, 18 row tiles over 16 warps (ff = 288) with a down product of k = 256 ... 1024"""
+    from tqllm_b200 import capi
+    down = 12 if ff % 256 == 0 else 20                       # Q4_K needs 256-column blocks; IQ4_NL down otherwise
+    shape = synth.LayerShape("q4k-dec", hidden, experts, topk, ff, gating=gating, sel_bias=gating == 2, shared=shared,
+                             types=(12, 12, down))
+    with capi.family("decode"):
+        err = run_case(orc, shape, experts, tokens, 99 + tokens)
+    assert err < 2e-3
+
+
+# ---- the benchmark configurations at their stated sizes against the oracle (one layer each) --------------------
+# c2: all 512 experts + the shared one, the decode batch sweep; c4: 256 experts, 16 decode tokens. The oracle's pass
+# over one such layer takes a fraction of a second per token on the host cores.
+@pytest.mark.parametrize("cfg,tokens", (("c2", 1), ("c2", 4), ("c2", 16), ("c2", 64), ("c4", 16)))
+def test_full_size_decode_configs(orc, cfg, tokens):
+    shape = synth.CONFIGS[cfg]
+    run_case(orc, shape, shape.experts, tokens, 4000 + tokens, inputs=device_made_inputs(shape, tokens, 4000 + tokens))
+
+
+def test_full_size_c2_gguf_layout(orc):
+    """the same c2 layer with the IQ3_S banks in the GGUF-sized layout (grid lookup inside the kernel)"""
+    shape = synth.CONFIGS["c2"]
+    run_case(orc, shape, shape.experts, 64, 4064, iq3s_layout="gguf", inputs=device_made_inputs(shape, 64, 4064))
+
+
+# c3 (512 experts, NVFP4G) and c5 (128 experts, IQ4_XS + IQ4_NL down) at the real hidden / ff sizes with the routing
+# concentrated on a few experts, so that those hold more than 256 tokens each: what exercises the grouped GEMM's two
+# accumulator sets, its multi-tile items and its ragged last token tile on a benchmark shape, with a token count the
+# oracle still finishes in about a minute (the oracle's cost is tokens x top-k x 3 H F multiply-adds, one thread per expert).
+@pytest.mark.parametrize("cfg,tokens,hot", (("c3", 320, 12), ("c5", 272, 4)))
+def test_full_size_prefill_configs_many_tokens_per_expert(orc, cfg, tokens, hot):
+    """Every token gets a common component along one direction and the router rows of `hot` experts point along it, so the
+    top-k of every token lies among them first: c3, top-10 of 12 hot experts -> about 267 tokens on each; c5, the 4 hot
+    experts hold all 272 tokens each (token tiles of 128 + 128 + 16) and the other four picks spread over 124 experts."""
+    from tqllm_b200 import capi, moe
+    shape = synth.CONFIGS[cfg]
+    layer, x = device_made_inputs(shape, tokens, 5000 + tokens)
+    direction = torch.zeros(shape.hidden)
+    direction[::7] = 1.0
+    direction /= direction.norm()
+    x = (x.float() + 4.0 * direction).to(x.dtype)
+    layer.router_w[:hot] += 3.0 * direction
+    dev = moe.MoeLayer.from_synth(layer, experts=shape.experts)
+    with capi.family("gemm"):
+        out = dev.forward(x.cuda()).cpu().numpy()
+    art = dev.artefacts()
+    assert art["status"] == 0
+    counts = art["counts"].cpu().numpy()[:shape.experts]
+    assert counts[:hot].min() >= 200, counts[:hot]
+    logits = art["logits"].cpu().numpy()[:, :shape.experts].copy()
+    res = oracle_layer(orc, shape, shape.experts, layer, x, logits)
+    assert np.array_equal(art["ids"].cpu().numpy(), res["ids"])
+    assert np.array_equal(counts, res["counts"])
+    assert np.array_equal(art["perm"].cpu().numpy()[:tokens * shape.topk], res["perm"])
+    assert rel_err(out, res["out"]) <= TOL
+
+
+def test_c2_layer_through_cuda_graph_replay(orc):
+    """the benchmark times the layer as a CUDA-graph replay: capture the full-size c2 layer, replay it on new activations
+    at the same address and hold the replay's output against the oracle"""
+    from tqllm_b200 import moe
+    shape = synth.CONFIGS["c2"]
+    layer, x = device_made_inputs(shape, 16, 4016)
+    dev = moe.MoeLayer.from_synth(layer)
+    xd = torch.zeros_like(x).cuda()
+    out = torch.empty(16, shape.hidden, dtype=torch.float32, device="cuda")
+    dev.forward(xd, out)                                  # warm-up outside the capture (kernel attributes, workspace)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            dev.forward(xd, out)
+        xd.copy_(x.cuda())
+        g.replay()
+    side.synchronize()
+    art = dev.artefacts()
+    logits = art["logits"].cpu().numpy()[:, :shape.experts].copy()
+    res = oracle_layer(orc, shape, shape.experts, layer, x, logits)
+    assert np.array_equal(art["ids"].cpu().numpy(), res["ids"])
+    assert rel_err(out.cpu().numpy(), res["out"]) <= TOL
+
+
+def test_bounded_wait_runs_out_and_the_kernel_returns():
+    """harness hook: the decode kernels skip the copy of one weight tile per warp, so the wait for it runs out (a short
+    limit): the launch must return with the plan's status word set (no trap, no hang), and the next launch is clean"""
+    from tqllm_b200 import capi, moe
+    shape = synth.LayerShape("wait-probe", 512, 8, 2, 256, shared=True, types=(12, 12, 12))
+    layer, x = layer_inputs(shape, 8, 12, 321)
+    dev = moe.MoeLayer.from_synth(layer, experts=8)
+    xd = x.cuda()
+    with capi.family("decode"):
+        want = dev.forward(xd).clone()
+        assert dev.artefacts()["status"] == 0
+        capi.lib.b2moe_harness_wait_probe(1, 2000)
+        try:
+            dev.forward(xd)
+            torch.cuda.synchronize()
+            assert dev.artefacts()["status"] != 0
+        finally:
+            capi.lib.b2moe_harness_wait_probe(-1, 0)
+        assert torch.equal(dev.forward(xd), want)
+        assert dev.artefacts()["status"] == 0
 
 
 def test_iq3s_activation_scale_invariance(orc):
     """activation rows of very different magnitude go through the per-row power-of-two scaling unchanged"""
     from tqllm_b200 import moe
     shape = synth.LayerShape("iq3s-scale", 512, 8, 2, 256, shared=True, types=(21, 21, 21))
-    layer, x = layer_inputs(shape, 8, 6, 99)
+    layer, x = layer_inputs(shape, 8, 6, 99)          # (default layout: the 4-bit codes)
     x = x.float()
     x[0] *= 1e-4
     x[1] *= 3e3

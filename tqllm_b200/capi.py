@@ -15,6 +15,8 @@ LIB_PATH = os.path.join(HERE, "libb2moe.so")
 OK, ERR_SHAPE, ERR_ALIGN, ERR_FORMAT, ERR_NULL, ERR_WORKSPACE, ERR_CUDA, ERR_CAPACITY = range(8)
 F32, F16, BF16 = 0, 1, 2
 Q4_K, IQ4_NL, IQ3_S, IQ4_XS, NVFP4G = 12, 20, 21, 23, 323
+IQ3_S_X4 = 0x1015        # bank layout of IQ3_S blocks as 4-bit codes (b2moe_type)
+FAMILY = {"auto": 0, "generic": 1, "decode": 2, "gemm": 3}
 SOFTMAX, SIGMOID = 1, 2
 
 
@@ -73,6 +75,8 @@ SIGNATURES = {
     "b2moe_static_scratch_bytes": (_sz, []),
     "b2moe_expert_down_static": (_i32, [C.POINTER(Bank)] * 2 + [_vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "b2moe_combine": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _i32, _vp]),
+    "b2moe_harness_select": (None, [_i32, _i32]),
+    "b2moe_harness_wait_probe": (None, [_i32, _u32]),
     "b2moe_layer_workspace": (_i32, [C.POINTER(Layer), _i32, C.POINTER(LayerWs)]),
     "b2moe_layer_forward": (_i32, [C.POINTER(Layer), _vp, _i32, _i32, _vp, _i32, _vp, _sz, _vp]),
 }
@@ -99,3 +103,18 @@ def codebooks():
     kv = (C.c_int8 * 16)()
     lib.b2moe_codebooks(grid, kv)
     return list(grid), list(kv)
+
+
+class family:
+    """Every expert product inside the block takes the named kernel family ("generic", "decode", "gemm") where it supports
+    the shape; `item_tokens` = 256 selects the wide work items of the grouped GEMM. Harness hook: process-wide."""
+
+    def __init__(self, name: str, item_tokens: int = 0):
+        self.name, self.item_tokens = name, item_tokens
+
+    def __enter__(self):
+        lib.b2moe_harness_select(FAMILY[self.name], self.item_tokens)
+        return self
+
+    def __exit__(self, *a):
+        lib.b2moe_harness_select(0, 0)

@@ -105,6 +105,7 @@ extern "C" B2MOE_API int32_t b2moe_bank_load(uint32_t type, const void * raw, in
     switch (type) {
         case T_Q4_K: return load_t<T_Q4_K>(raw, experts, rows, cols, data, s);
         case T_IQ3_S: return load_t<T_IQ3_S>(raw, experts, rows, cols, data, s);
+        case T_IQ3S4: return load_t<T_IQ3S4>(raw, experts, rows, cols, data, s);
         case T_IQ4_XS: return load_t<T_IQ4_XS>(raw, experts, rows, cols, data, s);
         case T_IQ4_NL: return load_t<T_IQ4_NL>(raw, experts, rows, cols, data, s);
         case T_NVFP4G: {
@@ -127,6 +128,7 @@ extern "C" B2MOE_API int32_t b2moe_dequant_dump(const b2moe_bank * bank, float *
     switch (bank->type) {
         case T_Q4_K: return dump_t<T_Q4_K>(*bank, out, s);
         case T_IQ3_S: return dump_t<T_IQ3_S>(*bank, out, s);
+        case T_IQ3S4: return dump_t<T_IQ3S4>(*bank, out, s);
         case T_IQ4_XS: return dump_t<T_IQ4_XS>(*bank, out, s);
         case T_IQ4_NL: return dump_t<T_IQ4_NL>(*bank, out, s);
         case T_NVFP4G: return dump_t<T_NVFP4G>(*bank, out, s);

@@ -1,0 +1,552 @@
+// Grouped expert products for banks of 4-bit codes when every expert sees only a few tokens: the bandwidth-bound
+// decode kernels of Q4_K and of IQ3_S held as 4-bit codes (formats.cuh, Fmt<T_IQ3S4>).
+// Replaces u4h_matvec_k<..., GROUPED> with its paired gate/up and dedup variants
+// (src/formats/weight/quant_u4h.inc:424-604, launchers src/formats/weight/quant.cu:69-233) and the separate SwiGLU
+// pass (src/experts/moe.cu:188-195).
+//
+// Arithmetic. A weight of a 32-weight sub-block is an affine function of its 4-bit code n with constants of the (row,
+// sub-block): Q4_K  d sc n - dmin m;  IQ3_S  d (1 + 2 s) (2 n - 15). The activations are brought to 16-bit fixed point
+// per row (a power-of-two scale; 14 or 15 significant bits) and split into a signed high and an unsigned low byte, so
+// that  sum_k n_k x_k  is two integer tensor-core products per sub-block (mma.m16n8k32, u8 x s8 and u8 x u8 -> s32: the
+// masked code words ARE the A fragment, no conversion) and every sum up to the end of a 256-column tile is an exact
+// integer: the 6-bit / 4-bit sub-block scales multiply as integers, and the offset terms (- dmin m, - 15 d (1 + 2 s))
+// times the activation sum of each sub-block, which the staging kernel takes once per activation row, are one more
+// small MMA per tile (fp16 operands that hold the integer factors and the sums exactly). Two fp32 multiply-adds per
+// tile and accumulator apply d / dmin. The only rounding that matters is that of the activations to fixed point
+// (absolute error <= 2^-15 of the row's largest magnitude).
+//
+// Work. One resident block per SM: 16 consumer warps and one producer warp. An item = (pass of up to 8 tokens of one
+// active expert, group of 16 * rpw row tiles); items are dealt round-robin over the blocks. Consumer warp w multiplies
+// row tile(s) w of the group; lane w of the producer warp is its feeder: it streams the tiles warp w will read, in order,
+// over all items of the launch, through that warp's own ring of bulk copies (cp.async.bulk + mbarrier, no multicast;
+// a full and an empty barrier per slot), so the ring never drains between row tiles or items. Lanes 16 .. 23 of the
+// producer copy the staged activation rows of an item's tokens into one of two shared buffers, one item ahead; the
+// consumers hand a buffer back through a barrier of their own, so no block-wide barrier sits in the loop.
+// Every wait is bounded; a wait that runs out sets the plan's status word and a block-wide flag, every warp stops at
+// its next wait or item, the producer lets the copies in flight land, and the block leaves.
+#include "common.cuh"
+#include "formats.cuh"
+
+namespace b2 {
+namespace {
+
+constexpr int CTA_WARPS = 16;
+constexpr int XPAD = 64;             // bytes added to an activation row in shared memory (bank spread)
+constexpr int MAX_STAGES = 4;
+constexpr int SLOT_TILES = 2;        // consecutive column tiles of one matrix per ring slot and bulk copy: an SM sustains its share of the
+                                     // HBM bandwidth with a few dozen large copies in flight, and loses half of it beyond about 64 copies
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_addr(const void * p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void * src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// try_wait suspends the thread for a hardware-chosen time while the phase is pending: the fast path of every wait
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint32_t h2u(__half2 v) { return *reinterpret_cast<const uint32_t *>(&v); }
+__device__ __forceinline__ __half2 u2h(uint32_t v) { return *reinterpret_cast<const __half2 *>(&v); }
+// m16n8k16 fp16 MMA from zero (the offset-correction product of a tile)
+__device__ __forceinline__ void mma_f16_zero(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+                 : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+// m16n8k32 integer MMA, A unsigned bytes, B signed (SB = 1) or unsigned (SB = 0) bytes, C = 0
+template <int SB>
+__device__ __forceinline__ void mma_i8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    if (SB)
+        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+                     : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+    else
+        asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+                     : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+// ---------------------------------------------------------------------------------------------------------------
+// Activation staging: rows [R][K] of any dtype -> 16-bit fixed point, the row scaled by a power of two so that the
+// largest magnitude lies in [2^(BITS-2), 2^(BITS-1)], split into a signed high byte and an unsigned low byte
+// (x16 = 256 hi + lo). One staged row = K / 32 sub-blocks of 64 bytes + K / 256 records of 32 bytes:
+//   sub-block: for t = 0..3 the 16 bytes {hi of columns 4t..4t+3, hi of 16+4t..16+4t+3, lo of 4t.., lo of 16+4t..}: the
+//              B fragments of the lane with that t for the high-byte and the low-byte MMA;
+//   record of 8 sub-blocks: their sums S = sum of x16 over the sub-block, each as the fp16 pair (16 (S >> 10), (S & 1023) / 64)
+//              (both exact; together S / 64), in the order 0, 4, 1, 5, 2, 6, 3, 7: the B fragment of the offset-correction
+//              MMA of a tile (m16n8k16: k = 2 sub-block + term).
+// inv_scale[R] = the inverse of the row's power of two. One block of four warps per row, one lane per column of a sub-block.
+// ---------------------------------------------------------------------------------------------------------------
+__host__ __device__ inline size_t staged_row_bytes(int k) { return size_t(k) * 2 + size_t(k / 256) * 32; }
+
+constexpr int STAGE_WARPS = 4;
+__global__ void __launch_bounds__(STAGE_WARPS * 32) dec4_stage_k(const void * __restrict__ x, int dtype, int rows, int k, int bits,
+                                                                 uint8_t * __restrict__ out, float * __restrict__ inv_scale) {
+    __shared__ float wmax[STAGE_WARPS];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, row = blockIdx.x;
+    float mx = 0.f;
+    for (int j = threadIdx.x; j < k; j += STAGE_WARPS * 32) mx = fmaxf(mx, fabsf(load_act(x, dtype, size_t(row) * k + j)));
+    for (int d = 16; d; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+    if (lane == 0) wmax[warp] = mx;
+    __syncthreads();
+#pragma unroll
+    for (int w = 0; w < STAGE_WARPS; ++w) mx = fmaxf(mx, wmax[w]);
+    int ex = int((__float_as_uint(mx) >> 23) & 255u) - 127;              // floor(log2(mx)) for a normal mx
+    ex = (mx > 0.f && mx < 3e38f) ? max(-100, min(100, ex)) : bits - 2;
+    const float scale = __uint_as_float(uint32_t(127 + bits - 2 - ex) << 23);  // 2^(bits - 2 - ex)
+    if (threadIdx.x == 0) inv_scale[row] = __uint_as_float(uint32_t(127 - (bits - 2) + ex) << 23);
+    const int t = (lane & 15) >> 2, j = lane & 3, h = lane >> 4;
+    uint8_t * orow = out + size_t(row) * staged_row_bytes(k);
+    uint8_t * recs = orow + size_t(k) * 2;
+    const int nsb = k >> 5;
+    for (int b = warp; b < nsb; b += STAGE_WARPS) {
+        const int v = __float2int_rn(load_act(x, dtype, size_t(row) * k + 32 * b + lane) * scale);
+        uint8_t * sb = orow + size_t(b) * 64 + t * 16 + h * 4 + j;
+        sb[0] = uint8_t(v >> 8);
+        sb[8] = uint8_t(v & 255);
+        int sum = v;
+        for (int d = 16; d; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+        if (lane == 0) {
+            const int bb = b & 7;
+            reinterpret_cast<__half2 *>(recs + size_t(b >> 3) * 32)[2 * (bb & 3) + (bb >> 2)] =
+                __floats2half2_rn(float((sum >> 10) * 16), float(sum & 1023) * 0.015625f);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Per-format pieces. A lane L = 4 g + t owns rows g, g + 8; of plane p (sub-blocks 2p, 2p + 1) it holds the words
+// {row g: wa, wb; row g + 8: wa, wb}: wa = codes of weights 4t .. 4t + 3, wb = of weights 16 + 4t .. 16 + 4t + 3, low
+// nibbles sub-block 2p, high nibbles sub-block 2p + 1: masked, the four words ARE the A fragment of the m16n8k32 MMA.
+// A weight is (per row and sub-block)  Q4_K: d (sc n) - dmin (m);  IQ3_S codes: d (1 + 2 s) (2 n - 15). With integer
+// activations the tile's sums stay integers:  main = sum_sb isc_sb * sum_k n_k x_k  and  corr = sum_sb ico_sb * S_sb
+// (isc = sc | 1 + 2 s, ico = m | 1 + 2 s, S_sb = sum_k x_k), then one fp32 step per tile:
+// acc += f_main * main + f_corr * corr  with (f_main, f_corr) = (d, -dmin) | (2 d, -15 d).
+// Hdr::isc[r][h]: the integer scales of row g + 8 r, byte q = sub-block 2 q + h. Hdr::ico[r]: the correction factors of
+// sub-block t in rows g / g + 8 and of sub-block t + 4 as fp16 pairs (ico, ico): the A fragment of the correction MMA (Hdr4::ca).
+// BITS: width of the fixed-point activations, chosen so that `main` cannot overflow 32 bits (32 * 15 * 2^(BITS-1) *
+// max isc * 8 sub-blocks < 2^31).
+// ---------------------------------------------------------------------------------------------------------------
+template <uint32_t T> struct D4;
+struct Hdr4 { uint32_t isc[2][2], ca[4]; float f_main[2], f_corr[2]; };
+// the byte of `word` that `sel` names, as the fp16 pair (v, v): 0x64 above a byte is the fp16 1024 + byte
+__device__ __forceinline__ uint32_t byte_h2(uint32_t word, uint32_t sel) {
+    return h2u(__hsub2(u2h(__byte_perm(word, 0x64646464u, sel)), __float2half2_rn(1024.f)));
+}
+
+template <> struct D4<T_Q4_K> {
+    static constexpr int TILE = 2304, BITS = 15, FLUSH_AT = 1;   // scales up to 63: two halves of a tile stay inside 32 bits
+    __device__ __forceinline__ static void load(Hdr4 & h, const uint8_t * tile, int lane) {
+        const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint4 q = *reinterpret_cast<const uint4 *>(tile + 2048 + 16 * (g + 8 * r));   // d, dmin | scales[12]
+            h.f_main[r] = __half2float(__ushort_as_half((unsigned short)(q.x & 0xffffu)));
+            h.f_corr[r] = -64.f * __half2float(__ushort_as_half((unsigned short)(q.x >> 16)));   // the correction product carries S / 64
+            // the 6-bit fields of sub-blocks 0..3 and 4..7 as bytes (src/formats/weight/dequant.cpp:56-64), four at a time
+            const uint32_t sc03 = q.y & 0x3F3F3F3Fu, mn03 = q.z & 0x3F3F3F3Fu;
+            const uint32_t sc47 = (q.w & 0x0F0F0F0Fu) | ((q.y >> 2) & 0x30303030u), mn47 = ((q.w >> 4) & 0x0F0F0F0Fu) | ((q.z >> 2) & 0x30303030u);
+            h.isc[r][0] = __byte_perm(sc03, sc47, 0x6420);    // sub-blocks 0, 2, 4, 6
+            h.isc[r][1] = __byte_perm(sc03, sc47, 0x7531);    // sub-blocks 1, 3, 5, 7
+            const uint32_t sel = 0x4040u | (uint32_t(t) * 0x0101u);           // byte t twice, 0x64 above each
+            h.ca[r] = byte_h2(mn03, sel);                     // min of sub-block t
+            h.ca[2 + r] = byte_h2(mn47, sel);                 // of sub-block t + 4
+        }
+    }
+};
+
+template <> struct D4<T_IQ3S4> {
+    static constexpr int TILE = 2144, BITS = 15, FLUSH_AT = -1;  // scales up to 31: a whole tile stays inside 32 bits
+    __device__ __forceinline__ static void load(Hdr4 & h, const uint8_t * tile, int lane) {
+        const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint32_t sc = *reinterpret_cast<const uint32_t *>(tile + 2048 + 4 * (g + 8 * r));
+            const float d = __half2float(*reinterpret_cast<const __half *>(tile + 2112 + 2 * (g + 8 * r)));
+            h.f_main[r] = 2.f * d;
+            h.f_corr[r] = -960.f * d;                                         // -15 d, and the correction product carries S / 64
+            h.isc[r][0] = ((sc & 0x0F0F0F0Fu) << 1) | 0x01010101u;          // 1 + 2 s of sub-blocks 0, 2, 4, 6
+            h.isc[r][1] = ((sc >> 3) & 0x1E1E1E1Eu) | 0x01010101u;          // of sub-blocks 1, 3, 5, 7
+            const uint32_t word = (t & 1) ? h.isc[r][1] : h.isc[r][0], sel = 0x4040u | (uint32_t(t >> 1) * 0x0101u);   // sub-block t: byte t / 2 of its word
+            h.ca[r] = byte_h2(word, sel);
+            h.ca[2 + r] = byte_h2(word, sel + 0x0202u);                       // sub-block t + 4: two bytes on
+        }
+    }
+};
+
+struct Dec4Args {
+    const uint8_t * w0, * w1, * s0, * s1;   // stacked banks (gate, up | down, -) and the shared expert's
+    size_t bank_bytes;
+    const uint8_t * x;                       // staged activation rows [rows_x][staged_row_bytes(k)]
+    const float * inv_scale;                 // [rows_x]
+    int * plan;
+    float * out;                             // [A + shared][rows]
+    int rows, k_tiles, experts, topk, A, rpw, nbuf, stages;
+    uint32_t wait_limit;
+    int drop_tile;                           // test hook: the copy into ring slot use number drop_tile (per warp, counted from 0) is never issued; -1 = none
+};
+
+// bytes of one activation row in shared memory: the staged row, padded so that consecutive rows start 64 bytes apart
+// modulo 128 (the 16-byte loads of two token columns then share no bank)
+__host__ __device__ inline uint32_t xrow_bytes(int k) { return uint32_t((staged_row_bytes(k) + 127) / 128 * 128 + XPAD); }
+__host__ __device__ inline size_t xs_bytes(int k, int nbuf) { return size_t(nbuf) * 8 * xrow_bytes(k); }
+// barriers: full[warp][stage], empty[warp][stage], xfull[2], xempty[2]; then the abort flag
+constexpr size_t BAR_BYTES = (2 * CTA_WARPS * MAX_STAGES + 4) * 8 + 16;
+constexpr int THREADS = (CTA_WARPS + 1) * 32;      // 16 consumer warps + the producer warp
+
+// MODE 0: out = act[a][row] = silu(gate . x) * (up . x);   MODE 1: out = y[a][row] = down . act[a]
+template <uint32_t T, int MODE>
+__global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
+    using F = D4<T>;
+    constexpr int NMAT = MODE == 0 ? 2 : 1, TILE = F::TILE;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t * bars = reinterpret_cast<uint64_t *>(smem);
+    volatile int * abort_flag = reinterpret_cast<volatile int *>(smem + BAR_BYTES - 16);
+    constexpr int SLOT = SLOT_TILES * TILE;
+    uint8_t * ring = smem + BAR_BYTES;                                        // [warp][stage][SLOT]
+    uint8_t * xs = ring + size_t(CTA_WARPS) * p.stages * SLOT;               // [buf][8 rows][xrow]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int K = p.k_tiles * 256;
+    const int e1 = p.experts + 1;
+    const int * counts = p.plan + PLAN_HDR, * offsets = counts + e1, * active = offsets + e1 + 1, * perm = active + e1;
+    const int * passes = perm + p.A + counts[p.experts];
+    const int na = p.plan[PLAN_NACTIVE], row_tiles = (p.rows + 15) >> 4;
+    const int groups = (row_tiles + CTA_WARPS * p.rpw - 1) / (CTA_WARPS * p.rpw);
+    const int n_items = p.plan[PLAN_NPASS] * groups;
+    const uint32_t xrow = xrow_bytes(K), xbuf = 8 * xrow, xglob = uint32_t(staged_row_bytes(K));
+    const int S = p.stages, kslots = (p.k_tiles + SLOT_TILES - 1) / SLOT_TILES, nslots = kslots * NMAT;   // slots of one row job
+    const uint32_t full0 = smem_addr(bars), empty0 = full0 + 8 * CTA_WARPS * MAX_STAGES, xfull = empty0 + 8 * CTA_WARPS * MAX_STAGES,
+                   xempty = xfull + 16, xs0 = smem_addr(xs);
+
+    if (threadIdx.x < CTA_WARPS * MAX_STAGES) { mbar_init(full0 + 8 * threadIdx.x, 1); mbar_init(empty0 + 8 * threadIdx.x, 1); }
+    if (threadIdx.x == 0) {
+        mbar_init(xfull, 1); mbar_init(xfull + 8, 1);
+        mbar_init(xempty, CTA_WARPS); mbar_init(xempty + 8, CTA_WARPS);
+        *abort_flag = 0;
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncthreads();
+
+    // pass w -> (expert, first token slot); the pass list runs over the active experts from the last to the first
+    auto locate = [&](int w, int & e, int & c0) {
+        int lo = 0, hi = na - 1;
+        while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (passes[mid] <= w) lo = mid; else hi = mid - 1; }
+        e = active[na - 1 - lo];
+        c0 = (w - passes[lo]) * PASS_TOKENS;
+    };
+    auto x_row = [&](int a) { return MODE == 0 ? size_t(a < p.A ? a / p.topk : a - p.A) : size_t(a); };
+    // a bounded wait that also gives up when another warp of the block has
+    auto wait = [&](uint32_t bar, uint32_t parity) {
+        if (mbar_try(bar, parity)) return true;
+        for (uint32_t i = 0; i < p.wait_limit; ++i) {
+            if (mbar_try(bar, parity)) return true;
+            if ((i & 63) == 63 && *abort_flag) return false;
+        }
+        return false;
+    };
+    const int items_q = int(gridDim.x) / groups, items_r = int(gridDim.x) % groups;   // item + gridDim = (pass + q, group + r)
+
+    if (warp == CTA_WARPS) {
+        // ---- producer: lane w < 16 feeds consumer warp w (its ring, its barriers); lanes 16 .. 23 copy the activation rows ----
+        const int w = lane & (CTA_WARPS - 1);
+        const uint32_t my_full = full0 + 8 * w * MAX_STAGES, my_empty = empty0 + 8 * w * MAX_STAGES, my_ring = smem_addr(ring) + uint32_t(w) * S * SLOT;
+        uint32_t slot = 0, issued = 0, xissued = 0;
+        bool ok = true;
+        auto stage_x = [&](int pass, uint32_t idx) {       // rows of the item with running index idx -> buffer idx % nbuf
+            const uint32_t b = p.nbuf == 2 ? (idx & 1u) : 0u, use = p.nbuf == 2 ? idx >> 1 : idx;
+            if (use > 0 && !wait(xempty + 8 * b, (use - 1) & 1u)) ok = false;     // the consumers are done with the buffer's previous rows
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) return;
+            int e, c0;
+            locate(pass, e, c0);
+            const int nv = min(PASS_TOKENS, counts[e] - c0);
+            if (lane == 16) mbar_expect_tx(xfull + 8 * b, uint32_t(nv) * xglob);
+            __syncwarp();
+            if (lane >= 16 && lane - 16 < nv)
+                bulk_g2s(xs0 + b * xbuf + (lane - 16) * xrow, p.x + x_row(perm[offsets[e] + c0 + lane - 16]) * xglob, xglob, xfull + 8 * b);
+            ++xissued;
+        };
+        int pass = int(blockIdx.x) / groups, grp = int(blockIdx.x) % groups;
+        uint32_t idx = 0;
+        if (int(blockIdx.x) < n_items) stage_x(pass, 0);
+        for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++idx) {
+            int e, c0;
+            locate(pass, e, c0);
+            const bool shared = e == p.experts;
+            int npass = pass + items_q, ngrp = grp + items_r;
+            if (ngrp >= groups) { ngrp -= groups; ++npass; }
+            bool next_staged = p.nbuf != 2 || it + int(gridDim.x) >= n_items;
+            int in_item = 0;
+            for (int jr = 0; jr < p.rpw && ok; ++jr) {
+                const int rt = (grp * p.rpw + jr) * CTA_WARPS + w;
+                const bool mine = lane < CTA_WARPS && rt < row_tiles;
+                const uint8_t * b0 = (shared ? p.s0 : p.w0 + size_t(e) * p.bank_bytes) + size_t(rt) * p.k_tiles * TILE;
+                const uint8_t * b1 = NMAT == 2 ? (shared ? p.s1 : p.w1 + size_t(e) * p.bank_bytes) + size_t(rt) * p.k_tiles * TILE : b0;
+                if ((grp * p.rpw + jr) * CTA_WARPS >= row_tiles) break;
+                for (int j = 0; j < nslots && ok; ++j, ++in_item) {
+                    if (mine) {
+                        if (issued >= uint32_t(S) && !wait(my_empty + 8 * slot, ((issued / S) - 1) & 1u)) ok = false;
+                        else if (int(issued) != p.drop_tile) {
+                            const int ks = NMAT == 2 ? j >> 1 : j;                                   // slot of column tiles of the job
+                            const uint8_t * src = ((NMAT == 2 && (j & 1)) ? b1 : b0) + size_t(ks) * SLOT;
+                            const uint32_t bytes = uint32_t(min(SLOT_TILES, p.k_tiles - ks * SLOT_TILES)) * TILE;
+                            mbar_expect_tx(my_full + 8 * slot, bytes);
+                            bulk_g2s(my_ring + slot * SLOT, src, bytes, my_full + 8 * slot);
+                        }
+                        ++issued;
+                        slot = slot + 1 == uint32_t(S) ? 0 : slot + 1;
+                    }
+                    ok = __all_sync(0xffffffffu, ok);
+                    // once every consumer is S slots into this item, the previous item's buffer is free: bring the next item's rows
+                    if (!next_staged && in_item == S) { stage_x(npass, idx + 1); next_staged = true; }
+                }
+            }
+            if (!next_staged && ok) stage_x(npass, idx + 1);
+            if (p.nbuf == 1 && it + int(gridDim.x) < n_items && ok) stage_x(npass, idx + 1);
+            pass = npass; grp = ngrp;
+        }
+        if (!ok) { *abort_flag = 1; if (lane == 0) atomicExch(p.plan + PLAN_STATUS, 3); }
+        // before leaving, every copy this lane issued must have landed: the last S slots of its ring (earlier ones were
+        // consumed, or their slot could not have been reused) and the last activation buffers. After a clean run these
+        // waits return at once.
+        if (lane < CTA_WARPS) {
+            const uint32_t first = issued > uint32_t(S) ? issued - S : 0;
+            for (uint32_t i = first; i < issued; ++i)
+                if (int(i) != p.drop_tile) wait(my_full + 8 * (i % S), (i / S) & 1u);
+        }
+        if (lane == 16)
+            for (uint32_t i = xissued > 2 ? xissued - 2 : 0; i < xissued; ++i)
+                wait(xfull + 8 * (p.nbuf == 2 ? (i & 1u) : 0u), (p.nbuf == 2 ? i >> 1 : i) & 1u);
+    } else {
+        // ---- consumers ----
+        const int g = lane >> 2, t = lane & 3;
+        const uint8_t * my_ring = ring + size_t(warp) * S * SLOT;
+        const uint32_t my_full = full0 + 8 * warp * MAX_STAGES, my_empty = empty0 + 8 * warp * MAX_STAGES;
+        uint32_t c_slot = 0, c_phase = 0;
+        bool alive = true;
+        int pass = int(blockIdx.x) / groups, grp = int(blockIdx.x) % groups;
+        uint32_t idx = 0;
+        for (int it = blockIdx.x; it < n_items && alive; it += gridDim.x, ++idx) {
+            const uint32_t b = p.nbuf == 2 ? (idx & 1u) : 0u, use = p.nbuf == 2 ? idx >> 1 : idx;
+            if (*abort_flag) break;
+            if (!__all_sync(0xffffffffu, wait(xfull + 8 * b, use & 1u))) { alive = false; break; }
+            int e, c0;
+            locate(pass, e, c0);
+            const int cnt = counts[e], off = offsets[e], nv = min(PASS_TOKENS, cnt - c0);
+            const uint8_t * xw = xs + b * xbuf + g * xrow + t * 16;          // + sub-block * 64
+            const uint8_t * rec = xs + b * xbuf + g * xrow + size_t(K) * 2 + t * 8;   // + tile * 32
+
+            for (int jr = 0; jr < p.rpw && alive; ++jr) {
+                const int rt = (grp * p.rpw + jr) * CTA_WARPS + warp;
+                if (rt >= row_tiles) break;
+                float acc[NMAT][4];
+#pragma unroll
+                for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[m][i] = 0.f;
+
+                for (int ks = 0; ks < kslots && alive; ++ks) {
+                    const int nt = min(SLOT_TILES, p.k_tiles - ks * SLOT_TILES);
+#pragma unroll
+                    for (int m = 0; m < NMAT; ++m) {
+                        if (!__all_sync(0xffffffffu, wait(my_full + 8 * c_slot, c_phase))) { alive = false; break; }
+                        if (p.drop_tile == -2) {     // TEMP experiment: stream only
+                            acc[m][0] += float(reinterpret_cast<const uint32_t *>(my_ring + c_slot * SLOT)[lane]);
+                        } else
+                        for (int kk = 0; kk < nt; ++kk) {
+                            const int kt = ks * SLOT_TILES + kk;
+                            const uint8_t * tile = my_ring + c_slot * SLOT + kk * TILE;
+                            // the sub-block sums of this tile's columns: B fragment of the correction MMA
+                            const uint2 sp = *reinterpret_cast<const uint2 *>(rec + kt * 32);
+                            const uint4 * xk = reinterpret_cast<const uint4 *>(xw + kt * 512);
+                            Hdr4 hdr;
+                            F::load(hdr, tile, lane);
+                            int main_[4] = {0, 0, 0, 0};
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const uint4 pl = reinterpret_cast<const uint4 *>(tile + 512 * q)[lane];
+#pragma unroll
+                                for (int half = 0; half < 2; ++half) {                     // sub-block 2q (low nibbles), 2q + 1 (high nibbles)
+                                    const uint32_t a0 = (half ? pl.x >> 4 : pl.x) & 0x0F0F0F0Fu, a2 = (half ? pl.y >> 4 : pl.y) & 0x0F0F0F0Fu;
+                                    const uint32_t a1 = (half ? pl.z >> 4 : pl.z) & 0x0F0F0F0Fu, a3 = (half ? pl.w >> 4 : pl.w) & 0x0F0F0F0Fu;
+                                    const uint4 xv = xk[(2 * q + half) * 4];             // dead token columns read stale rows: they feed dead C columns only
+                                    int rh[4], rl[4];
+                                    mma_i8<1>(rh, a0, a1, a2, a3, xv.x, xv.y);             // high bytes of the activations (signed)
+                                    mma_i8<0>(rl, a0, a1, a2, a3, xv.z, xv.w);             // low bytes (unsigned)
+                                    const int s0 = int(__byte_perm(hdr.isc[0][half], 0u, 0x4440 + q)), s8 = int(__byte_perm(hdr.isc[1][half], 0u, 0x4440 + q));
+                                    main_[0] += s0 * (rh[0] * 256 + rl[0]); main_[1] += s0 * (rh[1] * 256 + rl[1]);
+                                    main_[2] += s8 * (rh[2] * 256 + rl[2]); main_[3] += s8 * (rh[3] * 256 + rl[3]);
+                                }
+                                if (F::FLUSH_AT == q) {      // keep `main` inside 32 bits: hand the first half of the tile over now
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i) { acc[m][i] = fmaf(hdr.f_main[i >> 1], float(main_[i]), acc[m][i]); main_[i] = 0; }
+                                }
+                            }
+                            float corr[4];
+                            mma_f16_zero(corr, hdr.ca[0], hdr.ca[1], hdr.ca[2], hdr.ca[3], sp.x, sp.y);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                acc[m][i] = fmaf(hdr.f_main[i >> 1], float(main_[i]), fmaf(hdr.f_corr[i >> 1], corr[i], acc[m][i]));
+                        }
+                        __syncwarp();             // every lane has read its words: the slot can be refilled
+                        if (lane == 0) mbar_arrive(my_empty + 8 * c_slot);
+                        c_slot = c_slot + 1 == uint32_t(S) ? 0 : c_slot + 1;
+                        c_phase ^= c_slot == 0 ? 1u : 0u;
+                    }
+                }
+                if (!alive) break;
+                // epilogue: the lane holds rows g, g + 8 x token columns 2t, 2t + 1
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const int slot = 2 * t + q;
+                    if (slot >= nv) continue;
+                    const int a = perm[off + c0 + slot];
+                    const float is = p.inv_scale[x_row(a)];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int row = 16 * rt + g + 8 * h;
+                        if (row >= p.rows) continue;
+                        const float v0 = acc[0][2 * h + q] * is, v1 = acc[NMAT - 1][2 * h + q] * is;
+                        p.out[size_t(a) * p.rows + row] = MODE == 0 ? (v0 / (1.f + expf(-v0))) * v1 : v0;
+                    }
+                }
+            }
+            if (!alive) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(xempty + 8 * b);      // this warp is done with the item's activation rows
+            pass += items_q; grp += items_r;
+            if (grp >= groups) { grp -= groups; ++pass; }
+        }
+        if (!alive) { *abort_flag = 1; if (lane == 0) atomicExch(p.plan + PLAN_STATUS, 3); }
+    }
+    __syncthreads();          // nobody leaves while a copy into the block's shared memory may be in flight
+}
+
+int sm_count() {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    return sms;
+}
+constexpr size_t SMEM_LIMIT = 232448 - 1024;
+
+template <uint32_t T> size_t dec4_smem(int k, int nbuf, int stages) {
+    return BAR_BYTES + size_t(CTA_WARPS) * stages * SLOT_TILES * D4<T>::TILE + xs_bytes(k, nbuf);
+}
+// the largest (activation buffers, ring stages) that fit: two buffers before a fourth stage
+template <uint32_t T> bool dec4_fit(int k, int & nbuf, int & stages) {
+    const int opts[4][2] = {{2, 3}, {2, 2}, {1, 3}, {1, 2}};
+    for (const auto & o : opts)
+        if (dec4_smem<T>(k, o[0], o[1]) <= SMEM_LIMIT) { nbuf = o[0]; stages = o[1]; return true; }
+    return false;
+}
+
+int g_drop_tile = -1;                 // test hook (b2moe_debug_dec4_drop_tile)
+uint32_t g_wait_limit = WAIT_LIMIT;
+
+// max_items: an upper bound of passes * groups (the true count is read from the plan on the device)
+template <uint32_t T, int MODE>
+int32_t launch_dec4(Dec4Args a, long long max_items, cudaStream_t s) {
+    const int sms = sm_count(), k = a.k_tiles * 256;
+    if (sms <= 0) return B2MOE_ERR_CUDA;
+    if (!dec4_fit<T>(k, a.nbuf, a.stages)) return B2MOE_ERR_SHAPE;
+    const size_t smem = dec4_smem<T>(k, a.nbuf, a.stages);
+    if (cudaFuncSetAttribute(dec4_k<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
+    a.wait_limit = g_wait_limit;
+    a.drop_tile = g_drop_tile;
+    const int blocks = int(std::min<long long>(sms, std::max<long long>(1, max_items)));
+    dec4_k<T, MODE><<<blocks, THREADS, smem, s>>>(a);
+    return launch_status();
+}
+
+// row tiles per warp of one work item: as many as keep at least two items per SM (an item = a pass of <= 8 tokens x
+// CTA_WARPS * rpw row tiles), so that a handful of tokens still spreads over the SMs; at most row_tiles / 32
+inline int rpw_of(int rows, long long est_passes) {
+    const int row_tiles = ceil_div(rows, 16), sms = std::max(1, sm_count());
+    int rpw = std::max(1, row_tiles / (2 * CTA_WARPS));
+    while (rpw > 1 && est_passes * ceil_div(row_tiles, CTA_WARPS * rpw) < 2LL * sms) rpw >>= 1;
+    return rpw;
+}
+inline size_t staged_bytes(int rows_x, int k) { return align_up(size_t(rows_x) * staged_row_bytes(k), 256); }
+
+template <uint32_t T>
+int32_t stage(Dec4Args & a, const void * x, int dtype, int rows_x, int k, void * ws, cudaStream_t s) {
+    uint8_t * w = static_cast<uint8_t *>(ws);
+    float * inv = reinterpret_cast<float *>(w + staged_bytes(rows_x, k));
+    dec4_stage_k<<<rows_x, STAGE_WARPS * 32, 0, s>>>(x, dtype, rows_x, k, D4<T>::BITS, w, inv);
+    a.x = w; a.inv_scale = inv;
+    return launch_status();
+}
+
+template <uint32_t T>
+int32_t gateup_t(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_bank * sg, const b2moe_bank * su, const void * x, int x_dtype,
+                 const int * plan, int n, int topk, int shared_tokens, float * act, void * ws, int max_active, cudaStream_t s) {
+    const int k = gate->cols;
+    Dec4Args a{};
+    if (int32_t rc = stage<T>(a, x, x_dtype, n, k, ws, s)) return rc;
+    a.w0 = static_cast<const uint8_t *>(gate->data); a.w1 = static_cast<const uint8_t *>(up->data);
+    if (shared_tokens) { a.s0 = static_cast<const uint8_t *>(sg->data); a.s1 = static_cast<const uint8_t *>(su->data); }
+    a.bank_bytes = b2moe_bank_bytes(gate->type, gate->rows, gate->cols);
+    a.plan = const_cast<int *>(plan); a.out = act;
+    a.rows = gate->rows; a.k_tiles = k / 256; a.experts = gate->experts; a.topk = topk; a.A = n * topk;
+    const long long est = (long long)max_active + (n * topk + shared_tokens) / PASS_TOKENS;
+    a.rpw = rpw_of(gate->rows, est);
+    return launch_dec4<T, 0>(a, est * ceil_div(ceil_div(gate->rows, 16), CTA_WARPS * a.rpw), s);
+}
+template <uint32_t T>
+int32_t down_t(const b2moe_bank * down, const b2moe_bank * sd, const float * act, const int * plan, int n, int topk, int shared_tokens,
+               float * y, void * ws, int max_active, cudaStream_t s) {
+    const int rows_x = n * topk + shared_tokens, k = down->cols;
+    Dec4Args a{};
+    if (int32_t rc = stage<T>(a, act, B2MOE_F32, rows_x, k, ws, s)) return rc;
+    a.w0 = static_cast<const uint8_t *>(down->data);
+    if (shared_tokens) a.s0 = static_cast<const uint8_t *>(sd->data);
+    a.bank_bytes = b2moe_bank_bytes(down->type, down->rows, down->cols);
+    a.plan = const_cast<int *>(plan); a.out = y;
+    a.rows = down->rows; a.k_tiles = k / 256; a.experts = down->experts; a.topk = topk; a.A = n * topk;
+    const long long est = (long long)max_active + rows_x / PASS_TOKENS;
+    a.rpw = rpw_of(down->rows, est);
+    return launch_dec4<T, 1>(a, est * ceil_div(ceil_div(down->rows, 16), CTA_WARPS * a.rpw), s);
+}
+
+}  // namespace
+
+// true when the 4-bit decode kernels take banks of this type with rows of length k
+bool dec4_supported(uint32_t type, int k) {
+    int nbuf, stages;
+    if (k <= 0 || k % 256) return false;
+    if (type == T_Q4_K) return dec4_fit<T_Q4_K>(k, nbuf, stages);
+    if (type == T_IQ3S4) return dec4_fit<T_IQ3S4>(k, nbuf, stages);
+    return false;
+}
+// scratch: the staged form of `rows_x` activation rows of length k and one float per row
+size_t dec4_workspace_bytes(int rows_x, int k) {
+    return staged_bytes(rows_x, k) + align_up(size_t(rows_x) * sizeof(float), 256);
+}
+int32_t dec4_gateup(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_bank * sg, const b2moe_bank * su, const void * x,
+                    int x_dtype, const int * plan, int n, int topk, int shared_tokens, float * act, void * ws, int max_active,
+                    cudaStream_t s) {
+    if (gate->type == T_Q4_K) return gateup_t<T_Q4_K>(gate, up, sg, su, x, x_dtype, plan, n, topk, shared_tokens, act, ws, max_active, s);
+    if (gate->type == T_IQ3S4) return gateup_t<T_IQ3S4>(gate, up, sg, su, x, x_dtype, plan, n, topk, shared_tokens, act, ws, max_active, s);
+    return B2MOE_ERR_FORMAT;
+}
+int32_t dec4_down(const b2moe_bank * down, const b2moe_bank * sd, const float * act, const int * plan, int n, int topk,
+                  int shared_tokens, float * y, void * ws, int max_active, cudaStream_t s) {
+    if (down->type == T_Q4_K) return down_t<T_Q4_K>(down, sd, act, plan, n, topk, shared_tokens, y, ws, max_active, s);
+    if (down->type == T_IQ3S4) return down_t<T_IQ3S4>(down, sd, act, plan, n, topk, shared_tokens, y, ws, max_active, s);
+    return B2MOE_ERR_FORMAT;
+}
+void dec4_debug(int drop_tile, uint32_t wait_limit) {
+    g_drop_tile = drop_tile;
+    g_wait_limit = wait_limit ? wait_limit : WAIT_LIMIT;
+}
+
+}  // namespace b2

@@ -20,8 +20,6 @@
 // gave 3e-2 of the output RMS as the largest error, fp16 stays below the layer tolerance). An activation row is
 // multiplied by 2^e so that its largest magnitude lies in [2^14, 2^15) and rounded to fp16: exact for bf16 inputs down
 // to 2^-29 of the row maximum; the epilogue multiplies the sums (fp32) by 2^-e.
-#include <cstdlib>
-
 #include "common.cuh"
 #include "formats.cuh"
 #include "gemm_decode.cuh"
@@ -84,16 +82,6 @@ __global__ void rows_to_f16_k(const void * __restrict__ x, int dtype, int rows, 
         out[size_t(row) * k + j] = __float2half_rn(load_act(x, dtype, size_t(row) * k + (j & ~63) + gdec::colmap<T>(j & 63)) * scale);
 }
 
-#ifdef B2_GEMM_PROF
-__device__ unsigned long long g_gemm_prof[8];
-#define GP_DECL long long gp_acc[8] = {}, gp_last = clock64()
-#define GP_LAP(i) do { const long long _n = clock64(); gp_acc[i] += _n - gp_last; gp_last = _n; } while (0)
-#define GP_FLUSH(base, n) do { for (int _i = 0; _i < n; ++_i) atomicAdd(&g_gemm_prof[base + _i], (unsigned long long)gp_acc[_i]); } while (0)
-#else
-#define GP_DECL
-#define GP_LAP(i)
-#define GP_FLUSH(base, n)
-#endif
 
 // MODE 0: act[a][r] = silu(gate_r . x_tok(a)) * (up_r . x_tok(a));  MODE 1: y[a][r] = down_r . act[a]
 template <uint32_t T, int MODE, int NT>
@@ -168,7 +156,6 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
     if (warp == MMA_WARP) {
         // ---- MMA issuer ----
         uint32_t gk = 0, ic = 0;
-        GP_DECL;
         // descriptor halves: low = address / 16 | (bytes between k cores / 16) << 16; high = (128 / 16) | the format's fixed bit 46
         const uint32_t a_lo0 = ((saddr(a_st) & 0x3FFFFu) >> 4) | (uint32_t(A_LBO >> 4) << 16);
         const uint32_t b_lo0 = ((saddr(b_st) & 0x3FFFFu) >> 4) | (uint32_t(B_LBO >> 4) << 16);
@@ -177,16 +164,12 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
             const Item im = locate(it);
             const uint32_t npad = uint32_t(im.nv + 15) & ~15u, id = idesc(G_ROWS, npad, 0), ab = ic % ACC_SETS;
             if (lane == 0) {
-                GP_LAP(3);
                 if (ic >= ACC_SETS && !bar_wait(acc_empty + 8 * ab, ((ic / ACC_SETS) - 1) & 1u, 100)) give_up();
                 fence_after();
-                GP_LAP(0);
                 for (int ks = 0; ks < ksteps && !*abort_flag; ++ks, ++gk) {
                     const uint32_t sa = gk % A_STAGES, sb = gk % B_STAGES;
                     if (!bar_wait(a_full + 8 * sa, (gk / A_STAGES) & 1u, 40)) { give_up(); break; }
-                    GP_LAP(1);
                     if (!bar_wait(b_full + 8 * sb, (gk / B_STAGES) & 1u, 40)) { give_up(); break; }
-                    GP_LAP(2);
                     fence_after();
                     const uint32_t a_lo = a_lo0 + sa * uint32_t((NMAT * A_MAT) >> 4), b_lo = b_lo0 + sb * uint32_t(B_STAGE >> 4);
                     const uint32_t d0 = tmem + ab * (NMAT * G_NT);
@@ -199,13 +182,11 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
                     }
                     mma_commit(a_empty + 8 * sa);
                     mma_commit(b_empty + 8 * sb);
-                    GP_LAP(3);
                 }
                 mma_commit(acc_full + 8 * ab);
             }
             __syncwarp();
         }
-        if (lane == 0) GP_FLUSH(0, 4);
     } else if (warp < LOAD_WARP0) {
         // ---- epilogue: warp q reads TMEM lanes [32 q, 32 q + 32) = rows of the block ----
         const int q = warp & 3;
@@ -300,7 +281,6 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
         const uint32_t my_full = raw_full + 8 * tw * RAW_SLOTS, my_empty = raw_empty + 8 * tw * RAW_SLOTS;
         uint32_t gk = 0, gc = 0;
         bool ok = true;
-        GP_DECL;
         for (int it = blockIdx.x; it < n_items && ok && !*abort_flag; it += gridDim.x) {
             const Item im = locate(it);
             const int rt = im.rb * 8 + tw;
@@ -325,9 +305,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
                     if (!issue(c, gc + c)) { give_up(); break; }
             for (int c = 0; c < nchunks && ok; ++c, gc += live ? 1u : 0u) {     // a dead row tile (past the last row) uses no slot
                 const uint32_t slot = gc % RAW_SLOTS;
-                GP_LAP(3);
                 if (live && !__all_sync(0xffffffffu, bar_wait(my_full + 8 * slot, (gc / RAW_SLOTS) & 1u, DEC_BACKOFF))) { ok = false; break; }
-                GP_LAP(0);
                 const int steps = min(4, ksteps - 4 * c);
                 typename gdec::Dec<T>::Pre pre[NMAT];                  // per-chunk constants of the decoder
                 if (live) {
@@ -337,7 +315,6 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
                 for (int j = 0; j < steps; ++j, ++gk) {
                     const uint32_t sa = gk % A_STAGES;
                     if (gk >= A_STAGES && !__all_sync(0xffffffffu, bar_wait(a_empty + 8 * sa, ((gk / A_STAGES) - 1) & 1u, DEC_BACKOFF))) { ok = false; break; }
-                    GP_LAP(1);
                     if (live) {
 #pragma unroll
                         for (int m = 0; m < NMAT; ++m) {
@@ -354,7 +331,6 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0) bar_arrive(a_full + 8 * sa);
-                    GP_LAP(2);
                 }
                 __syncwarp();                                          // every lane is done with the slot
                 if (live && lane == 0) {
@@ -365,7 +341,6 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
             }
         }
         if (!ok && lane == 0) give_up();
-        if (lane == 0 && dwi == 0) GP_FLUSH(4, 4);
     }
     fence_before();
     __syncthreads();
@@ -389,13 +364,13 @@ int32_t gemm_launch_nt(const GemmArgs & a, int sms, cudaStream_t s) {
 }
 // 128-token items. The 256-token variant (weights decoded once per 256 tokens, but one accumulator set and two B stages) is
 // correct and slower where it was measured (c5, 512 tokens per expert: 261 against 395 TFLOP/s: the gathered B loads with one
-// step of lookahead become the limit); B2MOE_GEMM_NT=256 selects it for measurements
+// step of lookahead become the limit); b2moe_harness_select(.., 256) selects it for measurements
+int g_item_tokens = 128;
 template <uint32_t T, int MODE>
 int32_t gemm_launch_t(const GemmArgs & a, cudaStream_t s) {
     const int sms = gemm_sm_count();
     if (sms <= 0) return B2MOE_ERR_CUDA;
-    const char * v = std::getenv("B2MOE_GEMM_NT");
-    const bool wide = v && v[0] == '2';
+    const bool wide = g_item_tokens == 256;
     if (wide && gemm_smem<T, MODE == 0 ? 2 : 1, 256>(a.experts) <= GEMM_SMEM_LIMIT) return gemm_launch_nt<T, MODE, 256>(a, sms, s);
     return gemm_launch_nt<T, MODE, 128>(a, sms, s);
 }
@@ -404,6 +379,7 @@ int32_t gemm_launch(uint32_t type, const GemmArgs & a, cudaStream_t s) {
     switch (type) {
         case T_Q4_K: return gemm_launch_t<T_Q4_K, MODE>(a, s);
         case T_IQ3_S: return gemm_launch_t<T_IQ3_S, MODE>(a, s);
+        case T_IQ3S4: return gemm_launch_t<T_IQ3S4, MODE>(a, s);
         case T_IQ4_XS: return gemm_launch_t<T_IQ4_XS, MODE>(a, s);
         case T_IQ4_NL: return gemm_launch_t<T_IQ4_NL, MODE>(a, s);
         case T_NVFP4G: return gemm_launch_t<T_NVFP4G, MODE>(a, s);
@@ -414,6 +390,7 @@ size_t gemm_smem_of(uint32_t type, int nmat, int experts) {
     switch (type) {
         case T_Q4_K: return nmat == 2 ? gemm_smem<T_Q4_K, 2, 128>(experts) : gemm_smem<T_Q4_K, 1, 128>(experts);
         case T_IQ3_S: return nmat == 2 ? gemm_smem<T_IQ3_S, 2, 128>(experts) : gemm_smem<T_IQ3_S, 1, 128>(experts);
+        case T_IQ3S4: return nmat == 2 ? gemm_smem<T_IQ3S4, 2, 128>(experts) : gemm_smem<T_IQ3S4, 1, 128>(experts);
         case T_IQ4_XS: return nmat == 2 ? gemm_smem<T_IQ4_XS, 2, 128>(experts) : gemm_smem<T_IQ4_XS, 1, 128>(experts);
         case T_IQ4_NL: return nmat == 2 ? gemm_smem<T_IQ4_NL, 2, 128>(experts) : gemm_smem<T_IQ4_NL, 1, 128>(experts);
         case T_NVFP4G: return nmat == 2 ? gemm_smem<T_NVFP4G, 2, 128>(experts) : gemm_smem<T_NVFP4G, 1, 128>(experts);
@@ -425,6 +402,7 @@ int32_t convert_rows(uint32_t type, const void * x, int dtype, int rows, int k, 
     switch (type) {
         case T_Q4_K: rows_to_f16_k<T_Q4_K><<<blocks, 256, 0, s>>>(x, dtype, rows, k, out, inv); break;
         case T_IQ3_S: rows_to_f16_k<T_IQ3_S><<<blocks, 256, 0, s>>>(x, dtype, rows, k, out, inv); break;
+        case T_IQ3S4: rows_to_f16_k<T_IQ3S4><<<blocks, 256, 0, s>>>(x, dtype, rows, k, out, inv); break;
         case T_IQ4_XS: rows_to_f16_k<T_IQ4_XS><<<blocks, 256, 0, s>>>(x, dtype, rows, k, out, inv); break;
         case T_IQ4_NL: rows_to_f16_k<T_IQ4_NL><<<blocks, 256, 0, s>>>(x, dtype, rows, k, out, inv); break;
         case T_NVFP4G: rows_to_f16_k<T_NVFP4G><<<blocks, 256, 0, s>>>(x, dtype, rows, k, out, inv); break;
@@ -435,6 +413,7 @@ int32_t convert_rows(uint32_t type, const void * x, int dtype, int rows, int k, 
 
 }  // namespace
 
+void gemm_tc_item_tokens(int tokens) { g_item_tokens = tokens == 256 ? 256 : 128; }
 // true when the tensor-core GEMM takes banks of this type with rows of length k (nmat: 2 = gate/up, 1 = down)
 bool gemm_tc_supported(uint32_t type, int k, int nmat, int experts) {
     return k >= G_KS && k % G_KS == 0 && gemm_smem_of(type, nmat, experts) <= GEMM_SMEM_LIMIT;
@@ -480,12 +459,3 @@ int32_t gemm_tc_down(const b2moe_bank * down, const b2moe_bank * sd, const float
 }
 
 }  // namespace b2
-
-#ifdef B2_GEMM_PROF
-// debug builds only: reads and clears the cycle counters of gemm_tc_k
-extern "C" B2MOE_API int b2moe_gemm_prof_read(unsigned long long * out8) {
-    unsigned long long zero[8] = {};
-    if (cudaMemcpyFromSymbol(out8, b2::g_gemm_prof, sizeof(zero)) != cudaSuccess) return 1;
-    return cudaMemcpyToSymbol(b2::g_gemm_prof, zero, sizeof(zero)) != cudaSuccess;
-}
-#endif

@@ -93,6 +93,7 @@ int32_t launch(uint32_t type, const GroupArgs & g, const void * x, int x_dtype, 
     switch (type) {
         case T_Q4_K: return launch_t<T_Q4_K, MODE>(g, x, x_dtype, plan, out, max_active, s);
         case T_IQ3_S: return launch_t<T_IQ3_S, MODE>(g, x, x_dtype, plan, out, max_active, s);
+        case T_IQ3S4: return launch_t<T_IQ3S4, MODE>(g, x, x_dtype, plan, out, max_active, s);
         case T_IQ4_XS: return launch_t<T_IQ4_XS, MODE>(g, x, x_dtype, plan, out, max_active, s);
         case T_IQ4_NL: return launch_t<T_IQ4_NL, MODE>(g, x, x_dtype, plan, out, max_active, s);
         case T_NVFP4G: return launch_t<T_NVFP4G, MODE>(g, x, x_dtype, plan, out, max_active, s);

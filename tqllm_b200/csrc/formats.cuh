@@ -18,7 +18,9 @@
 
 namespace b2 {
 
-enum : uint32_t { T_Q4_K = 12, T_IQ4_NL = 20, T_IQ3_S = 21, T_IQ4_XS = 23, T_NVFP4G = 323 };
+enum : uint32_t { T_Q4_K = 12, T_IQ4_NL = 20, T_IQ3_S = 21, T_IQ4_XS = 23, T_NVFP4G = 323,
+                  // IQ3_S blocks held as 4-bit codes (no grid lookup on the read side): a bank layout of this library, not a GGUF type
+                  T_IQ3S4 = 0x1015 };
 
 struct FmtInfo {
     int kt;         // columns per tile
@@ -34,6 +36,7 @@ __host__ __device__ inline bool fmt_info(uint32_t type, FmtInfo & f) {
     switch (type) {
         case T_Q4_K: f = {256, 2304, 256, 144, 512, 8, false}; return true;
         case T_IQ3_S: f = {256, 1760, 256, 110, 1024, 4, false}; return true;
+        case T_IQ3S4: f = {256, 2144, 256, 110, 512, 8, false}; return true;
         case T_IQ4_XS: f = {256, 2176, 256, 136, 512, 8, false}; return true;
         case T_IQ4_NL: f = {32, 288, 32, 18, 64, 8, false}; return true;
         case T_NVFP4G: f = {128, 1152, 128, 76, 256, 8, true}; return true;
@@ -214,6 +217,63 @@ template <> struct Fmt<T_IQ3_S> {
     }
     static constexpr int STEP_UNITS = 256;
     __host__ __device__ static void step_unit(int j, int i, int & tl, int & u) { tl = 0; u = (i >> 4) * 64 + (2 * j + ((i >> 3) & 1)) * 8 + (i & 7); }
+};
+
+template <> struct Fmt<T_IQ3S4> {
+    // IQ3_S blocks with the grid lookup and the sign already applied when the bank is packed: an IQ3_S weight is
+    // d (1 + 2 s) (+-m), m an odd magnitude 1..15, so +-m = 2 n - 15 with a 4-bit code n = (15 +- m) / 2. The tile has the
+    // shape of the Q4_K tile: planes p = 0..3 (sub-blocks 2p, 2p + 1) at 512 p + 16 L: {row g: word t, word t + 4;
+    // row g + 8: the same}; byte i of word m holds the codes of weight 4 m + i of sub-block 2p (low nibble) and of
+    // sub-block 2p + 1 (high nibble). 2048 + 4 row: the raw scale bytes (nibble ib = 4-bit scale of sub-block ib);
+    // 2112 + 2 row: d (fp16). 134 bytes per 256 weights against the 110 of the GGUF block.
+    static constexpr int KT = 256, TILE = 2144, RAW = 110;
+    __host__ __device__ static uint32_t code(const uint8_t * blk, int ib, int j) {
+        const int w = j >> 2, i = j & 3;
+        const uint32_t idx = Fmt<T_IQ3_S>::grid_index(blk, ib, w);
+        const uint32_t mag = (B2_GRID(idx) >> (8 * i)) & 255u;
+        const uint32_t neg = (uint32_t(blk[74 + 4 * ib + (w >> 1)]) >> (4 * (w & 1) + i)) & 1u;
+        return neg ? (15u - mag) >> 1 : (15u + mag) >> 1;
+    }
+    __host__ __device__ static uint32_t pack_word(const uint8_t * raw, int rows, int nblk, int rt, int kt, int wi) {
+        if (wi < 512) {
+            const int p = wi >> 7, L = (wi >> 2) & 31, c = wi & 3;
+            const int row = 16 * rt + (L >> 2) + 8 * (c >> 1), m = (L & 3) + 4 * (c & 1);
+            if (row >= rows) return 0u;
+            const uint8_t * blk = raw + (size_t(row) * nblk + kt) * RAW;
+            uint32_t v = 0;
+            for (int i = 0; i < 4; ++i) v |= (code(blk, 2 * p, 4 * m + i) | (code(blk, 2 * p + 1, 4 * m + i) << 4)) << (8 * i);
+            return v;
+        }
+        if (wi < 528) {
+            const int row = 16 * rt + (wi - 512);
+            return row < rows ? ld_u32_bytes(raw + (size_t(row) * nblk + kt) * RAW + 106) : 0u;
+        }
+        uint32_t v = 0;
+        for (int i = 0; i < 2; ++i) {
+            const int row = 16 * rt + 2 * (wi - 528) + i;
+            if (row < rows) v |= ld_u16_bytes(raw + (size_t(row) * nblk + kt) * RAW) << (16 * i);
+        }
+        return v;
+    }
+    __host__ __device__ static void unit_vals(const uint8_t * tile, const float *, int u, float (&v)[8], int & row, int & k0, int & k1,
+                                              const uint32_t * = nullptr) {
+        row = u >> 5;
+        const int p = (u >> 3) & 3, m = u & 7;
+        const int L = 4 * (row & 7) + (m & 3);
+        const uint32_t w = *reinterpret_cast<const uint32_t *>(tile + 512 * p + 16 * L + 8 * (row >> 3) + 4 * (m >> 2));
+        const uint32_t sc = *reinterpret_cast<const uint32_t *>(tile + 2048 + 4 * row);
+        const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(tile + 2112 + 2 * row));
+        const float db1 = d * float(1 + 2 * int((sc >> (8 * p)) & 15u)), db2 = d * float(1 + 2 * int((sc >> (8 * p + 4)) & 15u));
+        k0 = 64 * p + 4 * m;
+        k1 = k0 + 32;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[i] = db1 * float(2 * int((w >> (8 * i)) & 15u) - 15);          // exact: the host decoder's db * magnitude, negated
+            v[4 + i] = db2 * float(2 * int((w >> (8 * i + 4)) & 15u) - 15);
+        }
+    }
+    static constexpr int STEP_UNITS = 128;
+    __host__ __device__ static void step_unit(int j, int i, int & tl, int & u) { tl = 0; u = (i >> 3) * 32 + j * 8 + (i & 7); }
 };
 
 template <> struct Fmt<T_IQ4_XS> {

@@ -26,7 +26,7 @@ constexpr int A_LBO = 2048 + 32;            // bytes between the k cores of the 
 // column (0..63, inside the step) held at operand position pos (0..63)
 template <uint32_t T> __host__ __device__ inline int colmap(int pos) {
     const int c = pos >> 3, q = pos & 7;                               // core, position inside the 16-byte row
-    if (T == T_Q4_K) return q < 4 ? 4 * c + q : 32 + 4 * c + (q - 4); // word c: low nibbles = sub-block 0, high = sub-block 1
+    if (T == T_Q4_K || T == T_IQ3S4) return q < 4 ? 4 * c + q : 32 + 4 * c + (q - 4); // word c: low nibbles = sub-block 0, high = sub-block 1
     if (T == T_IQ4_XS || T == T_IQ4_NL) return 32 * (c >> 2) + 4 * (c & 3) + (q >> 1) + 16 * (q & 1);   // byte i: columns i, i + 16
     return pos;                                                        // IQ3_S, NVFP4G: eight consecutive columns per word
 }
@@ -126,6 +126,30 @@ template <> struct Dec<T_Q4_K> {
         const float S2 = __shfl_sync(0xffffffffu, pre.S[1], src), C2 = __shfl_sync(0xffffffffu, pre.C[1], src);
         *core_row(dst, t, g + 8 * r) = word(wa, S1, C1, S2, C2);
         *core_row(dst, t + 4, g + 8 * r) = word(wb, S1, C1, S2, C2);
+    }
+};
+
+// IQ3_S held as 4-bit codes (formats.cuh, Fmt<T_IQ3S4>): the tile has the Q4_K shape and a weight is db (2 n - 15), so the
+// Q4_K word decoder serves it with S = 32 db and C = -47 db (S (1 + n / 16) + C = db (2 n - 15), exact in fp32)
+template <> struct Dec<T_IQ3S4> {
+    static constexpr int TAB_BYTES = 0;
+    __device__ static void init(void *, int, int) {}
+    using Pre = Dec<T_Q4_K>::Pre;
+    __device__ __forceinline__ static Pre prep(const uint8_t * chunk, int lane, int r) {
+        const int g = lane >> 2, t = lane & 3, row = g + 8 * r;
+        const uint32_t sc = *reinterpret_cast<const uint32_t *>(chunk + 2048 + 4 * row);
+        const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(chunk + 2112 + 2 * row)));
+        Pre p;
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            const float db = d * float(1 + 2 * int((sc >> (4 * (2 * t + b))) & 15u));
+            p.S[b] = 32.f * db;
+            p.C[b] = -47.f * db;
+        }
+        return p;
+    }
+    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void * tab, int r, const Pre & pre) {
+        Dec<T_Q4_K>::step<J>(chunk, lane, dst, tab, r, pre);
     }
 };
 

@@ -4,8 +4,6 @@
 #include "common.cuh"
 #include "formats.cuh"
 
-#include <cstdlib>
-
 namespace b2 {
 int32_t check_bank(const b2moe_bank * b);
 int32_t generic_gateup(const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const void *, int, const int *, int,
@@ -13,19 +11,21 @@ int32_t generic_gateup(const b2moe_bank *, const b2moe_bank *, const b2moe_bank 
 int32_t generic_down(const b2moe_bank *, const b2moe_bank *, const float *, const int *, int, int, int, float *, cudaStream_t);
 size_t iq3s_workspace_bytes(int rows_x, int k, int dtype);
 bool iq3s_supported(int k, int dtype);
-bool iq3s_tc_supported(int k, int dtype, int nmat);
-size_t iq3s_tc_workspace_bytes(int rows_x, int k, int dtype);
-int32_t iq3s_tc_gateup(const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const void *, int, const int *, int,
-                       int, int, float *, void *, int, cudaStream_t);
-int32_t iq3s_tc_down(const b2moe_bank *, const b2moe_bank *, const float *, const int *, int, int, int, float *, void *, int, cudaStream_t);
 int32_t iq3s_gateup(const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const void *, int, const int *, int,
                     int, int, float *, void *, int, cudaStream_t);
 int32_t iq3s_down(const b2moe_bank *, const b2moe_bank *, const float *, const int *, int, int, int, float *, void *, int, cudaStream_t);
+bool dec4_supported(uint32_t type, int k);
+size_t dec4_workspace_bytes(int rows_x, int k);
+int32_t dec4_gateup(const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const void *, int, const int *, int,
+                    int, int, float *, void *, int, cudaStream_t);
+int32_t dec4_down(const b2moe_bank *, const b2moe_bank *, const float *, const int *, int, int, int, float *, void *, int, cudaStream_t);
+void dec4_debug(int drop_tile, uint32_t wait_limit);
 bool gemm_tc_supported(uint32_t type, int k, int nmat, int experts);
 size_t gemm_tc_workspace_bytes(int rows_x, int k);
 int32_t gemm_tc_gateup(const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const void *, int, const int *, int,
                        int, int, float *, void *, cudaStream_t);
 int32_t gemm_tc_down(const b2moe_bank *, const b2moe_bank *, const float *, const int *, int, int, int, float *, void *, cudaStream_t);
+void gemm_tc_item_tokens(int tokens);
 
 namespace {
 int32_t same_shape(const b2moe_bank * a, const b2moe_bank * b, bool same_experts) {
@@ -38,35 +38,36 @@ int max_active_of(int experts, int n, int topk, int shared_tokens) {
     const long long a = (long long)n * topk;
     return int(a < experts ? a : experts) + (shared_tokens ? 1 : 0);
 }
-// Which IQ3_S decode kernel: 2 = tcgen05 (tensor-memory accumulators), 1 = mma.sync, 0 = none.
-// Default: mma.sync. B2MOE_IQ3S_PATH=tc selects the tcgen05 kernels, =generic none (A/B measurements).
-int iq3s_path(uint32_t type, int k, int dtype, int nmat) {
-    if (type != T_IQ3_S) return 0;
-    const char * v = std::getenv("B2MOE_IQ3S_PATH");
-    const int cap = !v ? 1 : (v[0] == 'g' ? 0 : v[0] == 'm' ? 1 : 2);
-    if (cap >= 2 && iq3s_tc_supported(k, dtype, nmat)) return 2;
-    if (cap >= 1 && iq3s_supported(k, dtype)) return 1;
-    return 0;
+// The decode kernel of a bank type: DEC_IQ3S for IQ3_S in its GGUF-sized layout (grid lookup in the kernel), DEC_4BIT for
+// banks of 4-bit codes (Q4_K, IQ3_S held as codes), DEC_NONE otherwise.
+enum { DEC_NONE = 0, DEC_IQ3S = 1, DEC_4BIT = 2 };
+int decode_kernel(uint32_t type, int k, int dtype) {
+    if (type == T_IQ3_S && iq3s_supported(k, dtype)) return DEC_IQ3S;
+    if (dec4_supported(type, k)) return DEC_4BIT;
+    return DEC_NONE;
 }
 // The kernel family of one expert product.
-//   PATH_DECODE  the IQ3_S decode kernels: every expert sees a few tokens, the product is bound by streaming the weights;
-//   PATH_GEMM    the tcgen05 grouped GEMM (all formats): the weights of an expert are decoded once per 128 tokens;
-//   PATH_GENERIC exact fp32 CUDA-core path: every shape, the floor under the other two.
-// Default: IQ3_S takes the decode kernels while the batch averages fewer than GEMM_MIN_PER assignments per expert or the bank
-// has fewer than GEMM_MIN_EXPERTS experts (too few 128-row x 128-token items to fill the SMs), everything else the GEMM. B2MOE_EXPERT_PATH=generic|decode|gemm forces a family where it supports the shape.
-enum { PATH_GENERIC = 0, PATH_DECODE = 1, PATH_GEMM = 3 };
+//   decode   every expert sees a few tokens, the product is bound by streaming the weights;
+//   GEMM     the tcgen05 grouped GEMM (all formats): the weights of an expert are decoded once per 128 tokens;
+//   generic  exact fp32 CUDA-core path: every shape, the floor under the other two.
+// Default: a type with a decode kernel takes it while the batch averages fewer than GEMM_MIN_PER assignments per expert
+// or the bank has fewer than GEMM_MIN_EXPERTS experts (too few 128-row x 128-token items to fill the SMs), everything
+// else the GEMM. b2moe_harness_select forces a family where it supports the shape (tests and benchmarks).
 constexpr int GEMM_MIN_PER = 32, GEMM_MIN_EXPERTS = 128;   // measured on the c2 shape: below either, the decode kernels' finer work items win
+int g_family = B2MOE_FAMILY_AUTO;
 int expert_path(uint32_t type, int k, int dtype, int nmat, int experts, long long assignments) {
-    const char * v = std::getenv("B2MOE_EXPERT_PATH");
-    const char f = v ? v[0] : 'a';
-    if (f == 'g' && v[1] == 'e' && v[2] == 'n') return PATH_GENERIC;
-    const bool dec = iq3s_path(type, k, dtype, nmat) > 0, gemm = gemm_tc_supported(type, k, nmat, experts);
-    if (f == 'd') return dec ? PATH_DECODE : PATH_GENERIC;
-    if (f == 'g') return gemm ? PATH_GEMM : dec ? PATH_DECODE : PATH_GENERIC;
-    if (dec && (!gemm || assignments < (long long)GEMM_MIN_PER * experts || experts < GEMM_MIN_EXPERTS)) return PATH_DECODE;
-    return gemm ? PATH_GEMM : PATH_GENERIC;
+    if (g_family == B2MOE_FAMILY_GENERIC) return B2MOE_FAMILY_GENERIC;
+    const bool dec = decode_kernel(type, k, dtype) != DEC_NONE, gemm = gemm_tc_supported(type, k, nmat, experts);
+    if (g_family == B2MOE_FAMILY_DECODE) return dec ? B2MOE_FAMILY_DECODE : B2MOE_FAMILY_GENERIC;
+    if (g_family == B2MOE_FAMILY_GEMM) return gemm ? B2MOE_FAMILY_GEMM : dec ? B2MOE_FAMILY_DECODE : B2MOE_FAMILY_GENERIC;
+    if (dec && (!gemm || assignments < (long long)GEMM_MIN_PER * experts || experts < GEMM_MIN_EXPERTS)) return B2MOE_FAMILY_DECODE;
+    return gemm ? B2MOE_FAMILY_GEMM : B2MOE_FAMILY_GENERIC;
 }
 }  // namespace
+// true when b2moe_expert_down would take the format-generic kernels (which use no scratch) for this call
+bool expert_down_is_generic(const b2moe_bank * down, int n, int topk) {
+    return expert_path(down->type, down->cols, B2MOE_F32, 1, down->experts, (long long)n * topk) == B2MOE_FAMILY_GENERIC;
+}
 }  // namespace b2
 
 using namespace b2;
@@ -90,17 +91,21 @@ extern "C" B2MOE_API void b2moe_codebooks(uint32_t * grid, int8_t * kv) {
     if (kv) for (int i = 0; i < 16; ++i) kv[i] = h_kvalues_iq4nl[i];
 }
 
+extern "C" B2MOE_API void b2moe_harness_select(int32_t family, int32_t gemm_item_tokens) {
+    g_family = family >= B2MOE_FAMILY_AUTO && family <= B2MOE_FAMILY_GEMM ? family : B2MOE_FAMILY_AUTO;
+    gemm_tc_item_tokens(gemm_item_tokens);
+}
+extern "C" B2MOE_API void b2moe_harness_wait_probe(int32_t drop_tile, uint32_t wait_limit) { dec4_debug(drop_tile, wait_limit); }
+
 extern "C" B2MOE_API size_t b2moe_expert_workspace_bytes(uint32_t type, int32_t rows_x, int32_t k, int32_t x_dtype) {
     if (rows_x <= 0 || k <= 0 || !valid_dtype(x_dtype)) return 0;
-    size_t need = 0;                       // the larger of what the gate/up (2 matrices) and the down (1) product would take
-    for (int nmat = 1; nmat <= 2; ++nmat) {
-        const int path = iq3s_path(type, k, x_dtype, nmat);
-        const size_t b = path == 2 ? iq3s_tc_workspace_bytes(rows_x, k, x_dtype) : path == 1 ? iq3s_workspace_bytes(rows_x, k, x_dtype) : 0;
-        const size_t g = gemm_tc_workspace_bytes(rows_x, k);
-        need = b > need ? b : need;
-        need = g > need ? g : need;
-    }
-    return need;
+    FmtInfo f;
+    if (!fmt_info(type, f)) return 0;
+    // the largest of what the families that can serve this type would take (the family is chosen per call)
+    const int dk = decode_kernel(type, k, x_dtype);
+    size_t need = dk == DEC_IQ3S ? iq3s_workspace_bytes(rows_x, k, x_dtype) : dk == DEC_4BIT ? dec4_workspace_bytes(rows_x, k) : 0;
+    const size_t g = gemm_tc_workspace_bytes(rows_x, k);
+    return g > need ? g : need;
 }
 
 extern "C" B2MOE_API int32_t b2moe_expert_gateup_swiglu(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_bank * shared_gate,
@@ -120,18 +125,17 @@ extern "C" B2MOE_API int32_t b2moe_expert_gateup_swiglu(const b2moe_bank * gate,
     if (!x || !plan || !act) return B2MOE_ERR_NULL;
     if (!aligned16(x) || !aligned16(act)) return B2MOE_ERR_ALIGN;
     const int path = expert_path(gate->type, gate->cols, x_dtype, 2, gate->experts, (long long)n * topk);
-    if (path != PATH_GENERIC) {
+    if (path != B2MOE_FAMILY_GENERIC) {
         const size_t need = b2moe_expert_workspace_bytes(gate->type, n, gate->cols, x_dtype);
         if (need && !workspace) return B2MOE_ERR_NULL;
         if (need && !aligned16(workspace)) return B2MOE_ERR_ALIGN;
         if (workspace_bytes < need) return B2MOE_ERR_WORKSPACE;
-        if (path == PATH_GEMM)
+        if (path == B2MOE_FAMILY_GEMM)
             return gemm_tc_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, workspace, as_stream(stream));
-        if (iq3s_path(gate->type, gate->cols, x_dtype, 2) == 2)
-            return iq3s_tc_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, workspace,
-                                  max_active_of(gate->experts, n, topk, shared_tokens), as_stream(stream));
-        return iq3s_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, workspace,
-                           max_active_of(gate->experts, n, topk, shared_tokens), as_stream(stream));
+        const int ma = max_active_of(gate->experts, n, topk, shared_tokens);
+        if (decode_kernel(gate->type, gate->cols, x_dtype) == DEC_4BIT)
+            return dec4_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, workspace, ma, as_stream(stream));
+        return iq3s_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, workspace, ma, as_stream(stream));
     }
     return generic_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, as_stream(stream));
 }
@@ -148,18 +152,17 @@ extern "C" B2MOE_API int32_t b2moe_expert_down(const b2moe_bank * down, const b2
     if (!act || !plan || !y) return B2MOE_ERR_NULL;
     if (!aligned16(act) || !aligned16(y)) return B2MOE_ERR_ALIGN;
     const int path = expert_path(down->type, down->cols, B2MOE_F32, 1, down->experts, (long long)n * topk);
-    if (path != PATH_GENERIC) {
+    if (path != B2MOE_FAMILY_GENERIC) {
         const int rows_x = n * topk + shared_tokens;
         if (!workspace) return B2MOE_ERR_NULL;
         if (!aligned16(workspace)) return B2MOE_ERR_ALIGN;
         if (workspace_bytes < b2moe_expert_workspace_bytes(down->type, rows_x, down->cols, B2MOE_F32)) return B2MOE_ERR_WORKSPACE;
-        if (path == PATH_GEMM)
+        if (path == B2MOE_FAMILY_GEMM)
             return gemm_tc_down(down, shared_down, act, plan, n, topk, shared_tokens, y, workspace, as_stream(stream));
-        if (iq3s_path(down->type, down->cols, B2MOE_F32, 1) == 2)
-            return iq3s_tc_down(down, shared_down, act, plan, n, topk, shared_tokens, y, workspace,
-                                max_active_of(down->experts, n, topk, shared_tokens), as_stream(stream));
-        return iq3s_down(down, shared_down, act, plan, n, topk, shared_tokens, y, workspace,
-                         max_active_of(down->experts, n, topk, shared_tokens), as_stream(stream));
+        const int ma = max_active_of(down->experts, n, topk, shared_tokens);
+        if (decode_kernel(down->type, down->cols, B2MOE_F32) == DEC_4BIT)
+            return dec4_down(down, shared_down, act, plan, n, topk, shared_tokens, y, workspace, ma, as_stream(stream));
+        return iq3s_down(down, shared_down, act, plan, n, topk, shared_tokens, y, workspace, ma, as_stream(stream));
     }
     return generic_down(down, shared_down, act, plan, n, topk, shared_tokens, y, as_stream(stream));
 }

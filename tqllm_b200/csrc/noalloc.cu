@@ -19,6 +19,7 @@
 
 namespace b2 {
 int32_t check_bank(const b2moe_bank * b);
+bool expert_down_is_generic(const b2moe_bank * down, int n, int topk);
 
 namespace {
 
@@ -64,7 +65,9 @@ extern "C" B2MOE_API int32_t b2moe_expert_down_static(const b2moe_bank * down, c
     if (!act || !plan || !y) return B2MOE_ERR_NULL;
     if (!aligned16(act) || !aligned16(y)) return B2MOE_ERR_ALIGN;
     // the same kernels as b2moe_expert_down, with the library's own array as their workspace
-    const size_t need = b2moe_expert_workspace_bytes(down->type, n * topk + shared_tokens, down->cols, B2MOE_F32);
+    // (a call that takes the format-generic kernels uses no scratch: b2moe_expert_down ignores the workspace then)
+    const size_t need = expert_down_is_generic(down, n, topk) ? 0
+                                                              : b2moe_expert_workspace_bytes(down->type, n * topk + shared_tokens, down->cols, B2MOE_F32);
     if (need > B2MOE_STATIC_SCRATCH_BYTES) return B2MOE_ERR_CAPACITY;
     void * scratch = nullptr;
     if (need) {

@@ -154,13 +154,16 @@ class MoeLayer:
     """A resident MoE layer: router weight, expert banks (+ shared expert), and a workspace sized for `max_tokens`."""
 
     def __init__(self, shape, router_w, raw, shared_raw=None, sel_bias=None, shared_gate_vec=None, experts=None,
-                 device="cuda"):
+                 device="cuda", iq3s_layout="codes"):
+        """iq3s_layout: "codes" loads IQ3_S blocks into the 4-bit-code bank layout (capi.IQ3_S_X4: 21.8 % more HBM, decode
+        kernels without a codebook lookup), "gguf" into the layout of the GGUF block size."""
         E = experts or shape.experts
         self.shape, self.experts, self.device = shape, E, torch.device(device)
         H, F = shape.hidden, shape.ff
         dev = lambda t: None if t is None else t.to(self.device).contiguous()
         self.router_w, self.sel_bias, self.shared_gate_vec = dev(router_w), dev(sel_bias), dev(shared_gate_vec)
-        tg, tu, td = shape.types
+        assert iq3s_layout in ("codes", "gguf")
+        tg, tu, td = (capi.IQ3_S_X4 if (t == capi.IQ3_S and iq3s_layout == "codes") else t for t in shape.types)
         self.gate = DeviceBank(tg, dev(raw[0]), E, F, H)
         self.up = DeviceBank(tu, dev(raw[1]), E, F, H)
         self.down = DeviceBank(td, dev(raw[2]), E, H, F)
@@ -179,9 +182,9 @@ class MoeLayer:
         self.ws, self.ws_view, self.ws_tokens = None, None, 0
 
     @classmethod
-    def from_synth(cls, layer, device="cuda", experts=None, shared_gate_vec=None):
+    def from_synth(cls, layer, device="cuda", experts=None, shared_gate_vec=None, iq3s_layout="codes"):
         return cls(layer.shape, layer.router_w, layer.raw, layer.shared_raw, layer.sel_bias, shared_gate_vec,
-                   experts=experts or layer.router_w.shape[0], device=device)
+                   experts=experts or layer.router_w.shape[0], device=device, iq3s_layout=iq3s_layout)
 
     def reserve(self, n: int):
         if self.ws is not None and self.ws_tokens == n:
