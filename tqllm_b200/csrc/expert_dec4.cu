@@ -15,13 +15,14 @@
 // tile and accumulator apply d / dmin. The only rounding that matters is that of the activations to fixed point
 // (absolute error <= 2^-15 of the row's largest magnitude).
 //
-// Work. One resident block per SM: 16 consumer warps and one producer warp. An item = (pass of up to 8 tokens of one
-// active expert, group of 16 * rpw row tiles); items are dealt round-robin over the blocks. Consumer warp w multiplies
-// row tile(s) w of the group; lane w of the producer warp is its feeder: it streams the tiles warp w will read, in order,
-// over all items of the launch, through that warp's own ring of bulk copies (cp.async.bulk + mbarrier, no multicast;
-// a full and an empty barrier per slot), so the ring never drains between row tiles or items. Lanes 16 .. 23 of the
-// producer copy the staged activation rows of an item's tokens into one of two shared buffers, one item ahead; the
-// consumers hand a buffer back through a barrier of their own, so no block-wide barrier sits in the loop.
+// Work. One resident block per SM: 16 consumer warps and one producer warp. A job = (pass of up to 8 tokens of one active
+// expert, 16-row tile); the pass-major list of all jobs of the launch is cut into one contiguous share per block, equal
+// to within a job, which the block walks as segments (runs of row tiles of one pass). Consumer warp w multiplies every
+// 16th row tile of a segment; lane w of the producer warp is its feeder: it streams the tiles warp w will read, in
+// order, over the whole share, through that warp's own ring of bulk copies (cp.async.bulk + mbarrier, no multicast;
+// a full and an empty barrier per slot), so the ring never drains between jobs or segments. Lanes 16 .. 23 of the
+// producer copy the staged activation rows of a segment's tokens into one of two shared buffers, one segment ahead;
+// the consumers hand a buffer back through a barrier of their own, so no block-wide barrier sits in the loop.
 // Every wait is bounded; a wait that runs out sets the plan's status word and a block-wide flag, every warp stops at
 // its next wait or item, the producer lets the copies in flight land, and the block leaves.
 #include "common.cuh"
@@ -190,7 +191,7 @@ struct Dec4Args {
     const float * inv_scale;                 // [rows_x]
     int * plan;
     float * out;                             // [A + shared][rows]
-    int rows, k_tiles, experts, topk, A, rpw, nbuf, stages;
+    int rows, k_tiles, experts, topk, A, nbuf, stages;
     uint32_t wait_limit;
     int drop_tile;                           // test hook: the copy into ring slot use number drop_tile (per warp, counted from 0) is never issued; -1 = none
 };
@@ -220,8 +221,15 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
     const int * counts = p.plan + PLAN_HDR, * offsets = counts + e1, * active = offsets + e1 + 1, * perm = active + e1;
     const int * passes = perm + p.A + counts[p.experts];
     const int na = p.plan[PLAN_NACTIVE], row_tiles = (p.rows + 15) >> 4;
-    const int groups = (row_tiles + CTA_WARPS * p.rpw - 1) / (CTA_WARPS * p.rpw);
-    const int n_items = p.plan[PLAN_NPASS] * groups;
+    // the block's share of the launch: jobs [u_begin, u_end) of the pass-major list of (pass, row tile) jobs; it walks the
+    // share as segments = runs of row tiles [r0, r1) of one pass
+    const long long n_jobs = (long long)p.plan[PLAN_NPASS] * row_tiles;
+    const long long u_begin = n_jobs * blockIdx.x / gridDim.x, u_end = n_jobs * (blockIdx.x + 1) / gridDim.x;
+    auto segment = [&](long long u, int & pass, int & r0, int & r1) {
+        pass = int(u / row_tiles);
+        r0 = int(u - (long long)pass * row_tiles);
+        r1 = int(min((long long)row_tiles, r0 + (u_end - u)));
+    };
     const uint32_t xrow = xrow_bytes(K), xbuf = 8 * xrow, xglob = uint32_t(staged_row_bytes(K));
     const int S = p.stages, kslots = (p.k_tiles + SLOT_TILES - 1) / SLOT_TILES, nslots = kslots * NMAT;   // slots of one row job
     const uint32_t full0 = smem_addr(bars), empty0 = full0 + 8 * CTA_WARPS * MAX_STAGES, xfull = empty0 + 8 * CTA_WARPS * MAX_STAGES,
@@ -253,7 +261,6 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
         }
         return false;
     };
-    const int items_q = int(gridDim.x) / groups, items_r = int(gridDim.x) % groups;   // item + gridDim = (pass + q, group + r)
 
     if (warp == CTA_WARPS) {
         // ---- producer: lane w < 16 feeds consumer warp w (its ring, its barriers); lanes 16 .. 23 copy the activation rows ----
@@ -275,24 +282,25 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
                 bulk_g2s(xs0 + b * xbuf + (lane - 16) * xrow, p.x + x_row(perm[offsets[e] + c0 + lane - 16]) * xglob, xglob, xfull + 8 * b);
             ++xissued;
         };
-        int pass = int(blockIdx.x) / groups, grp = int(blockIdx.x) % groups;
+        int pass, r0, r1;
         uint32_t idx = 0;
-        if (int(blockIdx.x) < n_items) stage_x(pass, 0);
-        for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++idx) {
+        if (u_begin < u_end) { segment(u_begin, pass, r0, r1); stage_x(pass, 0); }
+        for (long long u = u_begin; u < u_end && ok; u += r1 - r0, ++idx) {
+            segment(u, pass, r0, r1);
             int e, c0;
             locate(pass, e, c0);
             const bool shared = e == p.experts;
-            int npass = pass + items_q, ngrp = grp + items_r;
-            if (ngrp >= groups) { ngrp -= groups; ++npass; }
-            bool next_staged = p.nbuf != 2 || it + int(gridDim.x) >= n_items;
-            int in_item = 0;
-            for (int jr = 0; jr < p.rpw && ok; ++jr) {
-                const int rt = (grp * p.rpw + jr) * CTA_WARPS + w;
-                const bool mine = lane < CTA_WARPS && rt < row_tiles;
+            const long long u_next = u + (r1 - r0);
+            int npass = 0, nr0, nr1;
+            if (u_next < u_end) segment(u_next, npass, nr0, nr1);
+            bool next_staged = p.nbuf != 2 || u_next >= u_end;
+            int in_seg = 0;
+            for (int rb = r0; rb < r1 && ok; rb += CTA_WARPS) {           // 16 row tiles at a time, warp w its own
+                const int rt = rb + w;
+                const bool mine = lane < CTA_WARPS && rt < r1;
                 const uint8_t * b0 = (shared ? p.s0 : p.w0 + size_t(e) * p.bank_bytes) + size_t(rt) * p.k_tiles * TILE;
                 const uint8_t * b1 = NMAT == 2 ? (shared ? p.s1 : p.w1 + size_t(e) * p.bank_bytes) + size_t(rt) * p.k_tiles * TILE : b0;
-                if ((grp * p.rpw + jr) * CTA_WARPS >= row_tiles) break;
-                for (int j = 0; j < nslots && ok; ++j, ++in_item) {
+                for (int j = 0; j < nslots && ok; ++j, ++in_seg) {
                     if (mine) {
                         if (issued >= uint32_t(S) && !wait(my_empty + 8 * slot, ((issued / S) - 1) & 1u)) ok = false;
                         else if (int(issued) != p.drop_tile) {
@@ -306,13 +314,12 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
                         slot = slot + 1 == uint32_t(S) ? 0 : slot + 1;
                     }
                     ok = __all_sync(0xffffffffu, ok);
-                    // once every consumer is S slots into this item, the previous item's buffer is free: bring the next item's rows
-                    if (!next_staged && in_item == S) { stage_x(npass, idx + 1); next_staged = true; }
+                    // once every consumer is S slots into this segment, the previous segment's buffer is free: bring the next one's rows
+                    if (!next_staged && in_seg == S) { stage_x(npass, idx + 1); next_staged = true; }
                 }
             }
             if (!next_staged && ok) stage_x(npass, idx + 1);
-            if (p.nbuf == 1 && it + int(gridDim.x) < n_items && ok) stage_x(npass, idx + 1);
-            pass = npass; grp = ngrp;
+            if (p.nbuf == 1 && u_next < u_end && ok) stage_x(npass, idx + 1);
         }
         if (!ok) { *abort_flag = 1; if (lane == 0) atomicExch(p.plan + PLAN_STATUS, 3); }
         // before leaving, every copy this lane issued must have landed: the last S slots of its ring (earlier ones were
@@ -333,9 +340,10 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
         const uint32_t my_full = full0 + 8 * warp * MAX_STAGES, my_empty = empty0 + 8 * warp * MAX_STAGES;
         uint32_t c_slot = 0, c_phase = 0;
         bool alive = true;
-        int pass = int(blockIdx.x) / groups, grp = int(blockIdx.x) % groups;
+        int pass, r0, r1;
         uint32_t idx = 0;
-        for (int it = blockIdx.x; it < n_items && alive; it += gridDim.x, ++idx) {
+        for (long long u = u_begin; u < u_end && alive; u += r1 - r0, ++idx) {
+            segment(u, pass, r0, r1);
             const uint32_t b = p.nbuf == 2 ? (idx & 1u) : 0u, use = p.nbuf == 2 ? idx >> 1 : idx;
             if (*abort_flag) break;
             if (!__all_sync(0xffffffffu, wait(xfull + 8 * b, use & 1u))) { alive = false; break; }
@@ -344,10 +352,16 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
             const int cnt = counts[e], off = offsets[e], nv = min(PASS_TOKENS, cnt - c0);
             const uint8_t * xw = xs + b * xbuf + g * xrow + t * 16;          // + sub-block * 64
             const uint8_t * rec = xs + b * xbuf + g * xrow + size_t(K) * 2 + t * 8;   // + tile * 32
+            // the lane's two token columns (2t, 2t + 1): assignment index and inverse activation scale, once per item
+            int col_a[2];
+            float col_is[2];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                col_a[q] = 2 * t + q < nv ? perm[off + c0 + 2 * t + q] : -1;
+                col_is[q] = col_a[q] >= 0 ? p.inv_scale[x_row(col_a[q])] : 0.f;
+            }
 
-            for (int jr = 0; jr < p.rpw && alive; ++jr) {
-                const int rt = (grp * p.rpw + jr) * CTA_WARPS + warp;
-                if (rt >= row_tiles) break;
+            for (int rt = r0 + warp; rt < r1 && alive; rt += CTA_WARPS) {
                 float acc[NMAT][4];
 #pragma unroll
                 for (int m = 0; m < NMAT; ++m)
@@ -407,10 +421,9 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
                 // epilogue: the lane holds rows g, g + 8 x token columns 2t, 2t + 1
 #pragma unroll
                 for (int q = 0; q < 2; ++q) {
-                    const int slot = 2 * t + q;
-                    if (slot >= nv) continue;
-                    const int a = perm[off + c0 + slot];
-                    const float is = p.inv_scale[x_row(a)];
+                    const int a = col_a[q];
+                    if (a < 0) continue;
+                    const float is = col_is[q];
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const int row = 16 * rt + g + 8 * h;
@@ -423,8 +436,6 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
             if (!alive) break;
             __syncwarp();
             if (lane == 0) mbar_arrive(xempty + 8 * b);      // this warp is done with the item's activation rows
-            pass += items_q; grp += items_r;
-            if (grp >= groups) { grp -= groups; ++pass; }
         }
         if (!alive) { *abort_flag = 1; if (lane == 0) atomicExch(p.plan + PLAN_STATUS, 3); }
     }
@@ -452,9 +463,8 @@ template <uint32_t T> bool dec4_fit(int k, int & nbuf, int & stages) {
 int g_drop_tile = -1;                 // test hook (b2moe_debug_dec4_drop_tile)
 uint32_t g_wait_limit = WAIT_LIMIT;
 
-// max_items: an upper bound of passes * groups (the true count is read from the plan on the device)
 template <uint32_t T, int MODE>
-int32_t launch_dec4(Dec4Args a, long long max_items, cudaStream_t s) {
+int32_t launch_dec4(Dec4Args a, cudaStream_t s) {
     const int sms = sm_count(), k = a.k_tiles * 256;
     if (sms <= 0) return B2MOE_ERR_CUDA;
     if (!dec4_fit<T>(k, a.nbuf, a.stages)) return B2MOE_ERR_SHAPE;
@@ -462,19 +472,10 @@ int32_t launch_dec4(Dec4Args a, long long max_items, cudaStream_t s) {
     if (cudaFuncSetAttribute(dec4_k<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
     a.wait_limit = g_wait_limit;
     a.drop_tile = g_drop_tile;
-    const int blocks = int(std::min<long long>(sms, std::max<long long>(1, max_items)));
-    dec4_k<T, MODE><<<blocks, THREADS, smem, s>>>(a);
+    dec4_k<T, MODE><<<sms, THREADS, smem, s>>>(a);       // every block takes an equal share of the (pass, row tile) jobs
     return launch_status();
 }
 
-// row tiles per warp of one work item: as many as keep at least two items per SM (an item = a pass of <= 8 tokens x
-// CTA_WARPS * rpw row tiles), so that a handful of tokens still spreads over the SMs; at most row_tiles / 32
-inline int rpw_of(int rows, long long est_passes) {
-    const int row_tiles = ceil_div(rows, 16), sms = std::max(1, sm_count());
-    int rpw = std::max(1, row_tiles / (2 * CTA_WARPS));
-    while (rpw > 1 && est_passes * ceil_div(row_tiles, CTA_WARPS * rpw) < 2LL * sms) rpw >>= 1;
-    return rpw;
-}
 inline size_t staged_bytes(int rows_x, int k) { return align_up(size_t(rows_x) * staged_row_bytes(k), 256); }
 
 template <uint32_t T>
@@ -497,9 +498,7 @@ int32_t gateup_t(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_ban
     a.bank_bytes = b2moe_bank_bytes(gate->type, gate->rows, gate->cols);
     a.plan = const_cast<int *>(plan); a.out = act;
     a.rows = gate->rows; a.k_tiles = k / 256; a.experts = gate->experts; a.topk = topk; a.A = n * topk;
-    const long long est = (long long)max_active + (n * topk + shared_tokens) / PASS_TOKENS;
-    a.rpw = rpw_of(gate->rows, est);
-    return launch_dec4<T, 0>(a, est * ceil_div(ceil_div(gate->rows, 16), CTA_WARPS * a.rpw), s);
+    return launch_dec4<T, 0>(a, s);
 }
 template <uint32_t T>
 int32_t down_t(const b2moe_bank * down, const b2moe_bank * sd, const float * act, const int * plan, int n, int topk, int shared_tokens,
@@ -512,9 +511,7 @@ int32_t down_t(const b2moe_bank * down, const b2moe_bank * sd, const float * act
     a.bank_bytes = b2moe_bank_bytes(down->type, down->rows, down->cols);
     a.plan = const_cast<int *>(plan); a.out = y;
     a.rows = down->rows; a.k_tiles = k / 256; a.experts = down->experts; a.topk = topk; a.A = n * topk;
-    const long long est = (long long)max_active + rows_x / PASS_TOKENS;
-    a.rpw = rpw_of(down->rows, est);
-    return launch_dec4<T, 1>(a, est * ceil_div(ceil_div(down->rows, 16), CTA_WARPS * a.rpw), s);
+    return launch_dec4<T, 1>(a, s);
 }
 
 }  // namespace
