@@ -373,9 +373,6 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
 #pragma unroll
                     for (int m = 0; m < NMAT; ++m) {
                         if (!__all_sync(0xffffffffu, wait(my_full + 8 * c_slot, c_phase))) { alive = false; break; }
-                        if (p.drop_tile == -2) {     // TEMP experiment: stream only
-                            acc[m][0] += float(reinterpret_cast<const uint32_t *>(my_ring + c_slot * SLOT)[lane]);
-                        } else
                         for (int kk = 0; kk < nt; ++kk) {
                             const int kt = ks * SLOT_TILES + kk;
                             const uint8_t * tile = my_ring + c_slot * SLOT + kk * TILE;
