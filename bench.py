@@ -7,21 +7,26 @@ and experts and reads the step's activations). One step = one pass of the 64 tok
 combine. The expert weights of the 4 layers (2.8 GB) are far larger than L2, so every step streams them from HBM.
 
 One JSON line on stdout (rank 0):
-  value      layer-tokens per second = tokens * layers / step time, inputs resident in HBM, CUDA-event timed
+  value      layer-tokens per second = tokens * layers / step time, inputs resident in HBM, CUDA-event timed: the K-step
+             region is timed `--repeats` times and the median taken (min / max under "repeats")
   e2e        the same through host buffers: pinned-host -> device copy of the activations and device -> host copy of
              the layer outputs inside the timed region
-  roofline   the dominant kernel (the grouped gate/up + SwiGLU product): GGUF block bytes of the gate and up matrices
-             of the experts it touched / its CUDA-event duration, against the measured HBM copy bandwidth
-  cpu_baseline  the CPU path timed on this box's host cores on a bounded sample (one layer, the same 64 tokens)
+  roofline   the dominant kernel (the grouped gate/up + SwiGLU product, timed alone): GGUF block bytes of the gate and
+             up matrices of the experts it touched / its CUDA-event duration, against the measured HBM copy bandwidth
+  sweep, workloads   extra records, not the headline: the decode batch sweep (1 / 4 / 16 tokens) of the same layers and
+             one record per other benchmark configuration (c3 4096 tokens, c4 16 and 2048 tokens, c5 8192 tokens)
+  cpu_baseline  the reference's production CPU expert pool timed on this box's host cores on a bounded sample
 
-`--impl reference` times the reference's CPU implementation of the path (the reference's own sources compiled in place
-under oracle/_ref when present, else the oracle restatement) on the same workload, one layer per step.
+`--impl reference` times the reference's CPU implementation of the path on the same workload, one layer per step: its
+production expert pool (CpuMissPool: int8 AVX2 gate / up dots) where the checker library holds it, with the
+reference's fp32 host path (dequantize_host + moe_expert_ffn) as a second, labelled record.
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+import statistics
 import subprocess
 import sys
 import threading
@@ -34,6 +39,8 @@ METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 TOKENS, LAYERS = 64, 4
 SEED = 20261125
+# dense tensor-core peaks nobody measured on this pool: NVIDIA's per-GPU figures for B200 (labelled "nominal" wherever used)
+NOMINAL_TFLOPS = {"int8": 4500.0, "fp4": 9000.0}
 
 
 def parse():
@@ -46,10 +53,12 @@ def parse():
                    help="layer shape (tqllm_b200.synth.CONFIGS); c2 is the headline workload, the others are for profiling")
     p.add_argument("--tokens", type=int, default=0, help="tokens per step per GPU (default: 64; 4096 / 2048 / 8192 for c3 / c4 / c5)")
     p.add_argument("--layers", type=int, default=0, help="stacked layers per step (default: 4 for c2, else 1)")
-    p.add_argument("--graph", type=int, default=1, help="1: replay the step as a CUDA graph (expert parallel: the compute phases only, the collectives between them are "
-                        "issued directly); 0: launch everything directly")
+    p.add_argument("--graph", type=int, default=1, help="1: replay the step as a CUDA graph (expert parallel: the compute phases only, the "
+                        "collectives between them are issued directly); 0: launch everything directly")
+    p.add_argument("--repeats", type=int, default=30, help="how many times the K-step region is timed (the median is reported)")
     p.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    p.add_argument("--sweep", action="store_true", help="also time 1 / 4 / 16 tokens (extra keys, not the headline)")
+    p.add_argument("--no-extras", action="store_true", help="skip the sweep and the records of the other configurations")
+    p.add_argument("--iq3s-layout", default="codes", choices=("codes", "gguf"), help="bank layout of IQ3_S experts")
     return p.parse_args()
 
 
@@ -121,70 +130,268 @@ def make_layers(synth, shape, layers, device, experts=None):
     return [synth.make_layer(shape, SEED + 17 * l, device, experts=experts, router_scale=scale) for l in range(layers)], scale
 
 
-# ------------------------------------------------------------------------------------------------ CPU arm ----
-def cpu_layer_time(kind_wanted, shape, layer, x, threads):
-    """seconds for one layer forward of x on the host cores; returns (seconds, kind)"""
-    import numpy as np
+def cpu_model():
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("model name"):
+                return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
 
-    import oracle
-    orc = oracle.oracle()
-    ref = oracle.reference() if kind_wanted == "reference" else None
-    xf = x.float().cpu().numpy()
-    raw = [t.cpu().numpy() for t in layer.raw]
-    sh = tuple(t.cpu().numpy() for t in layer.shared_raw) if layer.shared_raw is not None else None
-    rw = layer.router_w.cpu().numpy()
-    E = rw.shape[0]
+
+# ------------------------------------------------------------------------------------------------ CPU arms ----
+class CpuLayer:
+    """one layer of the workload on the host: raw GGUF blocks as numpy arrays + the routing inputs"""
+
+    def __init__(self, shape, layer, x):
+        self.shape = shape
+        self.x = x.float().cpu().numpy()
+        self.raw = [t.cpu().numpy() for t in layer.raw]
+        self.sh = tuple(t.cpu().numpy() for t in layer.shared_raw) if layer.shared_raw is not None else None
+        self.rw = layer.router_w.cpu().numpy()
+        self.bias = None if layer.sel_bias is None else layer.sel_bias.cpu().numpy()
+        self.E = self.rw.shape[0]
+
+
+def pool_threads():
+    """workers of the reference's pool: it pins them to CPUs 1 .. T and the calling thread to CPU 0"""
+    return max(1, (os.cpu_count() or 2) - 1)
+
+
+def time_pool_layer(cl: CpuLayer, pool, orc, ref):
+    """seconds for one layer through the reference's production path: router logits (fp32 dots), moe_route, CpuMissPool, combine"""
+    sh = cl.shape
+    t0 = time.perf_counter()
+    logits = orc.router_logits(cl.rw, cl.x)
+    ids, w = (ref or orc).route(sh.gating, logits, sh.topk, sh.norm, sh.scale, cl.bias)
+    pool.layer(x=cl.x, ids=ids, weights=w, ff=sh.ff, types=sh.types, gate=cl.raw[0], up=cl.raw[1], down=cl.raw[2], experts=cl.E, shared=cl.sh)
+    return time.perf_counter() - t0
+
+
+def time_fp32_layer(cl: CpuLayer, orc, ref, threads):
+    """seconds for one layer through the fp32 host path (the reference's dequantize_host + moe_expert_ffn, or the oracle port)"""
+    sh = cl.shape
     t0 = time.perf_counter()
     if ref is not None:
-        logits = orc.router_logits(rw, xf)          # the reference CPU path has no router GEMV of its own (moe.cu is CUDA)
-        ref.moe_layer(x=xf, topk=shape.topk, ff=shape.ff, gating=shape.gating, norm=shape.norm, scale=shape.scale, types=shape.types,
-                      gate=raw[0], up=raw[1], down=raw[2], experts=E, logits_in=logits, shared=sh, threads=threads)
-        kind = "reference"
-    else:
-        orc.moe_layer(x=xf, router_w=rw, topk=shape.topk, ff=shape.ff, gating=shape.gating, norm=shape.norm, scale=shape.scale,
-                      types=shape.types, gate=raw[0], up=raw[1], down=raw[2], experts=E, shared=sh, threads=threads)
-        kind = "port"
-    return time.perf_counter() - t0, kind
+        logits = orc.router_logits(cl.rw, cl.x)          # the reference CPU path has no router GEMV of its own (moe.cu is CUDA)
+        ref.moe_layer(x=cl.x, topk=sh.topk, ff=sh.ff, gating=sh.gating, norm=sh.norm, scale=sh.scale, types=sh.types, gate=cl.raw[0],
+                      up=cl.raw[1], down=cl.raw[2], experts=cl.E, logits_in=logits, shared=cl.sh, sel_bias=cl.bias, threads=threads)
+        return time.perf_counter() - t0, "reference"
+    orc.moe_layer(x=cl.x, router_w=cl.rw, topk=sh.topk, ff=sh.ff, gating=sh.gating, norm=sh.norm, scale=sh.scale, types=sh.types,
+                  gate=cl.raw[0], up=cl.raw[1], down=cl.raw[2], experts=cl.E, shared=cl.sh, sel_bias=cl.bias, threads=threads)
+    return time.perf_counter() - t0, "port"
+
+
+def pool_usable(shape):
+    """the production pool has int8 kernels for IQ3_S gate / up rows (it dequantises any other type row by row); its job
+    arrays hold up to 8 token columns, which the shim respects"""
+    return shape.hidden % 256 == 0 and shape.ff % 32 == 0 and all(t in (12, 20, 21, 23) for t in shape.types)
+
+
+def cpu_arm(cl: CpuLayer, budget_s: float, max_reps: int, want_fp32: bool):
+    """the CPU records: production pool (when it can be had) and, if wanted, the fp32 path; each on about budget_s of work"""
+    import oracle
+    orc, ref = oracle.oracle(), oracle.reference()
+    ncpu = os.cpu_count() or 1
+    out = {}
+    if want_fp32:
+        dt, kind = time_fp32_layer(cl, orc, ref, ncpu)
+        reps = max(1, min(max_reps, int(budget_s / max(dt, 1e-3))))
+        tot = sum(time_fp32_layer(cl, orc, ref, ncpu)[0] for _ in range(reps))
+        out["fp32"] = {"value": cl.x.shape[0] * reps / tot, "unit": UNIT, "cores": ncpu, "kind": kind,
+                       "path": "fp32 host path: dequantize_host + moe_route + moe_expert_ffn + moe_combine, one thread per expert",
+                       "sample": f"1 layer, {cl.x.shape[0]} tokens, {reps} passes ({tot:.1f} s)", "ms_per_layer": tot / reps * 1e3}
+    pool = oracle.reference_pool() if pool_usable(cl.shape) else None
+    if pool is not None:
+        threads = pool_threads()
+        pool.create(threads, cl.shape.hidden, cl.shape.ff)       # pins this thread to CPU 0 from here on
+        dt = time_pool_layer(cl, pool, orc, ref)
+        reps = max(1, min(max_reps, int(budget_s / max(dt, 1e-3))))
+        tot = sum(time_pool_layer(cl, pool, orc, ref) for _ in range(reps))
+        out["pool"] = {"value": cl.x.shape[0] * reps / tot, "unit": UNIT, "cores": threads + 1, "kind": "reference",
+                       "path": "production CPU expert pool of the reference (CpuMissPool: int8 AVX2 gate / up dots, bf16 / fp16 rounding), "
+                               f"{threads} pinned workers + the calling thread",
+                       "sample": f"1 layer, {cl.x.shape[0]} tokens, {reps} passes ({tot:.1f} s)", "ms_per_layer": tot / reps * 1e3,
+                       "nproc": ncpu, "cpu": cpu_model()}
+    return out
 
 
 def run_reference(args):
     """the reference's CPU implementation of the path on this box's host cores; rank 0 only"""
     if int(os.environ.get("RANK", "0")) != 0:
         return
-    import torch
-
     from tqllm_b200 import synth
     shape = synth.CONFIGS[args.workload]
-    threads = os.cpu_count() or 1
     layers, rscale = make_layers(synth, shape, 1, "cpu")
     x = synth.make_tokens(shape, args.tokens, SEED, "cpu")
-    steps = max(1, min(args.steps, 200))          # one layer pass (about 0.3 s on 16 cores) per step
-    for _ in range(min(args.warmup, 3)):
-        cpu_layer_time("reference", shape, layers[0], x, threads)
-    times = []
-    kind = "port"
-    for _ in range(steps):
-        dt, kind = cpu_layer_time("reference", shape, layers[0], x, threads)
-        times.append(dt)
+    cl = CpuLayer(shape, layers[0], x)
+    import oracle
+    orc, ref = oracle.oracle(), oracle.reference()
+    ncpu = os.cpu_count() or 1
+    steps, warm = max(1, min(args.steps, 200)), min(args.warmup, 3)
+    fp32_dt, fp32_kind = time_fp32_layer(cl, orc, ref, ncpu)         # second record: the fp32 host path, a few passes
+    fp32_reps = max(1, min(10, int(5.0 / max(fp32_dt, 1e-3))))
+    fp32_t = sum(time_fp32_layer(cl, orc, ref, ncpu)[0] for _ in range(fp32_reps)) / fp32_reps
+    pool = oracle.reference_pool() if pool_usable(shape) else None
+    if pool is not None:
+        threads = pool_threads()
+        pool.create(threads, shape.hidden, shape.ff)
+        fn = lambda: time_pool_layer(cl, pool, orc, ref)
+        kind, cores, path = "reference-production", threads + 1, f"CpuMissPool, {threads} pinned workers + the calling thread"
+    else:
+        fn = lambda: time_fp32_layer(cl, orc, ref, ncpu)[0]
+        kind, cores, path = fp32_kind, ncpu, "fp32 host path (no production pool for this configuration or host)"
+    for _ in range(warm):
+        fn()
+    times = [fn() for _ in range(steps)]
     t = sum(times) / len(times)
     v = args.tokens / t
     print(json.dumps({
-        "metric": METRIC, "value": v, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 3),
-        "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "metric": METRIC, "value": v, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
+        "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8+f32" if pool is not None else "f32",
+        "data": "synthetic",
         "config": {"workload": workload_name(shape, args.tokens, args.layers), "sample": "one layer per step", "router_scale": rscale},
-        "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": kind,
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": kind, "path": path, "nproc": ncpu, "cpu": cpu_model(),
                          "sample": f"1 of {args.layers} layers, {args.tokens} tokens, {steps} steps"},
+        "fp32_path": {"value": args.tokens / fp32_t, "unit": UNIT, "cores": ncpu, "kind": fp32_kind, "ms_per_layer": fp32_t * 1e3,
+                      "path": "dequantize_host + moe_route + moe_expert_ffn + moe_combine, one thread per expert", "passes": fp32_reps},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
 
 
 # ------------------------------------------------------------------------------------------------ GPU arm ----
+def graph_of(torch, stream, fn):
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        fn()
+    return g
+
+
+def event_ms(torch, stream, fn, n):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    stream.synchronize()
+    e0.record(stream)
+    for _ in range(n):
+        fn()
+    e1.record(stream)
+    stream.synchronize()
+    return e0.elapsed_time(e1) / n
+
+
+def expert_products(torch, moe, lib, C, lay, x, shape, stream):
+    """closures that launch the two expert products of layer `lay` on tokens x, with their plan, for stage timing"""
+    T = x.shape[0]
+    ST = T if shape.shared else 0
+    lg = moe.router(lay.router_w, x)
+    if shape.gating == 1:
+        ids, _, _ = moe.topk_softmax(lg, lay.experts, shape.topk, shape.scale)
+    else:
+        ids, _ = moe.route_sigmoid(lg, lay.experts, shape.topk, lay.sel_bias, shape.norm, shape.scale)
+    plan = moe.dispatch(ids, lay.experts, ST)
+    A = T * shape.topk
+    XDT = {torch.bfloat16: 2, torch.float16: 1, torch.float32: 0}[x.dtype]
+    act = torch.zeros(A + ST, shape.ff, dtype=torch.float32, device=x.device)
+    y = torch.zeros(A + ST, shape.hidden, dtype=torch.float32, device=x.device)
+    gws = torch.empty(max(lib.b2moe_expert_workspace_bytes(lay.gate.type, T, shape.hidden, XDT), 16), dtype=torch.uint8, device=x.device)
+    dws = torch.empty(max(lib.b2moe_expert_workspace_bytes(lay.down.type, A + ST, shape.ff, 0), 16), dtype=torch.uint8, device=x.device)
+    shp = lambda i: C.byref(lay.sh[i].c) if shape.shared else None
+    st = stream.cuda_stream
+
+    def gateup():
+        rc = lib.b2moe_expert_gateup_swiglu(C.byref(lay.gate.c), C.byref(lay.up.c), shp(0), shp(1), x.data_ptr(), XDT, plan.buf.data_ptr(), T,
+                                            shape.topk, ST, act.data_ptr(), gws.data_ptr(), gws.numel(), st)
+        assert rc == 0, rc
+
+    def down():
+        rc = lib.b2moe_expert_down(C.byref(lay.down.c), shp(2), act.data_ptr(), plan.buf.data_ptr(), T, shape.topk, ST, y.data_ptr(),
+                                   dws.data_ptr(), dws.numel(), st)
+        assert rc == 0, rc
+    return gateup, down, plan, (act, y, gws, dws, ids, lg)
+
+
+def bank_bytes_of(lib, bank):
+    return lib.b2moe_bank_bytes(bank.type, bank.rows, bank.cols)
+
+
+def workload_record(torch, moe, synth, lib, C, stream, dev, cfg, tokens, layout):
+    """one record of another benchmark configuration: one layer, `tokens` tokens, the layer as a CUDA-graph replay and its
+    gate/up product alone, with both roofline fractions"""
+    shape = synth.CONFIGS[cfg]
+    sl = synth.make_layer(shape, SEED + 7, dev)
+    x = synth.make_tokens(shape, tokens, SEED + 9, dev)
+    bias_note = None
+    if cfg == "c5":
+        # Zipf(s = 1.2) pressure on the routing: router rows of expert e grow along a direction every token shares, by an
+        # amount that falls like log(rank^-1.2); the amount is tuned so that the hottest expert holds about 10x the mean
+        d = torch.zeros(shape.hidden, device=dev)
+        d[::5] = 1.0
+        d /= d.norm()
+        x = (x.float() + 3.0 * d).to(x.dtype)
+        rank = torch.arange(1, shape.experts + 1, device=dev, dtype=torch.float32)
+        base = sl.router_w.clone()
+        lo, hi, ratio, w = 0.0, 4.0, 1.0, base
+        for _ in range(18):
+            c = 0.5 * (lo + hi)
+            w = base + (c * -1.2 * torch.log(rank))[:, None] * d[None, :] / 3.0
+            cnt = torch.bincount((x.float() @ w.T).topk(shape.topk, -1).indices.flatten(), minlength=shape.experts).float()
+            ratio = float(cnt.max() / cnt.mean())
+            lo, hi = (c, hi) if ratio < 10.0 else (lo, c)
+        sl.router_w.copy_(w)
+        bias_note = f"Zipf(1.2) routing pressure through the router rows: hottest expert {ratio:.1f}x the mean token count"
+    lay = moe.MoeLayer.from_synth(sl, device=dev, iq3s_layout=layout)
+    del sl
+    torch.cuda.empty_cache()
+    out = torch.empty(tokens, shape.hidden, dtype=torch.bfloat16, device=dev)
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            lay.forward(x, out=out)
+        stream.synchronize()
+        g = graph_of(torch, stream, lambda: lay.forward(x, out=out))
+        for _ in range(2):
+            g.replay()
+        layer_ms = event_ms(torch, stream, g.replay, 10)
+        art = lay.artefacts()
+        n_active = art["n_active"]
+        counts = art["counts"].cpu().numpy()[:shape.experts]
+        gateup, down, plan, keep = expert_products(torch, moe, lib, C, lay, x, shape, stream)
+        gateup(); down()
+        gu_ms = event_ms(torch, stream, gateup, 10)
+        dn_ms = event_ms(torch, stream, down, 10)
+        status = int(plan.buf[3])
+    A = tokens * shape.topk + (tokens if shape.shared else 0)
+    gu_bytes = n_active * 2 * synth.raw_bytes(shape.types[0], shape.ff, shape.hidden)
+    flops_gu = 4.0 * shape.hidden * shape.ff * A
+    hbm, _ = peaks()
+    bf16, _ = peaks("bf16_tflops")
+    rec = {
+        "workload": workload_name(shape, tokens, 1), "tokens": tokens, "layer_us": layer_ms * 1e3, "layer_tokens_per_s": tokens / (layer_ms * 1e-3),
+        "gateup_us": gu_ms * 1e3, "down_us": dn_ms * 1e3, "active_experts": n_active, "tokens_per_expert_mean": tokens * shape.topk / shape.experts,
+        "tokens_per_expert_max": int(counts.max()), "status": status,
+        "gateup_gbs": gu_bytes / (gu_ms * 1e-3) / 1e9, "gateup_hbm_frac": gu_bytes / (gu_ms * 1e-3) / 1e9 / hbm,
+        "gateup_tflops": flops_gu / (gu_ms * 1e-3) / 1e12, "gateup_frac_of_bf16_measured": flops_gu / (gu_ms * 1e-3) / 1e12 / bf16,
+        "layer_expert_weight_gbs": n_active * shape.expert_bytes() / (layer_ms * 1e-3) / 1e9,
+    }
+    # which roofline binds: weights streamed once per active expert against the flops at the measured bf16 rate
+    t_hbm, t_tensor = gu_bytes / (hbm * 1e9), flops_gu / (bf16 * 1e12)
+    rec["bound"] = "hbm" if t_hbm >= t_tensor else "tensor"
+    rec["roofline_frac"] = max(t_hbm, t_tensor) / (gu_ms * 1e-3)
+    if bias_note:
+        rec["routing"] = bias_note
+    del lay, g
+    torch.cuda.empty_cache()
+    return rec
+
+
 def run_b200(args):
+    import ctypes as C
+
     import torch
     import torch.distributed as dist
 
-    from tqllm_b200 import moe, synth
+    from tqllm_b200 import capi, moe, synth
+    lib = capi.lib
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -194,57 +401,22 @@ def run_b200(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        return run_ep(args, torch, dist, capi, moe, synth, rank, world, local, dev)
     shape = synth.CONFIGS[args.workload]
     T, L = args.tokens, args.layers
-    if world > 1 and args.workload != "c2":
-        raise SystemExit("bench.py: the expert-parallel arm runs the c2 workload")
-    router_all = None
-    if world > 1:
-        # expert parallel: every rank draws the same layer (same seed), keeps the banks of its own expert block only
-        from tqllm_b200 import ep
-        first, count = ep.expert_range(shape.experts, world, rank)
-        rscale = synth.solve_router_scale(shape, 0.6)
-        layers, router_all = [], []
-        H, F = shape.hidden, shape.ff
-        for l in range(L):
-            sl = synth.make_layer(shape, SEED + 17 * l, dev, router_scale=rscale)
-            cut = lambda raw, i: raw[first * synth.raw_bytes(shape.types[i], (F, F, H)[i], (H, H, F)[i]):
-                                     (first + count) * synth.raw_bytes(shape.types[i], (F, F, H)[i], (H, H, F)[i])].clone()
-            layers.append(moe.MoeLayer(shape, sl.router_w[first:first + count], tuple(cut(sl.raw[i], i) for i in range(3)), sl.shared_raw,
-                                       experts=count, device=dev))
-            router_all.append(sl.router_w.contiguous())
-            del sl
-            torch.cuda.empty_cache()
-        synth_layers = []
-    else:
-        synth_layers, rscale = make_layers(synth, shape, L, dev)
-        layers = [moe.MoeLayer.from_synth(sl, device=dev) for sl in synth_layers]
-    host_layer0 = synth_layers[0] if rank == 0 and not args.no_cpu and world == 1 and args.workload == "c2" else None
-    if host_layer0 is not None:      # keep only the first layer's raw blocks (for the CPU baseline), on the host
-        host_layer0 = synth.Layer(shape, host_layer0.router_w.cpu(), None, tuple(t.cpu() for t in host_layer0.raw),
-                                  tuple(t.cpu() for t in host_layer0.shared_raw))
+    synth_layers, rscale = make_layers(synth, shape, L, dev)
+    layers = [moe.MoeLayer.from_synth(sl, device=dev, iq3s_layout=args.iq3s_layout) for sl in synth_layers]
+    x = synth.make_tokens(shape, T, SEED, dev)
+    cpu_layer = CpuLayer(shape, synth_layers[0], x) if not args.no_cpu and args.workload == "c2" else None
     del synth_layers
     torch.cuda.empty_cache()
-    x = synth.make_tokens(shape, T, SEED + rank, dev)
     outs = [torch.empty(T, shape.hidden, dtype=torch.bfloat16, device=dev) for _ in range(L)]
-    if world == 1:
-        for lay in layers:
-            lay.reserve(T)
+    for lay in layers:
+        lay.reserve(T)
 
-    if world > 1:
-        from tqllm_b200 import ep
-        comm = ep.TorchComm()
-        H, F = shape.hidden, shape.ff
-        eps = [ep.CudaEpLayer(lay, rw, shape.experts, world, rank) for lay, rw in zip(layers, router_all)]
-
-        def step():
-            for l, e in enumerate(eps):
-                outs[l] = ep.ep_forward(e, comm, x)
-        graphed = None            # built after the warm-up, on the timing stream: compute phases as CUDA graphs, collectives direct
-    else:
-        def step():
-            for lay, o in zip(layers, outs):
-                lay.forward(x, out=o)
+    def step():
+        for lay, o in zip(layers, outs):
+            lay.forward(x, out=o)
 
     # pinned host buffers of the end-to-end leg
     x_host = x.cpu().pin_memory()
@@ -257,156 +429,85 @@ def run_b200(args):
             out_host[l].copy_(outs[l], non_blocking=True)
 
     stream = torch.cuda.Stream(dev)
-    graph = None
     with torch.cuda.stream(stream):
         for _ in range(max(args.warmup, 3)):
             step()
         stream.synchronize()
-        if args.graph and world == 1:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                step()
-        elif args.graph:                   # expert parallel: only the compute phases are captured, no collective is
-            graphed = [ep.GraphedEpForward(e, comm, x) for e in eps]
-
-            def step():
-                for l, gf in enumerate(graphed):
-                    outs[l] = gf()
+        n0 = lib.b2moe_harness_launches()
+        step()
+        launches_per_step = int(lib.b2moe_harness_launches() - n0)       # counted by the library: every kernel it launched in one step
+        stream.synchronize()
+        graph = graph_of(torch, stream, step) if args.graph else None
         run = graph.replay if graph is not None else step
-
-        def timed(fn, steps):
-            if world > 1:
-                dist.barrier()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            for _ in range(steps):
-                fn()
-            e1.record(stream)
-            torch.cuda.synchronize()
-            ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-            if world > 1:
-                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-                dist.barrier()
-            return float(ms) / steps
-
         for _ in range(args.warmup):
             run()
+        R = max(1, args.repeats)
         with ClockSampler(local) as clocks:
-            ms_step = timed(run, args.steps)
+            reg = [event_ms(torch, stream, run, args.steps) for _ in range(R)]       # ms per step of each K-step region
         for _ in range(min(args.warmup, 3)):
             step_e2e()
-        ms_e2e = timed(step_e2e, args.steps)
+        reg_e2e = [event_ms(torch, stream, step_e2e, args.steps) for _ in range(max(1, min(R, 10)))]
+        ms_step, ms_e2e = statistics.median(reg), statistics.median(reg_e2e)
 
-        if world == 1:
-            # dominant kernel, timed alone with events on the launching stream: the grouped gate/up + SwiGLU product
-            art = [lay.artefacts() for lay in layers]
-            plans, ids = [], []
-            ST = T if shape.shared else 0                         # rows of the always-on shared expert
-            for lay in layers:
-                lg = moe.router(lay.router_w, x)
-                if shape.gating == 1:
-                    i, w, _ = moe.topk_softmax(lg, lay.experts, shape.topk, shape.scale)
-                else:
-                    i, w = moe.route_sigmoid(lg, lay.experts, shape.topk, lay.sel_bias, shape.norm, shape.scale)
-                plans.append(moe.dispatch(i, lay.experts, ST))
-            act = torch.zeros(T * shape.topk + ST, shape.ff, dtype=torch.float32, device=dev)
-            XDT = {torch.bfloat16: 2, torch.float16: 1, torch.float32: 0}[x.dtype]
-            shp = lambda lay, i: C.byref(lay.sh[i].c) if shape.shared else None
-            import ctypes as C
-            from tqllm_b200.capi import lib, BF16
+        # stage timings: every stage of a layer launched alone, bracketed by events on the launching stream, averaged over the layers
+        prods = [expert_products(torch, moe, lib, C, lay, x, shape, stream) for lay in layers]
 
-            wsb = lib.b2moe_expert_workspace_bytes(layers[0].gate.type, T, shape.hidden, XDT)
-            ews = torch.empty(max(wsb, 16), dtype=torch.uint8, device=dev)
+        def time_stage(fns, reps=max(3, min(args.steps, 20))):
+            for f in fns:
+                f()
+            evs = []
+            for _ in range(reps):
+                for f in fns:
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(stream); f(); b.record(stream)
+                    evs.append((a, b))
+            stream.synchronize()
+            return 1e3 * sum(a.elapsed_time(b) for a, b in evs) / len(evs)
 
-            def gateup(l):
-                lay = layers[l]
-                return lib.b2moe_expert_gateup_swiglu(C.byref(lay.gate.c), C.byref(lay.up.c), shp(lay, 0), shp(lay, 1),
-                                                      x.data_ptr(), XDT, plans[l].buf.data_ptr(), T, shape.topk, ST, act.data_ptr(),
-                                                      ews.data_ptr(), ews.numel(), stream.cuda_stream)
-            for l in range(L):
-                assert gateup(l) == 0
+        gu_call_us = time_stage([p[0] for p in prods])
+        dn_call_us = time_stage([p[1] for p in prods])
+        lib.b2moe_harness_skip_staging(1)          # the product kernels alone (their activation staging launch left out)
+        try:
+            gu_us = time_stage([p[0] for p in prods])
+            dn_us = time_stage([p[1] for p in prods])
+        finally:
+            lib.b2moe_harness_skip_staging(0)
+        st = stream.cuda_stream
+        ST = T if shape.shared else 0
+        A = T * shape.topk
+        XDT = {torch.bfloat16: 2, torch.float16: 1, torch.float32: 0}[x.dtype]
+        logits = torch.zeros(T, shape.experts + 1, dtype=torch.float32, device=dev)
+        idb = torch.zeros(T, shape.topk, dtype=torch.int32, device=dev)
+        wts = torch.zeros(T, shape.topk, dtype=torch.float32, device=dev)
+        ob = torch.zeros(T, shape.hidden, dtype=torch.bfloat16, device=dev)
+        plan2 = moe.Plan(shape.experts, T, shape.topk, ST, dev)
+        dsw = torch.empty(max(lib.b2moe_dispatch_workspace_bytes(shape.experts, A), 16), dtype=torch.uint8, device=dev)
+        bias = lambda lay: None if lay.sel_bias is None else lay.sel_bias.data_ptr()
 
-            def time_stage(fn):
-                """mean microseconds of fn(layer) over the layers, each launch bracketed by events on the launching stream"""
-                for l in range(L):
-                    assert fn(l) == 0
-                evs = []
-                for _ in range(max(3, min(args.steps, 20))):
-                    for l in range(L):
-                        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                        a.record(stream); fn(l); b.record(stream)
-                        evs.append((a, b))
-                torch.cuda.synchronize()
-                return 1e3 * sum(a.elapsed_time(b) for a, b in evs) / len(evs)
-
-            k_ms = time_stage(gateup) * 1e-3
-            # the other stages, the same way (reported as stage_us; they explain ms_per_step)
-            F32 = 0
-            st = stream.cuda_stream
-            A = T * shape.topk
-            logits = torch.zeros(T, shape.experts + 1, dtype=torch.float32, device=dev)
-            idb = torch.zeros(T, shape.topk, dtype=torch.int32, device=dev)
-            wts = torch.zeros(T, shape.topk, dtype=torch.float32, device=dev)
-            yb = torch.zeros(A + ST, shape.hidden, dtype=torch.float32, device=dev)
-            ob = torch.zeros(T, shape.hidden, dtype=torch.bfloat16, device=dev)
-            dws = torch.empty(max(lib.b2moe_expert_workspace_bytes(layers[0].down.type, A + ST, shape.ff, F32), 16), dtype=torch.uint8, device=dev)
-            plan2 = moe.Plan(shape.experts, T, shape.topk, ST, dev)
-            dsw = torch.empty(max(lib.b2moe_dispatch_workspace_bytes(shape.experts, A), 16), dtype=torch.uint8, device=dev)
-            bias = lambda l: None if layers[l].sel_bias is None else layers[l].sel_bias.data_ptr()
-            stage_us = {
-                "router": time_stage(lambda l: lib.b2moe_router(layers[l].router_w.data_ptr(), None, x.data_ptr(), XDT, logits.data_ptr(),
-                                                                shape.experts + 1, shape.hidden, shape.experts, T, st)),
-                "topk": time_stage((lambda l: lib.b2moe_topk_softmax(logits.data_ptr(), shape.experts + 1, idb.data_ptr(), wts.data_ptr(), None,
-                                                                     shape.experts, shape.topk, T, shape.scale, st)) if shape.gating == 1 else
-                                   (lambda l: lib.b2moe_route_sigmoid(logits.data_ptr(), shape.experts + 1, bias(l), idb.data_ptr(), wts.data_ptr(),
-                                                                      shape.experts, shape.topk, int(shape.norm), shape.scale, T, st))),
-                "dispatch": time_stage(lambda l: lib.b2moe_dispatch(idb.data_ptr(), T, shape.topk, shape.experts, ST, plan2.buf.data_ptr(),
-                                                                    dsw.data_ptr(), dsw.numel(), st)),
-                "gateup_swiglu": k_ms * 1e3,
-                "down": time_stage(lambda l: lib.b2moe_expert_down(C.byref(layers[l].down.c), shp(layers[l], 2), act.data_ptr(),
-                                                                   plans[l].buf.data_ptr(), T, shape.topk, ST, yb.data_ptr(), dws.data_ptr(),
-                                                                   dws.numel(), st)),
-                "combine": time_stage(lambda l: lib.b2moe_combine(yb.data_ptr(), None, wts.data_ptr(), None, T, shape.topk, shape.hidden, ST,
-                                                                  ob.data_ptr(), BF16, st)),
-            }
-        else:
-            torch.cuda.synchronize()
-            plans, stage_us, k_ms = None, None, None
-            n_active_rank = sum(int(e.buf["plan"][0]) for e in eps) / L      # this rank's active experts per layer (with the shared one)
-    gu_bytes = 2 * synth.raw_bytes(shape.types[0], shape.ff, shape.hidden)
-    peak, peak_kind = peaks()
-    bound, roof_unit = "hbm", "GB/s"
-    if world == 1:
+        def ok(rc):
+            assert rc == 0, rc
+        stage_us = {
+            "router": time_stage([(lambda lay=lay: ok(lib.b2moe_router(lay.router_w.data_ptr(), None, x.data_ptr(), XDT, logits.data_ptr(),
+                                                                       shape.experts + 1, shape.hidden, shape.experts, T, st))) for lay in layers]),
+            "route_dispatch": time_stage([(lambda lay=lay: ok(lib.b2moe_route_dispatch(shape.gating, logits.data_ptr(), shape.experts + 1, bias(lay),
+                                                                                    idb.data_ptr(), wts.data_ptr(), None, shape.experts, shape.topk,
+                                                                                    int(shape.norm), shape.scale, T, 0, ST, plan2.buf.data_ptr(),
+                                                                                    dsw.data_ptr(), dsw.numel(), st))) for lay in layers]),
+            "gateup_swiglu_call": gu_call_us, "gateup_swiglu_kernel": gu_us, "down_call": dn_call_us, "down_kernel": dn_us,
+            "combine": time_stage([(lambda p=p: ok(lib.b2moe_combine(p[3][1].data_ptr(), None, wts.data_ptr(), None, T, shape.topk, shape.hidden,
+                                                                     ST, ob.data_ptr(), capi.BF16, st))) for p in prods]),
+        }
+        plans = [p[2] for p in prods]
         n_active = sum(p.n_active for p in plans) / L            # includes the shared expert
-        achieved = n_active * gu_bytes / (k_ms * 1e-3) / 1e9
-        weight_bytes_step = sum(p.n_active for p in plans) * shape.expert_bytes()
-        roof_kernel = "grouped gate/up + SwiGLU"
-        if T * shape.topk >= 128 * shape.experts:                # >= 128 tokens per expert: the tensor cores bound the product
-            bound, roof_unit = "tensor", "TFLOP/s"
-            achieved = 4.0 * shape.hidden * shape.ff * (T * shape.topk + (T if shape.shared else 0)) / (k_ms * 1e-3) / 1e12
-            peak, peak_kind = peaks("bf16_tflops")
-    else:
-        # per-GPU view: the whole layer (exchanges included) against this GPU's HBM: expert bytes it streamed / step time
-        n_active = n_active_rank
-        weight_bytes_step = n_active_rank * L * shape.expert_bytes()
-        achieved = weight_bytes_step / (ms_step * 1e-3) / 1e9
-        k_ms = ms_step / L
-        roof_kernel = "whole expert-parallel layer on rank 0 (dispatch + combine exchanges included)"
-    value = world * T * L / (ms_step * 1e-3)
-    e2e = world * T * L / (ms_e2e * 1e-3)
-    # DRAM bytes per launch of the dominant kernel: one ncu capture of the c2 gate/up kernel (profiles/iq3s_grouped_decode_c2_t64.md:
-    # 317.7 MB read + 1.4 MB written with 353 experts active) scaled by the experts this launch touched; traffic grows with them
-    traffic, traffic_src = None, None
-    if world == 1 and args.workload == "c2" and T * shape.topk < 32 * shape.experts:
-        traffic = (317.7e6 + 1.4e6) / 353.0 * n_active
-        traffic_src = "ncu dram__bytes_read+write of one capture, scaled by active experts (profiles/iq3s_grouped_decode_c2_t64.md)"
+        status = max(int(p.buf[3]) for p in plans)
+        gu_bank = sum(bank_bytes_of(lib, lay.gate) + bank_bytes_of(lib, lay.up) for lay in layers) / L
+        del prods
+        torch.cuda.empty_cache()
 
-    sweep = None
-    if args.sweep and world == 1:
-        # decode batches of 1 / 4 / 16 tokens: all L layers per step, replayed as a CUDA graph like the headline step, CUDA events
-        sweep = {}
-        with torch.cuda.stream(stream):
+        # decode batch sweep on the same layers: 1 / 4 / 16 tokens, the L-layer step replayed as a CUDA graph
+        sweep = None
+        if not args.no_extras and args.workload == "c2":
+            sweep = {}
             for ts in (1, 4, 16):
                 xs = x[:ts].contiguous()
                 os_ = [torch.empty(ts, shape.hidden, dtype=torch.bfloat16, device=dev) for _ in range(L)]
@@ -417,20 +518,10 @@ def run_b200(args):
                 for _ in range(3):
                     small_step()
                 stream.synchronize()
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=stream):
-                    small_step()
+                g = graph_of(torch, stream, small_step)
                 for _ in range(5):
                     g.replay()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                reps = 50
-                stream.synchronize()
-                e0.record(stream)
-                for _ in range(reps):
-                    g.replay()
-                e1.record(stream)
-                stream.synchronize()
-                us_layer = e0.elapsed_time(e1) * 1e3 / (reps * L)
+                us_layer = event_ms(torch, stream, g.replay, 50) * 1e3 / L
                 act_l = sum(lay.artefacts()["n_active"] for lay in layers) / L
                 sweep[str(ts)] = {"us_per_layer": us_layer, "tokens_per_s": ts / (us_layer * 1e-6), "active_experts": act_l,
                                   "expert_weight_gbs": act_l * shape.expert_bytes() / (us_layer * 1e-6) / 1e9}
@@ -438,39 +529,174 @@ def run_b200(args):
             for lay in layers:
                 lay.reserve(T)
 
-    cpu = None
-    if host_layer0 is not None:
-        threads = os.cpu_count() or 1
-        xc = x.cpu()
-        dt, kind = cpu_layer_time("port", shape, host_layer0, xc, threads)          # warm-up pass, also sizes the sample
-        reps = max(1, min(64, int(10.0 / max(dt, 1e-3))))                            # about 10 s of CPU work
-        total = sum(cpu_layer_time("port", shape, host_layer0, xc, threads)[0] for _ in range(reps))
-        cpu = {"value": T * reps / total, "unit": UNIT, "cores": threads, "kind": kind,
-               "sample": f"1 of {L} layers, {T} tokens, {reps} passes ({total:.1f} s)"}
+    gu_bytes = 2 * synth.raw_bytes(shape.types[0], shape.ff, shape.hidden)
+    peak, peak_kind = peaks()
+    bound, roof_unit = "hbm", "GB/s"
+    k_ms = gu_us * 1e-3
+    achieved = n_active * gu_bytes / (k_ms * 1e-3) / 1e9
+    weight_bytes_step = n_active * L * shape.expert_bytes()
+    if T * shape.topk >= 128 * shape.experts:                # >= 128 tokens per expert: the tensor cores bound the product
+        bound, roof_unit = "tensor", "TFLOP/s"
+        achieved = 4.0 * shape.hidden * shape.ff * (T * shape.topk + (T if shape.shared else 0)) / (k_ms * 1e-3) / 1e12
+        peak, peak_kind = peaks("bf16_tflops")
+    value = T * L / (ms_step * 1e-3)
+    e2e = T * L / (ms_e2e * 1e-3)
+    # DRAM bytes of one launch of the dominant kernel: the bytes of the gate and up banks of the experts it touched, in the
+    # layout it reads (IQ3_S as 4-bit codes: 134 bytes per 256 weights against the 110 of the GGUF block). A constant of the
+    # layout, not a live counter; one ncu capture of this kernel measured 1.00x of it.
+    traffic = n_active * gu_bank / max(1, layers[0].experts)
+    graphed = graph is not None
 
+    workloads = None
+    if not args.no_extras and args.workload == "c2":
+        del layers, graph
+        torch.cuda.empty_cache()
+        workloads = {}
+        for key, cfg, toks in (("c4_decode_16", "c4", 16), ("c3_prefill_4096", "c3", 4096), ("c4_prefill_2048", "c4", 2048), ("c5_prefill_8192", "c5", 8192)):
+            try:
+                workloads[key] = workload_record(torch, moe, synth, lib, C, stream, dev, cfg, toks, args.iq3s_layout)
+            except Exception as e:                                  # a record that fails must not take the headline with it
+                workloads[key] = {"error": f"{type(e).__name__}: {e}"[:300]}
+
+    cpu = None
+    if cpu_layer is not None:
+        arms = cpu_arm(cpu_layer, 8.0, 64, want_fp32=True)       # last: the reference's pool pins this thread to CPU 0
+        cpu = arms.get("pool") or arms.get("fp32")
+        if cpu is not None and "fp32" in arms and cpu is not arms["fp32"]:
+            cpu = dict(cpu, fp32_path=arms["fp32"])
+
+    print(json.dumps({
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8+f32", "data": "synthetic",
+        "config": {"workload": workload_name(shape, T, L), "tokens": T, "layers": L, "router_scale": rscale, "parallelism": "single GPU",
+                   "l2": "per-step expert weights (GBs) exceed the 126 MB L2; no flush needed", "cuda_graph": graphed,
+                   "activations": "bf16 in, bf16 out; expert products on integer tensor-core MMA over 15-bit fixed-point activations, fp32 sums",
+                   "iq3s_bank_layout": args.iq3s_layout},
+        "repeats": {"n": len(reg), "ms_per_step_median": ms_step, "ms_per_step_min": min(reg), "ms_per_step_max": max(reg),
+                    "e2e_n": len(reg_e2e), "e2e_min": min(reg_e2e), "e2e_max": max(reg_e2e)},
+        "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": x_host.numel() * 2,
+                "d2h_bytes_per_step": out_host.numel() * 2},
+        "gpu_launches": args.steps * launches_per_step, "launches_per_step": launches_per_step,
+        "roofline": {"bound": bound, "kernel": "grouped gate/up + SwiGLU product (its launch alone)", "achieved": achieved, "peak": peak, "unit": roof_unit,
+                     "frac": achieved / peak, "peak_kind": peak_kind, "traffic": traffic,
+                     "traffic_source": "bytes of the banks the launch reads in their HBM layout (a constant of the layout, not a counter)",
+                     "kernel_ms": k_ms, "active_experts_per_launch": n_active, "bytes_per_expert": gu_bytes, "status": status},
+        "expert_weight_gbs": weight_bytes_step / (ms_step * 1e-3) / 1e9,
+        "expert_weight_frac_of_8tbs": weight_bytes_step / (ms_step * 1e-3) / 8e12,
+        "stage_us": stage_us, "sweep": sweep, "workloads": workloads,
+        "nominal_peaks_not_measured": {"int8_tops_dense": NOMINAL_TFLOPS["int8"], "fp4_tflops_dense": NOMINAL_TFLOPS["fp4"],
+                                       "note": "NVIDIA's per-GPU B200 figures; only the HBM copy rate and the bf16 GEMM rate were measured on this pool"},
+        "cpu_baseline": cpu, "clocks": clocks.summary(),
+    }))
+
+
+def run_ep(args, torch, dist, capi, moe, synth, rank, world, local, dev):
+    """expert parallel over `world` GPUs of one box: every rank keeps the banks of its own expert block and routes its own tokens"""
+    from tqllm_b200 import ep
+    lib = capi.lib
+    shape = synth.CONFIGS[args.workload]
+    T, L = args.tokens, args.layers
+    first, count = ep.expert_range(shape.experts, world, rank)
+    rscale = synth.solve_router_scale(shape, 0.6) if args.workload == "c2" else 1.0
+    layers, router_all, bias_all = [], [], []
+    H, F = shape.hidden, shape.ff
+    for l in range(L):
+        sl = synth.make_layer(shape, SEED + 17 * l, dev, router_scale=rscale)      # the same layer on every rank (same seed)
+        cut = lambda raw, i: raw[first * synth.raw_bytes(shape.types[i], (F, F, H)[i], (H, H, F)[i]):
+                                 (first + count) * synth.raw_bytes(shape.types[i], (F, F, H)[i], (H, H, F)[i])].clone()
+        layers.append(moe.MoeLayer(shape, sl.router_w[first:first + count], tuple(cut(sl.raw[i], i) for i in range(3)), sl.shared_raw,
+                                   experts=count, device=dev, iq3s_layout=args.iq3s_layout))
+        router_all.append(sl.router_w.contiguous())
+        bias_all.append(None if sl.sel_bias is None else sl.sel_bias.contiguous())
+        del sl
+        torch.cuda.empty_cache()
+    x = synth.make_tokens(shape, T, SEED + rank, dev)
+    comm = ep.TorchComm()
+    eps = [ep.CudaEpLayer(lay, rw, shape.experts, world, rank, sel_bias_all=b) for lay, rw, b in zip(layers, router_all, bias_all)]
+    outs = [None] * L
+
+    def step_direct():
+        for l, e in enumerate(eps):
+            outs[l] = ep.ep_forward(e, comm, x)
+    step = step_direct
+
+    x_host = x.cpu().pin_memory()
+    out_host = torch.empty(L, T, shape.hidden, dtype=torch.bfloat16).pin_memory()
+    stream = torch.cuda.Stream(dev)
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            step()
+        stream.synchronize()
+        n0 = lib.b2moe_harness_launches()
+        step()
+        launches_per_step = int(lib.b2moe_harness_launches() - n0)
+        stream.synchronize()
+        if args.graph:                   # only the compute phases are captured, no collective is
+            graphed = [ep.GraphedEpForward(e, comm, x) for e in eps]
+
+            def step_graphed():
+                for l, gf in enumerate(graphed):
+                    outs[l] = gf()
+            step = step_graphed
+
+        def step_e2e():
+            x.copy_(x_host, non_blocking=True)
+            step()
+            for l in range(L):
+                out_host[l].copy_(outs[l], non_blocking=True)
+
+        def timed(fn, steps):
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                fn()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            dist.barrier()
+            return float(ms) / steps
+
+        for _ in range(args.warmup):
+            step()
+        R = max(1, min(args.repeats, 10))
+        with ClockSampler(local) as clocks:
+            reg = [timed(step, args.steps) for _ in range(R)]
+        for _ in range(min(args.warmup, 3)):
+            step_e2e()
+        reg_e2e = [timed(step_e2e, args.steps) for _ in range(max(1, min(R, 5)))]
+        ms_step, ms_e2e = statistics.median(reg), statistics.median(reg_e2e)
+        # where a layer's time goes on this rank: every phase bracketed by events (direct launches, not the graphed ones)
+        phase_us = ep.phase_times(eps[0], comm, x, reps=20)
+        torch.cuda.synchronize()
+        n_active = sum(int(e.buf["plan"][0]) for e in eps) / L      # this rank's active experts per layer (with the shared one)
+    peak, peak_kind = peaks()
+    weight_bytes_step = n_active * L * shape.expert_bytes()
+    achieved = weight_bytes_step / (ms_step * 1e-3) / 1e9
+    value = world * T * L / (ms_step * 1e-3)
+    e2e = world * T * L / (ms_e2e * 1e-3)
     if rank == 0:
         print(json.dumps({
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8+f32", "data": "synthetic",
             "config": {"workload": workload_name(shape, T, L), "tokens": T, "layers": L, "router_scale": rscale,
-                       "parallelism": "single GPU" if world == 1 else f"ep{world}: {shape.experts // world} experts per GPU, {T} tokens per GPU, "
-                                      "NCCL all-gather dispatch + all-to-all combine",
-                       "l2": "per-step expert weights (GBs) exceed the 126 MB L2; no flush needed", "cuda_graph": (graph is not None) or ("compute phases only" if world > 1 and args.graph else False),
-                       "activations": "bf16 in, bf16 out, fp32 intermediates"},
+                       "parallelism": f"ep{world}: {shape.experts // world} experts per GPU, {T} tokens per GPU, NCCL all-gather dispatch + all-to-all combine",
+                       "l2": "per-step expert weights exceed the 126 MB L2; no flush needed",
+                       "cuda_graph": "compute phases only" if args.graph else False, "iq3s_bank_layout": args.iq3s_layout},
+            "repeats": {"n": len(reg), "ms_per_step_median": ms_step, "ms_per_step_min": min(reg), "ms_per_step_max": max(reg)},
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": x_host.numel() * 2,
                     "d2h_bytes_per_step": out_host.numel() * 2},
-            "gpu_launches": args.steps * L * (6 if world == 1 else 9),   # per layer: router, route + dispatch, gate/up, fp16 rows, down, combine
-                                                                      # (expert parallel: + top-k, local ids, rank-ordered reduce)
-            "roofline": {"bound": bound, "kernel": roof_kernel, "achieved": achieved, "peak": peak, "unit": roof_unit,
-                         "frac": achieved / peak, "peak_kind": peak_kind, "traffic": traffic, "traffic_source": traffic_src,
-                         "kernel_ms": k_ms,
-                         "active_experts_per_launch": n_active, "bytes_per_expert": gu_bytes},
-            "expert_weight_gbs": weight_bytes_step / (ms_step * 1e-3) / 1e9,
-            "expert_weight_frac_of_8tbs": weight_bytes_step / (ms_step * 1e-3) / 8e12,
-            "stage_us": stage_us, "sweep": sweep, "cpu_baseline": cpu, "clocks": clocks.summary(),
+            "gpu_launches": args.steps * launches_per_step, "launches_per_step": launches_per_step,
+            "roofline": {"bound": "hbm", "kernel": "whole expert-parallel layer on rank 0 (dispatch + combine exchanges included)",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                         "kernel_ms": ms_step / L, "active_experts_per_launch": n_active,
+                         "bytes_per_expert": 2 * synth.raw_bytes(shape.types[0], shape.ff, shape.hidden)},
+            "expert_weight_gbs": weight_bytes_step / (ms_step * 1e-3) / 1e9, "stage_us": phase_us,
+            "cpu_baseline": None, "clocks": clocks.summary(),
         }))
-    if world > 1:
-        dist.destroy_process_group()
+    dist.destroy_process_group()
 
 
 if __name__ == "__main__":

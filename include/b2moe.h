@@ -211,10 +211,15 @@ B2MOE_API int32_t b2moe_ep_reduce(const float * parts, int32_t ranks, const floa
  * same) or 256 tokens per work item of the grouped GEMM.
  * b2moe_harness_wait_probe: the 4-bit decode kernels skip the copy of weight tile number drop_tile of every warp
  * (-1 = none, the default) and bound each wait by wait_limit polls (0 = default), so that a test can watch a bounded
- * wait run out: the launch then sets plan word [3] and returns, its outputs invalid. */
+ * wait run out: the launch then sets plan word [3] and returns, its outputs invalid.
+ * b2moe_harness_skip_staging: while on, the 4-bit decode kernels skip their activation staging launch and read the
+ * staged rows the previous call left in the same workspace (a benchmark times the product kernel alone this way).
+ * b2moe_harness_launches: kernel launches the library has made in this process so far. */
 enum b2moe_family { B2MOE_FAMILY_AUTO = 0, B2MOE_FAMILY_GENERIC = 1, B2MOE_FAMILY_DECODE = 2, B2MOE_FAMILY_GEMM = 3 };
 B2MOE_API void b2moe_harness_select(int32_t family, int32_t gemm_item_tokens);
 B2MOE_API void b2moe_harness_wait_probe(int32_t drop_tile, uint32_t wait_limit);
+B2MOE_API void b2moe_harness_skip_staging(int32_t on);
+B2MOE_API uint64_t b2moe_harness_launches(void);
 
 /* ---- whole layer ----------------------------------------------------------------------------------------------
  * router -> top-k -> dispatch -> gate/up + SwiGLU -> down -> combine, the sequence of qwen35_forward.cpp:1121-1252,

@@ -228,3 +228,51 @@ def reference() -> Reference | None:
             return None
         _reference = Reference(path)
     return _reference
+
+
+class ReferencePool:
+    """The reference's production CPU expert pool (CpuMissPool) compiled in place: oracle/_ref/libtqrefpool.so. It is what
+    bench.py times as the CPU arm; its numerics are the reference's int8 / bf16 ones, so it is not a parity checker."""
+
+    def __init__(self, path: str):
+        self.lib = C.CDLL(path)
+        self.lib.refpool_create.argtypes = [C.c_int] * 3
+        self.lib.refpool_layer.argtypes = [C.c_int] * 5 + [_f32p, _i32p, _f32p, C.c_void_p] + [C.c_void_p] * 3 + [C.c_int] + [C.c_void_p] * 3 + [_f32p]
+        self.threads = 0
+
+    def create(self, threads: int, hidden: int, ff: int):
+        """threads workers pinned to CPUs 1 .. threads; the calling thread is pinned to CPU 0 (the pool's own policy)"""
+        rc = self.lib.refpool_create(threads, hidden, ff)
+        if rc:
+            raise ValueError(f"refpool_create failed ({rc}): one pool shape per process")
+        self.threads = threads
+
+    def layer(self, *, x, ids, weights, ff, types, gate, up, down, experts, shared=None):
+        x = np.ascontiguousarray(x, np.float32)
+        ids = np.ascontiguousarray(ids, np.int32)
+        weights = np.ascontiguousarray(weights, np.float32)
+        t, h = x.shape
+        keep = [np.ascontiguousarray(a, np.uint8) for a in (gate, up, down)]
+        sh = [np.ascontiguousarray(a, np.uint8) for a in shared] if shared is not None else [None] * 3
+        ty = (C.c_uint32 * 3)(*types)
+        out = np.empty((t, h), np.float32)
+        rc = self.lib.refpool_layer(t, h, experts, ids.shape[1], ff, x, ids, weights, C.cast(ty, C.c_void_p),
+                                    *[_vp(a) for a in keep], int(shared is not None), *[_vp(a) for a in sh], out)
+        if rc:
+            raise ValueError(f"refpool_layer failed ({rc})")
+        return out
+
+
+_pool = None
+
+
+def reference_pool() -> ReferencePool | None:
+    """The compiled production CPU pool of the reference, or None when it cannot be had (no checkout here and no prebuilt
+    library, or not an x86 host)."""
+    global _pool
+    if _pool is None:
+        path = _build.build_ref_pool()
+        if path is None:
+            return None
+        _pool = ReferencePool(path)
+    return _pool

@@ -4,6 +4,11 @@
   oracle/_ref/libtqref.so     from the reference's own sources compiled where they lie in the reference checkout
                               (src/experts/moe.cpp, src/formats/weight/dequant.cpp) plus oracle/ref_shim.cpp; built only
                               when that checkout is present. No reference source is copied into this tree.
+  oracle/_ref/libtqrefpool.so the reference's production CPU expert pool (CpuMissPool, a header:
+                              src/models/qwen/qwen4exp/fn_cpu_experts.hpp) + dequant.cpp + oracle/ref_pool_shim.cpp: the CPU
+                              arm the benchmark times (x86 with AVX2 only).
+
+The checkout is found through the environment variable TQLLM_REFERENCE (a directory holding src/experts/moe.cpp).
 
 Usage: python oracle/build.py [--force]
 """
@@ -15,9 +20,10 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
-REF = os.environ.get("TQLLM_REFERENCE", "/root/reference")
+REF = os.environ.get("TQLLM_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")   # sibling checkout unless told otherwise
 ORACLE_SO = os.path.join(HERE, "_build", "liboracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libtqref.so")
+POOL_SO = os.path.join(HERE, "_ref", "libtqrefpool.so")
 CXXFLAGS = ["-O2", "-std=c++20", "-shared", "-fPIC", "-pthread", "-mavx2", "-mfma", "-mf16c"]
 
 
@@ -63,7 +69,27 @@ def build_ref(force: bool = False) -> str | None:
     return REF_SO
 
 
+def build_ref_pool(force: bool = False) -> str | None:
+    """The reference's production CPU expert pool, compiled from its own header in place. None when it cannot be had."""
+    if not reference_present():
+        return POOL_SO if os.path.isfile(POOL_SO) else None
+    hdr = os.path.join(REF, "src", "models", "qwen", "qwen4exp", "fn_cpu_experts.hpp")
+    srcs = [os.path.join(REF, "src", "formats", "weight", "dequant.cpp"), os.path.join(HERE, "ref_pool_shim.cpp")]
+    if force or _stale(POOL_SO, srcs + [hdr]):
+        os.makedirs(os.path.dirname(POOL_SO), exist_ok=True)
+        inc = []
+        for d, _, _ in os.walk(os.path.join(REF, "src")):
+            inc.append(f"-I{d}")
+        inc += [f"-I{os.path.join(REF, 'include')}", f"-I{os.path.join(REF, 'third_party')}", "-I/usr/local/cuda/include"]
+        try:
+            _run(["g++", *CXXFLAGS, *inc, *srcs, "-o", POOL_SO])
+        except RuntimeError:
+            return None          # not an x86 / AVX2 host, or a checkout without the pool
+    return POOL_SO
+
+
 if __name__ == "__main__":
     force = "--force" in sys.argv
     print(build_oracle(force))
     print(build_ref(force))
+    print(build_ref_pool(force))

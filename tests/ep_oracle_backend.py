@@ -13,8 +13,9 @@ def slice_raw(raw, type_id, rows, cols, first, count):
 
 
 class OracleEpBackend:
-    def __init__(self, shape, layer, experts_total, world, rank):
+    def __init__(self, shape, layer, experts_total, world, rank, shared_gate_vec=None):
         self.orc = oracle.oracle()
+        self.gate_vec = None if shared_gate_vec is None else shared_gate_vec.numpy().astype(np.float32)
         self.shape, self.layer, self.E, self.world, self.rank = shape, layer, experts_total, world, rank
         self.first, self.count = ep.expert_range(experts_total, world, rank)
         H, F = shape.hidden, shape.ff
@@ -50,7 +51,10 @@ class OracleEpBackend:
         shared = None
         if self.sh is not None:
             shared = np.stack([self.orc.expert_ffn(xs[self.rank * T + t], *self.sh) for t in range(T)])
-            shared = torch.from_numpy(shared)
+            if self.gate_vec is not None:          # shared weight = sigmoid(v . x) of the rank's own tokens
+                s = xs[self.rank * T:(self.rank + 1) * T] @ self.gate_vec
+                shared = shared * (1.0 / (1.0 + np.exp(-s)))[:, None].astype(np.float32)
+            shared = torch.from_numpy(shared.astype(np.float32))
         return torch.from_numpy(parts), shared
 
     def finish(self, recv, shared):

@@ -27,7 +27,16 @@ def case(name):
     return {
         "softmax_shared": (S("ep-a", 256, 8, 3, 256, shared=True, types=(21, 21, 21)), 8, 5),
         "sigmoid_bias": (S("ep-b", 256, 6, 2, 256, gating=synth.SIGMOID, sel_bias=True, types=(12, 12, 12)), 6, 4),
+        "gated_shared": (S("ep-c", 256, 8, 3, 256, shared=True, types=(21, 21, 21)), 8, 4),
     }[name]
+
+
+def gate_vector(name):
+    if name != "gated_shared":
+        return None
+    g = torch.Generator()
+    g.manual_seed(77)
+    return torch.randn(256, generator=g) * 0.1
 
 
 def worker(rank, world, port, name, out_dir):
@@ -39,12 +48,12 @@ def worker(rank, world, port, name, out_dir):
     shape, E, T = case(name)
     layer = synth.make_layer(shape, 31, "cpu", experts=E)
     x = synth.make_tokens(shape, T * world, 31, "cpu")[rank * T:(rank + 1) * T]
-    out = ep.ep_forward(OracleEpBackend(shape, layer, E, world, rank), ep.TorchComm(), x)
+    out = ep.ep_forward(OracleEpBackend(shape, layer, E, world, rank, gate_vector(name)), ep.TorchComm(), x)
     np.save(os.path.join(out_dir, f"out{rank}.npy"), out.numpy())
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("name,world", (("softmax_shared", 2), ("softmax_shared", 3), ("sigmoid_bias", 2)))
+@pytest.mark.parametrize("name,world", (("softmax_shared", 2), ("softmax_shared", 3), ("sigmoid_bias", 2), ("gated_shared", 2)))
 def test_ep_matches_unsplit_oracle(orc, tmp_path, name, world):
     port = free_port()
     mp.spawn(worker, args=(world, port, name, str(tmp_path)), nprocs=world, join=True)
@@ -54,7 +63,8 @@ def test_ep_matches_unsplit_oracle(orc, tmp_path, name, world):
     want = orc.moe_layer(x=x.float().numpy(), router_w=layer.router_w.numpy(), topk=shape.topk, ff=shape.ff, gating=shape.gating,
                          norm=shape.norm, scale=shape.scale, types=shape.types, gate=layer.raw[0].numpy(), up=layer.raw[1].numpy(),
                          down=layer.raw[2].numpy(), experts=E, sel_bias=None if layer.sel_bias is None else layer.sel_bias.numpy(),
-                         shared=None if layer.shared_raw is None else tuple(t.numpy() for t in layer.shared_raw))["out"]
+                         shared=None if layer.shared_raw is None else tuple(t.numpy() for t in layer.shared_raw),
+                         shared_gate_vec=None if gate_vector(name) is None else gate_vector(name).numpy())["out"]
     got = np.concatenate([np.load(tmp_path / f"out{r}.npy") for r in range(world)])
     rms = np.sqrt((want.astype(np.float64) ** 2).mean())
     assert np.abs(got - want).max() <= 1e-5 * rms        # only the order of the fp32 partial sums differs

@@ -17,10 +17,10 @@ from util import rel_err
 pytestmark = pytest.mark.gpu
 
 
-def run_split(shape, E, T, world, seed):
+def run_split(shape, E, T, world, seed, gate_vec=None):
     from tqllm_b200 import ep, moe
     layer, x = layer_inputs(shape, E, T * world, seed)
-    full = moe.MoeLayer.from_synth(layer, experts=E)
+    full = moe.MoeLayer.from_synth(layer, experts=E, shared_gate_vec=gate_vec)
     xd = x.cuda()
     want = full.forward(xd).cpu().numpy()
     want_ids = full.artefacts()["ids"].cpu().numpy()
@@ -29,7 +29,7 @@ def run_split(shape, E, T, world, seed):
     for r in range(world):
         first, count = ep.expert_range(E, world, r)
         raw = tuple(slice_raw(layer.raw[i], shape.types[i], (F, F, H)[i], (H, H, F)[i], first, count) for i in range(3))
-        loc = moe.MoeLayer(shape, layer.router_w[first:first + count], raw, layer.shared_raw, experts=count)
+        loc = moe.MoeLayer(shape, layer.router_w[first:first + count], raw, layer.shared_raw, experts=count, shared_gate_vec=gate_vec)
         ranks.append(ep.CudaEpLayer(loc, layer.router_w.cuda(), E, world, r, out_dtype=torch.float32,
                                     sel_bias_all=None if layer.sel_bias is None else layer.sel_bias.cuda()))
     routed = [rk.route_local(xd[r * T:(r + 1) * T]) for r, rk in enumerate(ranks)]
@@ -53,6 +53,20 @@ def test_split_equals_unsplit(world, types, gating, shared):
     with capi.family("decode"):
         got, want = run_split(shape, 16, 6, world, 50 + world)
     assert rel_err(got, want) <= 1e-5
+
+
+def test_split_with_gated_shared_expert():
+    """a shared expert scaled by sigmoid(v . x): every rank weighs the shared rows of its own tokens exactly as one GPU does"""
+    from tqllm_b200 import capi
+    g = torch.Generator()
+    g.manual_seed(12)
+    v = torch.randn(512, generator=g) * 0.05
+    shape = synth.LayerShape("ep-gated", 512, 16, 4, 256, shared=True, types=(21, 21, 21))
+    with capi.family("decode"):
+        got, want = run_split(shape, 16, 6, 4, 61, gate_vec=v)
+        plain, _ = run_split(shape, 16, 6, 4, 61)
+    assert rel_err(got, want) <= 1e-5
+    assert rel_err(plain, want) > 1e-3          # the gate matters: without it the result is a different one
 
 
 @pytest.mark.parametrize("types", ((21, 21, 21), (12, 12, 12)))

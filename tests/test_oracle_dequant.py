@@ -12,7 +12,8 @@ from tqllm_b200 import synth
 from util import same_bits
 
 TYPES = (12, 21, 23, 20, 323)
-REF_GOLDEN = os.path.join(os.environ.get("TQLLM_REFERENCE", "/root/reference"), "tests", "data", "kquant_golden.bin")
+_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF_GOLDEN = os.path.join(os.environ.get("TQLLM_REFERENCE") or os.path.join(os.path.dirname(_ROOT), "reference"), "tests", "data", "kquant_golden.bin")
 
 
 @pytest.mark.parametrize("t", TYPES)

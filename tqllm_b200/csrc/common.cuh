@@ -9,7 +9,12 @@
 
 namespace b2 {
 
-inline int32_t launch_status() { return cudaGetLastError() == cudaSuccess ? B2MOE_OK : B2MOE_ERR_CUDA; }
+// every kernel launch of the library is followed by launch_status(): it also counts them (b2moe_harness_launches)
+extern unsigned long long g_launch_count;
+inline int32_t launch_status() {
+    ++g_launch_count;
+    return cudaGetLastError() == cudaSuccess ? B2MOE_OK : B2MOE_ERR_CUDA;
+}
 inline bool aligned16(const void * p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline cudaStream_t as_stream(b2moe_stream s) { return static_cast<cudaStream_t>(s); }
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

@@ -34,8 +34,8 @@ namespace {
 constexpr int CTA_WARPS = 16;
 constexpr int XPAD = 64;             // bytes added to an activation row in shared memory (bank spread)
 constexpr int MAX_STAGES = 4;
-constexpr int SLOT_TILES = 2;        // consecutive column tiles of one matrix per ring slot and bulk copy: an SM sustains its share of the
-                                     // HBM bandwidth with a few dozen large copies in flight, and loses half of it beyond about 64 copies
+constexpr int MAX_SLOT_TILES = 2;    // consecutive column tiles of one matrix per ring slot and bulk copy (1 or 2): an SM sustains its share of
+                                     // the HBM bandwidth with a few dozen large copies in flight, and loses half of it beyond about 64 copies
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_addr(const void * p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -191,7 +191,7 @@ struct Dec4Args {
     const float * inv_scale;                 // [rows_x]
     int * plan;
     float * out;                             // [A + shared][rows]
-    int rows, k_tiles, experts, topk, A, nbuf, stages;
+    int rows, k_tiles, experts, topk, A, nbuf, stages, slot_tiles;
     uint32_t wait_limit;
     int drop_tile;                           // test hook: the copy into ring slot use number drop_tile (per warp, counted from 0) is never issued; -1 = none
 };
@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t * bars = reinterpret_cast<uint64_t *>(smem);
     volatile int * abort_flag = reinterpret_cast<volatile int *>(smem + BAR_BYTES - 16);
-    constexpr int SLOT = SLOT_TILES * TILE;
+    const int SLOT_TILES = p.slot_tiles, SLOT = SLOT_TILES * TILE;
     uint8_t * ring = smem + BAR_BYTES;                                        // [warp][stage][SLOT]
     uint8_t * xs = ring + size_t(CTA_WARPS) * p.stages * SLOT;               // [buf][8 rows][xrow]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -330,8 +330,8 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
             for (uint32_t i = first; i < issued; ++i)
                 if (int(i) != p.drop_tile) wait(my_full + 8 * (i % S), (i / S) & 1u);
         }
-        if (lane == 16)
-            for (uint32_t i = xissued > 2 ? xissued - 2 : 0; i < xissued; ++i)
+        if (lane == 16)       // the last copy into each activation buffer (an earlier phase of a barrier can no longer be waited for)
+            for (uint32_t i = xissued > uint32_t(p.nbuf) ? xissued - p.nbuf : 0; i < xissued; ++i)
                 wait(xfull + 8 * (p.nbuf == 2 ? (i & 1u) : 0u), (p.nbuf == 2 ? i >> 1 : i) & 1u);
     } else {
         // ---- consumers ----
@@ -446,26 +446,29 @@ int sm_count() {
 }
 constexpr size_t SMEM_LIMIT = 232448 - 1024;
 
-template <uint32_t T> size_t dec4_smem(int k, int nbuf, int stages) {
-    return BAR_BYTES + size_t(CTA_WARPS) * stages * SLOT_TILES * D4<T>::TILE + xs_bytes(k, nbuf);
+template <uint32_t T> size_t dec4_smem(int k, int nbuf, int stages, int slot_tiles) {
+    return BAR_BYTES + size_t(CTA_WARPS) * stages * slot_tiles * D4<T>::TILE + xs_bytes(k, nbuf);
 }
-// the largest (activation buffers, ring stages) that fit: two buffers before a fourth stage
-template <uint32_t T> bool dec4_fit(int k, int & nbuf, int & stages) {
-    const int opts[4][2] = {{2, 3}, {2, 2}, {1, 3}, {1, 2}};
+// (activation buffers, ring stages, tiles per slot) in order of preference, the first that fits: large copies first (measured:
+// two-tile slots with one activation buffer beat one-tile slots with two), then two activation buffers (the next segment's
+// rows arrive while this one is multiplied), then a deeper ring
+template <uint32_t T> bool dec4_fit(int k, int & nbuf, int & stages, int & slot_tiles) {
+    const int opts[6][3] = {{2, 3, 2}, {2, 2, 2}, {1, 3, 2}, {1, 2, 2}, {2, 3, 1}, {1, 3, 1}};
     for (const auto & o : opts)
-        if (dec4_smem<T>(k, o[0], o[1]) <= SMEM_LIMIT) { nbuf = o[0]; stages = o[1]; return true; }
+        if (dec4_smem<T>(k, o[0], o[1], o[2]) <= SMEM_LIMIT) { nbuf = o[0]; stages = o[1]; slot_tiles = o[2]; return true; }
     return false;
 }
 
-int g_drop_tile = -1;                 // test hook (b2moe_debug_dec4_drop_tile)
+int g_drop_tile = -1;                 // test hooks (b2moe_harness_wait_probe, b2moe_harness_skip_staging)
+bool g_skip_stage = false;
 uint32_t g_wait_limit = WAIT_LIMIT;
 
 template <uint32_t T, int MODE>
 int32_t launch_dec4(Dec4Args a, cudaStream_t s) {
     const int sms = sm_count(), k = a.k_tiles * 256;
     if (sms <= 0) return B2MOE_ERR_CUDA;
-    if (!dec4_fit<T>(k, a.nbuf, a.stages)) return B2MOE_ERR_SHAPE;
-    const size_t smem = dec4_smem<T>(k, a.nbuf, a.stages);
+    if (!dec4_fit<T>(k, a.nbuf, a.stages, a.slot_tiles)) return B2MOE_ERR_SHAPE;
+    const size_t smem = dec4_smem<T>(k, a.nbuf, a.stages, a.slot_tiles);
     if (cudaFuncSetAttribute(dec4_k<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
     a.wait_limit = g_wait_limit;
     a.drop_tile = g_drop_tile;
@@ -479,8 +482,9 @@ template <uint32_t T>
 int32_t stage(Dec4Args & a, const void * x, int dtype, int rows_x, int k, void * ws, cudaStream_t s) {
     uint8_t * w = static_cast<uint8_t *>(ws);
     float * inv = reinterpret_cast<float *>(w + staged_bytes(rows_x, k));
-    dec4_stage_k<<<rows_x, STAGE_WARPS * 32, 0, s>>>(x, dtype, rows_x, k, D4<T>::BITS, w, inv);
     a.x = w; a.inv_scale = inv;
+    if (g_skip_stage) return B2MOE_OK;       // the workspace still holds the staged rows of the previous call (benchmarks: the product alone)
+    dec4_stage_k<<<rows_x, STAGE_WARPS * 32, 0, s>>>(x, dtype, rows_x, k, D4<T>::BITS, w, inv);
     return launch_status();
 }
 
@@ -515,10 +519,10 @@ int32_t down_t(const b2moe_bank * down, const b2moe_bank * sd, const float * act
 
 // true when the 4-bit decode kernels take banks of this type with rows of length k
 bool dec4_supported(uint32_t type, int k) {
-    int nbuf, stages;
+    int nbuf, stages, st;
     if (k <= 0 || k % 256) return false;
-    if (type == T_Q4_K) return dec4_fit<T_Q4_K>(k, nbuf, stages);
-    if (type == T_IQ3S4) return dec4_fit<T_IQ3S4>(k, nbuf, stages);
+    if (type == T_Q4_K) return dec4_fit<T_Q4_K>(k, nbuf, stages, st);
+    if (type == T_IQ3S4) return dec4_fit<T_IQ3S4>(k, nbuf, stages, st);
     return false;
 }
 // scratch: the staged form of `rows_x` activation rows of length k and one float per row
@@ -538,6 +542,7 @@ int32_t dec4_down(const b2moe_bank * down, const b2moe_bank * sd, const float * 
     if (down->type == T_IQ3S4) return down_t<T_IQ3S4>(down, sd, act, plan, n, topk, shared_tokens, y, ws, max_active, s);
     return B2MOE_ERR_FORMAT;
 }
+void dec4_skip_staging(bool on) { g_skip_stage = on; }
 void dec4_debug(int drop_tile, uint32_t wait_limit) {
     g_drop_tile = drop_tile;
     g_wait_limit = wait_limit ? wait_limit : WAIT_LIMIT;

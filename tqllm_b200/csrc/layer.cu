@@ -20,6 +20,8 @@ int32_t dec4_gateup(const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, 
                     int, int, float *, void *, int, cudaStream_t);
 int32_t dec4_down(const b2moe_bank *, const b2moe_bank *, const float *, const int *, int, int, int, float *, void *, int, cudaStream_t);
 void dec4_debug(int drop_tile, uint32_t wait_limit);
+void dec4_skip_staging(bool on);
+unsigned long long g_launch_count = 0;
 bool gemm_tc_supported(uint32_t type, int k, int nmat, int experts);
 size_t gemm_tc_workspace_bytes(int rows_x, int k);
 int32_t gemm_tc_gateup(const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const void *, int, const int *, int,
@@ -96,6 +98,8 @@ extern "C" B2MOE_API void b2moe_harness_select(int32_t family, int32_t gemm_item
     gemm_tc_item_tokens(gemm_item_tokens);
 }
 extern "C" B2MOE_API void b2moe_harness_wait_probe(int32_t drop_tile, uint32_t wait_limit) { dec4_debug(drop_tile, wait_limit); }
+extern "C" B2MOE_API void b2moe_harness_skip_staging(int32_t on) { dec4_skip_staging(on != 0); }
+extern "C" B2MOE_API uint64_t b2moe_harness_launches(void) { return g_launch_count; }
 
 extern "C" B2MOE_API size_t b2moe_expert_workspace_bytes(uint32_t type, int32_t rows_x, int32_t k, int32_t x_dtype) {
     if (rows_x <= 0 || k <= 0 || !valid_dtype(x_dtype)) return 0;

@@ -5,9 +5,9 @@ Per layer (the G-rank generalisation of the reference's two-rank `--split expert
 924-976, with NCCL all-gather / all-to-all in place of its grouped send / recv, tp_comm.cpp:94-101):
 
   1. route      every rank routes its own T tokens (router + top-k);
-  2. dispatch   exchange: all ranks gather every rank's activation rows, routed ids and weights (with top-k spread
-                over G ranks nearly every token has an expert on every rank, so the dispatch all-to-all at fixed
-                capacity T is an all-gather);
+  2. dispatch   exchange: all ranks gather every rank's activation rows, routed ids and weights, packed into one
+                record per token so that it is ONE all-gather (with top-k spread over G ranks nearly every token has an
+                expert on every rank, so the dispatch all-to-all at fixed capacity T is an all-gather);
   3. experts    ids outside the rank's block become -1; the usual dispatch -> gate/up + SwiGLU -> down runs on the
                 G*T tokens for the local experts, the shared expert only for the rank's own tokens; a combine over
                 the local assignments (slot order) leaves one fp32 partial sum per token;
@@ -71,15 +71,68 @@ class TorchComm:
         return out
 
 
+def pack_tokens(x: torch.Tensor, ids: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """one byte record per token: its activation row, its k routed ids and its k routing weights -> uint8 [n][record]"""
+    n = x.shape[0]
+    xb, ib, wb = x.shape[1] * x.element_size(), ids.shape[1] * 4, w.shape[1] * 4
+    if out is None:
+        out = torch.empty(n, xb + ib + wb, dtype=torch.uint8, device=x.device)
+    out[:, :xb].copy_(x.contiguous().view(torch.uint8).view(n, xb))
+    out[:, xb:xb + ib].copy_(ids.contiguous().view(torch.uint8).view(n, ib))
+    out[:, xb + ib:].copy_(w.contiguous().view(torch.uint8).view(n, wb))
+    return out
+
+
+def unpack_tokens(rec: torch.Tensor, hidden: int, topk: int, x_dtype, x=None, ids=None, w=None):
+    """the inverse of pack_tokens for [N][record] gathered records -> (x [N][hidden], ids [N][k] int32, w [N][k] f32)"""
+    N = rec.shape[0]
+    xb, ib = hidden * torch.empty((), dtype=x_dtype).element_size(), topk * 4
+    if x is None:
+        x = torch.empty(N, hidden, dtype=x_dtype, device=rec.device)
+        ids = torch.empty(N, topk, dtype=torch.int32, device=rec.device)
+        w = torch.empty(N, topk, dtype=torch.float32, device=rec.device)
+    x.view(torch.uint8).view(N, xb).copy_(rec[:, :xb])
+    ids.view(torch.uint8).view(N, ib).copy_(rec[:, xb:xb + ib])
+    w.view(torch.uint8).view(N, ib).copy_(rec[:, xb + ib:])
+    return x, ids, w
+
+
 def ep_forward(backend, comm, x_local: torch.Tensor) -> torch.Tensor:
     """one expert-parallel layer forward for this rank's tokens; `backend` supplies the three compute phases"""
     ids, weights = backend.route_local(x_local)
-    x_all = comm.all_gather(x_local)
-    ids_all = comm.all_gather(ids)
-    w_all = comm.all_gather(weights)
+    rec_all = comm.all_gather(pack_tokens(x_local, ids, weights))
+    x_all, ids_all, w_all = unpack_tokens(rec_all, x_local.shape[1], ids.shape[1], x_local.dtype)
     parts, shared = backend.partial_sums(x_all, ids_all, w_all)
     recv = comm.all_to_all(parts.view(comm.world, x_local.shape[0], -1))
     return backend.finish(recv, shared)
+
+
+def phase_times(backend, comm, x_local: torch.Tensor, reps: int = 20) -> dict:
+    """mean microseconds of every phase of one expert-parallel layer on this rank (CUDA events on the current stream, every
+    rank must call it): route, pack + all-gather + unpack, the local expert products, the all-to-all of the partial sums,
+    the rank-ordered reduce. The sum is a direct-launch layer; the graphed step is faster by the launch overheads."""
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    names = ("route", "dispatch_exchange", "local_experts", "combine_exchange", "reduce")
+    acc = dict.fromkeys(names, 0.0)
+    for it in range(reps + 2):
+        e = [ev() for _ in range(6)]
+        e[0].record()
+        ids, weights = backend.route_local(x_local)
+        e[1].record()
+        rec_all = comm.all_gather(pack_tokens(x_local, ids, weights))
+        x_all, ids_all, w_all = unpack_tokens(rec_all, x_local.shape[1], ids.shape[1], x_local.dtype)
+        e[2].record()
+        parts, shared = backend.partial_sums(x_all, ids_all, w_all)
+        e[3].record()
+        recv = comm.all_to_all(parts.view(comm.world, x_local.shape[0], -1))
+        e[4].record()
+        backend.finish(recv, shared)
+        e[5].record()
+        torch.cuda.synchronize()
+        if it >= 2:
+            for i, n in enumerate(names):
+                acc[n] += e[i].elapsed_time(e[i + 1]) * 1e3 / reps
+    return acc
 
 
 class CudaEpLayer:
@@ -117,10 +170,16 @@ class CudaEpLayer:
         ids = self._b("ids", (n, sh.topk), torch.int32)
         w = self._b("w", (n, sh.topk), torch.float32)
         dt = moe._DT[x.dtype]
-        self.capi.check(lib.b2moe_router(self.router_w.data_ptr(), None, x.data_ptr(), dt, logits.data_ptr(), self.E + 1, sh.hidden,
-                                         self.E, n, self._st()), "b2moe_router")
+        # a gated shared expert (weight = sigmoid(v . x), the router's extra logits column): the weights of this rank's own tokens
+        gate_vec = self.layer.shared_gate_vec if self.layer.sh is not None else None
+        if gate_vec is not None and sh.gating != self.capi.SOFTMAX:
+            raise self.capi.B2moeError(self.capi.ERR_SHAPE, "the sigmoid routing family adds its shared expert unscaled")
+        self.shared_w = self._b("shared_w", (n,), torch.float32) if gate_vec is not None else None
+        self.capi.check(lib.b2moe_router(self.router_w.data_ptr(), None if gate_vec is None else gate_vec.data_ptr(), x.data_ptr(), dt,
+                                         logits.data_ptr(), self.E + 1, sh.hidden, self.E, n, self._st()), "b2moe_router")
         if sh.gating == self.capi.SOFTMAX:
-            self.capi.check(lib.b2moe_topk_softmax(logits.data_ptr(), self.E + 1, ids.data_ptr(), w.data_ptr(), None, self.E, sh.topk, n,
+            self.capi.check(lib.b2moe_topk_softmax(logits.data_ptr(), self.E + 1, ids.data_ptr(), w.data_ptr(),
+                                                   None if self.shared_w is None else self.shared_w.data_ptr(), self.E, sh.topk, n,
                                                    sh.scale, self._st()), "b2moe_topk_softmax")
         else:
             bias = None if self.sel_bias is None else self.sel_bias.data_ptr()
@@ -166,14 +225,16 @@ class CudaEpLayer:
         G, T, H = recv.shape
         out = self._b("out", (T, H), self.out_dtype)
         from . import moe
-        self.capi.check(self.lib.b2moe_ep_reduce(recv.data_ptr(), G, None if shared is None else shared.data_ptr(), None, T, H,
-                                                 out.data_ptr(), moe._DT[self.out_dtype], self._st()), "b2moe_ep_reduce")
+        sw = getattr(self, "shared_w", None) if shared is not None else None
+        self.capi.check(self.lib.b2moe_ep_reduce(recv.data_ptr(), G, None if shared is None else shared.data_ptr(),
+                                                 None if sw is None else sw.data_ptr(), T, H, out.data_ptr(), moe._DT[self.out_dtype],
+                                                 self._st()), "b2moe_ep_reduce")
         return out
 
 
 class GraphedEpForward:
     """ep_forward for a CUDA backend with the three compute phases replayed as CUDA graphs (one launch each instead of
-    about ten) and the collectives issued between them in the ordinary way: no collective is ever captured. The input
+    about ten) and the two collectives issued between them in the ordinary way: no collective is ever captured. The input
     tensor and every exchange buffer keep their addresses; `x_local` must be the same tensor at every call."""
 
     def __init__(self, backend: CudaEpLayer, comm, x_local: torch.Tensor):
@@ -183,19 +244,25 @@ class GraphedEpForward:
         stream = torch.cuda.current_stream()
         # eager pass: allocates the backend's buffers and gives the exchange buffers their shapes
         ids, w = backend.route_local(x_local)
+        k = ids.shape[1]
+        self.rec = pack_tokens(x_local, ids, w)
+        self.rec_all = torch.empty((G * T, self.rec.shape[1]), dtype=torch.uint8, device=dev)
         self.x_all = torch.empty((G * T,) + tuple(x_local.shape[1:]), dtype=x_local.dtype, device=dev)
-        self.ids_all = torch.empty((G * T, ids.shape[1]), dtype=ids.dtype, device=dev)
-        self.w_all = torch.empty((G * T, w.shape[1]), dtype=w.dtype, device=dev)
-        comm.all_gather(x_local, self.x_all); comm.all_gather(ids, self.ids_all); comm.all_gather(w, self.w_all)
+        self.ids_all = torch.empty((G * T, k), dtype=ids.dtype, device=dev)
+        self.w_all = torch.empty((G * T, k), dtype=w.dtype, device=dev)
+        comm.all_gather(self.rec, self.rec_all)
+        unpack_tokens(self.rec_all, x_local.shape[1], k, x_local.dtype, self.x_all, self.ids_all, self.w_all)
         parts, shared = backend.partial_sums(self.x_all, self.ids_all, self.w_all)
         self.recv = torch.empty((G, T, parts.shape[1]), dtype=parts.dtype, device=dev)
         comm.all_to_all(parts.view(G, T, -1), self.recv)
         backend.finish(self.recv, shared)
         stream.synchronize()
         self.g_route, self.g_part, self.g_fin = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.g_route, stream=stream):
+        with torch.cuda.graph(self.g_route, stream=stream):             # route + pack
             self.ids, self.w = backend.route_local(x_local)
-        with torch.cuda.graph(self.g_part, stream=stream):
+            pack_tokens(x_local, self.ids, self.w, self.rec)
+        with torch.cuda.graph(self.g_part, stream=stream):              # unpack + local experts + partial sums
+            unpack_tokens(self.rec_all, x_local.shape[1], k, x_local.dtype, self.x_all, self.ids_all, self.w_all)
             self.parts, self.shared = backend.partial_sums(self.x_all, self.ids_all, self.w_all)
         with torch.cuda.graph(self.g_fin, stream=stream):
             self.out = backend.finish(self.recv, self.shared)
@@ -203,7 +270,7 @@ class GraphedEpForward:
     def __call__(self) -> torch.Tensor:
         c = self.comm
         self.g_route.replay()
-        c.all_gather(self.x, self.x_all); c.all_gather(self.ids, self.ids_all); c.all_gather(self.w, self.w_all)
+        c.all_gather(self.rec, self.rec_all)
         self.g_part.replay()
         c.all_to_all(self.parts.view(c.world, self.x.shape[0], -1), self.recv)
         self.g_fin.replay()
