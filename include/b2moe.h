@@ -87,6 +87,9 @@ B2MOE_API size_t b2moe_bank_aux_bytes(uint32_t type, int32_t rows, int32_t cols)
 /* raw GGUF blocks (device, [experts*rows] rows) -> bank. `data`/`aux` are the caller's buffers of experts * the sizes above. */
 B2MOE_API int32_t b2moe_bank_load(uint32_t type, const void * raw, int32_t experts, int32_t rows, int32_t cols, void * data,
                         void * aux, b2moe_stream stream);
+/* The same bank built on the host: raw, data and aux are HOST memory and no CUDA call is made (a loader that uploads
+ * finished banks through the engine's own upload callback, or packs expert files offline). */
+B2MOE_API int32_t b2moe_bank_pack_host(uint32_t type, const void * raw, int32_t experts, int32_t rows, int32_t cols, void * data, void * aux);
 /* bank -> fp32 [experts*rows][cols], bit-identical to dequantize_host (src/formats/weight/dequant.cpp:393-606) */
 B2MOE_API int32_t b2moe_dequant_dump(const b2moe_bank * bank, float * out, b2moe_stream stream);
 
@@ -180,6 +183,40 @@ B2MOE_API size_t b2moe_static_scratch_bytes(void);
 B2MOE_API int32_t b2moe_expert_down_static(const b2moe_bank * down, const b2moe_bank * shared_down, const float * act,
                                  const int32_t * plan, int32_t n, int32_t topk, int32_t shared_tokens, float * y,
                                  b2moe_stream stream);
+/* ---- the reference's per-matrix expert calls ------------------------------------------------------------------
+ * The same products with the argument shapes of tqllm::WeightFormat's expert virtuals, for an adapter that implements
+ * them (tqllm_b200/adapter/b200_expert_format.cpp): device ids or moe_group's (counts, groups) in, bf16 / fp16 rows per
+ * assignment out, no plan to keep. Each call dispatches, multiplies and converts inside the caller's workspace.
+ * b2moe_expert_matvec replaces WeightFormat::expert_matvec (src/formats/weight/weight_format.hpp:62-63):
+ *   y[a][r] = W_ids[a][r] . x[per_expert_input ? a : a / topk] for every a with ids[a] >= 0; other rows stay untouched.
+ * b2moe_expert_gemm replaces WeightFormat::expert_gemm (weight_format.hpp:51-53): the same over groups [experts][capacity]
+ *   and counts [experts] as moe_group leaves them (src/experts/moe_kernels.cuh:29; capacity = tokens).
+ * b2moe_expert_gemm_gateup replaces WeightFormat::expert_gemm_gateup (weight_format.hpp:58-59): act[a] = silu(gate . x) * (up . x).
+ * b2moe_plan_from_groups turns moe_group's lists into a plan (no shared expert) for the plan-driven entry points.
+ * Workspace: b2moe_expert_matvec_workspace_bytes(bank, n, topk) serves the first two,
+ * b2moe_expert_gemm_gateup_workspace_bytes(gate, n, topk, x_dtype) the third; 16-byte aligned. */
+B2MOE_API size_t b2moe_expert_matvec_workspace_bytes(const b2moe_bank * bank, int32_t n, int32_t topk);
+B2MOE_API size_t b2moe_expert_gemm_gateup_workspace_bytes(const b2moe_bank * gate, int32_t n, int32_t topk, int32_t x_dtype);
+B2MOE_API int32_t b2moe_plan_from_groups(const int32_t * counts, const int32_t * groups, int32_t capacity, int32_t experts,
+                               int32_t assignments, int32_t * plan, b2moe_stream stream);
+B2MOE_API int32_t b2moe_expert_matvec(const b2moe_bank * bank, const void * x, int32_t x_dtype, void * y, int32_t y_dtype, const int32_t * ids,
+                            int32_t n, int32_t topk, int32_t per_expert_input, void * workspace, size_t workspace_bytes,
+                            b2moe_stream stream);
+B2MOE_API int32_t b2moe_expert_gemm(const b2moe_bank * bank, const void * x, int32_t x_dtype, void * y, int32_t y_dtype, const int32_t * counts,
+                          const int32_t * groups, int32_t capacity, int32_t topk, int32_t per_expert_input, void * workspace,
+                          size_t workspace_bytes, b2moe_stream stream);
+B2MOE_API int32_t b2moe_expert_gemm_gateup(const b2moe_bank * gate, const b2moe_bank * up, const void * x, int32_t x_dtype, void * act,
+                                 int32_t act_dtype, const int32_t * counts, const int32_t * groups, int32_t capacity, int32_t topk,
+                                 void * workspace, size_t workspace_bytes, b2moe_stream stream);
+/* moe_sum (src/experts/moe_kernels.cuh:73-74) and moe_swiglu (:71-72) on the reference's row types, and
+ * WeightFormat::dequant_h (weight_format.hpp:78; workspace: experts * rows * cols floats). */
+B2MOE_API int32_t b2moe_sum_rows(const void * routed, const void * shared, int32_t in_dtype, const float * weights, const float * shared_weights,
+                       void * out, int32_t out_dtype, int32_t hidden, int32_t topk, int32_t n, b2moe_stream stream);
+B2MOE_API int32_t b2moe_swiglu(const void * gate, const void * up, int32_t in_dtype, void * act, int32_t act_dtype, int64_t count,
+                     b2moe_stream stream);
+B2MOE_API int32_t b2moe_dequant_dump_as(const b2moe_bank * bank, void * out, int32_t out_dtype, void * workspace, size_t workspace_bytes,
+                              b2moe_stream stream);
+
 /* out[t] = sum_s weights[t][s] * y[t*topk + s] (slot order, skipped where ids[t][s] < 0 when ids is given)
  *          + shared_weights[t] (1 when null) * y[n*topk + t] when shared_tokens = n.
  * Replaces moe_sum / moe_common::moe_sum / fn_moe_combine (src/experts/moe.cu:223-234, src/experts/moe_common.cu:186-194,

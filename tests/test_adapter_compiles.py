@@ -1,11 +1,15 @@
-"""The reference-side shims (tqllm_b200/adapter/tqllm_shims.cpp: tqLLM's free functions of the expert path written against
-include/b2moe.h) compile as plain C++ against the header and link against the built library with no undefined symbol:
-the argument lists of the C ABI are what a tqLLM build would bind."""
+"""The reference-side code compiles and links on its own: the free-function shims (tqllm_b200/adapter/tqllm_shims.cpp)
+against include/b2moe.h, and the WeightFormat adapter (tqllm_b200/adapter/b200_expert_format.cpp) against the reference's
+own weight_format.hpp where that checkout exists, both with -Wall -Werror and --no-undefined, and the driver program of the
+GPU adapter test links the shims through the reference's declarations (moe_kernels.cuh): a signature that differs from the
+reference's would be an undefined symbol."""
 import os
 import shutil
 import subprocess
 
 import pytest
+
+import adapter_build
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SRC = os.path.join(ROOT, "tqllm_b200", "adapter", "tqllm_shims.cpp")
@@ -21,3 +25,12 @@ def test_shims_compile_and_link(tmp_path):
            "-o", out, "-Wl,--no-undefined", lib, "-L/usr/local/cuda/lib64", "-lcudart"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
+
+
+@pytest.mark.skipif(shutil.which("g++") is None or not adapter_build.reference_headers(), reason="needs g++ and the reference checkout's headers")
+def test_adapter_compiles_against_the_reference_header():
+    try:
+        driver = adapter_build.build()
+    except subprocess.CalledProcessError as e:
+        pytest.fail(e.stderr[-3000:])
+    assert os.path.isfile(driver) and os.path.isfile(adapter_build.LIB)

@@ -3,6 +3,7 @@
 // libb2moe.so instead of src/experts/moe.cu / moe_common.cu. Same argument order and meaning as the reference; errors
 // become the reference's exceptions (std::invalid_argument for shapes, std::runtime_error for launch failures,
 // src/experts/moe.cu:239,250, src/experts/moe_common.cu:10-13). Compile check: tests/test_adapter_compiles.py.
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -38,33 +39,32 @@ void route(const float * logits, const float * bias, int * ids, float * w, int e
 }
 }  // namespace moe_common
 
-// moe_kernels.cuh:29: counts [experts], groups [experts][n]. `plan` and `scratch` come from the engine's per-layer arena
-// (b2moe_plan_ints, b2moe_dispatch_workspace_bytes). Unlike the reference's atomics the lists come out in ascending
-// assignment order every time.
-void moe_group(const int * ids, int * counts, int * groups, int experts, int n, int topk, cudaStream_t s, int32_t * plan, void * scratch,
-               size_t scratch_bytes) {
-    b2_check(b2moe_dispatch(ids, n, topk, experts, 0, plan, scratch, scratch_bytes, s), "moe_group");
+// Device scratch of the shims that need one (moe_group): owned by the engine, set once per engine thread.
+static thread_local struct { void * p = nullptr; size_t bytes = 0; } g_scratch;
+void b200_set_shim_scratch(void * device_ptr, size_t bytes) { g_scratch.p = device_ptr; g_scratch.bytes = bytes; }
+size_t b200_shim_scratch_bytes(int experts, int n, int topk) {
+    return size_t(b2moe_plan_ints(experts, n * topk, 0)) * sizeof(int32_t) + 256 + b2moe_dispatch_workspace_bytes(experts, n * topk);
+}
+
+// moe_kernels.cuh:29: counts [experts], groups [experts][n]; negative ids are skipped. Unlike the reference's atomics the
+// lists come out in ascending assignment order every time. The plan and the dispatch scratch live in the shim scratch.
+void moe_group(const int * ids, int * counts, int * groups, int experts, int n, int topk, cudaStream_t s) {
+    const size_t plan_bytes = (size_t(b2moe_plan_ints(experts, n * topk, 0)) * sizeof(int32_t) + 255) / 256 * 256;
+    if (!g_scratch.p || g_scratch.bytes < b200_shim_scratch_bytes(experts, n, topk)) throw std::invalid_argument("moe_group: shim scratch missing or too small");
+    int32_t * plan = static_cast<int32_t *>(g_scratch.p);
+    b2_check(b2moe_dispatch(ids, n, topk, experts, 0, plan, static_cast<char *>(g_scratch.p) + plan_bytes, g_scratch.bytes - plan_bytes, s), "moe_group");
     b2_check(b2moe_plan_to_groups(plan, n, topk, experts, counts, groups, s), "moe_group");
 }
 
-// moe_kernels.cuh:71-72 (moe_sum): out[t] = sum over the token's slots of weights[t][s] * y[t * topk + s] (+ the shared
-// expert's row times its weight); per-assignment rows are fp32 here, the output bf16 as in the reference
-void moe_sum(const float * y, const float * weights, const float * shared_weights, int n, int topk, int hidden, int shared_tokens,
-             void * out_bf16, cudaStream_t s) {
-    b2_check(b2moe_combine(y, nullptr, weights, shared_weights, n, topk, hidden, shared_tokens, out_bf16, B2MOE_BF16, s), "moe_sum");
+// moe_kernels.cuh:71-72: act = silu(gate) * up over `count` values, bf16 in, fp16 out
+void moe_swiglu(const __nv_bfloat16 * gate, const __nv_bfloat16 * up, __half * act, int count, cudaStream_t s) {
+    b2_check(b2moe_swiglu(gate, up, B2MOE_BF16, act, B2MOE_F16, count, s), "moe_swiglu");
 }
 
-// The gate/up product with the SwiGLU fused and the down product, over a plan built by moe_group / b2moe_dispatch: what
-// WeightFormat::expert_matvec2 + moe_swiglu and WeightFormat::expert_matvec(per_expert_input) compute
-// (src/formats/weight/weight_format.hpp:62-73), for an adapter class to forward to.
-void expert_gateup_swiglu(const b2moe_bank & gate, const b2moe_bank & up, const __half * x, const int32_t * plan, int n, int topk, float * act,
-                          void * workspace, size_t workspace_bytes, cudaStream_t s) {
-    b2_check(b2moe_expert_gateup_swiglu(&gate, &up, nullptr, nullptr, x, B2MOE_F16, plan, n, topk, 0, act, workspace, workspace_bytes, s),
-             "expert_gateup_swiglu");
-}
-void expert_down(const b2moe_bank & down, const float * act, const int32_t * plan, int n, int topk, float * y, void * workspace,
-                 size_t workspace_bytes, cudaStream_t s) {
-    b2_check(b2moe_expert_down(&down, nullptr, act, plan, n, topk, 0, y, workspace, workspace_bytes, s), "expert_down");
+// moe_kernels.cuh:73-74: out[t] = sum_s weights[t][s] * routed[t * topk + s] + shared_weights[t] * shared[t]; bf16 rows
+void moe_sum(const __nv_bfloat16 * routed, const __nv_bfloat16 * shared, const float * weights, const float * shared_weights,
+             __nv_bfloat16 * out, int hidden, int topk, int n, cudaStream_t s) {
+    b2_check(b2moe_sum_rows(routed, shared, B2MOE_BF16, weights, shared_weights, out, B2MOE_BF16, hidden, topk, n, s), "moe_sum");
 }
 
 }  // namespace tqllm_cuda

@@ -72,6 +72,16 @@ SIGNATURES = {
     "b2moe_expert_workspace_bytes": (_sz, [_u32, _i32, _i32, _i32]),
     "b2moe_expert_gateup_swiglu": (_i32, [C.POINTER(Bank)] * 4 + [_vp, _i32, _vp, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
     "b2moe_expert_down": (_i32, [C.POINTER(Bank)] * 2 + [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
+    "b2moe_expert_matvec_workspace_bytes": (_sz, [C.POINTER(Bank), _i32, _i32]),
+    "b2moe_expert_gemm_gateup_workspace_bytes": (_sz, [C.POINTER(Bank), _i32, _i32, _i32]),
+    "b2moe_plan_from_groups": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp, _vp]),
+    "b2moe_expert_matvec": (_i32, [C.POINTER(Bank), _vp, _i32, _vp, _i32, _vp, _i32, _i32, _i32, _vp, _sz, _vp]),
+    "b2moe_expert_gemm": (_i32, [C.POINTER(Bank), _vp, _i32, _vp, _i32, _vp, _vp, _i32, _i32, _i32, _vp, _sz, _vp]),
+    "b2moe_expert_gemm_gateup": (_i32, [C.POINTER(Bank)] * 2 + [_vp, _i32, _vp, _i32, _vp, _vp, _i32, _i32, _vp, _sz, _vp]),
+    "b2moe_bank_pack_host": (_i32, [_u32, _vp, _i32, _i32, _i32, _vp, _vp]),
+    "b2moe_sum_rows": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
+    "b2moe_swiglu": (_i32, [_vp, _vp, _i32, _vp, _i32, _i64, _vp]),
+    "b2moe_dequant_dump_as": (_i32, [C.POINTER(Bank), _vp, _i32, _vp, _sz, _vp]),
     "b2moe_static_scratch_bytes": (_sz, []),
     "b2moe_expert_down_static": (_i32, [C.POINTER(Bank)] * 2 + [_vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "b2moe_combine": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _i32, _vp]),

@@ -121,6 +121,53 @@ extern "C" B2MOE_API int32_t b2moe_bank_load(uint32_t type, const void * raw, in
     return B2MOE_ERR_FORMAT;
 }
 
+namespace b2 {
+namespace {
+template <uint32_t T>
+void pack_host_t(const uint8_t * raw, int experts, int rows, int cols, uint8_t * data) {
+    const int row_tiles = ceil_div(rows, 16), k_tiles = cols / Fmt<T>::KT;
+    for (int e = 0; e < experts; ++e)
+        for (int rt = 0; rt < row_tiles; ++rt)
+            for (int kt = 0; kt < k_tiles; ++kt) {
+                uint32_t * dst = reinterpret_cast<uint32_t *>(data + ((size_t(e) * row_tiles + rt) * k_tiles + kt) * Fmt<T>::TILE);
+                const uint8_t * src = raw + size_t(e) * rows * k_tiles * Fmt<T>::RAW;
+                for (int wi = 0; wi < Fmt<T>::TILE / 4; ++wi) dst[wi] = Fmt<T>::pack_word(src, rows, k_tiles, rt, kt, wi);
+            }
+}
+}  // namespace
+}  // namespace b2
+
+// The bank of b2moe_bank_load built on the host (all pointers host memory): the same bytes, for a loader that uploads
+// finished banks through the engine's own upload path (WeightFormat::load, src/formats/weight/weight_format.hpp:39) and
+// for packing expert files offline. No CUDA call is made.
+extern "C" B2MOE_API int32_t b2moe_bank_pack_host(uint32_t type, const void * raw, int32_t experts, int32_t rows, int32_t cols, void * data,
+                                                  void * aux) {
+    FmtInfo f;
+    if (!fmt_info(type, f)) return B2MOE_ERR_FORMAT;
+    if (experts <= 0 || rows <= 0 || cols <= 0 || cols % f.kt) return B2MOE_ERR_SHAPE;
+    if (!raw || !data || (f.aux && !aux)) return B2MOE_ERR_NULL;
+    const uint8_t * r = static_cast<const uint8_t *>(raw);
+    uint8_t * d = static_cast<uint8_t *>(data);
+    switch (type) {
+        case T_Q4_K: pack_host_t<T_Q4_K>(r, experts, rows, cols, d); break;
+        case T_IQ3_S: pack_host_t<T_IQ3_S>(r, experts, rows, cols, d); break;
+        case T_IQ3S4: pack_host_t<T_IQ3S4>(r, experts, rows, cols, d); break;
+        case T_IQ4_XS: pack_host_t<T_IQ4_XS>(r, experts, rows, cols, d); break;
+        case T_IQ4_NL: pack_host_t<T_IQ4_NL>(r, experts, rows, cols, d); break;
+        case T_NVFP4G: {
+            const int rows_pad = 16 * ceil_div(rows, 16), nblk = cols / 128;
+            float * a = static_cast<float *>(aux);
+            for (int e = 0; e < experts; ++e)
+                for (int rr = 0; rr < rows_pad; ++rr)
+                    a[size_t(e) * rows_pad + rr] = rr < rows ? bits_to_float(ld_u32_bytes(r + (size_t(e) * rows + rr) * nblk * 76)) : 0.f;
+            pack_host_t<T_NVFP4G>(r, experts, rows, cols, d);
+            break;
+        }
+        default: return B2MOE_ERR_FORMAT;
+    }
+    return B2MOE_OK;
+}
+
 extern "C" B2MOE_API int32_t b2moe_dequant_dump(const b2moe_bank * bank, float * out, b2moe_stream stream) {
     if (const int32_t rc = check_bank(bank)) return rc;
     if (!out) return B2MOE_ERR_NULL;

@@ -59,6 +59,7 @@ __device__ __forceinline__ void dispatch_small_body(const int * __restrict__ ids
         const int id = valid_id(ids, a, A, e);
         const unsigned peers = __match_any_sync(0xffffffffu, id);
         if (id >= 0 && lane == __ffs(peers) - 1) hist[warp * e + id] += (unsigned short)__popc(peers);
+        __syncwarp();                 // the leader's update is in place before the next step's leaders read the counter
     }
     __syncthreads();
     for (int x = threadIdx.x; x < e; x += blockDim.x) {
