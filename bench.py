@@ -449,20 +449,18 @@ def run_b200(args):
         reg_e2e = [event_ms(torch, stream, step_e2e, args.steps) for _ in range(max(1, min(R, 10)))]
         ms_step, ms_e2e = statistics.median(reg), statistics.median(reg_e2e)
 
-        # stage timings: every stage of a layer launched alone, bracketed by events on the launching stream, averaged over the layers
+        # stage timings: every stage of a layer alone (CUDA events on the launching stream around graph replays), averaged over the layers
         prods = [expert_products(torch, moe, lib, C, lay, x, shape, stream) for lay in layers]
 
         def time_stage(fns, reps=max(3, min(args.steps, 20))):
+            """mean microseconds of one call: the calls (one per layer) replayed as a CUDA graph, so that the host's launch cost
+            is not on the clock"""
             for f in fns:
                 f()
-            evs = []
-            for _ in range(reps):
-                for f in fns:
-                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    a.record(stream); f(); b.record(stream)
-                    evs.append((a, b))
             stream.synchronize()
-            return 1e3 * sum(a.elapsed_time(b) for a, b in evs) / len(evs)
+            g = graph_of(torch, stream, lambda: [f() for f in fns])
+            g.replay()
+            return event_ms(torch, stream, g.replay, reps) * 1e3 / len(fns)
 
         gu_call_us = time_stage([p[0] for p in prods])
         dn_call_us = time_stage([p[1] for p in prods])

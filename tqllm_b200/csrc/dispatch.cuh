@@ -45,14 +45,14 @@ __device__ inline void finish_plan(int * plan, int * counts, int * offsets, int 
     if (lane == 31) { passes[na] = pp; plan[PLAN_NPASS] = pp; }
 }
 
-// ---- single block of 1024 threads: every phase in shared memory (decode-sized batches); hist = [32 warps][e] ----
+// ---- single block (up to 32 warps): every phase in shared memory (decode-sized batches); hist = [warps][e] ----
 __device__ __forceinline__ void dispatch_small_body(const int * __restrict__ ids, int A, int e, int shared_first, int shared_tokens,
                                                     int * __restrict__ plan, unsigned short * hist) {
     const int e1 = e + 1;
     int * counts = plan + PLAN_HDR, * offsets = counts + e1, * active = offsets + e1 + 1, * perm = active + e1;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int chunk = ((A + 31) / 32 + 31) / 32 * 32;   // per warp, a multiple of 32
-    for (int i = threadIdx.x; i < 32 * e; i += blockDim.x) hist[i] = 0;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int chunk = ((A + nw - 1) / nw + 31) / 32 * 32;   // per warp, a multiple of 32
+    for (int i = threadIdx.x; i < nw * e; i += blockDim.x) hist[i] = 0;
     __syncthreads();
     const int a0 = warp * chunk;
     for (int a = a0 + lane; a - lane < min(A, a0 + chunk); a += 32) {
@@ -64,7 +64,7 @@ __device__ __forceinline__ void dispatch_small_body(const int * __restrict__ ids
     __syncthreads();
     for (int x = threadIdx.x; x < e; x += blockDim.x) {
         int run = 0;
-        for (int w = 0; w < 32; ++w) { const int c = hist[w * e + x]; hist[w * e + x] = (unsigned short)run; run += c; }
+        for (int w = 0; w < nw; ++w) { const int c = hist[w * e + x]; hist[w * e + x] = (unsigned short)run; run += c; }
         counts[x] = run;
     }
     if (threadIdx.x == 0) counts[e] = shared_tokens;

@@ -278,17 +278,19 @@ __global__ void route_k(const float * __restrict__ logits, int ld, const float *
     route_token<GATING>(logits, ld, bias, ids, weights, shared_weights, e, k, norm, scale, token, lane, p, p + e);
 }
 
-// Top-k routing and dispatch in one launch for decode-sized batches: the block's 32 warps route the tokens (round
+// Top-k routing and dispatch in one launch for decode-sized batches: the block's 16 warps route the tokens (round
 // robin), then the same block builds the plan from the ids it just wrote. Saves a launch and a device-wide drain.
+// 512 threads: the register-resident top-k keeps 32 values per lane, which a 1024-thread block's 64 registers would spill.
+constexpr int RD_THREADS = 512;
 template <int GATING>
-__global__ void __launch_bounds__(1024) route_dispatch_k(const float * __restrict__ logits, int ld, const float * __restrict__ bias,
+__global__ void __launch_bounds__(RD_THREADS) route_dispatch_k(const float * __restrict__ logits, int ld, const float * __restrict__ bias,
                                                          int * __restrict__ ids, float * __restrict__ weights,
                                                          float * __restrict__ shared_weights, int e, int k, int norm, float scale, int n,
                                                          int shared_first, int shared_count, int * __restrict__ plan) {
     extern __shared__ float smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float * p = smem + size_t(warp) * 2 * e;
-    for (int token = warp; token < n; token += 32) {
+    for (int token = warp; token < n; token += RD_THREADS / 32) {
         route_token<GATING>(logits, ld, bias, ids, weights, shared_weights, e, k, norm, scale, token, lane, p, p + e);
         __syncwarp();
     }
@@ -370,16 +372,19 @@ extern "C" B2MOE_API int32_t b2moe_route_dispatch(int32_t gating, const float * 
     if (experts <= 0 || experts > 4096 || topk <= 0 || topk > experts || n <= 0 || ld < experts + (shared_weights ? 1 : 0)) return B2MOE_ERR_SHAPE;
     if (shared_first < 0 || shared_count < 0 || shared_first + shared_count > n || (long long)n * topk > 0x3fffffffLL) return B2MOE_ERR_SHAPE;
     if (!logits || !ids || !weights || !plan) return B2MOE_ERR_NULL;
-    const size_t smem = size_t(32) * 2 * experts * sizeof(float);
-    if (dispatch_small_path(experts, n * topk) && smem <= 160 * 1024) {
+    const size_t smem = size_t(RD_THREADS / 32) * 2 * experts * sizeof(float);
+    // one launch only while every token has a warp of its own: the single block routes its tokens RD_THREADS / 32 at a time,
+    // and a token's ten selection rounds are a dependent chain of about ten microseconds (measured: 64 tokens, 512 experts:
+    // 53 us fused against 12 + 10 us as two launches)
+    if (n <= RD_THREADS / 32 && dispatch_small_path(experts, n * topk) && smem <= 160 * 1024) {
         cudaStream_t s = as_stream(stream);
         if (gating == B2MOE_SOFTMAX) {
             if (cudaFuncSetAttribute(route_dispatch_k<B2MOE_SOFTMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
-            route_dispatch_k<B2MOE_SOFTMAX><<<1, 1024, smem, s>>>(logits, ld, nullptr, ids, weights, shared_weights, experts, topk, 1, scale, n,
+            route_dispatch_k<B2MOE_SOFTMAX><<<1, RD_THREADS, smem, s>>>(logits, ld, nullptr, ids, weights, shared_weights, experts, topk, 1, scale, n,
                                                                   shared_first, shared_count, plan);
         } else {
             if (cudaFuncSetAttribute(route_dispatch_k<B2MOE_SIGMOID>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
-            route_dispatch_k<B2MOE_SIGMOID><<<1, 1024, smem, s>>>(logits, ld, bias, ids, weights, nullptr, experts, topk, norm, scale, n,
+            route_dispatch_k<B2MOE_SIGMOID><<<1, RD_THREADS, smem, s>>>(logits, ld, bias, ids, weights, nullptr, experts, topk, norm, scale, n,
                                                                   shared_first, shared_count, plan);
         }
         return launch_status();
