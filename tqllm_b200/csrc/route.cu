@@ -181,7 +181,10 @@ __device__ __forceinline__ void route_token_regs(const float * __restrict__ logi
             key[r] = in ? ordered_bits(bias ? p[r] + bias[lane + 32 * r] : p[r]) : 0u;
         }
     }
-    float sel_sum = 0.f;
+    // lane q keeps the q-th selection (k <= 32 on this path): one coalesced store of ids and weights at the end instead of a
+    // store per round and a read-modify-write pass of lane 0 over global memory
+    float sel_sum = 0.f, my_p = 0.f;
+    int my_idx = 0;
     for (int q = 0; q < k; ++q) {
         uint32_t best = 0;
         int br = 0;
@@ -194,21 +197,17 @@ __device__ __forceinline__ void route_token_regs(const float * __restrict__ logi
 #pragma unroll
         for (int r = 0; r < R; ++r) if (r == orow) { pv = p[r]; if (lane == owner) key[r] = 0u; }
         pv = __shfl_sync(0xffffffffu, pv, owner);
-        if (lane == 0) {
-            ids[size_t(token) * k + q] = idx == 0x7fffffff ? 0 : idx;
-            weights[size_t(token) * k + q] = pv;
-        }
+        if (lane == q) { my_idx = idx == 0x7fffffff ? 0 : idx; my_p = pv; }
         sel_sum += pv;
     }
-    if (lane == 0) {
-        float * w = weights + size_t(token) * k;
-        if (norm) {
-            const float total = fmaxf(sel_sum, 6.103515625e-5f);
-            for (int r = 0; r < k; ++r) w[r] = w[r] / total;
-        }
-        if (scale != 0.f && scale != 1.f) for (int r = 0; r < k; ++r) w[r] *= scale;
-        if (shared_weights) shared_weights[token] = 1.f / (1.f + expf(-x[e]));
+    if (lane < k) {
+        float w = my_p;
+        if (norm) w = w / fmaxf(sel_sum, 6.103515625e-5f);
+        if (scale != 0.f && scale != 1.f) w *= scale;
+        ids[size_t(token) * k + lane] = my_idx;
+        weights[size_t(token) * k + lane] = w;
     }
+    if (lane == 0 && shared_weights) shared_weights[token] = 1.f / (1.f + expf(-x[e]));
 }
 
 // One warp per token. p[] = unbiased probabilities, key[] = selection keys (p, or p + bias), both in shared memory.
@@ -217,9 +216,9 @@ template <int GATING>
 __device__ __forceinline__ void route_token(const float * __restrict__ logits, int ld, const float * __restrict__ bias, int * __restrict__ ids,
                                             float * __restrict__ weights, float * __restrict__ shared_weights, int e, int k, int norm,
                                             float scale, int token, int lane, float * p, float * key) {
-    if (e <= 128) return route_token_regs<GATING, 4>(logits, ld, bias, ids, weights, shared_weights, e, k, norm, scale, token, lane);
-    if (e <= 256) return route_token_regs<GATING, 8>(logits, ld, bias, ids, weights, shared_weights, e, k, norm, scale, token, lane);
-    if (e <= 512) return route_token_regs<GATING, 16>(logits, ld, bias, ids, weights, shared_weights, e, k, norm, scale, token, lane);
+    if (k <= 32 && e <= 128) return route_token_regs<GATING, 4>(logits, ld, bias, ids, weights, shared_weights, e, k, norm, scale, token, lane);
+    if (k <= 32 && e <= 256) return route_token_regs<GATING, 8>(logits, ld, bias, ids, weights, shared_weights, e, k, norm, scale, token, lane);
+    if (k <= 32 && e <= 512) return route_token_regs<GATING, 16>(logits, ld, bias, ids, weights, shared_weights, e, k, norm, scale, token, lane);
     const float * x = logits + size_t(token) * ld;
     if (GATING == B2MOE_SOFTMAX) {
         float m = -CUDART_INF_F;
