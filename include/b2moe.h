@@ -240,6 +240,28 @@ B2MOE_API int32_t b2moe_ep_local_ids(const int32_t * ids, int32_t * local_ids, i
 B2MOE_API int32_t b2moe_ep_reduce(const float * parts, int32_t ranks, const float * shared_y, const float * shared_weights,
                         int32_t n, int32_t hidden, void * out, int32_t out_dtype, b2moe_stream stream);
 
+/* All-to-all dispatch, for batches where gathering every token on every rank is too much: a rank sends a token only to the
+ * ranks that own one of its routed experts, and always to itself (the shared expert then finds every own token in the local
+ * batch). The exchange itself is two variable-size all-to-alls driven by the host (NCCL), preceded by a count exchange.
+ * b2moe_ep_peer_lists: bounds [peers + 1] = first expert of every rank's block (device). For peer p, ascending token order:
+ *   list[p][j] = j-th token sent to p, pos[p][t] = position of token t in p's list or -1, counts[p] = list length
+ *   (pos, list: [peers][n] ints).
+ * b2moe_ep_pack: records = sum of counts; offsets [peers + 1] = prefix sums of counts (device). A record is the activation
+ *   row (x_row_bytes, a multiple of 16), topk int32 routed ids, topk fp32 weights; 8 * topk must be a multiple of 16.
+ * b2moe_ep_unpack: received records -> x rows, local ids (ids outside [first_expert, first_expert + local_experts) become -1)
+ *   and weights, ready for b2moe_dispatch_range and the expert products.
+ * b2moe_ep_return_reduce: back = the partial sums that came home, in the order the records were sent;
+ *   out[t] = sum over peers in ascending order of back[offsets[p] + pos[p][t]] + shared_weights[t] * shared_y[t]. */
+B2MOE_API int32_t b2moe_ep_peer_lists(const int32_t * ids, int32_t n, int32_t topk, const int32_t * bounds, int32_t peers, int32_t self,
+                            int32_t * counts, int32_t * pos, int32_t * list, b2moe_stream stream);
+B2MOE_API int32_t b2moe_ep_pack(const void * x, int32_t x_row_bytes, const int32_t * ids, const float * weights, int32_t topk, int32_t n,
+                      const int32_t * list, const int32_t * offsets, int32_t peers, int32_t records, void * out, b2moe_stream stream);
+B2MOE_API int32_t b2moe_ep_unpack(const void * records_in, int32_t records, int32_t x_row_bytes, int32_t topk, int32_t first_expert,
+                        int32_t local_experts, void * x, int32_t * local_ids, float * weights, b2moe_stream stream);
+B2MOE_API int32_t b2moe_ep_return_reduce(const float * back, const int32_t * pos, const int32_t * offsets, int32_t peers, const float * shared_y,
+                               const float * shared_weights, int32_t n, int32_t hidden, void * out, int32_t out_dtype,
+                               b2moe_stream stream);
+
 /* ---- harness hooks ---------------------------------------------------------------------------------------------
  * For tests and benchmarks, not for engines: process-wide switches, not thread-safe, to be set while no call of this
  * library is running. They have no counterpart in the reference.

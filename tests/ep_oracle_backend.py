@@ -64,3 +64,59 @@ class OracleEpBackend:
         if shared is not None:
             out += shared
         return out
+
+    # ---- all-to-all dispatch (numpy restatement of b2moe_ep_peer_lists / pack / unpack / return_reduce) ----
+    def peer_lists(self, ids):
+        ids = ids.numpy()
+        n = ids.shape[0]
+        G = self.world
+        bounds = [ep.expert_range(self.E, G, p)[0] for p in range(G)] + [self.E]
+        counts, pos, lst = np.zeros(G, np.int32), np.full((G, n), -1, np.int32), np.zeros((G, n), np.int32)
+        for p in range(G):
+            flag = ((ids >= bounds[p]) & (ids < bounds[p + 1])).any(1) | (p == self.rank)
+            toks = np.nonzero(flag)[0]
+            counts[p] = len(toks)
+            pos[p, toks] = np.arange(len(toks))
+            lst[p, :len(toks)] = toks
+        return torch.from_numpy(counts), torch.from_numpy(pos), torch.from_numpy(lst)
+
+    def pack_records(self, x, ids, w, lst, offsets, records):
+        k, H = ids.shape[1], x.shape[1]
+        rows = []
+        off = offsets.numpy()
+        for p in range(self.world):
+            for j in range(off[p + 1] - off[p]):
+                t = int(lst[p, j])
+                rows.append(np.concatenate([x[t].float().numpy(), ids[t].numpy().astype(np.float32), w[t].numpy()]))
+        return torch.from_numpy(np.stack(rows).astype(np.float32)) if rows else torch.zeros(0, H + 2 * k)
+
+    def partial_sums_records(self, recv, records, self_off, T):
+        k, H = self.shape.topk, self.shape.hidden
+        r = recv.numpy()
+        xs, ids, w = r[:, :H], r[:, H:H + k].astype(np.int64), r[:, H + k:]
+        parts = np.zeros((records, H), np.float32)
+        for j in range(records):
+            for s in range(k):
+                e = ids[j, s] - self.first
+                if 0 <= e < self.count:
+                    parts[j] += w[j, s] * self.orc.expert_ffn(xs[j], *self.w[e])
+        shared = None
+        if self.sh is not None:
+            own = xs[self_off:self_off + T]
+            shared = np.stack([self.orc.expert_ffn(own[t], *self.sh) for t in range(T)])
+            if self.gate_vec is not None:
+                shared = shared * (1.0 / (1.0 + np.exp(-(own @ self.gate_vec))))[:, None].astype(np.float32)
+            shared = torch.from_numpy(shared.astype(np.float32))
+        return torch.from_numpy(parts), shared
+
+    def finish_records(self, back, pos, offsets, shared):
+        G, T = pos.shape
+        out = torch.zeros(T, back.shape[1])
+        for t in range(T):
+            for p in range(G):
+                q = int(pos[p, t])
+                if q >= 0:
+                    out[t] += back[int(offsets[p]) + q]
+        if shared is not None:
+            out += shared
+        return out

@@ -39,7 +39,7 @@ def gate_vector(name):
     return torch.randn(256, generator=g) * 0.1
 
 
-def worker(rank, world, port, name, out_dir):
+def worker(rank, world, port, name, out_dir, a2a=False):
     import sys
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
     from ep_oracle_backend import OracleEpBackend
@@ -48,15 +48,17 @@ def worker(rank, world, port, name, out_dir):
     shape, E, T = case(name)
     layer = synth.make_layer(shape, 31, "cpu", experts=E)
     x = synth.make_tokens(shape, T * world, 31, "cpu")[rank * T:(rank + 1) * T]
-    out = ep.ep_forward(OracleEpBackend(shape, layer, E, world, rank, gate_vector(name)), ep.TorchComm(), x)
+    fwd = ep.ep_forward_a2a if a2a else ep.ep_forward
+    out = fwd(OracleEpBackend(shape, layer, E, world, rank, gate_vector(name)), ep.TorchComm(), x)
     np.save(os.path.join(out_dir, f"out{rank}.npy"), out.numpy())
     dist.destroy_process_group()
 
 
 @pytest.mark.parametrize("name,world", (("softmax_shared", 2), ("softmax_shared", 3), ("sigmoid_bias", 2), ("gated_shared", 2)))
-def test_ep_matches_unsplit_oracle(orc, tmp_path, name, world):
+@pytest.mark.parametrize("a2a", (False, True), ids=("allgather", "alltoall"))
+def test_ep_matches_unsplit_oracle(orc, tmp_path, name, world, a2a):
     port = free_port()
-    mp.spawn(worker, args=(world, port, name, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(worker, args=(world, port, name, str(tmp_path), a2a), nprocs=world, join=True)
     shape, E, T = case(name)
     layer = synth.make_layer(shape, 31, "cpu", experts=E)
     x = synth.make_tokens(shape, T * world, 31, "cpu")

@@ -44,6 +44,66 @@ def run_split(shape, E, T, world, seed, gate_vec=None):
     return np.concatenate(outs), want
 
 
+def run_split_a2a(shape, E, T, world, seed, gate_vec=None):
+    """the all-to-all dispatch with every rank on this device: the exchanges are slices of the ranks' send buffers"""
+    from tqllm_b200 import ep, moe
+    layer, x = layer_inputs(shape, E, T * world, seed)
+    full = moe.MoeLayer.from_synth(layer, experts=E, shared_gate_vec=gate_vec)
+    xd = x.cuda()
+    want = full.forward(xd).cpu().numpy()
+    H, F = shape.hidden, shape.ff
+    ranks = []
+    for r in range(world):
+        first, count = ep.expert_range(E, world, r)
+        raw = tuple(slice_raw(layer.raw[i], shape.types[i], (F, F, H)[i], (H, H, F)[i], first, count) for i in range(3))
+        loc = moe.MoeLayer(shape, layer.router_w[first:first + count], raw, layer.shared_raw, experts=count, shared_gate_vec=gate_vec)
+        ranks.append(ep.CudaEpLayer(loc, layer.router_w.cuda(), E, world, r, out_dtype=torch.float32,
+                                    sel_bias_all=None if layer.sel_bias is None else layer.sel_bias.cuda()))
+    st = []
+    for r, rk in enumerate(ranks):
+        xl = xd[r * T:(r + 1) * T].contiguous()
+        ids, w = rk.route_local(xl)
+        ids, w = ids.clone(), w.clone()
+        counts, pos, lst = (t.clone() for t in rk.peer_lists(ids))
+        n = [int(v) for v in counts.cpu()]
+        off = torch.zeros(world + 1, dtype=torch.int32)
+        off[1:] = torch.cumsum(torch.tensor(n, dtype=torch.int32), 0)
+        send = rk.pack_records(xl, ids, w, lst, off.cuda(), sum(n)).clone()
+        st.append(dict(n=n, off=[int(v) for v in off], offd=off.cuda(), pos=pos, send=send, sw=None if rk.shared_w is None else rk.shared_w.clone()))
+    outs = []
+    backs = [[None] * world for _ in range(world)]
+    for p, rk in enumerate(ranks):                      # rank p receives segment p of every rank's send buffer, in rank order
+        segs = [st[r]["send"][st[r]["off"][p]:st[r]["off"][p + 1]] for r in range(world)]
+        recv_n = [s_.shape[0] for s_ in segs]
+        recv = torch.cat(segs).contiguous()
+        parts, shared = rk.partial_sums_records(recv, sum(recv_n), sum(recv_n[:p]), T)
+        assert int(rk.buf["plan"][3]) == 0
+        st[p]["shared"] = None if shared is None else shared.clone()
+        o = 0
+        for r in range(world):
+            backs[r][p] = parts[o:o + recv_n[r]].clone()
+            o += recv_n[r]
+    for r, rk in enumerate(ranks):
+        back = torch.cat(backs[r]).contiguous()
+        rk.shared_w = st[r]["sw"]
+        outs.append(rk.finish_records(back, st[r]["pos"], st[r]["offd"], st[r]["shared"]).cpu().numpy())
+    sent = sum(sum(s_["n"]) for s_ in st)
+    return np.concatenate(outs), want, sent
+
+
+@pytest.mark.parametrize("world", (2, 4))
+@pytest.mark.parametrize("types,gating,shared,topk", (((21, 21, 21), 1, True, 2), ((12, 12, 12), 2, False, 4)))
+def test_alltoall_dispatch_equals_unsplit(world, types, gating, shared, topk):
+    from tqllm_b200 import capi
+    shape = synth.LayerShape("ep-a2a", 512, 16, topk, 256, gating=gating, sel_bias=gating == 2, shared=shared, types=types)
+    with capi.family("decode"):
+        got, want, sent = run_split_a2a(shape, 16, 7, world, 80 + world)
+    assert rel_err(got, want) <= 1e-5
+    assert sent <= world * world * 7                    # never more records than the all-gather moves
+    if topk == 2 and world == 4:
+        assert sent < world * world * 7                 # two experts cannot sit on four ranks: some token rows stay home
+
+
 @pytest.mark.parametrize("world", (2, 4))
 @pytest.mark.parametrize("types,gating,shared", (((21, 21, 21), 1, True), ((12, 12, 12), 2, False), ((23, 23, 20), 1, True)))
 def test_split_equals_unsplit(world, types, gating, shared):

@@ -67,6 +67,10 @@ SIGNATURES = {
     "b2moe_dispatch_range": (_i32, [_vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
     "b2moe_ep_local_ids": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp]),
     "b2moe_ep_reduce": (_i32, [_vp, _i32, _vp, _vp, _i32, _i32, _vp, _i32, _vp]),
+    "b2moe_ep_peer_lists": (_i32, [_vp, _i32, _i32, _vp, _i32, _i32, _vp, _vp, _vp, _vp]),
+    "b2moe_ep_pack": (_i32, [_vp, _i32, _vp, _vp, _i32, _i32, _vp, _vp, _i32, _i32, _vp, _vp]),
+    "b2moe_ep_unpack": (_i32, [_vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
+    "b2moe_ep_return_reduce": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _i32, _i32, _vp, _i32, _vp]),
     "b2moe_route_dispatch": (_i32, [_i32, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _f32, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
     "b2moe_plan_to_groups": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp, _vp]),
     "b2moe_expert_workspace_bytes": (_sz, [_u32, _i32, _i32, _i32]),

@@ -9,8 +9,8 @@ namespace {
 template <int DT>
 __global__ void combine_k(const float * __restrict__ y, const int * __restrict__ ids, const float * __restrict__ w,
                           const float * __restrict__ sw, int n, int k, int h, int shared_tokens, typename Elem<DT>::type * __restrict__ out) {
-    const int t = blockIdx.y;
-    const int j = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const int t = blockIdx.x;                     // tokens on gridDim.x: any batch size
+    const int j = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
     if (j >= h) return;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s = 0; s < k; ++s) {
@@ -40,11 +40,11 @@ using namespace b2;
 extern "C" B2MOE_API int32_t b2moe_combine(const float * y, const int32_t * ids, const float * weights, const float * shared_weights, int32_t n,
                                  int32_t topk, int32_t hidden, int32_t shared_tokens, void * out, int32_t out_dtype,
                                  b2moe_stream stream) {
-    if (n <= 0 || topk <= 0 || hidden <= 0 || hidden % 4 || n > 65535 || (shared_tokens != 0 && shared_tokens != n)) return B2MOE_ERR_SHAPE;
+    if (n <= 0 || topk <= 0 || hidden <= 0 || hidden % 4 || (shared_tokens != 0 && shared_tokens != n)) return B2MOE_ERR_SHAPE;
     if (!valid_dtype(out_dtype)) return B2MOE_ERR_SHAPE;
     if (!y || !weights || !out) return B2MOE_ERR_NULL;
     if (!aligned16(y) || !aligned16(out)) return B2MOE_ERR_ALIGN;
-    const dim3 grid(ceil_div(hidden / 4, 128), n);
+    const dim3 grid(n, ceil_div(hidden / 4, 128));
     cudaStream_t s = as_stream(stream);
     if (out_dtype == B2MOE_F32)
         combine_k<B2MOE_F32><<<grid, 128, 0, s>>>(y, ids, weights, shared_weights, n, topk, hidden, shared_tokens, static_cast<float *>(out));

@@ -14,6 +14,13 @@ Per layer (the G-rank generalisation of the reference's two-rank `--split expert
   4. combine    exchange: all-to-all returns slice h of the partial sums to home rank h, which adds the G slices in
                 ascending rank order (deterministic) plus its shared expert.
 
+For batches where gathering every token on every rank is too much (prefill), `ep_forward_a2a` is the all-to-all form of
+steps 2 - 4: a rank sends a token only to the ranks that own one of its routed experts (and always to itself, so that
+its shared expert finds every own token in the local batch); a count exchange gives both sides the exact sizes, so there
+is no fixed capacity and no overflow rule (the reference's two-rank exchange caps the result rows and computes the
+overflow locally, src/models/qwen/qwen4exp/decode_rules.hpp:210, which needs every expert resident on every rank).
+The partial sums travel home by the reverse all-to-all and are added in ascending peer order.
+
 The orchestration below is backend-agnostic (phases + a communicator) so that the same code runs on NCCL, on gloo
 with a CPU backend in the tests, and in-process with all ranks on one GPU (the reference tests EP the same way,
 tests/ep_split.cu:87-151). The CUDA backend calls the C ABI only.
@@ -70,6 +77,30 @@ class TorchComm:
                 q.wait()
         return out
 
+    def all_to_all_v(self, t: torch.Tensor, send_counts, recv_counts) -> torch.Tensor:
+        """rows of t in peer segments of send_counts rows -> the rows received, in peer segments of recv_counts rows"""
+        out = torch.empty((sum(recv_counts),) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        try:
+            dist.all_to_all_single(out, t.contiguous(), list(recv_counts), list(send_counts), group=self.group)
+        except (RuntimeError, NotImplementedError):
+            so, ro = [0], [0]
+            for c in send_counts:
+                so.append(so[-1] + c)
+            for c in recv_counts:
+                ro.append(ro[-1] + c)
+            reqs = []
+            for p in range(self.world):
+                if p == self.rank:
+                    out[ro[p]:ro[p + 1]].copy_(t[so[p]:so[p + 1]])
+                else:
+                    if send_counts[p]:
+                        reqs.append(dist.isend(t[so[p]:so[p + 1]].contiguous(), p, group=self.group))
+                    if recv_counts[p]:
+                        reqs.append(dist.irecv(out[ro[p]:ro[p + 1]], p, group=self.group))
+            for q in reqs:
+                q.wait()
+        return out
+
 
 def pack_tokens(x: torch.Tensor, ids: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """one byte record per token: its activation row, its k routed ids and its k routing weights -> uint8 [n][record]"""
@@ -105,6 +136,23 @@ def ep_forward(backend, comm, x_local: torch.Tensor) -> torch.Tensor:
     parts, shared = backend.partial_sums(x_all, ids_all, w_all)
     recv = comm.all_to_all(parts.view(comm.world, x_local.shape[0], -1))
     return backend.finish(recv, shared)
+
+
+def ep_forward_a2a(backend, comm, x_local: torch.Tensor) -> torch.Tensor:
+    """one expert-parallel layer forward with the all-to-all dispatch (two host reads of G counts per layer)"""
+    G, r, T = comm.world, comm.rank, x_local.shape[0]
+    ids, weights = backend.route_local(x_local)
+    counts, pos, lst = backend.peer_lists(ids)                       # device: [G], [G][T], [G][T]
+    recv_counts = comm.all_to_all(counts.view(G, 1)).view(G)
+    send_n, recv_n = [int(v) for v in counts.cpu()], [int(v) for v in recv_counts.cpu()]
+    offsets = torch.zeros(G + 1, dtype=torch.int32)
+    offsets[1:] = torch.cumsum(torch.tensor(send_n, dtype=torch.int32), 0)
+    offsets = offsets.to(counts.device)
+    send = backend.pack_records(x_local, ids, weights, lst, offsets, sum(send_n))
+    recv = comm.all_to_all_v(send, send_n, recv_n)
+    parts, shared = backend.partial_sums_records(recv, sum(recv_n), sum(recv_n[:r]), T)
+    back = comm.all_to_all_v(parts, recv_n, send_n)
+    return backend.finish_records(back, pos, offsets, shared)
 
 
 def phase_times(backend, comm, x_local: torch.Tensor, reps: int = 20) -> dict:
@@ -220,6 +268,82 @@ class CudaEpLayer:
                                           self.capi.F32, self._st()), "b2moe_combine")
         shared = y[A + self.rank * T:A + (self.rank + 1) * T] if has_sh else None
         return parts, shared
+
+    # ---- all-to-all dispatch ----
+    def _bounds(self):
+        b = self.buf.get("bounds")
+        if b is None:
+            b = torch.tensor([expert_range(self.E, self.world, p)[0] for p in range(self.world)] + [self.E], dtype=torch.int32,
+                             device=self.router_w.device)
+            self.buf["bounds"] = b
+        return b
+
+    def peer_lists(self, ids):
+        n, k = ids.shape
+        G = self.world
+        counts, pos, lst = self._b("pl_counts", (G,), torch.int32), self._b("pl_pos", (G, n), torch.int32), self._b("pl_list", (G, n), torch.int32)
+        self.capi.check(self.lib.b2moe_ep_peer_lists(ids.data_ptr(), n, k, self._bounds().data_ptr(), G, self.rank, counts.data_ptr(),
+                                                     pos.data_ptr(), lst.data_ptr(), self._st()), "b2moe_ep_peer_lists")
+        return counts, pos, lst
+
+    def pack_records(self, x, ids, w, lst, offsets, records):
+        n, k = ids.shape
+        xb = x.shape[1] * x.element_size()
+        out = torch.empty(max(records, 1), xb + 8 * k, dtype=torch.uint8, device=x.device)[:records]
+        self.capi.check(self.lib.b2moe_ep_pack(x.data_ptr(), xb, ids.data_ptr(), w.data_ptr(), k, n, lst.data_ptr(), offsets.data_ptr(),
+                                               self.world, records, out.data_ptr(), self._st()), "b2moe_ep_pack")
+        return out
+
+    def partial_sums_records(self, recv, records, self_off, T):
+        """the local expert products over the received records; the shared expert for the T records at self_off (the rank's own tokens)"""
+        from . import moe
+        lib, sh, L = self.lib, self.shape, self.layer
+        k, H = sh.topk, sh.hidden
+        x_dtype = torch.bfloat16 if sh.act_dtype != "f32" else torch.float32
+        xb = H * (2 if x_dtype != torch.float32 else 4)
+        N = max(records, 1)
+        x = torch.empty(N, H, dtype=x_dtype, device=recv.device)
+        ids = torch.full((N, k), -1, dtype=torch.int32, device=recv.device)
+        w = torch.zeros(N, k, dtype=torch.float32, device=recv.device)
+        self.capi.check(lib.b2moe_ep_unpack(recv.data_ptr(), records, xb, k, self.first, self.count, x.data_ptr(), ids.data_ptr(), w.data_ptr(),
+                                            self._st()), "b2moe_ep_unpack")
+        has_sh = L.sh is not None
+        A, shared_n = N * k, (N if has_sh else 0)
+        pv = self.capi.PlanView()
+        lib.b2moe_plan_view_of(self.count, A, T if has_sh else 0, C.byref(pv))
+        plan = torch.zeros(pv.total, dtype=torch.int32, device=recv.device)
+        dws = torch.empty(max(lib.b2moe_dispatch_workspace_bytes(self.count, A), 16), dtype=torch.uint8, device=recv.device)
+        self.capi.check(lib.b2moe_dispatch_range(ids.data_ptr(), N, k, self.count, self_off if has_sh else 0, T if has_sh else 0, plan.data_ptr(),
+                                                 dws.data_ptr(), dws.numel(), self._st()), "b2moe_dispatch_range")
+        act = torch.empty(A + shared_n, sh.ff, dtype=torch.float32, device=recv.device)
+        y = torch.empty(A + shared_n, H, dtype=torch.float32, device=recv.device)
+        dt = moe._DT[x_dtype]
+        eg = lib.b2moe_expert_workspace_bytes(L.gate.type, N, H, dt)
+        ed = lib.b2moe_expert_workspace_bytes(L.down.type, A + shared_n, sh.ff, self.capi.F32)
+        ews = torch.empty(max(eg, ed, 16), dtype=torch.uint8, device=recv.device)
+        br = lambda b: C.byref(b.c)
+        shg, shu, shd = (br(L.sh[0]), br(L.sh[1]), br(L.sh[2])) if has_sh else (None, None, None)
+        self.capi.check(lib.b2moe_expert_gateup_swiglu(br(L.gate), br(L.up), shg, shu, x.data_ptr(), dt, plan.data_ptr(), N, k, shared_n,
+                                                       act.data_ptr(), ews.data_ptr(), ews.numel(), self._st()), "gateup")
+        self.capi.check(lib.b2moe_expert_down(br(L.down), shd, act.data_ptr(), plan.data_ptr(), N, k, shared_n, y.data_ptr(), ews.data_ptr(),
+                                              ews.numel(), self._st()), "down")
+        parts = torch.empty(N, H, dtype=torch.float32, device=recv.device)
+        self.capi.check(lib.b2moe_combine(y.data_ptr(), ids.data_ptr(), w.data_ptr(), None, N, k, H, 0, parts.data_ptr(), self.capi.F32,
+                                          self._st()), "b2moe_combine")
+        self.buf["plan"] = plan
+        shared = y[A + self_off:A + self_off + T] if has_sh else None
+        return parts[:records], shared
+
+    def finish_records(self, back, pos, offsets, shared):
+        from . import moe
+        G, T = pos.shape
+        H = self.shape.hidden
+        out = self._b("out", (T, H), self.out_dtype)
+        sw = getattr(self, "shared_w", None) if shared is not None else None
+        self.capi.check(self.lib.b2moe_ep_return_reduce(back.data_ptr(), pos.data_ptr(), offsets.data_ptr(), G,
+                                                        None if shared is None else shared.data_ptr(), None if sw is None else sw.data_ptr(),
+                                                        T, H, out.data_ptr(), moe._DT[self.out_dtype], self._st()), "b2moe_ep_return_reduce")
+        return out
 
     def finish(self, recv, shared):
         G, T, H = recv.shape
