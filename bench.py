@@ -323,23 +323,7 @@ def workload_record(torch, moe, synth, lib, C, stream, dev, cfg, tokens, layout)
     x = synth.make_tokens(shape, tokens, SEED + 9, dev)
     bias_note = None
     if cfg == "c5":
-        # Zipf(s = 1.2) pressure on the routing: router rows of expert e grow along a direction every token shares, by an
-        # amount that falls like log(rank^-1.2); the amount is tuned so that the hottest expert holds about 10x the mean
-        d = torch.zeros(shape.hidden, device=dev)
-        d[::5] = 1.0
-        d /= d.norm()
-        x = (x.float() + 3.0 * d).to(x.dtype)
-        rank = torch.arange(1, shape.experts + 1, device=dev, dtype=torch.float32)
-        base = sl.router_w.clone()
-        lo, hi, ratio, w = 0.0, 4.0, 1.0, base
-        for _ in range(18):
-            c = 0.5 * (lo + hi)
-            w = base + (c * -1.2 * torch.log(rank))[:, None] * d[None, :] / 3.0
-            cnt = torch.bincount((x.float() @ w.T).topk(shape.topk, -1).indices.flatten(), minlength=shape.experts).float()
-            ratio = float(cnt.max() / cnt.mean())
-            lo, hi = (c, hi) if ratio < 10.0 else (lo, c)
-        sl.router_w.copy_(w)
-        bias_note = f"Zipf(1.2) routing pressure through the router rows: hottest expert {ratio:.1f}x the mean token count"
+        x, bias_note = zipf_router(torch, shape, sl.router_w, x, dev)
     lay = moe.MoeLayer.from_synth(sl, device=dev, iq3s_layout=layout)
     del sl
     torch.cuda.empty_cache()
@@ -527,6 +511,26 @@ def run_b200(args):
             for lay in layers:
                 lay.reserve(T)
 
+        # the fixed-total-batch anchor of the multi-GPU runs: 512 tokens on this one GPU, the same 4 layers
+        fixed = None
+        if not args.no_extras and args.workload == "c2":
+            xf = synth.make_tokens(shape, 512, SEED + 100, dev)
+            of = [torch.empty(512, shape.hidden, dtype=torch.bfloat16, device=dev) for _ in range(L)]
+
+            def step_fixed():
+                for lay, o in zip(layers, of):
+                    lay.forward(xf, out=o)
+            for _ in range(3):
+                step_fixed()
+            stream.synchronize()
+            g = graph_of(torch, stream, step_fixed)
+            g.replay()
+            ms_f = event_ms(torch, stream, g.replay, 20)
+            fixed = {"tokens_total": 512, "tokens_per_gpu": 512, "ms_per_step": ms_f, "layer_tokens_per_s": 512 * L / (ms_f * 1e-3)}
+            del g, of
+            for lay in layers:
+                lay.reserve(T)
+
     gu_bytes = 2 * synth.raw_bytes(shape.types[0], shape.ff, shape.hidden)
     peak, peak_kind = peaks()
     bound, roof_unit = "hbm", "GB/s"
@@ -581,11 +585,96 @@ def run_b200(args):
                      "kernel_ms": k_ms, "active_experts_per_launch": n_active, "bytes_per_expert": gu_bytes, "status": status},
         "expert_weight_gbs": weight_bytes_step / (ms_step * 1e-3) / 1e9,
         "expert_weight_frac_of_8tbs": weight_bytes_step / (ms_step * 1e-3) / 8e12,
-        "stage_us": stage_us, "sweep": sweep, "workloads": workloads,
+        "stage_us": stage_us, "sweep": sweep, "fixed_total_512": fixed, "workloads": workloads,
         "nominal_peaks_not_measured": {"int8_tops_dense": NOMINAL_TFLOPS["int8"], "fp4_tflops_dense": NOMINAL_TFLOPS["fp4"],
                                        "note": "NVIDIA's per-GPU B200 figures; only the HBM copy rate and the bf16 GEMM rate were measured on this pool"},
         "cpu_baseline": cpu, "clocks": clocks.summary(),
     }))
+
+
+def zipf_router(torch, shape, router_w, x, dev):
+    """Zipf(s = 1.2) pressure on the routing: router rows of expert e grow along a direction every token shares, by an amount
+    that falls like log(rank^-1.2), tuned so that the hottest expert holds about 10x the mean token count; returns (x, note)"""
+    d = torch.zeros(shape.hidden, device=dev)
+    d[::5] = 1.0
+    d /= d.norm()
+    x = (x.float() + 3.0 * d).to(x.dtype)
+    rank = torch.arange(1, shape.experts + 1, device=dev, dtype=torch.float32)
+    base = router_w.clone()
+    lo, hi, ratio, w = 0.0, 4.0, 1.0, base
+    for _ in range(18):
+        c = 0.5 * (lo + hi)
+        w = base + (c * -1.2 * torch.log(rank))[:, None] * d[None, :] / 3.0
+        cnt = torch.bincount((x.float() @ w.T).topk(shape.topk, -1).indices.flatten(), minlength=shape.experts).float()
+        ratio = float(cnt.max() / cnt.mean())
+        lo, hi = (c, hi) if ratio < 10.0 else (lo, c)
+    router_w.copy_(w)
+    return x, f"Zipf(1.2) routing pressure through the router rows: hottest expert {ratio:.1f}x the mean token count"
+
+
+def ep_layers(torch, moe, synth, ep, shape, L, rank, world, dev, layout, rscale=1.0, zipf_tokens=None):
+    """every rank draws the same layers (same seed) and keeps the banks of its own expert block only"""
+    first, count = ep.expert_range(shape.experts, world, rank)
+    H, F = shape.hidden, shape.ff
+    out, note = [], None
+    for l in range(L):
+        sl = synth.make_layer(shape, SEED + 17 * l, dev, router_scale=rscale)
+        if zipf_tokens is not None:
+            _, note = zipf_router(torch, shape, sl.router_w, zipf_tokens, dev)
+        cut = lambda raw, i: raw[first * synth.raw_bytes(shape.types[i], (F, F, H)[i], (H, H, F)[i]):
+                                 (first + count) * synth.raw_bytes(shape.types[i], (F, F, H)[i], (H, H, F)[i])].clone()
+        lay = moe.MoeLayer(shape, sl.router_w[first:first + count], tuple(cut(sl.raw[i], i) for i in range(3)), sl.shared_raw,
+                           experts=count, device=dev, iq3s_layout=layout)
+        out.append(ep.CudaEpLayer(lay, sl.router_w.contiguous(), shape.experts, world, rank,
+                                  sel_bias_all=None if sl.sel_bias is None else sl.sel_bias.contiguous()))
+        del sl
+        torch.cuda.empty_cache()
+    return out, note
+
+
+def ep_record(torch, dist, moe, synth, ep, comm, stream, dev, rank, world, cfg, total_tokens, a2a, layout, reps=10):
+    """one expert-parallel record of another configuration: one layer, total_tokens over all ranks, direct launches; the time is
+    the maximum over the ranks"""
+    shape = synth.CONFIGS[cfg]
+    T = max(1, total_tokens // world)
+    x_all = synth.make_tokens(shape, T * world, SEED + 9, dev)                # the same tokens on every rank; a rank routes its slice
+    zx = None
+    if cfg == "c5":
+        zx = x_all
+    eps, note = ep_layers(torch, moe, synth, ep, shape, 1, rank, world, dev, layout, zipf_tokens=zx)
+    if cfg == "c5":
+        d = torch.zeros(shape.hidden, device=dev)
+        d[::5] = 1.0
+        d /= d.norm()
+        x_all = (x_all.float() + 3.0 * d).to(x_all.dtype)
+    x = x_all[rank * T:(rank + 1) * T].contiguous()
+    fwd = ep.ep_forward_a2a if a2a else ep.ep_forward
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            fwd(eps[0], comm, x)
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            fwd(eps[0], comm, x)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        n_active = torch.tensor([float(int(eps[0].buf["plan"][0]))], device=dev)
+        status = torch.tensor([float(int(eps[0].buf["plan"][3]))], device=dev)
+        dist.all_reduce(n_active, op=dist.ReduceOp.SUM)
+        dist.all_reduce(status, op=dist.ReduceOp.MAX)
+    rec = {"workload": workload_name(shape, T * world, 1), "tokens_total": T * world, "tokens_per_gpu": T,
+           "dispatch": "all-to-all (count exchange + variable-size records)" if a2a else "all-gather",
+           "layer_us": float(ms) * 1e3, "layer_tokens_per_s": T * world / (float(ms) * 1e-3), "active_experts_all_ranks": float(n_active),
+           "expert_weight_gbs_all_ranks": float(n_active) * shape.expert_bytes() / (float(ms) * 1e-3) / 1e9, "status": int(status)}
+    if note:
+        rec["routing"] = note
+    del eps
+    torch.cuda.empty_cache()
+    return rec
 
 
 def run_ep(args, torch, dist, capi, moe, synth, rank, world, local, dev):
@@ -594,23 +683,11 @@ def run_ep(args, torch, dist, capi, moe, synth, rank, world, local, dev):
     lib = capi.lib
     shape = synth.CONFIGS[args.workload]
     T, L = args.tokens, args.layers
-    first, count = ep.expert_range(shape.experts, world, rank)
     rscale = synth.solve_router_scale(shape, 0.6) if args.workload == "c2" else 1.0
-    layers, router_all, bias_all = [], [], []
-    H, F = shape.hidden, shape.ff
-    for l in range(L):
-        sl = synth.make_layer(shape, SEED + 17 * l, dev, router_scale=rscale)      # the same layer on every rank (same seed)
-        cut = lambda raw, i: raw[first * synth.raw_bytes(shape.types[i], (F, F, H)[i], (H, H, F)[i]):
-                                 (first + count) * synth.raw_bytes(shape.types[i], (F, F, H)[i], (H, H, F)[i])].clone()
-        layers.append(moe.MoeLayer(shape, sl.router_w[first:first + count], tuple(cut(sl.raw[i], i) for i in range(3)), sl.shared_raw,
-                                   experts=count, device=dev, iq3s_layout=args.iq3s_layout))
-        router_all.append(sl.router_w.contiguous())
-        bias_all.append(None if sl.sel_bias is None else sl.sel_bias.contiguous())
-        del sl
-        torch.cuda.empty_cache()
+    eps, _ = ep_layers(torch, moe, synth, ep, shape, L, rank, world, dev, args.iq3s_layout, rscale)
+    layers = [e.layer for e in eps]
     x = synth.make_tokens(shape, T, SEED + rank, dev)
     comm = ep.TorchComm()
-    eps = [ep.CudaEpLayer(lay, rw, shape.experts, world, rank, sel_bias_all=b) for lay, rw, b in zip(layers, router_all, bias_all)]
     outs = [None] * L
 
     def step_direct():
@@ -670,6 +747,31 @@ def run_ep(args, torch, dist, capi, moe, synth, rank, world, local, dev):
         phase_us = ep.phase_times(eps[0], comm, x, reps=20)
         torch.cuda.synchronize()
         n_active = sum(int(e.buf["plan"][0]) for e in eps) / L      # this rank's active experts per layer (with the shared one)
+        # a fixed total batch beside the weak-scaling value: 512 tokens over all ranks, the same 4 layers
+        fixed = None
+        if not args.no_extras and args.workload == "c2" and 512 % world == 0:
+            xf = synth.make_tokens(shape, 512 // world, SEED + 100 + rank, dev)
+            gf = [ep.GraphedEpForward(e, comm, xf) for e in eps] if args.graph else None
+
+            def step_fixed():
+                for l, e in enumerate(eps):
+                    gf[l]() if gf is not None else ep.ep_forward(e, comm, xf)
+            for _ in range(3):
+                step_fixed()
+            ms_f = statistics.median([timed(step_fixed, args.steps) for _ in range(3)])
+            fixed = {"tokens_total": 512, "tokens_per_gpu": 512 // world, "ms_per_step": ms_f, "layer_tokens_per_s": 512 * L / (ms_f * 1e-3)}
+            del gf
+    workloads = None
+    if not args.no_extras and args.workload == "c2":
+        del eps, layers
+        graphed = None
+        torch.cuda.empty_cache()
+        workloads = {}
+        for key, cfg, toks, a2a in (("c4_decode_16", "c4", 16, False), ("c4_prefill_2048", "c4", 2048, True), ("c5_prefill_8192", "c5", 8192, True)):
+            try:
+                workloads[key] = ep_record(torch, dist, moe, synth, ep, comm, stream, dev, rank, world, cfg, toks, a2a, args.iq3s_layout)
+            except Exception as e:                                  # every rank fails or none does: the shapes are the same everywhere
+                workloads[key] = {"error": f"{type(e).__name__}: {e}"[:300]}
     peak, peak_kind = peaks()
     weight_bytes_step = n_active * L * shape.expert_bytes()
     achieved = weight_bytes_step / (ms_step * 1e-3) / 1e9
@@ -692,6 +794,7 @@ def run_ep(args, torch, dist, capi, moe, synth, rank, world, local, dev):
                          "kernel_ms": ms_step / L, "active_experts_per_launch": n_active,
                          "bytes_per_expert": 2 * synth.raw_bytes(shape.types[0], shape.ff, shape.hidden)},
             "expert_weight_gbs": weight_bytes_step / (ms_step * 1e-3) / 1e9, "stage_us": phase_us,
+            "fixed_total_512": fixed, "workloads": workloads,
             "cpu_baseline": None, "clocks": clocks.summary(),
         }))
     dist.destroy_process_group()
