@@ -59,6 +59,8 @@ def parse():
     p.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     p.add_argument("--no-extras", action="store_true", help="skip the sweep and the records of the other configurations")
     p.add_argument("--iq3s-layout", default="codes", choices=("codes", "gguf"), help="bank layout of IQ3_S experts")
+    p.add_argument("--ring", default="", help="nbuf,stages,slot_tiles: force the decode kernels' shared-memory configuration (A/B timing)")
+    p.add_argument("--overlap", type=int, default=1, help="0: plain stream order between the launches of a layer instead of programmatic dependent launch")
     return p.parse_args()
 
 
@@ -376,6 +378,9 @@ def run_b200(args):
 
     from tqllm_b200 import capi, moe, synth
     lib = capi.lib
+    lib.b2moe_harness_overlap(1 if args.overlap else 0)
+    if args.ring:
+        lib.b2moe_harness_ring(*[int(v) for v in args.ring.split(",")])
 
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -571,7 +576,7 @@ def run_b200(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8+f32", "data": "synthetic",
         "config": {"workload": workload_name(shape, T, L), "tokens": T, "layers": L, "router_scale": rscale, "parallelism": "single GPU",
-                   "l2": "per-step expert weights (GBs) exceed the 126 MB L2; no flush needed", "cuda_graph": graphed,
+                   "l2": "per-step expert weights (GBs) exceed the 126 MB L2; no flush needed", "cuda_graph": graphed, "dependent_launch_overlap": bool(args.overlap),
                    "activations": "bf16 in, bf16 out; expert products on integer tensor-core MMA over 15-bit fixed-point activations, fp32 sums",
                    "iq3s_bank_layout": args.iq3s_layout},
         "repeats": {"n": len(reg), "ms_per_step_median": ms_step, "ms_per_step_min": min(reg), "ms_per_step_max": max(reg),

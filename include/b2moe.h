@@ -273,11 +273,18 @@ B2MOE_API int32_t b2moe_ep_return_reduce(const float * back, const int32_t * pos
  * wait run out: the launch then sets plan word [3] and returns, its outputs invalid.
  * b2moe_harness_skip_staging: while on, the 4-bit decode kernels skip their activation staging launch and read the
  * staged rows the previous call left in the same workspace (a benchmark times the product kernel alone this way).
+ * b2moe_harness_overlap: on (the default), the launches of a layer call are chained by programmatic dependent launch: a
+ * kernel may become resident and set up its shared memory while the one before it drains, and waits on the device for
+ * that one's completion before it touches global memory; off = plain stream order (for A/B timing).
+ * b2moe_harness_ring: forces the shared-memory configuration of the 4-bit decode kernels (activation buffers 1-2, ring
+ * stages 2-4, tiles per slot 1-2) where it fits; zeros = the library's own order of preference.
  * b2moe_harness_launches: kernel launches the library has made in this process so far. */
 enum b2moe_family { B2MOE_FAMILY_AUTO = 0, B2MOE_FAMILY_GENERIC = 1, B2MOE_FAMILY_DECODE = 2, B2MOE_FAMILY_GEMM = 3 };
 B2MOE_API void b2moe_harness_select(int32_t family, int32_t gemm_item_tokens);
 B2MOE_API void b2moe_harness_wait_probe(int32_t drop_tile, uint32_t wait_limit);
 B2MOE_API void b2moe_harness_skip_staging(int32_t on);
+B2MOE_API void b2moe_harness_overlap(int32_t on);
+B2MOE_API void b2moe_harness_ring(int32_t activation_buffers, int32_t stages, int32_t slot_tiles);
 B2MOE_API uint64_t b2moe_harness_launches(void);
 
 /* ---- whole layer ----------------------------------------------------------------------------------------------

@@ -11,6 +11,8 @@ __global__ void combine_k(const float * __restrict__ y, const int * __restrict__
                           const float * __restrict__ sw, int n, int k, int h, int shared_tokens, typename Elem<DT>::type * __restrict__ out) {
     const int t = blockIdx.x;                     // tokens on gridDim.x: any batch size
     const int j = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+    grid_release();
+    grid_wait();
     if (j >= h) return;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s = 0; s < k; ++s) {
@@ -47,10 +49,10 @@ extern "C" B2MOE_API int32_t b2moe_combine(const float * y, const int32_t * ids,
     const dim3 grid(n, ceil_div(hidden / 4, 128));
     cudaStream_t s = as_stream(stream);
     if (out_dtype == B2MOE_F32)
-        combine_k<B2MOE_F32><<<grid, 128, 0, s>>>(y, ids, weights, shared_weights, n, topk, hidden, shared_tokens, static_cast<float *>(out));
+        launch_overlapped(combine_k<B2MOE_F32>, grid, dim3(128), 0, s, y, ids, weights, shared_weights, n, topk, hidden, shared_tokens, static_cast<float *>(out));
     else if (out_dtype == B2MOE_BF16)
-        combine_k<B2MOE_BF16><<<grid, 128, 0, s>>>(y, ids, weights, shared_weights, n, topk, hidden, shared_tokens, static_cast<__nv_bfloat16 *>(out));
+        launch_overlapped(combine_k<B2MOE_BF16>, grid, dim3(128), 0, s, y, ids, weights, shared_weights, n, topk, hidden, shared_tokens, static_cast<__nv_bfloat16 *>(out));
     else
-        combine_k<B2MOE_F16><<<grid, 128, 0, s>>>(y, ids, weights, shared_weights, n, topk, hidden, shared_tokens, static_cast<__half *>(out));
+        launch_overlapped(combine_k<B2MOE_F16>, grid, dim3(128), 0, s, y, ids, weights, shared_weights, n, topk, hidden, shared_tokens, static_cast<__half *>(out));
     return launch_status();
 }

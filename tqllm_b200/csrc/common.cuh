@@ -15,6 +15,25 @@ inline int32_t launch_status() {
     ++g_launch_count;
     return cudaGetLastError() == cudaSuccess ? B2MOE_OK : B2MOE_ERR_CUDA;
 }
+// Programmatic dependent launch for the chain of small launches of one layer call: a kernel launched through launch_overlapped
+// may become resident while the launch before it on the stream is still running; it runs its prologue (barrier and shared-
+// memory setup, no global access) and then every thread calls grid_wait(), which returns once the earlier launches have
+// completed and their writes are visible. grid_release() lets the launch after this one do the same. A kernel that is
+// launched this way must call grid_wait() in every thread before its first global access and before any early return,
+// so that completion stays transitive along the chain. g_overlap = false (b2moe_harness_overlap) falls back to plain launches.
+extern bool g_overlap;
+__device__ __forceinline__ void grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+template <typename... KArgs, typename... Args>
+inline void launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args &&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = g_overlap ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);       // the error, if any, is read by launch_status()
+}
 inline bool aligned16(const void * p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline cudaStream_t as_stream(b2moe_stream s) { return static_cast<cudaStream_t>(s); }
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

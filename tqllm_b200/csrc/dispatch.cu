@@ -19,6 +19,8 @@ constexpr int CHUNK = 256;   // assignments per warp-chunk on the multi-block pa
 
 __global__ void dispatch_small_k(const int * __restrict__ ids, int A, int e, int shared_first, int shared_tokens, int * __restrict__ plan) {
     extern __shared__ unsigned short hist[];       // [32 warps][e]
+    grid_release();
+    grid_wait();
     dispatch_small_body(ids, A, e, shared_first, shared_tokens, plan, hist);
 }
 
@@ -112,7 +114,7 @@ extern "C" B2MOE_API int32_t b2moe_dispatch_range(const int32_t * ids, int32_t n
     const int A = n * topk;
     cudaStream_t s = as_stream(stream);
     if (small_path(experts, A)) {
-        dispatch_small_k<<<1, 1024, size_t(32) * experts * sizeof(unsigned short), s>>>(ids, A, experts, shared_first, shared_count, plan);
+        launch_overlapped(dispatch_small_k, dim3(1), dim3(1024), size_t(32) * experts * sizeof(unsigned short), s, ids, A, experts, shared_first, shared_count, plan);
         return launch_status();
     }
     const size_t need = b2moe_dispatch_workspace_bytes(experts, A);

@@ -26,6 +26,7 @@
 // Every wait is bounded; a wait that runs out sets the plan's status word and a block-wide flag, every warp stops at
 // its next wait or item, the producer lets the copies in flight land, and the block leaves.
 #include "common.cuh"
+#include "dec4_stage.cuh"
 #include "formats.cuh"
 
 namespace b2 {
@@ -76,24 +77,14 @@ __device__ __forceinline__ void mma_i8(int (&c)[4], uint32_t a0, uint32_t a1, ui
         asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
                      : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
-// ---------------------------------------------------------------------------------------------------------------
-// Activation staging: rows [R][K] of any dtype -> 16-bit fixed point, the row scaled by a power of two so that the
-// largest magnitude lies in [2^(BITS-2), 2^(BITS-1)], split into a signed high byte and an unsigned low byte
-// (x16 = 256 hi + lo). One staged row = K / 32 sub-blocks of 64 bytes + K / 256 records of 32 bytes:
-//   sub-block: for t = 0..3 the 16 bytes {hi of columns 4t..4t+3, hi of 16+4t..16+4t+3, lo of 4t.., lo of 16+4t..}: the
-//              B fragments of the lane with that t for the high-byte and the low-byte MMA;
-//   record of 8 sub-blocks: their sums S = sum of x16 over the sub-block, each as the fp16 pair (16 (S >> 10), (S & 1023) / 64)
-//              (both exact; together S / 64), in the order 0, 4, 1, 5, 2, 6, 3, 7: the B fragment of the offset-correction
-//              MMA of a tile (m16n8k16: k = 2 sub-block + term).
-// inv_scale[R] = the inverse of the row's power of two. One block of four warps per row, one lane per column of a sub-block.
-// ---------------------------------------------------------------------------------------------------------------
-__host__ __device__ inline size_t staged_row_bytes(int k) { return size_t(k) * 2 + size_t(k / 256) * 32; }
-
+// Activation staging (layout and row code: dec4_stage.cuh): one block of four warps per row.
 constexpr int STAGE_WARPS = 4;
 __global__ void __launch_bounds__(STAGE_WARPS * 32) dec4_stage_k(const void * __restrict__ x, int dtype, int rows, int k, int bits,
                                                                  uint8_t * __restrict__ out, float * __restrict__ inv_scale) {
     __shared__ float wmax[STAGE_WARPS];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, row = blockIdx.x;
+    grid_release();
+    grid_wait();
     float mx = 0.f;
     for (int j = threadIdx.x; j < k; j += STAGE_WARPS * 32) mx = fmaxf(mx, fabsf(load_act(x, dtype, size_t(row) * k + j)));
     for (int d = 16; d; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
@@ -101,27 +92,12 @@ __global__ void __launch_bounds__(STAGE_WARPS * 32) dec4_stage_k(const void * __
     __syncthreads();
 #pragma unroll
     for (int w = 0; w < STAGE_WARPS; ++w) mx = fmaxf(mx, wmax[w]);
-    int ex = int((__float_as_uint(mx) >> 23) & 255u) - 127;              // floor(log2(mx)) for a normal mx
-    ex = (mx > 0.f && mx < 3e38f) ? max(-100, min(100, ex)) : bits - 2;
-    const float scale = __uint_as_float(uint32_t(127 + bits - 2 - ex) << 23);  // 2^(bits - 2 - ex)
-    if (threadIdx.x == 0) inv_scale[row] = __uint_as_float(uint32_t(127 - (bits - 2) + ex) << 23);
-    const int t = (lane & 15) >> 2, j = lane & 3, h = lane >> 4;
+    float inv;
+    const float scale = stage_scale(mx, bits, inv);
+    if (threadIdx.x == 0) inv_scale[row] = inv;
     uint8_t * orow = out + size_t(row) * staged_row_bytes(k);
     uint8_t * recs = orow + size_t(k) * 2;
-    const int nsb = k >> 5;
-    for (int b = warp; b < nsb; b += STAGE_WARPS) {
-        const int v = __float2int_rn(load_act(x, dtype, size_t(row) * k + 32 * b + lane) * scale);
-        uint8_t * sb = orow + size_t(b) * 64 + t * 16 + h * 4 + j;
-        sb[0] = uint8_t(v >> 8);
-        sb[8] = uint8_t(v & 255);
-        int sum = v;
-        for (int d = 16; d; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
-        if (lane == 0) {
-            const int bb = b & 7;
-            reinterpret_cast<__half2 *>(recs + size_t(b >> 3) * 32)[2 * (bb & 3) + (bb >> 2)] =
-                __floats2half2_rn(float((sum >> 10) * 16), float(sum & 1023) * 0.015625f);
-        }
-    }
+    for (int b = warp; b < (k >> 5); b += STAGE_WARPS) stage_sub_block(x, dtype, size_t(row) * k, b, scale, orow, recs, lane);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -200,8 +176,11 @@ struct Dec4Args {
 // modulo 128 (the 16-byte loads of two token columns then share no bank)
 __host__ __device__ inline uint32_t xrow_bytes(int k) { return uint32_t((staged_row_bytes(k) + 127) / 128 * 128 + XPAD); }
 __host__ __device__ inline size_t xs_bytes(int k, int nbuf) { return size_t(nbuf) * 8 * xrow_bytes(k); }
-// barriers: full[warp][stage], empty[warp][stage], xfull[2], xempty[2]; then the abort flag
-constexpr size_t BAR_BYTES = (2 * CTA_WARPS * MAX_STAGES + 4) * 8 + 16;
+// what the consumers need to know about a segment's tokens, written by the producer beside the activation rows it copies:
+// per token column the assignment index (-1 = no token) and the inverse activation scale
+struct SegMeta { int col_a[PASS_TOKENS]; float col_is[PASS_TOKENS]; };
+// barriers: full[warp][stage], empty[warp][stage], xfull[2], xempty[2]; then the abort flag; then SegMeta[2]
+constexpr size_t BAR_BYTES = (2 * CTA_WARPS * MAX_STAGES + 4) * 8 + 16 + 2 * sizeof(SegMeta);
 constexpr int THREADS = (CTA_WARPS + 1) * 32;      // 16 consumer warps + the producer warp
 
 // MODE 0: out = act[a][row] = silu(gate . x) * (up . x);   MODE 1: out = y[a][row] = down . act[a]
@@ -211,25 +190,14 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
     constexpr int NMAT = MODE == 0 ? 2 : 1, TILE = F::TILE;
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t * bars = reinterpret_cast<uint64_t *>(smem);
-    volatile int * abort_flag = reinterpret_cast<volatile int *>(smem + BAR_BYTES - 16);
+    volatile int * abort_flag = reinterpret_cast<volatile int *>(smem + (2 * CTA_WARPS * MAX_STAGES + 4) * 8);
+    SegMeta * meta = reinterpret_cast<SegMeta *>(smem + (2 * CTA_WARPS * MAX_STAGES + 4) * 8 + 16);
     const int SLOT_TILES = p.slot_tiles, SLOT = SLOT_TILES * TILE;
     uint8_t * ring = smem + BAR_BYTES;                                        // [warp][stage][SLOT]
     uint8_t * xs = ring + size_t(CTA_WARPS) * p.stages * SLOT;               // [buf][8 rows][xrow]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int K = p.k_tiles * 256;
     const int e1 = p.experts + 1;
-    const int * counts = p.plan + PLAN_HDR, * offsets = counts + e1, * active = offsets + e1 + 1, * perm = active + e1;
-    const int * passes = perm + p.A + counts[p.experts];
-    const int na = p.plan[PLAN_NACTIVE], row_tiles = (p.rows + 15) >> 4;
-    // the block's share of the launch: jobs [u_begin, u_end) of the pass-major list of (pass, row tile) jobs; it walks the
-    // share as segments = runs of row tiles [r0, r1) of one pass
-    const long long n_jobs = (long long)p.plan[PLAN_NPASS] * row_tiles;
-    const long long u_begin = n_jobs * blockIdx.x / gridDim.x, u_end = n_jobs * (blockIdx.x + 1) / gridDim.x;
-    auto segment = [&](long long u, int & pass, int & r0, int & r1) {
-        pass = int(u / row_tiles);
-        r0 = int(u - (long long)pass * row_tiles);
-        r1 = int(min((long long)row_tiles, r0 + (u_end - u)));
-    };
     const uint32_t xrow = xrow_bytes(K), xbuf = 8 * xrow, xglob = uint32_t(staged_row_bytes(K));
     const int S = p.stages, kslots = (p.k_tiles + SLOT_TILES - 1) / SLOT_TILES, nslots = kslots * NMAT;   // slots of one row job
     const uint32_t full0 = smem_addr(bars), empty0 = full0 + 8 * CTA_WARPS * MAX_STAGES, xfull = empty0 + 8 * CTA_WARPS * MAX_STAGES,
@@ -242,7 +210,21 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
         *abort_flag = 0;
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    grid_wait();              // the plan and the staged rows come from the launches before this one: no global access above this line
     __syncthreads();
+
+    const int * counts = p.plan + PLAN_HDR, * offsets = counts + e1, * active = offsets + e1 + 1, * perm = active + e1;
+    const int * passes = perm + p.A + counts[p.experts];
+    const int na = p.plan[PLAN_NACTIVE], row_tiles = (p.rows + 15) >> 4;
+    // the block's share of the launch: jobs [u_begin, u_end) of the pass-major list of (pass, row tile) jobs; it walks the
+    // share as segments = runs of row tiles [r0, r1) of one pass
+    const long long n_jobs = (long long)p.plan[PLAN_NPASS] * row_tiles;
+    const long long u_begin = n_jobs * blockIdx.x / gridDim.x, u_end = n_jobs * (blockIdx.x + 1) / gridDim.x;
+    auto segment = [&](long long u, int & pass, int & r0, int & r1) {
+        pass = int(u / row_tiles);
+        r0 = int(u - (long long)pass * row_tiles);
+        r1 = int(min((long long)row_tiles, r0 + (u_end - u)));
+    };
 
     // pass w -> (expert, first token slot); the pass list runs over the active experts from the last to the first
     auto locate = [&](int w, int & e, int & c0) {
@@ -276,10 +258,17 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
             int e, c0;
             locate(pass, e, c0);
             const int nv = min(PASS_TOKENS, counts[e] - c0);
+            const int col = lane - 16;                                        // lanes 16 .. 23: one token column each
+            int a = -1;
+            if (col >= 0 && col < PASS_TOKENS) {
+                if (col < nv) a = perm[offsets[e] + c0 + col];
+                meta[b].col_a[col] = a;
+                meta[b].col_is[col] = a >= 0 ? p.inv_scale[x_row(a)] : 0.f;
+            }
+            __syncwarp();                                                     // the columns are written before lane 16's arrival publishes them
             if (lane == 16) mbar_expect_tx(xfull + 8 * b, uint32_t(nv) * xglob);
             __syncwarp();
-            if (lane >= 16 && lane - 16 < nv)
-                bulk_g2s(xs0 + b * xbuf + (lane - 16) * xrow, p.x + x_row(perm[offsets[e] + c0 + lane - 16]) * xglob, xglob, xfull + 8 * b);
+            if (a >= 0) bulk_g2s(xs0 + b * xbuf + col * xrow, p.x + x_row(a) * xglob, xglob, xfull + 8 * b);
             ++xissued;
         };
         int pass, r0, r1;
@@ -347,19 +336,13 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
             const uint32_t b = p.nbuf == 2 ? (idx & 1u) : 0u, use = p.nbuf == 2 ? idx >> 1 : idx;
             if (*abort_flag) break;
             if (!__all_sync(0xffffffffu, wait(xfull + 8 * b, use & 1u))) { alive = false; break; }
-            int e, c0;
-            locate(pass, e, c0);
-            const int cnt = counts[e], off = offsets[e], nv = min(PASS_TOKENS, cnt - c0);
             const uint8_t * xw = xs + b * xbuf + g * xrow + t * 16;          // + sub-block * 64
             const uint8_t * rec = xs + b * xbuf + g * xrow + size_t(K) * 2 + t * 8;   // + tile * 32
-            // the lane's two token columns (2t, 2t + 1): assignment index and inverse activation scale, once per item
+            // the lane's two token columns (2t, 2t + 1): assignment index and inverse activation scale, as the producer left them
             int col_a[2];
             float col_is[2];
 #pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                col_a[q] = 2 * t + q < nv ? perm[off + c0 + 2 * t + q] : -1;
-                col_is[q] = col_a[q] >= 0 ? p.inv_scale[x_row(col_a[q])] : 0.f;
-            }
+            for (int q = 0; q < 2; ++q) { col_a[q] = meta[b].col_a[2 * t + q]; col_is[q] = meta[b].col_is[2 * t + q]; }
 
             for (int rt = r0 + warp; rt < r1 && alive; rt += CTA_WARPS) {
                 float acc[NMAT][4];
@@ -436,6 +419,7 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
         }
         if (!alive) { *abort_flag = 1; if (lane == 0) atomicExch(p.plan + PLAN_STATUS, 3); }
     }
+    grid_release();           // only now: a launch that became resident earlier would share this SM's issue slots for the whole kernel
     __syncthreads();          // nobody leaves while a copy into the block's shared memory may be in flight
 }
 
@@ -452,7 +436,13 @@ template <uint32_t T> size_t dec4_smem(int k, int nbuf, int stages, int slot_til
 // (activation buffers, ring stages, tiles per slot) in order of preference, the first that fits: large copies first (measured:
 // two-tile slots with one activation buffer beat one-tile slots with two), then two activation buffers (the next segment's
 // rows arrive while this one is multiplied), then a deeper ring
+int g_ring[3] = {0, 0, 0};            // test hook: (activation buffers, stages, tiles per slot) forced, 0 = the first that fits
 template <uint32_t T> bool dec4_fit(int k, int & nbuf, int & stages, int & slot_tiles) {
+    if (g_ring[0] >= 1 && g_ring[0] <= 2 && g_ring[1] >= 2 && g_ring[1] <= MAX_STAGES && g_ring[2] >= 1 && g_ring[2] <= MAX_SLOT_TILES &&
+        dec4_smem<T>(k, g_ring[0], g_ring[1], g_ring[2]) <= SMEM_LIMIT) {
+        nbuf = g_ring[0]; stages = g_ring[1]; slot_tiles = g_ring[2];
+        return true;
+    }
     const int opts[6][3] = {{2, 3, 2}, {2, 2, 2}, {1, 3, 2}, {1, 2, 2}, {2, 3, 1}, {1, 3, 1}};
     for (const auto & o : opts)
         if (dec4_smem<T>(k, o[0], o[1], o[2]) <= SMEM_LIMIT) { nbuf = o[0]; stages = o[1]; slot_tiles = o[2]; return true; }
@@ -472,28 +462,27 @@ int32_t launch_dec4(Dec4Args a, cudaStream_t s) {
     if (cudaFuncSetAttribute(dec4_k<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
     a.wait_limit = g_wait_limit;
     a.drop_tile = g_drop_tile;
-    dec4_k<T, MODE><<<sms, THREADS, smem, s>>>(a);       // every block takes an equal share of the (pass, row tile) jobs
+    launch_overlapped(dec4_k<T, MODE>, dim3(sms), dim3(THREADS), smem, s, a);       // every block takes an equal share of the (pass, row tile) jobs
     return launch_status();
 }
 
-inline size_t staged_bytes(int rows_x, int k) { return align_up(size_t(rows_x) * staged_row_bytes(k), 256); }
-
 template <uint32_t T>
-int32_t stage(Dec4Args & a, const void * x, int dtype, int rows_x, int k, void * ws, cudaStream_t s) {
+int32_t stage(Dec4Args & a, const void * x, int dtype, int rows_x, int k, void * ws, cudaStream_t s, bool already = false) {
     uint8_t * w = static_cast<uint8_t *>(ws);
     float * inv = reinterpret_cast<float *>(w + staged_bytes(rows_x, k));
     a.x = w; a.inv_scale = inv;
+    if (already) return B2MOE_OK;            // an earlier launch of the caller wrote the staged rows (route_plan_stage)
     if (g_skip_stage) return B2MOE_OK;       // the workspace still holds the staged rows of the previous call (benchmarks: the product alone)
-    dec4_stage_k<<<rows_x, STAGE_WARPS * 32, 0, s>>>(x, dtype, rows_x, k, D4<T>::BITS, w, inv);
+    launch_overlapped(dec4_stage_k, dim3(rows_x), dim3(STAGE_WARPS * 32), 0, s, x, dtype, rows_x, k, int(D4<T>::BITS), w, inv);
     return launch_status();
 }
 
 template <uint32_t T>
 int32_t gateup_t(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_bank * sg, const b2moe_bank * su, const void * x, int x_dtype,
-                 const int * plan, int n, int topk, int shared_tokens, float * act, void * ws, int max_active, cudaStream_t s) {
+                 const int * plan, int n, int topk, int shared_tokens, float * act, void * ws, int max_active, cudaStream_t s, bool x_staged) {
     const int k = gate->cols;
     Dec4Args a{};
-    if (int32_t rc = stage<T>(a, x, x_dtype, n, k, ws, s)) return rc;
+    if (int32_t rc = stage<T>(a, x, x_dtype, n, k, ws, s, x_staged)) return rc;
     a.w0 = static_cast<const uint8_t *>(gate->data); a.w1 = static_cast<const uint8_t *>(up->data);
     if (shared_tokens) { a.s0 = static_cast<const uint8_t *>(sg->data); a.s1 = static_cast<const uint8_t *>(su->data); }
     a.bank_bytes = b2moe_bank_bytes(gate->type, gate->rows, gate->cols);
@@ -531,9 +520,9 @@ size_t dec4_workspace_bytes(int rows_x, int k) {
 }
 int32_t dec4_gateup(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_bank * sg, const b2moe_bank * su, const void * x,
                     int x_dtype, const int * plan, int n, int topk, int shared_tokens, float * act, void * ws, int max_active,
-                    cudaStream_t s) {
-    if (gate->type == T_Q4_K) return gateup_t<T_Q4_K>(gate, up, sg, su, x, x_dtype, plan, n, topk, shared_tokens, act, ws, max_active, s);
-    if (gate->type == T_IQ3S4) return gateup_t<T_IQ3S4>(gate, up, sg, su, x, x_dtype, plan, n, topk, shared_tokens, act, ws, max_active, s);
+                    cudaStream_t s, bool x_staged) {
+    if (gate->type == T_Q4_K) return gateup_t<T_Q4_K>(gate, up, sg, su, x, x_dtype, plan, n, topk, shared_tokens, act, ws, max_active, s, x_staged);
+    if (gate->type == T_IQ3S4) return gateup_t<T_IQ3S4>(gate, up, sg, su, x, x_dtype, plan, n, topk, shared_tokens, act, ws, max_active, s, x_staged);
     return B2MOE_ERR_FORMAT;
 }
 int32_t dec4_down(const b2moe_bank * down, const b2moe_bank * sd, const float * act, const int * plan, int n, int topk,
@@ -543,6 +532,13 @@ int32_t dec4_down(const b2moe_bank * down, const b2moe_bank * sd, const float * 
     return B2MOE_ERR_FORMAT;
 }
 void dec4_skip_staging(bool on) { g_skip_stage = on; }
+void dec4_ring(int nbuf, int stages, int slot_tiles) { g_ring[0] = nbuf; g_ring[1] = stages; g_ring[2] = slot_tiles; }
+// where dec4_gateup expects the staged form of n activation rows of length k inside its workspace, and with how many bits
+void dec4_stage_target(uint32_t type, void * ws, int n, int k, uint8_t ** rows, float ** inv_scale, int * bits) {
+    *rows = static_cast<uint8_t *>(ws);
+    *inv_scale = reinterpret_cast<float *>(static_cast<uint8_t *>(ws) + staged_bytes(n, k));
+    *bits = type == T_Q4_K ? D4<T_Q4_K>::BITS : D4<T_IQ3S4>::BITS;
+}
 void dec4_debug(int drop_tile, uint32_t wait_limit) {
     g_drop_tile = drop_tile;
     g_wait_limit = wait_limit ? wait_limit : WAIT_LIMIT;

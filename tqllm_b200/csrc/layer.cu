@@ -17,11 +17,18 @@ int32_t iq3s_down(const b2moe_bank *, const b2moe_bank *, const float *, const i
 bool dec4_supported(uint32_t type, int k);
 size_t dec4_workspace_bytes(int rows_x, int k);
 int32_t dec4_gateup(const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const void *, int, const int *, int,
-                    int, int, float *, void *, int, cudaStream_t);
+                    int, int, float *, void *, int, cudaStream_t, bool x_staged);
+void dec4_stage_target(uint32_t type, void * ws, int n, int k, uint8_t ** rows, float ** inv_scale, int * bits);
+bool route_cluster_fits(int experts, int topk, int n);
+int32_t route_plan_stage(int gating, const float * logits, int ld, const float * bias, int * ids, float * weights, float * shared_weights,
+                         int experts, int topk, int norm, float scale, int n, int shared_first, int shared_count, int * plan, const void * x,
+                         int x_dtype, int k, int bits, uint8_t * staged_rows, float * inv_scale, cudaStream_t s, bool * took);
 int32_t dec4_down(const b2moe_bank *, const b2moe_bank *, const float *, const int *, int, int, int, float *, void *, int, cudaStream_t);
 void dec4_debug(int drop_tile, uint32_t wait_limit);
 void dec4_skip_staging(bool on);
+void dec4_ring(int nbuf, int stages, int slot_tiles);
 unsigned long long g_launch_count = 0;
+bool g_overlap = true;
 bool gemm_tc_supported(uint32_t type, int k, int nmat, int experts);
 size_t gemm_tc_workspace_bytes(int rows_x, int k);
 int32_t gemm_tc_gateup(const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const b2moe_bank *, const void *, int, const int *, int,
@@ -99,6 +106,8 @@ extern "C" B2MOE_API void b2moe_harness_select(int32_t family, int32_t gemm_item
 }
 extern "C" B2MOE_API void b2moe_harness_wait_probe(int32_t drop_tile, uint32_t wait_limit) { dec4_debug(drop_tile, wait_limit); }
 extern "C" B2MOE_API void b2moe_harness_skip_staging(int32_t on) { dec4_skip_staging(on != 0); }
+extern "C" B2MOE_API void b2moe_harness_ring(int32_t nbuf, int32_t stages, int32_t slot_tiles) { dec4_ring(nbuf, stages, slot_tiles); }
+extern "C" B2MOE_API void b2moe_harness_overlap(int32_t on) { g_overlap = on != 0; }
 extern "C" B2MOE_API uint64_t b2moe_harness_launches(void) { return g_launch_count; }
 
 extern "C" B2MOE_API size_t b2moe_expert_workspace_bytes(uint32_t type, int32_t rows_x, int32_t k, int32_t x_dtype) {
@@ -112,10 +121,10 @@ extern "C" B2MOE_API size_t b2moe_expert_workspace_bytes(uint32_t type, int32_t 
     return g > need ? g : need;
 }
 
-extern "C" B2MOE_API int32_t b2moe_expert_gateup_swiglu(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_bank * shared_gate,
-                                              const b2moe_bank * shared_up, const void * x, int32_t x_dtype, const int32_t * plan,
-                                              int32_t n, int32_t topk, int32_t shared_tokens, float * act, void * workspace,
-                                              size_t workspace_bytes, b2moe_stream stream) {
+// x_staged: the caller has already written the staged form of x where the 4-bit decode kernels expect it (b2moe_layer_forward)
+static int32_t expert_gateup(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_bank * shared_gate, const b2moe_bank * shared_up,
+                             const void * x, int32_t x_dtype, const int32_t * plan, int32_t n, int32_t topk, int32_t shared_tokens, float * act,
+                             void * workspace, size_t workspace_bytes, b2moe_stream stream, bool x_staged) {
     if (int32_t rc = check_bank(gate)) return rc;
     if (int32_t rc = check_bank(up)) return rc;
     if (int32_t rc = same_shape(gate, up, true)) return rc;
@@ -138,10 +147,17 @@ extern "C" B2MOE_API int32_t b2moe_expert_gateup_swiglu(const b2moe_bank * gate,
             return gemm_tc_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, workspace, as_stream(stream));
         const int ma = max_active_of(gate->experts, n, topk, shared_tokens);
         if (decode_kernel(gate->type, gate->cols, x_dtype) == DEC_4BIT)
-            return dec4_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, workspace, ma, as_stream(stream));
+            return dec4_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, workspace, ma, as_stream(stream), x_staged);
         return iq3s_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, workspace, ma, as_stream(stream));
     }
     return generic_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, as_stream(stream));
+}
+
+extern "C" B2MOE_API int32_t b2moe_expert_gateup_swiglu(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_bank * shared_gate,
+                                              const b2moe_bank * shared_up, const void * x, int32_t x_dtype, const int32_t * plan,
+                                              int32_t n, int32_t topk, int32_t shared_tokens, float * act, void * workspace,
+                                              size_t workspace_bytes, b2moe_stream stream) {
+    return expert_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, workspace, workspace_bytes, stream, false);
 }
 
 extern "C" B2MOE_API int32_t b2moe_expert_down(const b2moe_bank * down, const b2moe_bank * shared_down, const float * act, const int32_t * plan,
@@ -219,11 +235,24 @@ extern "C" B2MOE_API int32_t b2moe_layer_forward(const b2moe_layer * L, const vo
     if (L->gating == B2MOE_SIGMOID && gated_shared) return B2MOE_ERR_SHAPE;   // the sigmoid family adds its shared expert unscaled (moe_common.cu:191)
     void * es = base + ws.expert_scratch;
     const size_t es_bytes = ws.total - ws.expert_scratch;
-    if (int32_t rc = b2moe_route_dispatch(L->gating, logits, ld, L->sel_bias, ids, weights, gated_shared ? shw : nullptr, L->experts, L->topk,
-                                          L->norm, L->scale, n, 0, sh, plan, base + ws.scratch, ws.expert_scratch - ws.scratch, stream))
+    // decode-sized call on the 4-bit decode kernels: top-k, dispatch and the staging of x in one cluster launch
+    bool x_staged = false;
+    if (route_cluster_fits(L->experts, L->topk, n) && es_bytes >= b2moe_expert_workspace_bytes(L->gate.type, n, L->gate.cols, x_dtype) &&
+        expert_path(L->gate.type, L->gate.cols, x_dtype, 2, L->gate.experts, (long long)n * L->topk) == B2MOE_FAMILY_DECODE &&
+        decode_kernel(L->gate.type, L->gate.cols, x_dtype) == DEC_4BIT && valid_dtype(x_dtype)) {
+        uint8_t * rows;
+        float * inv;
+        int bits;
+        dec4_stage_target(L->gate.type, es, n, L->gate.cols, &rows, &inv, &bits);
+        if (int32_t rc = route_plan_stage(L->gating, logits, ld, L->sel_bias, ids, weights, gated_shared ? shw : nullptr, L->experts, L->topk, L->norm,
+                                          L->scale, n, 0, sh, plan, x, x_dtype, L->gate.cols, bits, rows, inv, as_stream(stream), &x_staged)) return rc;
+    }
+    if (!x_staged)
+        if (int32_t rc = b2moe_route_dispatch(L->gating, logits, ld, L->sel_bias, ids, weights, gated_shared ? shw : nullptr, L->experts, L->topk,
+                                              L->norm, L->scale, n, 0, sh, plan, base + ws.scratch, ws.expert_scratch - ws.scratch, stream))
+            return rc;
+    if (int32_t rc = expert_gateup(&L->gate, &L->up, &L->sh_gate, &L->sh_up, x, x_dtype, plan, n, L->topk, sh, act, es, es_bytes, stream, x_staged))
         return rc;
-    if (int32_t rc = b2moe_expert_gateup_swiglu(&L->gate, &L->up, &L->sh_gate, &L->sh_up, x, x_dtype, plan, n, L->topk, sh, act, es,
-                                                es_bytes, stream)) return rc;
     if (int32_t rc = b2moe_expert_down(&L->down, &L->sh_down, act, plan, n, L->topk, sh, y, es, es_bytes, stream)) return rc;
     return b2moe_combine(y, nullptr, weights, gated_shared ? shw : nullptr, n, L->topk, L->hidden, sh, out, out_dtype, stream);
 }

@@ -7,6 +7,7 @@
 #include <math_constants.h>
 
 #include "common.cuh"
+#include "dec4_stage.cuh"
 #include "dispatch.cuh"
 
 namespace b2 {
@@ -72,6 +73,8 @@ __global__ void __launch_bounds__(RM_WARPS * 32) router_mma_k(const float * __re
     __shared__ float tile[16][65];                                      // this block's sums over its slice of the columns
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();                    // the gridDim.z blocks that split the hidden dimension
+    grid_release();
+    grid_wait();                                                       // x may be the output of the launch before this one
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int r0 = blockIdx.x * 16, t0 = blockIdx.y * 64;
     const int ra = min(r0 + g, rows - 1), rb = min(r0 + g + 8, rows - 1);
@@ -272,6 +275,8 @@ __global__ void route_k(const float * __restrict__ logits, int ld, const float *
     extern __shared__ float smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const int token = blockIdx.x * warps + warp;
+    grid_release();
+    grid_wait();
     if (token >= n) return;
     float * p = smem + size_t(warp) * 2 * e;
     route_token<GATING>(logits, ld, bias, ids, weights, shared_weights, e, k, norm, scale, token, lane, p, p + e);
@@ -289,6 +294,8 @@ __global__ void __launch_bounds__(RD_THREADS) route_dispatch_k(const float * __r
     extern __shared__ float smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float * p = smem + size_t(warp) * 2 * e;
+    grid_release();
+    grid_wait();
     for (int token = warp; token < n; token += RD_THREADS / 32) {
         route_token<GATING>(logits, ld, bias, ids, weights, shared_weights, e, k, norm, scale, token, lane, p, p + e);
         __syncwarp();
@@ -297,16 +304,88 @@ __global__ void __launch_bounds__(RD_THREADS) route_dispatch_k(const float * __r
     dispatch_small_body(ids, n * k, e, shared_first, shared_count, plan, reinterpret_cast<unsigned short *>(smem));
 }
 
+// The same for up to RC_BLOCKS * RD_THREADS / 32 tokens, as one thread-block cluster: every block routes its share of the tokens
+// (a warp per token), the cluster meets once, block 0 builds the plan from the ids and the other blocks meanwhile bring the
+// layer's activation rows into the staged form of the 4-bit decode kernels (dec4_stage.cuh), which depends on the rows
+// alone. One launch instead of three (top-k, dispatch, staging) on the critical path of a decode-sized layer call.
+constexpr int RC_BLOCKS = 8;
+struct StageJob { const void * x; int dtype, k, bits; uint8_t * rows; float * inv_scale; };     // x = nullptr: nothing to stage
+template <int GATING>
+__global__ void __launch_bounds__(RD_THREADS) route_cluster_k(const float * __restrict__ logits, int ld, const float * __restrict__ bias,
+                                                        int * __restrict__ ids, float * __restrict__ weights,
+                                                        float * __restrict__ shared_weights, int e, int k, int norm, float scale, int n,
+                                                        int shared_first, int shared_count, int * __restrict__ plan, const StageJob st) {
+    extern __shared__ float smem[];
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rank = int(cluster.block_rank()), nb = int(cluster.num_blocks());
+    float * p = smem + size_t(warp) * 2 * e;
+    grid_release();
+    grid_wait();
+    for (int token = rank + nb * warp; token < n; token += nb * (RD_THREADS / 32)) {
+        route_token<GATING>(logits, ld, bias, ids, weights, shared_weights, e, k, norm, scale, token, lane, p, p + e);
+        __syncwarp();
+    }
+    __threadfence();
+    cluster.sync();                               // every block's ids are written and visible
+    if (rank == 0) {
+        dispatch_small_body(ids, n * k, e, shared_first, shared_count, plan, reinterpret_cast<unsigned short *>(smem));
+    } else if (st.x) {
+        for (int row = (rank - 1) + (nb - 1) * warp; row < n; row += (nb - 1) * (RD_THREADS / 32))
+            stage_row_warp(st.x, st.dtype, row, st.k, st.bits, st.rows, st.inv_scale, lane);
+    }
+}
+
 template <int GATING>
 int32_t route_launch(const float * logits, int ld, const float * bias, int * ids, float * weights, float * shared_weights, int e,
                      int k, int norm, float scale, int n, cudaStream_t s) {
     const int warps = e <= 1024 ? 4 : 1;
     const size_t smem = size_t(warps) * 2 * e * sizeof(float);
-    route_k<GATING><<<ceil_div(n, warps), warps * 32, smem, s>>>(logits, ld, bias, ids, weights, shared_weights, e, k, norm, scale, n);
+    launch_overlapped(route_k<GATING>, dim3(ceil_div(n, warps)), dim3(warps * 32), smem, s, logits, ld, bias, ids, weights, shared_weights, e, k, norm, scale, n);
     return launch_status();
 }
 
 }  // namespace
+
+// true when the one-cluster routing launch takes this shape: a warp per token, the plan built by one block
+bool route_cluster_fits(int experts, int topk, int n) {
+    return n >= 1 && n <= RC_BLOCKS * (RD_THREADS / 32) && dispatch_small_path(experts, n * topk) &&
+           size_t(RD_THREADS / 32) * 2 * experts * sizeof(float) <= 160 * 1024;
+}
+// Top-k + dispatch (+ staging of the n activation rows x[n][k] for the 4-bit decode kernels when x is given) as one cluster
+// launch. *took = false and B2MOE_OK when the shape does not fit: the caller takes the separate launches.
+int32_t route_plan_stage(int gating, const float * logits, int ld, const float * bias, int * ids, float * weights, float * shared_weights,
+                         int experts, int topk, int norm, float scale, int n, int shared_first, int shared_count, int * plan, const void * x,
+                         int x_dtype, int k, int bits, uint8_t * staged_rows, float * inv_scale, cudaStream_t s, bool * took) {
+    *took = false;
+    if (!route_cluster_fits(experts, topk, n)) return B2MOE_OK;
+    const size_t smem = size_t(RD_THREADS / 32) * 2 * experts * sizeof(float);
+    const StageJob st{x, x_dtype, k, bits, staged_rows, inv_scale};
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(RC_BLOCKS);
+    cfg.blockDim = dim3(RD_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = RC_BLOCKS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_overlap ? 2 : 1;
+    if (gating == B2MOE_SOFTMAX) {
+        if (cudaFuncSetAttribute(route_cluster_k<B2MOE_SOFTMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
+        cudaLaunchKernelEx(&cfg, route_cluster_k<B2MOE_SOFTMAX>, logits, ld, (const float *)nullptr, ids, weights, shared_weights, experts, topk, 1, scale, n,
+                           shared_first, shared_count, plan, st);
+    } else {
+        if (cudaFuncSetAttribute(route_cluster_k<B2MOE_SIGMOID>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
+        cudaLaunchKernelEx(&cfg, route_cluster_k<B2MOE_SIGMOID>, logits, ld, bias, ids, weights, (float *)nullptr, experts, topk, norm, scale, n,
+                           shared_first, shared_count, plan, st);
+    }
+    *took = true;
+    return launch_status();
+}
 }  // namespace b2
 
 using namespace b2;
@@ -331,11 +410,13 @@ extern "C" B2MOE_API int32_t b2moe_router(const float * router_w, const float * 
         cfg.gridDim = dim3(ceil_div(rows, 16), ceil_div(n, 64), ks);
         cfg.blockDim = dim3(RM_WARPS * 32);
         cfg.stream = s;
-        cudaLaunchAttribute attr;
-        attr.id = cudaLaunchAttributeClusterDimension;
-        attr.val.clusterDim.x = 1; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = ks;
-        cfg.attrs = &attr;
-        cfg.numAttrs = 1;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = ks;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = g_overlap ? 2 : 1;
         if (cudaLaunchKernelEx(&cfg, router_mma_k, router_w, shared_gate, static_cast<const __nv_bfloat16 *>(x), logits, ld, hidden, experts,
                                rows, n) != cudaSuccess) return B2MOE_ERR_CUDA;
     }
@@ -379,14 +460,20 @@ extern "C" B2MOE_API int32_t b2moe_route_dispatch(int32_t gating, const float * 
         cudaStream_t s = as_stream(stream);
         if (gating == B2MOE_SOFTMAX) {
             if (cudaFuncSetAttribute(route_dispatch_k<B2MOE_SOFTMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
-            route_dispatch_k<B2MOE_SOFTMAX><<<1, RD_THREADS, smem, s>>>(logits, ld, nullptr, ids, weights, shared_weights, experts, topk, 1, scale, n,
-                                                                  shared_first, shared_count, plan);
+            launch_overlapped(route_dispatch_k<B2MOE_SOFTMAX>, dim3(1), dim3(RD_THREADS), smem, s, logits, ld, nullptr, ids, weights, shared_weights, experts,
+                              topk, 1, scale, n, shared_first, shared_count, plan);
         } else {
             if (cudaFuncSetAttribute(route_dispatch_k<B2MOE_SIGMOID>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
-            route_dispatch_k<B2MOE_SIGMOID><<<1, RD_THREADS, smem, s>>>(logits, ld, bias, ids, weights, nullptr, experts, topk, norm, scale, n,
-                                                                  shared_first, shared_count, plan);
+            launch_overlapped(route_dispatch_k<B2MOE_SIGMOID>, dim3(1), dim3(RD_THREADS), smem, s, logits, ld, bias, ids, weights, nullptr, experts, topk,
+                              norm, scale, n, shared_first, shared_count, plan);
         }
         return launch_status();
+    }
+    if (route_cluster_fits(experts, topk, n)) {
+        bool took = false;
+        const int32_t rc = route_plan_stage(gating, logits, ld, bias, ids, weights, shared_weights, experts, topk, norm, scale, n, shared_first,
+                                            shared_count, plan, nullptr, 0, 0, 0, nullptr, nullptr, as_stream(stream), &took);
+        if (rc || took) return rc;
     }
     if (int32_t rc = gating == B2MOE_SOFTMAX ? b2moe_topk_softmax(logits, ld, ids, weights, shared_weights, experts, topk, n, scale, stream)
                                              : b2moe_route_sigmoid(logits, ld, bias, ids, weights, experts, topk, norm, scale, n, stream)) return rc;
