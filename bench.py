@@ -617,8 +617,9 @@ def zipf_router(torch, shape, router_w, x, dev):
     return x, f"Zipf(1.2) routing pressure through the router rows: hottest expert {ratio:.1f}x the mean token count"
 
 
-def ep_layers(torch, moe, synth, ep, shape, L, rank, world, dev, layout, rscale=1.0, zipf_tokens=None):
-    """every rank draws the same layers (same seed) and keeps the banks of its own expert block only"""
+def ep_layers(torch, moe, synth, ep, shape, L, rank, world, dev, layout, rscale=1.0, zipf_tokens=None, order_of=None):
+    """every rank draws the same layers (same seed) and keeps the banks of its own expert block only; order_of(layer) may
+    return a placement (b2moe_place_experts) in which the experts are stacked before the blocks are cut"""
     first, count = ep.expert_range(shape.experts, world, rank)
     H, F = shape.hidden, shape.ff
     out, note = [], None
@@ -626,6 +627,8 @@ def ep_layers(torch, moe, synth, ep, shape, L, rank, world, dev, layout, rscale=
         sl = synth.make_layer(shape, SEED + 17 * l, dev, router_scale=rscale)
         if zipf_tokens is not None:
             _, note = zipf_router(torch, shape, sl.router_w, zipf_tokens, dev)
+        if order_of is not None:
+            sl = synth.permute_experts(sl, order_of(sl))
         cut = lambda raw, i: raw[first * synth.raw_bytes(shape.types[i], (F, F, H)[i], (H, H, F)[i]):
                                  (first + count) * synth.raw_bytes(shape.types[i], (F, F, H)[i], (H, H, F)[i])].clone()
         lay = moe.MoeLayer(shape, sl.router_w[first:first + count], tuple(cut(sl.raw[i], i) for i in range(3)), sl.shared_raw,
@@ -639,46 +642,76 @@ def ep_layers(torch, moe, synth, ep, shape, L, rank, world, dev, layout, rscale=
 
 def ep_record(torch, dist, moe, synth, ep, comm, stream, dev, rank, world, cfg, total_tokens, a2a, layout, reps=10):
     """one expert-parallel record of another configuration: one layer, total_tokens over all ranks, direct launches; the time is
-    the maximum over the ranks"""
+    the maximum over the ranks. The Zipf-routed configuration (c5) is timed twice: contiguous expert blocks, and the load-aware
+    placement that b2moe_place_experts derives from the routing histogram of the same tokens (b2moe_count)."""
     shape = synth.CONFIGS[cfg]
     T = max(1, total_tokens // world)
     x_all = synth.make_tokens(shape, T * world, SEED + 9, dev)                # the same tokens on every rank; a rank routes its slice
-    zx = None
-    if cfg == "c5":
-        zx = x_all
-    eps, note = ep_layers(torch, moe, synth, ep, shape, 1, rank, world, dev, layout, zipf_tokens=zx)
+    zx = x_all if cfg == "c5" else None
     if cfg == "c5":
         d = torch.zeros(shape.hidden, device=dev)
         d[::5] = 1.0
         d /= d.norm()
-        x_all = (x_all.float() + 3.0 * d).to(x_all.dtype)
-    x = x_all[rank * T:(rank + 1) * T].contiguous()
+        x_shift = (x_all.float() + 3.0 * d).to(x_all.dtype)
+    else:
+        x_shift = x_all
+    x = x_shift[rank * T:(rank + 1) * T].contiguous()
     fwd = ep.ep_forward_a2a if a2a else ep.ep_forward
-    with torch.cuda.stream(stream):
-        for _ in range(2):
-            fwd(eps[0], comm, x)
-        dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(reps):
-            fwd(eps[0], comm, x)
-        e1.record(stream)
-        torch.cuda.synchronize()
-        ms = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        n_active = torch.tensor([float(int(eps[0].buf["plan"][0]))], device=dev)
-        status = torch.tensor([float(int(eps[0].buf["plan"][3]))], device=dev)
-        dist.all_reduce(n_active, op=dist.ReduceOp.SUM)
-        dist.all_reduce(status, op=dist.ReduceOp.MAX)
+    loads = {}
+
+    def histogram(sl):                      # routed-id counts of all tokens on the full expert set: the same on every rank
+        logits = moe.router(sl.router_w.contiguous(), x_shift, None)
+        if shape.gating == synth.SOFTMAX:
+            ids, _, _ = moe.topk_softmax(logits, shape.experts, shape.topk, shape.scale)
+        else:
+            ids, _ = moe.route_sigmoid(logits, shape.experts, shape.topk, sl.sel_bias, shape.norm, shape.scale)
+        counts = torch.zeros(shape.experts, dtype=torch.int64, device=dev)
+        moe.count_ids(ids.contiguous().view(-1), counts)
+        return counts
+
+    def placed(sl):
+        counts = histogram(sl)
+        order, load = moe.place_experts(counts, world)
+        loads["contiguous"] = [int(v) for v in counts.view(world, -1).sum(1).tolist()]
+        loads["load_aware"] = [int(v) for v in load.tolist()]
+        return order
+
+    def timed(order_of):
+        eps, note = ep_layers(torch, moe, synth, ep, shape, 1, rank, world, dev, layout, zipf_tokens=zx, order_of=order_of)
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                fwd(eps[0], comm, x)
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                fwd(eps[0], comm, x)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            ms = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            n_active = torch.tensor([float(int(eps[0].buf["plan"][0]))], device=dev)
+            status = torch.tensor([float(int(eps[0].buf["plan"][3]))], device=dev)
+            dist.all_reduce(n_active, op=dist.ReduceOp.SUM)
+            dist.all_reduce(status, op=dist.ReduceOp.MAX)
+        del eps
+        torch.cuda.empty_cache()
+        return float(ms), float(n_active), int(status), note
+
+    ms, n_active, status, note = timed(None)
     rec = {"workload": workload_name(shape, T * world, 1), "tokens_total": T * world, "tokens_per_gpu": T,
-           "dispatch": "all-to-all (count exchange + variable-size records)" if a2a else "all-gather",
-           "layer_us": float(ms) * 1e3, "layer_tokens_per_s": T * world / (float(ms) * 1e-3), "active_experts_all_ranks": float(n_active),
-           "expert_weight_gbs_all_ranks": float(n_active) * shape.expert_bytes() / (float(ms) * 1e-3) / 1e9, "status": int(status)}
+           "dispatch": "all-to-all (count exchange + variable-size records)" if a2a else "all-gather", "placement": "contiguous expert blocks",
+           "layer_us": ms * 1e3, "layer_tokens_per_s": T * world / (ms * 1e-3), "active_experts_all_ranks": n_active,
+           "expert_weight_gbs_all_ranks": n_active * shape.expert_bytes() / (ms * 1e-3) / 1e9, "status": status}
     if note:
         rec["routing"] = note
-    del eps
-    torch.cuda.empty_cache()
+    if cfg == "c5":
+        ms2, _, status2, _ = timed(placed)
+        rec["load_aware_placement"] = {"layer_us": ms2 * 1e3, "layer_tokens_per_s": T * world / (ms2 * 1e-3), "status": status2,
+                                       "assignments_per_rank_contiguous": loads.get("contiguous"),
+                                       "assignments_per_rank_load_aware": loads.get("load_aware"),
+                                       "how": "b2moe_count histogram of the same tokens -> b2moe_place_experts -> experts stacked in that order"}
     return rec
 
 

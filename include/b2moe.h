@@ -104,6 +104,12 @@ B2MOE_API int32_t b2moe_router(const float * router_w, const float * shared_gate
  * sigmoid(logits[t][experts]) when shared_weights is given. experts <= 4096. */
 B2MOE_API int32_t b2moe_topk_softmax(const float * logits, int32_t ld, int32_t * ids, float * weights, float * shared_weights,
                            int32_t experts, int32_t topk, int32_t n, float scale, b2moe_stream stream);
+/* replaces moe_topk2 (src/experts/moe.cu:160-166,255-267, src/experts/moe_kernels.cuh:24-25): b2moe_topk_softmax on two
+ * routings of the same n tokens in one launch (this layer's logits and the next layer's predicted ones); both logit
+ * arrays have row stride ld; outputs and bits are those of two separate calls. */
+B2MOE_API int32_t b2moe_topk_softmax2(const float * logits, int32_t * ids, float * weights, float * shared_weights, const float * logits2,
+                            int32_t * ids2, float * weights2, float * shared_weights2, int32_t ld, int32_t experts, int32_t topk,
+                            int32_t n, float scale, b2moe_stream stream);
 /* replaces moe_common::route (src/experts/moe_common.cu:18-70,197-203): p = sigmoid(logits); select top-k of p + bias
  * (bias may be null); weights = p[selected], divided by their clamped sum when norm, times scale unless 0 or 1. */
 B2MOE_API int32_t b2moe_route_sigmoid(const float * logits, int32_t ld, const float * bias, int32_t * ids, float * weights,
@@ -261,6 +267,16 @@ B2MOE_API int32_t b2moe_ep_unpack(const void * records_in, int32_t records, int3
 B2MOE_API int32_t b2moe_ep_return_reduce(const float * back, const int32_t * pos, const int32_t * offsets, int32_t peers, const float * shared_y,
                                const float * shared_weights, int32_t n, int32_t hidden, void * out, int32_t out_dtype,
                                b2moe_stream stream);
+
+/* Skew handling. b2moe_count replaces moe_count (src/experts/moe.cu:183-186, src/experts/moe_kernels.cuh:54): counts[e] += the
+ * number of ids equal to e, accumulated over calls into a device array of `experts` 64-bit counters the caller zeroed
+ * (ids outside [0, experts) are skipped). b2moe_place_experts (host code, host pointers) turns such a histogram into a
+ * load-aware placement for `ranks` GPUs: greedy longest-first bin packing under the constraint that every rank holds
+ * experts / ranks experts. order[r * per + i] = the expert in slot i of rank r; a loader that stacks the router rows, the
+ * selection bias and the three banks in this order keeps the contiguous-block ownership the other calls assume (the layer's
+ * result does not depend on the order). rank_load (may be null) receives the summed counts per rank. */
+B2MOE_API int32_t b2moe_count(const int32_t * ids, uint64_t * counts, int32_t count, int32_t experts, b2moe_stream stream);
+B2MOE_API int32_t b2moe_place_experts(const uint64_t * counts, int32_t experts, int32_t ranks, int32_t * order, uint64_t * rank_load);
 
 /* ---- harness hooks ---------------------------------------------------------------------------------------------
  * For tests and benchmarks, not for engines: process-wide switches, not thread-safe, to be set while no call of this

@@ -6,7 +6,9 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cmath>
 #include <cstdio>
+#include <cstring>
 #include <cstdlib>
 #include <stdexcept>
 #include <vector>
@@ -104,13 +106,32 @@ int main(int argc, char ** argv) {
         fmt->matvec(e1, dx, y_dense, n, s);
         __half * deq = dev_buf<__half>(size_t(rows) * cols);
         fmt->dequant_h(e1, deq, s);
+        // 6. moe_topk2 through the reference's declaration: two routings in one launch equal two moe_topk calls
+        const int tk = std::min(topk, experts);
+        std::vector<float> la(size_t(n) * (experts + 1)), lb(la.size());
+        for (size_t i = 0; i < la.size(); ++i) { la[i] = 3.f * std::sin(0.37f * float(i) + 0.11f * float(i % 7)); lb[i] = 3.f * std::cos(0.23f * float(i) + 1.f); }
+        const float * dla = to_dev(la), * dlb = to_dev(lb);
+        int * i1 = dev_buf<int>(size_t(n) * tk), * i2 = dev_buf<int>(size_t(n) * tk), * j1 = dev_buf<int>(size_t(n) * tk), * j2 = dev_buf<int>(size_t(n) * tk);
+        float * w1 = dev_buf<float>(size_t(n) * tk), * w2 = dev_buf<float>(size_t(n) * tk), * v1 = dev_buf<float>(size_t(n) * tk), * v2 = dev_buf<float>(size_t(n) * tk);
+        float * s1 = dev_buf<float>(n), * s2 = dev_buf<float>(n), * r1 = dev_buf<float>(n), * r2 = dev_buf<float>(n);
+        tqllm_cuda::moe_topk2(dla, i1, w1, s1, dlb, i2, w2, s2, experts, tk, n, 1.f, s);
+        tqllm_cuda::moe_topk(dla, j1, v1, r1, experts, tk, n, 1.f, s);
+        tqllm_cuda::moe_topk(dlb, j2, v2, r2, experts, tk, n, 1.f, s);
         CK(cudaDeviceSynchronize());
-        const int flags[4] = {ok1 ? 1 : 0, ok2 ? 1 : 0, pick, 0};
+        auto same = [&](const void * a, const void * b, size_t bytes) {
+            std::vector<char> ha(bytes), hb(bytes);
+            CK(cudaMemcpy(ha.data(), a, bytes, cudaMemcpyDeviceToHost));
+            CK(cudaMemcpy(hb.data(), b, bytes, cudaMemcpyDeviceToHost));
+            return std::memcmp(ha.data(), hb.data(), bytes) == 0;
+        };
+        const size_t ib = size_t(n) * tk * 4;
+        const bool topk2_ok = same(i1, j1, ib) && same(i2, j2, ib) && same(w1, v1, ib) && same(w2, v2, ib) && same(s1, r1, size_t(n) * 4) && same(s2, r2, size_t(n) * 4);
+        const int flags[4] = {ok1 ? 1 : 0, ok2 ? 1 : 0, pick, topk2_ok ? 1 : 0};
         std::fwrite(flags, sizeof(int), 4, out);
         wr(out, y_tok, size_t(A) * rows); wr(out, y_pei, size_t(A) * rows); wr(out, yg, size_t(A) * rows); wr(out, yu, size_t(A) * rows);
         wr(out, act2, size_t(A) * rows); wr(out, y_gemm, size_t(A) * rows); wr(out, act_f, size_t(A) * rows); wr(out, sum, size_t(n) * rows);
         wr(out, y_dense, size_t(n) * rows); wr(out, deq, size_t(rows) * cols);
-        // 6. errors reach the caller as the reference's exceptions: a row count that is not a multiple of 16
+        // 7. errors reach the caller as the reference's exceptions: a row count that is not a multiple of 16
         int threw = 0;
         try { fmt->expert_matvec(g, dx, y_tok, rows - 1, dids, n, topk, false, s); } catch (const std::invalid_argument &) { threw = 1; }
         std::fwrite(&threw, sizeof(int), 1, out);

@@ -99,3 +99,29 @@ def test_arguments_are_rejected_before_any_launch():
     assert lib.b2moe_combine(16, None, 16, None, 2, 2, 30, 0, 16, capi.F32, None) == capi.ERR_SHAPE
     with pytest.raises(capi.B2moeError):
         capi.check(capi.ERR_WORKSPACE, "x")
+
+
+def test_load_aware_placement_balances_a_zipf_histogram():
+    """b2moe_place_experts: a permutation, equal expert counts per rank, never worse than contiguous blocks, deterministic."""
+    import numpy as np
+    from tqllm_b200 import moe
+    rng = np.random.default_rng(5)
+    for experts, ranks in ((128, 8), (128, 2), (512, 4), (16, 16)):
+        counts = (1e6 / np.arange(1, experts + 1) ** 1.2).astype(np.uint64)
+        rng.shuffle(counts)
+        order, load = moe.place_experts(counts, ranks)
+        per = experts // ranks
+        assert sorted(order.tolist()) == list(range(experts))
+        got = np.array([counts[order[r * per:(r + 1) * per]].sum() for r in range(ranks)])
+        assert np.array_equal(got, load)
+        contiguous = counts.reshape(ranks, per).sum(1)
+        assert load.max() <= contiguous.max()
+        if per > 1:
+            # longest-first bound; a rank that holds the heaviest expert still has to take per - 1 more (the lightest ones)
+            assert load.max() <= max(counts.max() + np.sort(counts)[:per - 1].sum(), 1.34 * counts.sum() / ranks)
+        order2, _ = moe.place_experts(counts, ranks)
+        assert np.array_equal(order, order2)
+    assert lib.b2moe_place_experts(None, 8, 2, None, None) != 0
+    c = np.ones(10, np.uint64)
+    o = np.empty(10, np.int32)
+    assert lib.b2moe_place_experts(c.ctypes.data, 10, 3, o.ctypes.data, None) != 0               # 10 experts do not split over 3 ranks

@@ -56,6 +56,7 @@ def test_adapter_calls_match_fp32_references(orc, tmp_path, type_id, codes, expe
         return a
     flags = take(4, np.int32)
     assert flags[0] == 1 and flags[1] == 1
+    assert flags[3] == 1, "moe_topk2 differs from two moe_topk calls"
     pick = int(flags[2])
     u16 = lambda c: take(c, np.uint16)
     y_tok, y_pei, yg, yu = (bf16_to_f32(u16(A * rows)).reshape(A, rows) for _ in range(4))

@@ -93,6 +93,33 @@ def test_benchmark_shapes_reduced_experts(orc, cfg, experts, tokens):
     run_case(orc, synth.CONFIGS[cfg], experts, tokens, 1234 + tokens)
 
 
+def test_routing_histogram_and_placement_leave_the_layer_unchanged(orc):
+    """skew handling: b2moe_count gives the histogram of the routed ids (the reference's moe_count), b2moe_place_experts
+    a placement from it, and the layer with its experts stacked in that order computes the same outputs: routed ids map
+    through the permutation; weights and outputs agree to rounding (the softmax denominator is summed in index order, so
+    the last bits may move)."""
+    from tqllm_b200 import moe
+    shape = synth.CONFIGS["c5"]
+    experts, tokens = 16, 48
+    layer, x = layer_inputs(shape, experts, tokens, 4321)
+    dev = moe.MoeLayer.from_synth(layer, experts=experts)
+    out = dev.forward(x.cuda()).cpu().numpy()
+    ids = dev.artefacts()["ids"]
+    counts = torch.zeros(experts, dtype=torch.int64, device="cuda")
+    moe.count_ids(ids.contiguous().view(-1), counts)
+    moe.count_ids(ids.contiguous().view(-1), counts)                                   # accumulates over calls
+    want = np.bincount(ids.cpu().numpy().reshape(-1), minlength=experts)
+    assert np.array_equal(counts.cpu().numpy(), 2 * want)
+    order, load = moe.place_experts(counts, 4)
+    assert load.max() <= (2 * want).reshape(4, -1).sum(1).max()
+    moved = synth.permute_experts(layer, order)
+    dev2 = moe.MoeLayer.from_synth(moved, experts=experts)
+    out2 = dev2.forward(x.cuda()).cpu().numpy()
+    ids2 = dev2.artefacts()["ids"].cpu().numpy()
+    assert np.array_equal(order[ids2], ids.cpu().numpy())
+    assert rel_err(out2, out) < 1e-5
+
+
 def test_step_by_step_equals_layer_forward(orc):
     """the separate entry points chained by hand give the bits of b2moe_layer_forward"""
     from tqllm_b200 import moe

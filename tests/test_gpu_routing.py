@@ -56,6 +56,20 @@ def test_topk_softmax_matches_cpu_route_on_device_logits(orc, e, k, n):
         assert np.abs(w.sum(-1) - (scale or 1.0)).max() < 1e-5
 
 
+@pytest.mark.parametrize("e,k,n", ((512, 10, 17), (256, 8, 1), (1000, 8, 5)))
+def test_two_routings_in_one_launch_equal_two_calls(e, k, n):
+    """The reference's moe_topk2 (src/experts/moe.cu:160-166): this layer's routing and the next layer's predicted one."""
+    from tqllm_b200 import moe
+    g = torch.Generator()
+    g.manual_seed(e + n)
+    la, lb = (torch.randn(n, e + 1, generator=g) * 2.0).cuda(), (torch.randn(n, e + 1, generator=g) * 2.0).cuda()
+    (i1, w1, s1), (i2, w2, s2) = moe.topk_softmax2(la, lb, e, k, 1.0, shared=True)
+    for logits, got in ((la, (i1, w1, s1)), (lb, (i2, w2, s2))):
+        want = moe.topk_softmax(logits, e, k, 1.0, shared=True)
+        for a, b in zip(got, want):
+            assert torch.equal(a, b)
+
+
 def test_topk_ties_and_extremes(orc):
     from tqllm_b200 import moe
     rows = np.zeros((4, 17), np.float32)

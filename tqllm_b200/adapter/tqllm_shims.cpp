@@ -31,6 +31,13 @@ void moe_topk(const float * logits, int * ids, float * weights, float * shared_w
     b2_check(b2moe_topk_softmax(logits, experts + 1, ids, weights, shared_weights, experts, topk, n, scale, s), "moe_topk");
 }
 
+// moe_kernels.cuh:24-25: moe_topk on two routings in one launch (this layer's and the next layer's prediction); e <= 1024
+void moe_topk2(const float * logits, int * ids, float * weights, float * shared_weights, const float * logits2, int * ids2, float * weights2,
+               float * shared_weights2, int e, int k, int n, float scale, cudaStream_t s) {
+    if (e > 1024) throw std::invalid_argument("moe_topk2: invalid shape");
+    b2_check(b2moe_topk_softmax2(logits, ids, weights, shared_weights, logits2, ids2, weights2, shared_weights2, e + 1, e, k, n, scale, s), "moe_topk2");
+}
+
 namespace moe_common {
 // moe_common.cuh:11-12: sigmoid scores, bias only in the selection, optional renormalisation, scale
 void route(const float * logits, const float * bias, int * ids, float * w, int experts, int k, bool norm, float scale, cudaStream_t s,

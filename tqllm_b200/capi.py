@@ -59,6 +59,7 @@ SIGNATURES = {
     "b2moe_dequant_dump": (_i32, [C.POINTER(Bank), _vp, _vp]),
     "b2moe_router": (_i32, [_vp, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _vp]),
     "b2moe_topk_softmax": (_i32, [_vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _f32, _vp]),
+    "b2moe_topk_softmax2": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f32, _vp]),
     "b2moe_route_sigmoid": (_i32, [_vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _f32, _i32, _vp]),
     "b2moe_plan_ints": (_i64, [_i32, _i32, _i32]),
     "b2moe_plan_view_of": (None, [_i32, _i32, _i32, C.POINTER(PlanView)]),
@@ -89,6 +90,8 @@ SIGNATURES = {
     "b2moe_static_scratch_bytes": (_sz, []),
     "b2moe_expert_down_static": (_i32, [C.POINTER(Bank)] * 2 + [_vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "b2moe_combine": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _i32, _vp]),
+    "b2moe_count": (_i32, [_vp, _vp, _i32, _i32, _vp]),
+    "b2moe_place_experts": (_i32, [_vp, _i32, _i32, _vp, _vp]),
     "b2moe_harness_select": (None, [_i32, _i32]),
     "b2moe_harness_wait_probe": (None, [_i32, _u32]),
     "b2moe_harness_skip_staging": (None, [_i32]),

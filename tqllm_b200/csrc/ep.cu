@@ -7,6 +7,13 @@
 namespace b2 {
 namespace {
 
+// routing histogram, added up over calls (count_k, src/experts/moe.cu:183-186); ids outside [0, experts) are skipped
+__global__ void count_ids_k(const int * __restrict__ ids, unsigned long long * __restrict__ counts, int count, int experts) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) { const int e = ids[i]; if (e >= 0 && e < experts) atomicAdd(counts + e, 1ull); }
+}
+
+
 // local[i] = ids[i] - first when the expert is this rank's, else -1 (every grouped kernel skips -1)
 __global__ void ep_local_ids_k(const int * __restrict__ ids, int * __restrict__ local, int count, int first, int experts) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -200,4 +207,43 @@ extern "C" B2MOE_API int32_t b2moe_ep_return_reduce(const float * back, const in
     else if (out_dtype == B2MOE_BF16) ep_return_reduce_k<B2MOE_BF16><<<n, 256, 0, s>>>(back, pos, offsets, peers, shared_y, shared_weights, n, hidden, static_cast<__nv_bfloat16 *>(out));
     else ep_return_reduce_k<B2MOE_F16><<<n, 256, 0, s>>>(back, pos, offsets, peers, shared_y, shared_weights, n, hidden, static_cast<__half *>(out));
     return launch_status();
+}
+
+extern "C" B2MOE_API int32_t b2moe_count(const int32_t * ids, uint64_t * counts, int32_t count, int32_t experts, b2moe_stream stream) {
+    if (count <= 0 || experts <= 0) return B2MOE_ERR_SHAPE;
+    if (!ids || !counts) return B2MOE_ERR_NULL;
+    count_ids_k<<<ceil_div(count, 256), 256, 0, as_stream(stream)>>>(ids, reinterpret_cast<unsigned long long *>(counts), count, experts);
+    return launch_status();
+}
+
+// Load-aware placement (host): experts in descending order of their counts, each to the rank with the smallest load so far
+// that still has a free slot (every rank holds exactly experts / ranks: the banks stay equal in size). order[] lists the
+// experts rank by rank: rank r owns order[r * per .. (r + 1) * per), so a loader that stacks router rows, selection bias
+// and banks in this order keeps the library's contiguous-block ownership. Ties: lower expert id first, lower rank first.
+extern "C" B2MOE_API int32_t b2moe_place_experts(const uint64_t * counts, int32_t experts, int32_t ranks, int32_t * order, uint64_t * rank_load) {
+    if (experts <= 0 || ranks <= 0 || experts % ranks) return B2MOE_ERR_SHAPE;
+    if (!counts || !order) return B2MOE_ERR_NULL;
+    const int per = experts / ranks;
+    int * by_count = new int[experts];
+    for (int e = 0; e < experts; ++e) by_count[e] = e;
+    // insertion sort by (count descending, id ascending): a few thousand experts at most, run once per placement
+    for (int i = 1; i < experts; ++i) {
+        const int e = by_count[i];
+        int j = i - 1;
+        while (j >= 0 && (counts[by_count[j]] < counts[e])) { by_count[j + 1] = by_count[j]; --j; }
+        by_count[j + 1] = e;
+    }
+    uint64_t * load = new uint64_t[ranks]();
+    int * filled = new int[ranks]();
+    for (int i = 0; i < experts; ++i) {
+        const int e = by_count[i];
+        int best = -1;
+        for (int r = 0; r < ranks; ++r)
+            if (filled[r] < per && (best < 0 || load[r] < load[best])) best = r;
+        order[best * per + filled[best]++] = e;
+        load[best] += counts[e];
+    }
+    if (rank_load) for (int r = 0; r < ranks; ++r) rank_load[r] = load[r];
+    delete[] by_count; delete[] load; delete[] filled;
+    return B2MOE_OK;
 }

@@ -282,6 +282,22 @@ __global__ void route_k(const float * __restrict__ logits, int ld, const float *
     route_token<GATING>(logits, ld, bias, ids, weights, shared_weights, e, k, norm, scale, token, lane, p, p + e);
 }
 
+// Two routings in one launch (blockIdx.y picks the set): this layer's logits and the next layer's predicted ones
+// (topk_warp2_k, src/experts/moe.cu:160-166). Each token's selection is route_k's.
+struct RouteSet { const float * logits; int * ids; float * weights; float * shared_weights; };
+template <int GATING>
+__global__ void route2_k(const RouteSet a, const RouteSet b, int ld, const float * __restrict__ bias, int e, int k, int norm, float scale, int n) {
+    extern __shared__ float smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int token = blockIdx.x * warps + warp;
+    const RouteSet & t = blockIdx.y ? b : a;
+    grid_release();
+    grid_wait();
+    if (token >= n) return;
+    float * p = smem + size_t(warp) * 2 * e;
+    route_token<GATING>(t.logits, ld, bias, t.ids, t.weights, t.shared_weights, e, k, norm, scale, token, lane, p, p + e);
+}
+
 // Top-k routing and dispatch in one launch for decode-sized batches: the block's 16 warps route the tokens (round
 // robin), then the same block builds the plan from the ids it just wrote. Saves a launch and a device-wide drain.
 // 512 threads: the register-resident top-k keeps 32 values per lane, which a 1024-thread block's 64 registers would spill.
@@ -433,6 +449,20 @@ extern "C" B2MOE_API int32_t b2moe_topk_softmax(const float * logits, int32_t ld
         return B2MOE_ERR_SHAPE;
     if (!logits || !ids || !weights) return B2MOE_ERR_NULL;
     return route_launch<B2MOE_SOFTMAX>(logits, ld, nullptr, ids, weights, shared_weights, experts, topk, 1, scale, n, as_stream(stream));
+}
+
+extern "C" B2MOE_API int32_t b2moe_topk_softmax2(const float * logits, int32_t * ids, float * weights, float * shared_weights, const float * logits2,
+                                                 int32_t * ids2, float * weights2, float * shared_weights2, int32_t ld, int32_t experts, int32_t topk,
+                                                 int32_t n, float scale, b2moe_stream stream) {
+    if (experts <= 0 || experts > 4096 || topk <= 0 || topk > experts || n <= 0 || ld < experts + ((shared_weights || shared_weights2) ? 1 : 0))
+        return B2MOE_ERR_SHAPE;
+    if (!logits || !ids || !weights || !logits2 || !ids2 || !weights2) return B2MOE_ERR_NULL;
+    const int warps = experts <= 1024 ? 4 : 1;
+    const size_t smem = size_t(warps) * 2 * experts * sizeof(float);
+    const RouteSet a{logits, ids, weights, shared_weights}, b{logits2, ids2, weights2, shared_weights2};
+    launch_overlapped(route2_k<B2MOE_SOFTMAX>, dim3(ceil_div(n, warps), 2), dim3(warps * 32), smem, as_stream(stream), a, b, ld, (const float *)nullptr,
+                      experts, topk, 1, scale, n);
+    return launch_status();
 }
 
 extern "C" B2MOE_API int32_t b2moe_route_sigmoid(const float * logits, int32_t ld, const float * bias, int32_t * ids, float * weights,

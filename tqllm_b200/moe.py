@@ -65,6 +65,20 @@ def topk_softmax(logits, experts, k, scale=0.0, shared=False):
     return ids, w, sw
 
 
+
+def topk_softmax2(logits, logits2, experts, k, scale=0.0, shared=False):
+    """Two routings of the same tokens in one launch (the reference's moe_topk2): returns ((ids, w, sw), (ids2, w2, sw2))."""
+    n, ld = logits.shape
+    assert logits2.shape == logits.shape
+    out = []
+    for _ in range(2):
+        out.append((torch.empty(n, k, dtype=torch.int32, device=logits.device), torch.empty(n, k, dtype=torch.float32, device=logits.device),
+                    torch.empty(n, dtype=torch.float32, device=logits.device) if shared else None))
+    (i1, w1, s1), (i2, w2, s2) = out
+    check(lib.b2moe_topk_softmax2(logits.data_ptr(), i1.data_ptr(), w1.data_ptr(), _ptr(s1), logits2.data_ptr(), i2.data_ptr(), w2.data_ptr(),
+                                  _ptr(s2), ld, experts, k, n, scale, _stream()), "b2moe_topk_softmax2")
+    return out
+
 def route_sigmoid(logits, experts, k, bias=None, norm=True, scale=0.0):
     n, ld = logits.shape
     ids = torch.empty(n, k, dtype=torch.int32, device=logits.device)
@@ -72,6 +86,24 @@ def route_sigmoid(logits, experts, k, bias=None, norm=True, scale=0.0):
     check(lib.b2moe_route_sigmoid(logits.data_ptr(), ld, _ptr(bias), ids.data_ptr(), w.data_ptr(), experts, k, int(norm), scale, n,
                                   _stream()), "b2moe_route_sigmoid")
     return ids, w
+
+
+def count_ids(ids: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
+    """counts[e] += occurrences of e in ids (the reference's moe_count): counts is an int64 device tensor [experts]"""
+    assert counts.dtype == torch.int64 and ids.dtype == torch.int32
+    check(lib.b2moe_count(ids.data_ptr(), counts.data_ptr(), ids.numel(), counts.numel(), _stream()), "b2moe_count")
+    return counts
+
+
+def place_experts(counts, ranks: int):
+    """Load-aware placement from a routing histogram: (order, rank_load) with order[r * per + i] = the expert in slot i of
+    rank r (host arithmetic, b2moe_place_experts); feed `order` to synth.permute_experts or the loader's equivalent."""
+    import numpy as np
+    c = np.ascontiguousarray(np.asarray(counts.cpu() if hasattr(counts, "cpu") else counts), dtype=np.uint64)
+    order = np.empty(c.size, np.int32)
+    load = np.empty(ranks, np.uint64)
+    check(lib.b2moe_place_experts(c.ctypes.data, c.size, ranks, order.ctypes.data, load.ctypes.data), "b2moe_place_experts")
+    return order, load
 
 
 class Plan:

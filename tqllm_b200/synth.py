@@ -284,6 +284,23 @@ def make_layer(shape: LayerShape, seed: int, device="cpu", experts: int | None =
     return Layer(shape, router, bias, raw, shared)
 
 
+def permute_experts(layer: Layer, order) -> Layer:
+    """The same layer with its experts stacked in `order` (order[i] = the expert that takes position i): router rows,
+    selection bias and the raw blocks of the three banks move together, so the layer computes the same function and a
+    routed id i now means the former expert order[i]. Used to apply a load-aware placement (b2moe_place_experts)."""
+    shape = layer.shape
+    order = torch.as_tensor(order, dtype=torch.long, device=layer.router_w.device)
+    E = layer.router_w.shape[0]
+    assert sorted(order.tolist()) == list(range(E))
+    H, F = shape.hidden, shape.ff
+    raws = []
+    for i, (rows, cols) in enumerate(((F, H), (F, H), (H, F))):
+        per = raw_bytes(shape.types[i], rows, cols)
+        raws.append(layer.raw[i].view(E, per)[order].reshape(-1).contiguous())
+    return Layer(shape, layer.router_w[order].contiguous(), None if layer.sel_bias is None else layer.sel_bias[order].contiguous(),
+                 tuple(raws), layer.shared_raw)
+
+
 def make_tokens(shape: LayerShape, tokens: int, seed: int, device="cpu") -> torch.Tensor:
     """activations N(0,1); rounded to bf16 (and returned as bf16) unless the config feeds fp32"""
     g = _gen(seed ^ 0x5DEECE66D, device)
