@@ -268,6 +268,30 @@ B2MOE_API int32_t b2moe_ep_return_reduce(const float * back, const int32_t * pos
                                const float * shared_weights, int32_t n, int32_t hidden, void * out, int32_t out_dtype,
                                b2moe_stream stream);
 
+/* ---- GGUF expert reader and bank packer (host code, host pointers; no CUDA call) ------------------------------------
+ * Replaces the expert-serving part of the reference's reader: gguf_expert_count / gguf_expert_slice
+ * (src/core/gguf.hpp:77-91, src/core/gguf.cpp:174-213) with the block table of the five expert formats (gguf.cpp:116-152),
+ * and the loaders' device repack: the packed result is a finished bank, like the reference's packed expert file
+ * (src/experts/packed_experts.hpp:2-5). The file (GGUF version 2 or 3) is mapped read-only by b2moe_gguf_open; a file whose
+ * header, alignment or byte ranges are inconsistent is refused with B2MOE_ERR_FORMAT.
+ * b2moe_gguf_tensor: type, dims {cols, rows, experts} (1 beyond the rank), offset in the file and byte count (0 when the
+ *   block format is not one of the five) of a tensor by name; B2MOE_ERR_SHAPE when there is no such tensor.
+ * b2moe_gguf_expert_slice: experts [first, first + count) of a 3-D expert tensor as a pointer into the mapping (raw GGUF
+ *   rows, expert-major): one expert or a rank's block without reading the others. A 2-D tensor (a shared expert's matrix)
+ *   counts as one expert.
+ * b2moe_gguf_expert_bank: the same experts packed into the bank layout of bank_type (the tensor's type, or
+ *   B2MOE_IQ3_S_X4 for an IQ3_S tensor): data / aux sized by b2moe_bank_bytes / b2moe_bank_aux_bytes(bank_type, count *
+ *   rows, cols); rows must be a multiple of 16. */
+B2MOE_API int32_t b2moe_gguf_open(const char * path, void ** handle);
+B2MOE_API void b2moe_gguf_close(void * handle);
+B2MOE_API int32_t b2moe_gguf_tensor_count(const void * handle);
+B2MOE_API int32_t b2moe_gguf_tensor_name(const void * handle, int32_t index, char * name, int32_t name_bytes);
+B2MOE_API int32_t b2moe_gguf_tensor(const void * handle, const char * name, uint32_t * type, int64_t dims[3], uint64_t * offset, uint64_t * bytes);
+B2MOE_API int32_t b2moe_gguf_expert_slice(const void * handle, const char * name, int32_t first, int32_t count, uint32_t * type, int32_t * rows,
+                                int32_t * cols, const void ** raw, uint64_t * raw_bytes);
+B2MOE_API int32_t b2moe_gguf_expert_bank(const void * handle, const char * name, int32_t first, int32_t count, uint32_t bank_type, void * data,
+                               void * aux);
+
 /* Skew handling. b2moe_count replaces moe_count (src/experts/moe.cu:183-186, src/experts/moe_kernels.cuh:54): counts[e] += the
  * number of ids equal to e, accumulated over calls into a device array of `experts` 64-bit counters the caller zeroed
  * (ids outside [0, experts) are skipped). b2moe_place_experts (host code, host pointers) turns such a histogram into a

@@ -120,6 +120,31 @@ def test_routing_histogram_and_placement_leave_the_layer_unchanged(orc):
     assert rel_err(out2, out) < 1e-5
 
 
+def test_layer_loaded_from_a_gguf_file_equals_the_layer_loaded_from_its_raw_rows(tmp_path):
+    """the GGUF expert reader and host bank packer against the device loader: same banks, same output bits"""
+    from tqllm_b200 import gguf, moe
+    shape = synth.CONFIGS["c2"]
+    experts, tokens = 8, 12
+    layer, x = layer_inputs(shape, experts, tokens, 99)
+    H, F = shape.hidden, shape.ff
+    tensors = [("blk.3.ffn_gate_inp.weight", 0, (H, experts), layer.router_w.numpy().tobytes())]
+    for i, (m, dims) in enumerate((("gate", (H, F)), ("up", (H, F)), ("down", (F, H)))):
+        tensors.append((f"blk.3.ffn_{m}_exps.weight", shape.types[i], (*dims, experts), layer.raw[i].numpy().tobytes()))
+        tensors.append((f"blk.3.ffn_{m}_shexp.weight", shape.types[i], dims, layer.shared_raw[i].numpy().tobytes()))
+    path = str(tmp_path / "layer.gguf")
+    gguf.write_gguf(path, tensors)
+    for layout in ("codes", "gguf"):
+        a = moe.MoeLayer.from_synth(layer, experts=experts, iq3s_layout=layout)
+        b = moe.MoeLayer.from_gguf(path, shape, layer_index=3, iq3s_layout=layout)
+        assert torch.equal(a.gate.data, b.gate.data) and torch.equal(a.down.data, b.down.data) and torch.equal(a.sh[1].data, b.sh[1].data)
+        assert torch.equal(a.forward(x.cuda()), b.forward(x.cuda()))
+    # a rank's block of experts only
+    half = moe.MoeLayer.from_gguf(path, shape, layer_index=3, first_expert=4, experts=4)
+    full = moe.MoeLayer.from_synth(layer, experts=experts)
+    per = full.gate.data.numel() // experts
+    assert torch.equal(half.gate.data, full.gate.data[4 * per:]) and torch.equal(half.router_w, full.router_w[4:])
+
+
 def test_step_by_step_equals_layer_forward(orc):
     """the separate entry points chained by hand give the bits of b2moe_layer_forward"""
     from tqllm_b200 import moe

@@ -90,6 +90,14 @@ SIGNATURES = {
     "b2moe_static_scratch_bytes": (_sz, []),
     "b2moe_expert_down_static": (_i32, [C.POINTER(Bank)] * 2 + [_vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "b2moe_combine": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _i32, _vp]),
+    "b2moe_gguf_open": (_i32, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "b2moe_gguf_close": (None, [_vp]),
+    "b2moe_gguf_tensor_count": (_i32, [_vp]),
+    "b2moe_gguf_tensor_name": (_i32, [_vp, _i32, C.c_char_p, _i32]),
+    "b2moe_gguf_tensor": (_i32, [_vp, C.c_char_p, C.POINTER(C.c_uint32), C.POINTER(C.c_int64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "b2moe_gguf_expert_slice": (_i32, [_vp, C.c_char_p, _i32, _i32, C.POINTER(C.c_uint32), C.POINTER(C.c_int32), C.POINTER(C.c_int32),
+                                       C.POINTER(C.c_void_p), C.POINTER(C.c_uint64)]),
+    "b2moe_gguf_expert_bank": (_i32, [_vp, C.c_char_p, _i32, _i32, C.c_uint32, _vp, _vp]),
     "b2moe_count": (_i32, [_vp, _vp, _i32, _i32, _vp]),
     "b2moe_place_experts": (_i32, [_vp, _i32, _i32, _vp, _vp]),
     "b2moe_harness_select": (None, [_i32, _i32]),

@@ -39,6 +39,18 @@ class DeviceBank:
               "b2moe_bank_load")
         self.c = capi.Bank(self.data.data_ptr(), _ptr(self.aux), type_id, experts, rows, cols)
 
+    @classmethod
+    def from_packed(cls, type_id: int, data, aux, experts: int, rows: int, cols: int, device="cuda"):
+        """a bank that was packed on the host (b2moe_bank_pack_host, b2moe_gguf_expert_bank): one upload, no device repack"""
+        self = cls.__new__(cls)
+        self.type, self.experts, self.rows, self.cols = type_id, experts, rows, cols
+        if len(data) != lib.b2moe_bank_bytes(type_id, experts * rows, cols):
+            raise capi.B2moeError(capi.ERR_SHAPE, "DeviceBank.from_packed: byte count does not match the shape")
+        self.data = torch.as_tensor(data).to(device)
+        self.aux = None if aux is None else torch.as_tensor(aux).to(device)
+        self.c = capi.Bank(self.data.data_ptr(), _ptr(self.aux), type_id, experts, rows, cols)
+        return self
+
     def dequant(self) -> torch.Tensor:
         out = torch.empty(self.experts * self.rows, self.cols, dtype=torch.float32, device=self.data.device)
         check(lib.b2moe_dequant_dump(C.byref(self.c), out.data_ptr(), _stream()), "b2moe_dequant_dump")
@@ -203,6 +215,10 @@ class MoeLayer:
         if shared_raw is not None:
             self.sh = (DeviceBank(tg, dev(shared_raw[0]), 1, F, H), DeviceBank(tu, dev(shared_raw[1]), 1, F, H),
                        DeviceBank(td, dev(shared_raw[2]), 1, H, F))
+        self._finish()
+
+    def _finish(self):
+        shape, E, H, F = self.shape, self.experts, self.shape.hidden, self.shape.ff
         L = capi.Layer()
         L.hidden, L.experts, L.topk, L.ff = H, E, shape.topk, F
         L.gating, L.norm, L.scale, L.has_shared = shape.gating, int(shape.norm), shape.scale, int(self.sh is not None)
@@ -212,6 +228,34 @@ class MoeLayer:
             L.sh_gate, L.sh_up, L.sh_down = self.sh[0].c, self.sh[1].c, self.sh[2].c
         self.c = L
         self.ws, self.ws_view, self.ws_tokens = None, None, 0
+
+    @classmethod
+    def from_gguf(cls, path, shape, layer_index=0, first_expert=0, experts=None, device="cuda", iq3s_layout="codes"):
+        """Experts [first_expert, first_expert + experts) of layer `layer_index` of a GGUF checkpoint (tensor names
+        blk.N.ffn_{gate,up,down}_exps.weight, router blk.N.ffn_gate_inp.weight, optional blk.N.ffn_{gate,up,down}_shexp.weight):
+        the banks are packed on the host by the library's reader and uploaded once."""
+        import numpy as np
+        from . import gguf
+        pre = f"blk.{layer_index}."
+        with gguf.GgufExperts(path) as g:
+            names = g.names()
+            t, (h, e_all, _), off, _ = g.tensor(pre + "ffn_gate_inp.weight")
+            assert t == 0 and h == shape.hidden, "router must be an F32 [hidden, experts] tensor"
+            E = experts or e_all - first_expert
+            router = np.array(np.memmap(path, np.float32, "r", off, (e_all, h))[first_expert:first_expert + E])
+            codes = iq3s_layout == "codes"
+            banks = [g.expert_bank(pre + f"ffn_{m}_exps.weight", first_expert, E, codes) for m in ("gate", "up", "down")]
+            shared = None
+            if pre + "ffn_gate_shexp.weight" in names:
+                shared = [g.expert_bank(pre + f"ffn_{m}_shexp.weight", 0, 1, codes) for m in ("gate", "up", "down")]
+        self = cls.__new__(cls)
+        self.shape, self.experts, self.device = shape, E, torch.device(device)
+        self.router_w, self.sel_bias, self.shared_gate_vec = torch.from_numpy(router).to(device), None, None
+        mk = lambda b, n: DeviceBank.from_packed(b[0], b[3], b[4], n, b[1], b[2], device)
+        self.gate, self.up, self.down = (mk(b, E) for b in banks)
+        self.sh = tuple(mk(b, 1) for b in shared) if shared else None
+        self._finish()
+        return self
 
     @classmethod
     def from_synth(cls, layer, device="cuda", experts=None, shared_gate_vec=None, iq3s_layout="codes"):
