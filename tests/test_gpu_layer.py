@@ -124,7 +124,7 @@ def test_layer_loaded_from_a_gguf_file_equals_the_layer_loaded_from_its_raw_rows
     """the GGUF expert reader and host bank packer against the device loader: same banks, same output bits"""
     from tqllm_b200 import gguf, moe
     shape = synth.CONFIGS["c2"]
-    experts, tokens = 8, 12
+    experts, tokens = 16, 12
     layer, x = layer_inputs(shape, experts, tokens, 99)
     H, F = shape.hidden, shape.ff
     tensors = [("blk.3.ffn_gate_inp.weight", 0, (H, experts), layer.router_w.numpy().tobytes())]
@@ -139,7 +139,7 @@ def test_layer_loaded_from_a_gguf_file_equals_the_layer_loaded_from_its_raw_rows
         assert torch.equal(a.gate.data, b.gate.data) and torch.equal(a.down.data, b.down.data) and torch.equal(a.sh[1].data, b.sh[1].data)
         assert torch.equal(a.forward(x.cuda()), b.forward(x.cuda()))
     # a rank's block of experts only
-    half = moe.MoeLayer.from_gguf(path, shape, layer_index=3, first_expert=4, experts=4)
+    half = moe.MoeLayer.from_gguf(path, shape, layer_index=3, first_expert=4, experts=12)
     full = moe.MoeLayer.from_synth(layer, experts=experts)
     per = full.gate.data.numel() // experts
     assert torch.equal(half.gate.data, full.gate.data[4 * per:]) and torch.equal(half.router_w, full.router_w[4:])
