@@ -60,6 +60,7 @@ def parse():
     p.add_argument("--no-extras", action="store_true", help="skip the sweep and the records of the other configurations")
     p.add_argument("--iq3s-layout", default="codes", choices=("codes", "gguf"), help="bank layout of IQ3_S experts")
     p.add_argument("--ring", default="", help="nbuf,stages,slot_tiles: force the decode kernels' shared-memory configuration (A/B timing)")
+    p.add_argument("--column-split", type=int, default=0, help="1 / 2 / 4: most warps of the decode kernels that share a row job (0: the library's default)")
     p.add_argument("--overlap", type=int, default=1, help="0: plain stream order between the launches of a layer instead of programmatic dependent launch")
     return p.parse_args()
 
@@ -379,6 +380,8 @@ def run_b200(args):
     from tqllm_b200 import capi, moe, synth
     lib = capi.lib
     lib.b2moe_harness_overlap(1 if args.overlap else 0)
+    if args.column_split:
+        lib.b2moe_harness_column_split(args.column_split)
     if args.ring:
         lib.b2moe_harness_ring(*[int(v) for v in args.ring.split(",")])
 

@@ -318,6 +318,8 @@ B2MOE_API int32_t b2moe_place_experts(const uint64_t * counts, int32_t experts, 
  * that one's completion before it touches global memory; off = plain stream order (for A/B timing).
  * b2moe_harness_ring: forces the shared-memory configuration of the 4-bit decode kernels (activation buffers 1-2, ring
  * stages 2-4, tiles per slot 1-2) where it fits; zeros = the library's own order of preference.
+ * b2moe_harness_column_split: the most warps (1, 2 or 4; default 4) that the 4-bit decode kernels let share one row job
+ * when a launch has only a few jobs per block; 1 switches the split off.
  * b2moe_harness_launches: kernel launches the library has made in this process so far. */
 enum b2moe_family { B2MOE_FAMILY_AUTO = 0, B2MOE_FAMILY_GENERIC = 1, B2MOE_FAMILY_DECODE = 2, B2MOE_FAMILY_GEMM = 3 };
 B2MOE_API void b2moe_harness_select(int32_t family, int32_t gemm_item_tokens);
@@ -325,6 +327,7 @@ B2MOE_API void b2moe_harness_wait_probe(int32_t drop_tile, uint32_t wait_limit);
 B2MOE_API void b2moe_harness_skip_staging(int32_t on);
 B2MOE_API void b2moe_harness_overlap(int32_t on);
 B2MOE_API void b2moe_harness_ring(int32_t activation_buffers, int32_t stages, int32_t slot_tiles);
+B2MOE_API void b2moe_harness_column_split(int32_t max_warps_per_job);
 B2MOE_API uint64_t b2moe_harness_launches(void);
 
 /* ---- whole layer ----------------------------------------------------------------------------------------------

@@ -105,6 +105,7 @@ SIGNATURES = {
     "b2moe_harness_skip_staging": (None, [_i32]),
     "b2moe_harness_overlap": (None, [_i32]),
     "b2moe_harness_ring": (None, [_i32, _i32, _i32]),
+    "b2moe_harness_column_split": (None, [_i32]),
     "b2moe_harness_launches": (C.c_uint64, []),
     "b2moe_layer_workspace": (_i32, [C.POINTER(Layer), _i32, C.POINTER(LayerWs)]),
     "b2moe_layer_forward": (_i32, [C.POINTER(Layer), _vp, _i32, _i32, _vp, _i32, _vp, _sz, _vp]),

@@ -168,6 +168,9 @@ struct Dec4Args {
     int * plan;
     float * out;                             // [A + shared][rows]
     int rows, k_tiles, experts, topk, A, nbuf, stages, slot_tiles;
+    int shared_rows;                         // rows of the always-on expert in the plan (its count: known to the host)
+    int passes_bound;                        // host: an upper bound of the plan's pass count, from the call's shape
+    int ksplit;                              // consumer warps that share one row job, each taking 1 / ksplit of its columns (1, 2 or 4)
     uint32_t wait_limit;
     int drop_tile;                           // test hook: the copy into ring slot use number drop_tile (per warp, counted from 0) is never issued; -1 = none
 };
@@ -179,8 +182,10 @@ __host__ __device__ inline size_t xs_bytes(int k, int nbuf) { return size_t(nbuf
 // what the consumers need to know about a segment's tokens, written by the producer beside the activation rows it copies:
 // per token column the assignment index (-1 = no token) and the inverse activation scale
 struct SegMeta { int col_a[PASS_TOKENS]; float col_is[PASS_TOKENS]; };
-// barriers: full[warp][stage], empty[warp][stage], xfull[2], xempty[2]; then the abort flag; then SegMeta[2]
-constexpr size_t BAR_BYTES = (2 * CTA_WARPS * MAX_STAGES + 4) * 8 + 16 + 2 * sizeof(SegMeta);
+// barriers: full[warp][stage], empty[warp][stage], xfull[2], xempty[2]; then the abort flag; then SegMeta[2]; then the
+// barriers of the split-column reduction: red_full[8], red_free[8] (one pair per group of warps that share a row job)
+constexpr size_t BAR_BYTES = (2 * CTA_WARPS * MAX_STAGES + 4) * 8 + 16 + 2 * sizeof(SegMeta) + 16 * 8;
+constexpr size_t RED_BYTES = size_t(CTA_WARPS) * 8 * 32 * sizeof(float);     // partial sums of every warp: [warp][8 accumulators][lane]
 constexpr int THREADS = (CTA_WARPS + 1) * 32;      // 16 consumer warps + the producer warp
 
 // MODE 0: out = act[a][row] = silu(gate . x) * (up . x);   MODE 1: out = y[a][row] = down . act[a]
@@ -192,14 +197,18 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
     uint64_t * bars = reinterpret_cast<uint64_t *>(smem);
     volatile int * abort_flag = reinterpret_cast<volatile int *>(smem + (2 * CTA_WARPS * MAX_STAGES + 4) * 8);
     SegMeta * meta = reinterpret_cast<SegMeta *>(smem + (2 * CTA_WARPS * MAX_STAGES + 4) * 8 + 16);
+    const uint32_t red_full = smem_addr(meta + 2), red_free = red_full + 64;
     const int SLOT_TILES = p.slot_tiles, SLOT = SLOT_TILES * TILE;
     uint8_t * ring = smem + BAR_BYTES;                                        // [warp][stage][SLOT]
     uint8_t * xs = ring + size_t(CTA_WARPS) * p.stages * SLOT;               // [buf][8 rows][xrow]
+    float * red = reinterpret_cast<float *>(xs + xs_bytes(p.k_tiles * 256, p.nbuf));   // [warp][8][32], only when ksplit > 1
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int K = p.k_tiles * 256;
     const int e1 = p.experts + 1;
     const uint32_t xrow = xrow_bytes(K), xbuf = 8 * xrow, xglob = uint32_t(staged_row_bytes(K));
-    const int S = p.stages, kslots = (p.k_tiles + SLOT_TILES - 1) / SLOT_TILES, nslots = kslots * NMAT;   // slots of one row job
+    const int S = p.stages, kslots = (p.k_tiles + SLOT_TILES - 1) / SLOT_TILES;                            // column slots of one row job
+    // ksplit warps share a row job: warp w takes part w % ksplit of its column slots (ksplit divides kslots); JW jobs run side by side
+    const int KSP = p.ksplit, JW = CTA_WARPS / KSP, kpart = kslots / KSP, nslots = kpart * NMAT;           // slots of one warp's part of a job
     const uint32_t full0 = smem_addr(bars), empty0 = full0 + 8 * CTA_WARPS * MAX_STAGES, xfull = empty0 + 8 * CTA_WARPS * MAX_STAGES,
                    xempty = xfull + 16, xs0 = smem_addr(xs);
 
@@ -207,6 +216,7 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
     if (threadIdx.x == 0) {
         mbar_init(xfull, 1); mbar_init(xfull + 8, 1);
         mbar_init(xempty, CTA_WARPS); mbar_init(xempty + 8, CTA_WARPS);
+        for (int i = 0; i < 8; ++i) { mbar_init(red_full + 8 * i, uint32_t(p.ksplit)); mbar_init(red_free + 8 * i, 1); }
         *abort_flag = 0;
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -214,7 +224,7 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
     __syncthreads();
 
     const int * counts = p.plan + PLAN_HDR, * offsets = counts + e1, * active = offsets + e1 + 1, * perm = active + e1;
-    const int * passes = perm + p.A + counts[p.experts];
+    const int * passes = perm + p.A + p.shared_rows;
     const int na = p.plan[PLAN_NACTIVE], row_tiles = (p.rows + 15) >> 4;
     // the block's share of the launch: jobs [u_begin, u_end) of the pass-major list of (pass, row tile) jobs; it walks the
     // share as segments = runs of row tiles [r0, r1) of one pass
@@ -226,10 +236,19 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
         r1 = int(min((long long)row_tiles, r0 + (u_end - u)));
     };
 
-    // pass w -> (expert, first token slot); the pass list runs over the active experts from the last to the first
+    // pass w -> (expert, first token slot); the pass list runs over the active experts from the last to the first. Called by
+    // all lanes of the producer warp together: two rounds of 32 probes instead of a ten-step chain of dependent loads.
     auto locate = [&](int w, int & e, int & c0) {
-        int lo = 0, hi = na - 1;
-        while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (passes[mid] <= w) lo = mid; else hi = mid - 1; }
+        const int stride = (na + 31) >> 5;                                         // first round: every stride-th entry
+        const int i1 = min(lane * stride, na - 1);
+        const unsigned m1 = __ballot_sync(0xffffffffu, lane * stride < na && passes[i1] <= w);
+        const int base = (31 - __clz(int(m1 | 1u))) * stride;                      // passes[0] = 0 <= w always
+        int lo = base;
+        for (int o = 0; o < stride; o += 32) {                                     // second round: the entries of that stretch
+            const int i2 = base + o + lane;
+            const unsigned m2 = __ballot_sync(0xffffffffu, i2 < min(na, base + stride) && passes[min(i2, na - 1)] <= w);
+            if (m2) lo = base + o + 31 - __clz(int(m2));
+        }
         e = active[na - 1 - lo];
         c0 = (w - passes[lo]) * PASS_TOKENS;
     };
@@ -273,7 +292,7 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
         };
         int pass, r0, r1;
         uint32_t idx = 0;
-        if (u_begin < u_end) { segment(u_begin, pass, r0, r1); stage_x(pass, 0); }
+        bool first_staged = false;                         // the first segment's rows are asked for right after its first weight copies
         for (long long u = u_begin; u < u_end && ok; u += r1 - r0, ++idx) {
             segment(u, pass, r0, r1);
             int e, c0;
@@ -284,8 +303,8 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
             if (u_next < u_end) segment(u_next, npass, nr0, nr1);
             bool next_staged = p.nbuf != 2 || u_next >= u_end;
             int in_seg = 0;
-            for (int rb = r0; rb < r1 && ok; rb += CTA_WARPS) {           // 16 row tiles at a time, warp w its own
-                const int rt = rb + w;
+            for (int rb = r0; rb < r1 && ok; rb += JW) {                  // JW row tiles at a time, warp w its part of its own
+                const int rt = rb + w / KSP, k_first = (w % KSP) * kpart;
                 const bool mine = lane < CTA_WARPS && rt < r1;
                 const uint8_t * b0 = (shared ? p.s0 : p.w0 + size_t(e) * p.bank_bytes) + size_t(rt) * p.k_tiles * TILE;
                 const uint8_t * b1 = NMAT == 2 ? (shared ? p.s1 : p.w1 + size_t(e) * p.bank_bytes) + size_t(rt) * p.k_tiles * TILE : b0;
@@ -293,7 +312,7 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
                     if (mine) {
                         if (issued >= uint32_t(S) && !wait(my_empty + 8 * slot, ((issued / S) - 1) & 1u)) ok = false;
                         else if (int(issued) != p.drop_tile) {
-                            const int ks = NMAT == 2 ? j >> 1 : j;                                   // slot of column tiles of the job
+                            const int ks = k_first + (NMAT == 2 ? j >> 1 : j);                       // slot of column tiles of the job
                             const uint8_t * src = ((NMAT == 2 && (j & 1)) ? b1 : b0) + size_t(ks) * SLOT;
                             const uint32_t bytes = uint32_t(min(SLOT_TILES, p.k_tiles - ks * SLOT_TILES)) * TILE;
                             mbar_expect_tx(my_full + 8 * slot, bytes);
@@ -303,6 +322,7 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
                         slot = slot + 1 == uint32_t(S) ? 0 : slot + 1;
                     }
                     ok = __all_sync(0xffffffffu, ok);
+                    if (!first_staged) { stage_x(pass, 0); first_staged = true; }
                     // once every consumer is S slots into this segment, the previous segment's buffer is free: bring the next one's rows
                     if (!next_staged && in_seg == S) { stage_x(npass, idx + 1); next_staged = true; }
                 }
@@ -327,7 +347,7 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
         const int g = lane >> 2, t = lane & 3;
         const uint8_t * my_ring = ring + size_t(warp) * S * SLOT;
         const uint32_t my_full = full0 + 8 * warp * MAX_STAGES, my_empty = empty0 + 8 * warp * MAX_STAGES;
-        uint32_t c_slot = 0, c_phase = 0;
+        uint32_t c_slot = 0, c_phase = 0, red_use = 0;
         bool alive = true;
         int pass, r0, r1;
         uint32_t idx = 0;
@@ -344,14 +364,15 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
 #pragma unroll
             for (int q = 0; q < 2; ++q) { col_a[q] = meta[b].col_a[2 * t + q]; col_is[q] = meta[b].col_is[2 * t + q]; }
 
-            for (int rt = r0 + warp; rt < r1 && alive; rt += CTA_WARPS) {
+            const int grp = warp / KSP, part = warp % KSP;                  // row-job slot of this warp and its part of the columns
+            for (int rt = r0 + grp; rt < r1 && alive; rt += JW) {
                 float acc[NMAT][4];
 #pragma unroll
                 for (int m = 0; m < NMAT; ++m)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) acc[m][i] = 0.f;
 
-                for (int ks = 0; ks < kslots && alive; ++ks) {
+                for (int ks = part * kpart; ks < (part + 1) * kpart && alive; ++ks) {
                     const int nt = min(SLOT_TILES, p.k_tiles - ks * SLOT_TILES);
 #pragma unroll
                     for (int m = 0; m < NMAT; ++m) {
@@ -398,6 +419,32 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
                     }
                 }
                 if (!alive) break;
+                if (KSP > 1) {
+                    // the parts of the row job meet in shared memory: every warp leaves its sums, part 0 adds them in part order
+                    // (the same bits every run) and carries on alone. red_use counts this group's jobs of the whole launch.
+                    float * mine = red + size_t(warp) * 8 * 32;
+                    if (part != 0) {
+                        if (red_use > 0 && !__all_sync(0xffffffffu, wait(red_free + 8 * grp, (red_use - 1) & 1u))) { alive = false; break; }
+#pragma unroll
+                        for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) mine[(m * 4 + i) * 32 + lane] = acc[m][i];
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(red_full + 8 * grp);
+                        ++red_use;
+                        continue;
+                    }
+                    if (lane == 0) mbar_arrive(red_full + 8 * grp);
+                    if (!__all_sync(0xffffffffu, wait(red_full + 8 * grp, red_use & 1u))) { alive = false; break; }
+                    for (int o = 1; o < KSP; ++o)
+#pragma unroll
+                        for (int m = 0; m < NMAT; ++m)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) acc[m][i] += red[size_t(warp + o) * 8 * 32 + (m * 4 + i) * 32 + lane];
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(red_free + 8 * grp);
+                    ++red_use;
+                }
                 // epilogue: the lane holds rows g, g + 8 x token columns 2t, 2t + 1
 #pragma unroll
                 for (int q = 0; q < 2; ++q) {
@@ -449,6 +496,7 @@ template <uint32_t T> bool dec4_fit(int k, int & nbuf, int & stages, int & slot_
     return false;
 }
 
+int g_ksplit_max = 4;                 // test hook: 1 switches the column split of small launches off
 int g_drop_tile = -1;                 // test hooks (b2moe_harness_wait_probe, b2moe_harness_skip_staging)
 bool g_skip_stage = false;
 uint32_t g_wait_limit = WAIT_LIMIT;
@@ -458,7 +506,16 @@ int32_t launch_dec4(Dec4Args a, cudaStream_t s) {
     const int sms = sm_count(), k = a.k_tiles * 256;
     if (sms <= 0) return B2MOE_ERR_CUDA;
     if (!dec4_fit<T>(k, a.nbuf, a.stages, a.slot_tiles)) return B2MOE_ERR_SHAPE;
-    const size_t smem = dec4_smem<T>(k, a.nbuf, a.stages, a.slot_tiles);
+    // When the launch cannot have more than a few row jobs per block (a handful of tokens), 2 or 4 warps share a job, each
+    // taking a part of its columns: a job is then a chain of kslots / ksplit copies instead of kslots. The bound comes from
+    // the call's shape (every pass holds at least one assignment), never from the plan, so a captured launch keeps it.
+    const int kslots = (a.k_tiles + a.slot_tiles - 1) / a.slot_tiles;
+    const long long jobs_bound = (long long)a.passes_bound * ((a.rows + 15) / 16), per_block = (jobs_bound + sms - 1) / sms;
+    a.ksplit = 1;
+    for (int ks = 4; ks >= 2; ks >>= 1)
+        if (per_block <= CTA_WARPS / ks && kslots % ks == 0 && g_ksplit_max >= ks &&
+            dec4_smem<T>(k, a.nbuf, a.stages, a.slot_tiles) + RED_BYTES <= SMEM_LIMIT) { a.ksplit = ks; break; }
+    const size_t smem = dec4_smem<T>(k, a.nbuf, a.stages, a.slot_tiles) + (a.ksplit > 1 ? RED_BYTES : 0);
     if (cudaFuncSetAttribute(dec4_k<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
     a.wait_limit = g_wait_limit;
     a.drop_tile = g_drop_tile;
@@ -488,6 +545,8 @@ int32_t gateup_t(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_ban
     a.bank_bytes = b2moe_bank_bytes(gate->type, gate->rows, gate->cols);
     a.plan = const_cast<int *>(plan); a.out = act;
     a.rows = gate->rows; a.k_tiles = k / 256; a.experts = gate->experts; a.topk = topk; a.A = n * topk;
+    a.shared_rows = shared_tokens;
+    a.passes_bound = n * topk + (shared_tokens + PASS_TOKENS - 1) / PASS_TOKENS;
     return launch_dec4<T, 0>(a, s);
 }
 template <uint32_t T>
@@ -501,6 +560,8 @@ int32_t down_t(const b2moe_bank * down, const b2moe_bank * sd, const float * act
     a.bank_bytes = b2moe_bank_bytes(down->type, down->rows, down->cols);
     a.plan = const_cast<int *>(plan); a.out = y;
     a.rows = down->rows; a.k_tiles = k / 256; a.experts = down->experts; a.topk = topk; a.A = n * topk;
+    a.shared_rows = shared_tokens;
+    a.passes_bound = n * topk + (shared_tokens + PASS_TOKENS - 1) / PASS_TOKENS;
     return launch_dec4<T, 1>(a, s);
 }
 
@@ -533,6 +594,7 @@ int32_t dec4_down(const b2moe_bank * down, const b2moe_bank * sd, const float * 
 }
 void dec4_skip_staging(bool on) { g_skip_stage = on; }
 void dec4_ring(int nbuf, int stages, int slot_tiles) { g_ring[0] = nbuf; g_ring[1] = stages; g_ring[2] = slot_tiles; }
+void dec4_ksplit_max(int ks) { g_ksplit_max = ks < 1 ? 1 : ks; }
 // where dec4_gateup expects the staged form of n activation rows of length k inside its workspace, and with how many bits
 void dec4_stage_target(uint32_t type, void * ws, int n, int k, uint8_t ** rows, float ** inv_scale, int * bits) {
     *rows = static_cast<uint8_t *>(ws);

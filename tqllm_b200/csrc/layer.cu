@@ -27,6 +27,7 @@ int32_t dec4_down(const b2moe_bank *, const b2moe_bank *, const float *, const i
 void dec4_debug(int drop_tile, uint32_t wait_limit);
 void dec4_skip_staging(bool on);
 void dec4_ring(int nbuf, int stages, int slot_tiles);
+void dec4_ksplit_max(int ks);
 unsigned long long g_launch_count = 0;
 bool g_overlap = true;
 bool gemm_tc_supported(uint32_t type, int k, int nmat, int experts);
@@ -107,6 +108,7 @@ extern "C" B2MOE_API void b2moe_harness_select(int32_t family, int32_t gemm_item
 extern "C" B2MOE_API void b2moe_harness_wait_probe(int32_t drop_tile, uint32_t wait_limit) { dec4_debug(drop_tile, wait_limit); }
 extern "C" B2MOE_API void b2moe_harness_skip_staging(int32_t on) { dec4_skip_staging(on != 0); }
 extern "C" B2MOE_API void b2moe_harness_ring(int32_t nbuf, int32_t stages, int32_t slot_tiles) { dec4_ring(nbuf, stages, slot_tiles); }
+extern "C" B2MOE_API void b2moe_harness_column_split(int32_t max_warps_per_job) { dec4_ksplit_max(max_warps_per_job); }
 extern "C" B2MOE_API void b2moe_harness_overlap(int32_t on) { g_overlap = on != 0; }
 extern "C" B2MOE_API uint64_t b2moe_harness_launches(void) { return g_launch_count; }
 
