@@ -23,7 +23,8 @@ __device__ __forceinline__ float stage_scale(float mx, int bits, float & inv) {
     inv = __uint_as_float(uint32_t(127 - (bits - 2) + ex) << 23);
     return __uint_as_float(uint32_t(127 + bits - 2 - ex) << 23);         // 2^(bits - 2 - ex)
 }
-// sub-block b of a row: one lane per column; every lane of the warp calls it
+// sub-block b of a row: one lane per column; every lane of the warp calls it. orow / recs: the row's staged bytes and records
+// (global or shared memory)
 __device__ __forceinline__ void stage_sub_block(const void * x, int dtype, size_t row_first, int b, float scale, uint8_t * orow, uint8_t * recs, int lane) {
     const int t = (lane & 15) >> 2, j = lane & 3, h = lane >> 4;
     const int v = __float2int_rn(load_act(x, dtype, row_first + 32 * b + lane) * scale);
@@ -38,18 +39,56 @@ __device__ __forceinline__ void stage_sub_block(const void * x, int dtype, size_
             __floats2half2_rn(float((sum >> 10) * 16), float(sum & 1023) * 0.015625f);
     }
 }
-// one whole row by one warp
-__device__ inline void stage_row_warp(const void * x, int dtype, int row, int k, int bits, uint8_t * out, float * inv_scale, int lane) {
-    const size_t first = size_t(row) * k;
+// one whole row (elements [first, first + k) of x) by one warp into `orow`; returns the row's inverse scale
+__device__ inline float stage_row_to(const void * x, int dtype, size_t first, int k, int bits, uint8_t * orow, int lane) {
     float mx = 0.f;
     for (int j = lane; j < k; j += 32) mx = fmaxf(mx, fabsf(load_act(x, dtype, first + j)));
     for (int d = 16; d; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
     float inv;
     const float scale = stage_scale(mx, bits, inv);
-    if (lane == 0) inv_scale[row] = inv;
-    uint8_t * orow = out + size_t(row) * staged_row_bytes(k);
     uint8_t * recs = orow + size_t(k) * 2;
+#pragma unroll 4
     for (int b = 0; b < (k >> 5); ++b) stage_sub_block(x, dtype, first, b, scale, orow, recs, lane);
+    return inv;
+}
+// The same row with a lane per sub-block (32 consecutive columns each): no cross-lane step except the row maximum, for the
+// warp that stages rows inside the down product while the consumer warps take most issue slots. fp32 rows, k a multiple of 32.
+__device__ inline float stage_row_f32_lanes(const float * __restrict__ x, size_t first, int k, int bits, uint8_t * orow, int lane) {
+    const float4 * row4 = reinterpret_cast<const float4 *>(x + first);
+    float mx = 0.f;
+    for (int j = lane; j < (k >> 2); j += 32) {
+        const float4 v = row4[j];
+        mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+    }
+    for (int d = 16; d; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+    float inv;
+    const float scale = stage_scale(mx, bits, inv);
+    uint8_t * recs = orow + size_t(k) * 2;
+    for (int b = lane; b < (k >> 5); b += 32) {
+        uint32_t hi[8], lo[8];                      // bytes of columns 4 i .. 4 i + 3
+        int sum = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float4 v = row4[b * 8 + i];
+            const int a = __float2int_rn(v.x * scale), c = __float2int_rn(v.y * scale), d = __float2int_rn(v.z * scale), e = __float2int_rn(v.w * scale);
+            sum += a + c + d + e;
+            // byte 1 (high) and byte 0 (low) of the four values, in column order
+            hi[i] = __byte_perm(__byte_perm(uint32_t(a), uint32_t(c), 0x0051), __byte_perm(uint32_t(d), uint32_t(e), 0x0051), 0x5410);
+            lo[i] = __byte_perm(__byte_perm(uint32_t(a), uint32_t(c), 0x0040), __byte_perm(uint32_t(d), uint32_t(e), 0x0040), 0x5410);
+        }
+        uint4 * sb = reinterpret_cast<uint4 *>(orow + size_t(b) * 64);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) sb[t] = make_uint4(hi[t], hi[4 + t], lo[t], lo[4 + t]);
+        const int bb = b & 7;
+        reinterpret_cast<__half2 *>(recs + size_t(b >> 3) * 32)[2 * (bb & 3) + (bb >> 2)] =
+            __floats2half2_rn(float((sum >> 10) * 16), float(sum & 1023) * 0.015625f);
+    }
+    return inv;
+}
+// row `row` of x[.][k] into the array of staged rows `out`, its inverse scale into inv_scale[row]
+__device__ inline void stage_row_warp(const void * x, int dtype, int row, int k, int bits, uint8_t * out, float * inv_scale, int lane) {
+    const float inv = stage_row_to(x, dtype, size_t(row) * k, k, bits, out + size_t(row) * staged_row_bytes(k), lane);
+    if (lane == 0) inv_scale[row] = inv;
 }
 
 }  // namespace b2

@@ -163,7 +163,8 @@ template <> struct D4<T_IQ3S4> {
 struct Dec4Args {
     const uint8_t * w0, * w1, * s0, * s1;   // stacked banks (gate, up | down, -) and the shared expert's
     size_t bank_bytes;
-    const uint8_t * x;                       // staged activation rows [rows_x][staged_row_bytes(k)]
+    const uint8_t * x;                       // MODE 0: staged activation rows [rows_x][staged_row_bytes(k)]
+    const float * x_raw;                     // MODE 1: the fp32 activation rows [A + shared][k], staged inside the kernel
     const float * inv_scale;                 // [rows_x]
     int * plan;
     float * out;                             // [A + shared][rows]
@@ -186,11 +187,16 @@ struct SegMeta { int col_a[PASS_TOKENS]; float col_is[PASS_TOKENS]; };
 // barriers of the split-column reduction: red_full[8], red_free[8] (one pair per group of warps that share a row job)
 constexpr size_t BAR_BYTES = (2 * CTA_WARPS * MAX_STAGES + 4) * 8 + 16 + 2 * sizeof(SegMeta) + 16 * 8;
 constexpr size_t RED_BYTES = size_t(CTA_WARPS) * 8 * 32 * sizeof(float);     // partial sums of every warp: [warp][8 accumulators][lane]
-constexpr int THREADS = (CTA_WARPS + 1) * 32;      // 16 consumer warps + the producer warp
+// 16 consumer warps + the producer warp; the STAGER instance of the down product (small launches) has one more warp that brings
+// its activation rows (fp32, the gate/up product's output) into the staged form inside the kernel, a segment ahead of the
+// consumers: no staging launch between the two products. A scheduler partition holds 16 K registers, so its five warps may take 96 each: the launch bound is given
+// as 640 threads to make the compiler stay at 96 (65536 / 640 rounds down to it), whatever the block really has.
+template <bool STAGER> constexpr int threads_of() { return (CTA_WARPS + (STAGER ? 2 : 1)) * 32; }
+template <bool STAGER> constexpr int bound_threads() { return STAGER ? 640 : threads_of<false>(); }
 
 // MODE 0: out = act[a][row] = silu(gate . x) * (up . x);   MODE 1: out = y[a][row] = down . act[a]
-template <uint32_t T, int MODE>
-__global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
+template <uint32_t T, int MODE, bool STAGER>
+__global__ void __launch_bounds__(bound_threads<STAGER>(), 1) dec4_k(const Dec4Args p) {
     using F = D4<T>;
     constexpr int NMAT = MODE == 0 ? 2 : 1, TILE = F::TILE;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -252,6 +258,7 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
         e = active[na - 1 - lo];
         c0 = (w - passes[lo]) * PASS_TOKENS;
     };
+    constexpr bool in_kernel = STAGER;                             // the down product stages its rows itself (small launches)
     auto x_row = [&](int a) { return MODE == 0 ? size_t(a < p.A ? a / p.topk : a - p.A) : size_t(a); };
     // a bounded wait that also gives up when another warp of the block has
     auto wait = [&](uint32_t bar, uint32_t parity) {
@@ -322,13 +329,13 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
                         slot = slot + 1 == uint32_t(S) ? 0 : slot + 1;
                     }
                     ok = __all_sync(0xffffffffu, ok);
-                    if (!first_staged) { stage_x(pass, 0); first_staged = true; }
+                    if (!in_kernel && !first_staged) { stage_x(pass, 0); first_staged = true; }
                     // once every consumer is S slots into this segment, the previous segment's buffer is free: bring the next one's rows
-                    if (!next_staged && in_seg == S) { stage_x(npass, idx + 1); next_staged = true; }
+                    if (!in_kernel && !next_staged && in_seg == S) { stage_x(npass, idx + 1); next_staged = true; }
                 }
             }
-            if (!next_staged && ok) stage_x(npass, idx + 1);
-            if (p.nbuf == 1 && u_next < u_end && ok) stage_x(npass, idx + 1);
+            if (!in_kernel && !next_staged && ok) stage_x(npass, idx + 1);
+            if (!in_kernel && p.nbuf == 1 && u_next < u_end && ok) stage_x(npass, idx + 1);
         }
         if (!ok) { *abort_flag = 1; if (lane == 0) atomicExch(p.plan + PLAN_STATUS, 3); }
         // before leaving, every copy this lane issued must have landed: the last S slots of its ring (earlier ones were
@@ -339,9 +346,33 @@ __global__ void __launch_bounds__(THREADS, 1) dec4_k(const Dec4Args p) {
             for (uint32_t i = first; i < issued; ++i)
                 if (int(i) != p.drop_tile) wait(my_full + 8 * (i % S), (i / S) & 1u);
         }
-        if (lane == 16)       // the last copy into each activation buffer (an earlier phase of a barrier can no longer be waited for)
+        if (!in_kernel && lane == 16)       // the last copy into each activation buffer (an earlier phase of a barrier can no longer be waited for)
             for (uint32_t i = xissued > uint32_t(p.nbuf) ? xissued - p.nbuf : 0; i < xissued; ++i)
                 wait(xfull + 8 * (p.nbuf == 2 ? (i & 1u) : 0u), (p.nbuf == 2 ? i >> 1 : i) & 1u);
+    } else if (STAGER && warp == CTA_WARPS + 1) {
+        {
+        // ---- stager (down product): segment q's activation rows, fp32 in global memory -> staged form in buffer q % nbuf ----
+        const int pass_first = u_begin < u_end ? int(u_begin / row_tiles) : 0;
+        const int nseg = u_begin < u_end ? int((u_end - 1) / row_tiles) - pass_first + 1 : 0;
+        bool ok = true;
+        for (int q = 0; q < nseg && ok; ++q) {
+            const uint32_t b = p.nbuf == 2 ? (uint32_t(q) & 1u) : 0u, use = p.nbuf == 2 ? uint32_t(q) >> 1 : uint32_t(q);
+            if (use > 0 && !__all_sync(0xffffffffu, wait(xempty + 8 * b, (use - 1) & 1u))) { ok = false; break; }   // the consumers are done with the buffer
+            int e, c0;
+            locate(pass_first + q, e, c0);
+            const int nv = min(PASS_TOKENS, counts[e] - c0);
+            const int mine = lane < nv ? perm[offsets[e] + c0 + lane] : -1;
+            for (int col = 0; col < PASS_TOKENS; ++col) {
+                const int a = __shfl_sync(0xffffffffu, mine, col);
+                float inv = 0.f;
+                if (a >= 0) inv = stage_row_f32_lanes(p.x_raw, size_t(a) * K, K, F::BITS, xs + b * xbuf + col * xrow, lane);
+                if (lane == 0) { meta[b].col_a[col] = a; meta[b].col_is[col] = inv; }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(xfull + 8 * b);
+        }
+        if (!ok) { *abort_flag = 1; if (lane == 0) atomicExch(p.plan + PLAN_STATUS, 3); }
+        }
     } else {
         // ---- consumers ----
         const int g = lane >> 2, t = lane & 3;
@@ -501,7 +532,7 @@ int g_drop_tile = -1;                 // test hooks (b2moe_harness_wait_probe, b
 bool g_skip_stage = false;
 uint32_t g_wait_limit = WAIT_LIMIT;
 
-template <uint32_t T, int MODE>
+template <uint32_t T, int MODE, bool STAGER = false>
 int32_t launch_dec4(Dec4Args a, cudaStream_t s) {
     const int sms = sm_count(), k = a.k_tiles * 256;
     if (sms <= 0) return B2MOE_ERR_CUDA;
@@ -516,10 +547,10 @@ int32_t launch_dec4(Dec4Args a, cudaStream_t s) {
         if (per_block <= CTA_WARPS / ks && kslots % ks == 0 && g_ksplit_max >= ks &&
             dec4_smem<T>(k, a.nbuf, a.stages, a.slot_tiles) + RED_BYTES <= SMEM_LIMIT) { a.ksplit = ks; break; }
     const size_t smem = dec4_smem<T>(k, a.nbuf, a.stages, a.slot_tiles) + (a.ksplit > 1 ? RED_BYTES : 0);
-    if (cudaFuncSetAttribute(dec4_k<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
+    if (cudaFuncSetAttribute(dec4_k<T, MODE, STAGER>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
     a.wait_limit = g_wait_limit;
     a.drop_tile = g_drop_tile;
-    launch_overlapped(dec4_k<T, MODE>, dim3(sms), dim3(THREADS), smem, s, a);       // every block takes an equal share of the (pass, row tile) jobs
+    launch_overlapped(dec4_k<T, MODE, STAGER>, dim3(sms), dim3(threads_of<STAGER>()), smem, s, a);       // every block takes an equal share of the (pass, row tile) jobs
     return launch_status();
 }
 
@@ -554,7 +585,14 @@ int32_t down_t(const b2moe_bank * down, const b2moe_bank * sd, const float * act
                float * y, void * ws, int max_active, cudaStream_t s) {
     const int rows_x = n * topk + shared_tokens, k = down->cols;
     Dec4Args a{};
-    if (int32_t rc = stage<T>(a, act, B2MOE_F32, rows_x, k, ws, s)) return rc;
+    // A launch of a few jobs per block is a chain of latencies: its rows are staged inside the kernel by a warp of their own
+    // (one launch less). A full launch keeps the staging kernel: measured at 64 tokens the in-kernel staging costs 11 us more
+    // than the launch it saves (the staging warp shares a scheduler with five busy warps).
+    const long long jobs_bound = (long long)(n * topk + (shared_tokens + PASS_TOKENS - 1) / PASS_TOKENS) * ((down->rows + 15) / 16);
+    const int sms = sm_count();
+    const bool in_kernel = sms > 0 && jobs_bound <= 24LL * sms && !g_skip_stage;
+    if (in_kernel) a.x_raw = act;
+    else if (int32_t rc = stage<T>(a, act, B2MOE_F32, rows_x, k, ws, s)) return rc;
     a.w0 = static_cast<const uint8_t *>(down->data);
     if (shared_tokens) a.s0 = static_cast<const uint8_t *>(sd->data);
     a.bank_bytes = b2moe_bank_bytes(down->type, down->rows, down->cols);
@@ -562,7 +600,7 @@ int32_t down_t(const b2moe_bank * down, const b2moe_bank * sd, const float * act
     a.rows = down->rows; a.k_tiles = k / 256; a.experts = down->experts; a.topk = topk; a.A = n * topk;
     a.shared_rows = shared_tokens;
     a.passes_bound = n * topk + (shared_tokens + PASS_TOKENS - 1) / PASS_TOKENS;
-    return launch_dec4<T, 1>(a, s);
+    return in_kernel ? launch_dec4<T, 1, true>(a, s) : launch_dec4<T, 1>(a, s);
 }
 
 }  // namespace
