@@ -169,7 +169,6 @@ struct Dec4Args {
     int * plan;
     float * out;                             // [A + shared][rows]
     int rows, k_tiles, experts, topk, A, nbuf, stages, slot_tiles;
-    int shared_rows;                         // rows of the always-on expert in the plan (its count: known to the host)
     int passes_bound;                        // host: an upper bound of the plan's pass count, from the call's shape
     int ksplit;                              // consumer warps that share one row job, each taking 1 / ksplit of its columns (1, 2 or 4)
     uint32_t wait_limit;
@@ -230,7 +229,7 @@ __global__ void __launch_bounds__(bound_threads<STAGER>(), 1) dec4_k(const Dec4A
     __syncthreads();
 
     const int * counts = p.plan + PLAN_HDR, * offsets = counts + e1, * active = offsets + e1 + 1, * perm = active + e1;
-    const int * passes = perm + p.A + p.shared_rows;
+    const int * passes = perm + p.A + counts[p.experts];     // the plan's own count of always-on rows (a range of the tokens under expert parallelism)
     const int na = p.plan[PLAN_NACTIVE], row_tiles = (p.rows + 15) >> 4;
     // the block's share of the launch: jobs [u_begin, u_end) of the pass-major list of (pass, row tile) jobs; it walks the
     // share as segments = runs of row tiles [r0, r1) of one pass
@@ -576,7 +575,6 @@ int32_t gateup_t(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_ban
     a.bank_bytes = b2moe_bank_bytes(gate->type, gate->rows, gate->cols);
     a.plan = const_cast<int *>(plan); a.out = act;
     a.rows = gate->rows; a.k_tiles = k / 256; a.experts = gate->experts; a.topk = topk; a.A = n * topk;
-    a.shared_rows = shared_tokens;
     a.passes_bound = n * topk + (shared_tokens + PASS_TOKENS - 1) / PASS_TOKENS;
     return launch_dec4<T, 0>(a, s);
 }
@@ -598,7 +596,6 @@ int32_t down_t(const b2moe_bank * down, const b2moe_bank * sd, const float * act
     a.bank_bytes = b2moe_bank_bytes(down->type, down->rows, down->cols);
     a.plan = const_cast<int *>(plan); a.out = y;
     a.rows = down->rows; a.k_tiles = k / 256; a.experts = down->experts; a.topk = topk; a.A = n * topk;
-    a.shared_rows = shared_tokens;
     a.passes_bound = n * topk + (shared_tokens + PASS_TOKENS - 1) / PASS_TOKENS;
     return in_kernel ? launch_dec4<T, 1, true>(a, s) : launch_dec4<T, 1>(a, s);
 }
