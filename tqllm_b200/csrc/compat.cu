@@ -23,7 +23,7 @@ __global__ void groups_head_k(const int * __restrict__ counts_in, int experts, i
     for (int x = threadIdx.x; x < experts; x += blockDim.x) counts[x] = max(0, min(counts_in[x], capacity));
     if (threadIdx.x == 0) counts[experts] = 0;
     __syncthreads();
-    if (threadIdx.x < 32) finish_plan(plan, counts, offsets, active, perm + assignments, e1, threadIdx.x);
+    if (threadIdx.x < 32) finish_plan(plan, counts, offsets, active, offsets, active, perm + assignments, e1, threadIdx.x);
 }
 __global__ void groups_perm_k(const int * __restrict__ groups, int experts, int capacity, int * __restrict__ plan) {
     const int e1 = experts + 1;

@@ -51,14 +51,43 @@ __device__ inline float stage_row_to(const void * x, int dtype, size_t first, in
     for (int b = 0; b < (k >> 5); ++b) stage_sub_block(x, dtype, first, b, scale, orow, recs, lane);
     return inv;
 }
-// The same row with a lane per sub-block (32 consecutive columns each): no cross-lane step except the row maximum, for the
-// warp that stages rows inside the down product while the consumer warps take most issue slots. fp32 rows, k a multiple of 32.
-__device__ inline float stage_row_f32_lanes(const float * __restrict__ x, size_t first, int k, int bits, uint8_t * orow, int lane) {
-    const float4 * row4 = reinterpret_cast<const float4 *>(x + first);
+// The same row with a lane per sub-block (32 consecutive columns each): no cross-lane step except the row maximum, so a warp
+// that shares its scheduler with busy warps still stages a row in about a microsecond. Rows must start on 16 bytes.
+template <int DT> struct RowLoad;
+template <> struct RowLoad<B2MOE_F32> {      // eight columns from two 16-byte loads
+    __device__ static void eight(const void * x, size_t first, int i, float (&v)[8]) {
+        const float4 * p = reinterpret_cast<const float4 *>(static_cast<const float *>(x) + first) + 2 * i;
+        const float4 a = p[0], b = p[1];
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+};
+template <> struct RowLoad<B2MOE_BF16> {
+    __device__ static void eight(const void * x, size_t first, int i, float (&v)[8]) {
+        const uint4 q = (reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(x) + first))[i];
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { v[2 * j] = __uint_as_float(w[j] << 16); v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u); }
+    }
+};
+template <> struct RowLoad<B2MOE_F16> {
+    __device__ static void eight(const void * x, size_t first, int i, float (&v)[8]) {
+        const uint4 q = (reinterpret_cast<const uint4 *>(static_cast<const __half *>(x) + first))[i];
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[j]));
+            v[2 * j] = f.x; v[2 * j + 1] = f.y;
+        }
+    }
+};
+template <int DT>
+__device__ inline float stage_row_lanes(const void * __restrict__ x, size_t first, int k, int bits, uint8_t * orow, int lane) {
     float mx = 0.f;
-    for (int j = lane; j < (k >> 2); j += 32) {
-        const float4 v = row4[j];
-        mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+    for (int i = lane; i < (k >> 3); i += 32) {
+        float v[8];
+        RowLoad<DT>::eight(x, first, i, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(v[j]));
     }
     for (int d = 16; d; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
     float inv;
@@ -68,13 +97,19 @@ __device__ inline float stage_row_f32_lanes(const float * __restrict__ x, size_t
         uint32_t hi[8], lo[8];                      // bytes of columns 4 i .. 4 i + 3
         int sum = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float4 v = row4[b * 8 + i];
-            const int a = __float2int_rn(v.x * scale), c = __float2int_rn(v.y * scale), d = __float2int_rn(v.z * scale), e = __float2int_rn(v.w * scale);
-            sum += a + c + d + e;
-            // byte 1 (high) and byte 0 (low) of the four values, in column order
-            hi[i] = __byte_perm(__byte_perm(uint32_t(a), uint32_t(c), 0x0051), __byte_perm(uint32_t(d), uint32_t(e), 0x0051), 0x5410);
-            lo[i] = __byte_perm(__byte_perm(uint32_t(a), uint32_t(c), 0x0040), __byte_perm(uint32_t(d), uint32_t(e), 0x0040), 0x5410);
+        for (int i = 0; i < 4; ++i) {
+            float v[8];
+            RowLoad<DT>::eight(x, first, b * 4 + i, v);
+            int q[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { q[j] = __float2int_rn(v[j] * scale); sum += q[j]; }
+            // byte 1 (high) and byte 0 (low) of four values, in column order
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t a = uint32_t(q[4 * h]), c = uint32_t(q[4 * h + 1]), d = uint32_t(q[4 * h + 2]), e = uint32_t(q[4 * h + 3]);
+                hi[2 * i + h] = __byte_perm(__byte_perm(a, c, 0x0051), __byte_perm(d, e, 0x0051), 0x5410);
+                lo[2 * i + h] = __byte_perm(__byte_perm(a, c, 0x0040), __byte_perm(d, e, 0x0040), 0x5410);
+            }
         }
         uint4 * sb = reinterpret_cast<uint4 *>(orow + size_t(b) * 64);
 #pragma unroll
@@ -85,9 +120,14 @@ __device__ inline float stage_row_f32_lanes(const float * __restrict__ x, size_t
     }
     return inv;
 }
+__device__ inline float stage_row_lanes(const void * x, int dtype, size_t first, int k, int bits, uint8_t * orow, int lane) {
+    if (dtype == B2MOE_F32) return stage_row_lanes<B2MOE_F32>(x, first, k, bits, orow, lane);
+    if (dtype == B2MOE_BF16) return stage_row_lanes<B2MOE_BF16>(x, first, k, bits, orow, lane);
+    return stage_row_lanes<B2MOE_F16>(x, first, k, bits, orow, lane);
+}
 // row `row` of x[.][k] into the array of staged rows `out`, its inverse scale into inv_scale[row]
 __device__ inline void stage_row_warp(const void * x, int dtype, int row, int k, int bits, uint8_t * out, float * inv_scale, int lane) {
-    const float inv = stage_row_to(x, dtype, size_t(row) * k, k, bits, out + size_t(row) * staged_row_bytes(k), lane);
+    const float inv = stage_row_lanes(x, dtype, size_t(row) * k, k, bits, out + size_t(row) * staged_row_bytes(k), lane);
     if (lane == 0) inv_scale[row] = inv;
 }
 

@@ -47,7 +47,7 @@ __global__ void dispatch_scan_k(int * __restrict__ hist, int chunks, int e, int 
     }
     if (threadIdx.x == 0) counts[e] = shared_tokens;
     __syncthreads();
-    if (threadIdx.x < 32) finish_plan(plan, counts, offsets, active, active + e1 + A + shared_tokens, e1, threadIdx.x);
+    if (threadIdx.x < 32) finish_plan(plan, counts, offsets, active, offsets, active, active + e1 + A + shared_tokens, e1, threadIdx.x);
 }
 __global__ void dispatch_scatter_k(const int * __restrict__ ids, int A, int e, int shared_first, int shared_tokens, int * __restrict__ hist,
                                    int * __restrict__ plan) {
@@ -114,7 +114,7 @@ extern "C" B2MOE_API int32_t b2moe_dispatch_range(const int32_t * ids, int32_t n
     const int A = n * topk;
     cudaStream_t s = as_stream(stream);
     if (small_path(experts, A)) {
-        launch_overlapped(dispatch_small_k, dim3(1), dim3(1024), size_t(32) * experts * sizeof(unsigned short), s, ids, A, experts, shared_first, shared_count, plan);
+        launch_overlapped(dispatch_small_k, dim3(1), dim3(1024), dispatch_small_smem(32, experts), s, ids, A, experts, shared_first, shared_count, plan);
         return launch_status();
     }
     const size_t need = b2moe_dispatch_workspace_bytes(experts, A);

@@ -364,7 +364,7 @@ __global__ void __launch_bounds__(bound_threads<STAGER>(), 1) dec4_k(const Dec4A
             for (int col = 0; col < PASS_TOKENS; ++col) {
                 const int a = __shfl_sync(0xffffffffu, mine, col);
                 float inv = 0.f;
-                if (a >= 0) inv = stage_row_f32_lanes(p.x_raw, size_t(a) * K, K, F::BITS, xs + b * xbuf + col * xrow, lane);
+                if (a >= 0) inv = stage_row_lanes<B2MOE_F32>(p.x_raw, size_t(a) * K, K, F::BITS, xs + b * xbuf + col * xrow, lane);
                 if (lane == 0) { meta[b].col_a[col] = a; meta[b].col_is[col] = inv; }
             }
             __syncwarp();
