@@ -275,25 +275,27 @@ __global__ void __launch_bounds__(bound_threads<STAGER>(), 1) dec4_k(const Dec4A
         const uint32_t my_full = full0 + 8 * w * MAX_STAGES, my_empty = empty0 + 8 * w * MAX_STAGES, my_ring = smem_addr(ring) + uint32_t(w) * S * SLOT;
         uint32_t slot = 0, issued = 0, xissued = 0;
         bool ok = true;
-        auto stage_x = [&](int pass, uint32_t idx) {       // rows of the item with running index idx -> buffer idx % nbuf
+        // known = the caller has already located this pass (e_in, c0_in)
+        auto stage_x = [&](int pass, uint32_t idx, bool known = false, int e_in = 0, int c0_in = 0) {       // rows of the item with running index idx -> buffer idx % nbuf
             const uint32_t b = p.nbuf == 2 ? (idx & 1u) : 0u, use = p.nbuf == 2 ? idx >> 1 : idx;
             if (use > 0 && !wait(xempty + 8 * b, (use - 1) & 1u)) ok = false;     // the consumers are done with the buffer's previous rows
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) return;
-            int e, c0;
-            locate(pass, e, c0);
+            int e = e_in, c0 = c0_in;
+            if (!known) locate(pass, e, c0);
             const int nv = min(PASS_TOKENS, counts[e] - c0);
             const int col = lane - 16;                                        // lanes 16 .. 23: one token column each
             int a = -1;
             if (col >= 0 && col < PASS_TOKENS) {
                 if (col < nv) a = perm[offsets[e] + c0 + col];
+                // the row's copy leaves first; its bytes count against the phase that lane 16's arrival below opens (the
+                // transaction count may run ahead of the expectation; the phase cannot complete before that arrival)
+                if (a >= 0) bulk_g2s(xs0 + b * xbuf + col * xrow, p.x + x_row(a) * xglob, xglob, xfull + 8 * b);
                 meta[b].col_a[col] = a;
                 meta[b].col_is[col] = a >= 0 ? p.inv_scale[x_row(a)] : 0.f;
             }
             __syncwarp();                                                     // the columns are written before lane 16's arrival publishes them
             if (lane == 16) mbar_expect_tx(xfull + 8 * b, uint32_t(nv) * xglob);
-            __syncwarp();
-            if (a >= 0) bulk_g2s(xs0 + b * xbuf + col * xrow, p.x + x_row(a) * xglob, xglob, xfull + 8 * b);
             ++xissued;
         };
         int pass, r0, r1;
@@ -328,7 +330,7 @@ __global__ void __launch_bounds__(bound_threads<STAGER>(), 1) dec4_k(const Dec4A
                         slot = slot + 1 == uint32_t(S) ? 0 : slot + 1;
                     }
                     ok = __all_sync(0xffffffffu, ok);
-                    if (!in_kernel && !first_staged) { stage_x(pass, 0); first_staged = true; }
+                    if (!in_kernel && !first_staged) { stage_x(pass, 0, true, e, c0); first_staged = true; }
                     // once every consumer is S slots into this segment, the previous segment's buffer is free: bring the next one's rows
                     if (!in_kernel && !next_staged && in_seg == S) { stage_x(npass, idx + 1); next_staged = true; }
                 }
