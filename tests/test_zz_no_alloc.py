@@ -26,12 +26,20 @@ def down_both_ways(shape, experts, tokens, seed):
     act = moe.expert_gateup_swiglu(dev.gate, dev.up, xd, plan, dev.sh[0], dev.sh[1])
     want = moe.expert_down(dev.down, act, plan, dev.sh[2])
     got = torch.zeros_like(want)
-    before = torch.cuda.memory_allocated()
+    # one call first so that the module's one-time look-up of the array is behind us; then the driver's own figure of free
+    # device memory (which also sees an allocation made behind torch's back) must not move over a second call
+    rc = lib.b2moe_expert_down_static(C.byref(dev.down.c), C.byref(dev.sh[2].c), act.data_ptr(), plan.buf.data_ptr(), tokens, shape.topk,
+                                      tokens, got.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == capi.OK, capi.status_string(rc)
+    torch.cuda.synchronize()
+    got.zero_()
+    before, free_before = torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]
     rc = lib.b2moe_expert_down_static(C.byref(dev.down.c), C.byref(dev.sh[2].c), act.data_ptr(), plan.buf.data_ptr(), tokens, shape.topk,
                                       tokens, got.data_ptr(), torch.cuda.current_stream().cuda_stream)
     assert rc == capi.OK, capi.status_string(rc)
     torch.cuda.synchronize()
     assert torch.cuda.memory_allocated() == before
+    assert torch.cuda.mem_get_info()[0] == free_before
     assert int(plan.buf[3]) == 0
     return got.cpu().numpy(), want.cpu().numpy()
 

@@ -155,7 +155,7 @@ struct Iq3sArgs {
     int rows, k_tiles, experts, topk, A, rpw, nbuf;
 };
 
-constexpr size_t TABLE_BYTES = 512 * 16 * 8, RING_BYTES = size_t(CTA_WARPS) * STAGES * TILE, BAR_BYTES = (CTA_WARPS * STAGES + 2) * 8;
+constexpr size_t TABLE_BYTES = 512 * 16 * 8, RING_BYTES = size_t(CTA_WARPS) * STAGES * TILE, BAR_BYTES = (CTA_WARPS * STAGES + 2) * 8 + 16;   // the ring barriers, two activation barriers, the block's abort flag
 inline size_t xs_bytes(int k, int nterm, int nbuf) { return size_t(nbuf) * 8 * nterm * (size_t(k) * 2 + XPAD); }
 
 template <int MODE, int NTERM, int OP>
@@ -188,7 +188,8 @@ __global__ void __launch_bounds__(CTA_WARPS * 32, 1) iq3s_grouped_k(Iq3sArgs p) 
     const uint32_t bar0 = smem_addr(bars + warp * STAGES), ring0 = smem_addr(my_ring);
     const uint32_t xbar = smem_addr(bars + CTA_WARPS * STAGES), xs0 = smem_addr(xs);
     if (lane == 0) for (int s = 0; s < STAGES; ++s) mbar_init(bar0 + 8 * s, 1);
-    if (threadIdx.x == 0) { mbar_init(xbar, 1); mbar_init(xbar + 8, 1); }
+    volatile int * abort_flag = reinterpret_cast<volatile int *>(bars + CTA_WARPS * STAGES + 2);   // set by a warp whose bounded wait ran out
+    if (threadIdx.x == 0) { mbar_init(xbar, 1); mbar_init(xbar + 8, 1); *abort_flag = 0; }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
 
@@ -217,18 +218,20 @@ __global__ void __launch_bounds__(CTA_WARPS * 32, 1) iq3s_grouped_k(Iq3sArgs p) 
     const int ntiles = p.k_tiles * NMAT;
     uint32_t filled = 0, drained = 0;      // tiles issued into / taken out of this warp's ring since launch
     bool alive = true;
-    if (threadIdx.x == 0 && int(blockIdx.x) < n_items) stage_x(blockIdx.x, 0);
+    uint32_t xissued = 0;                  // thread 0: activation stagings issued (their copies must land before the block leaves)
+    if (threadIdx.x == 0 && int(blockIdx.x) < n_items) { stage_x(blockIdx.x, 0); ++xissued; }
 
     int iter = 0;
     for (int it = blockIdx.x; it < n_items; it += gridDim.x, ++iter) {
         const int b = p.nbuf == 2 ? (iter & 1) : 0;
         __syncthreads();                     // every warp is done with the previous item's activation buffer
+        if (*abort_flag) break;              // uniform over the block after the barrier: nobody stages or multiplies any more
         if (threadIdx.x == 0) {
-            if (p.nbuf == 2) { if (it + int(gridDim.x) < n_items) stage_x(it + gridDim.x, b ^ 1); }
-            else if (iter > 0) stage_x(it, 0);
+            if (p.nbuf == 2) { if (it + int(gridDim.x) < n_items) { stage_x(it + gridDim.x, b ^ 1); ++xissued; } }
+            else if (iter > 0) { stage_x(it, 0); ++xissued; }
         }
         if (!alive) continue;
-        if (!__all_sync(0xffffffffu, mbar_wait(xbar + 8 * b, (p.nbuf == 2 ? iter >> 1 : iter) & 1u))) { alive = false; continue; }
+        if (!__all_sync(0xffffffffu, mbar_wait(xbar + 8 * b, (p.nbuf == 2 ? iter >> 1 : iter) & 1u))) { alive = false; *abort_flag = 1; continue; }
         int e, c0;
         locate(it / groups, e, c0);
         const int grp = it % groups, cnt = counts[e], off = offsets[e], nv = min(PASS_TOKENS, cnt - c0);
@@ -259,7 +262,7 @@ __global__ void __launch_bounds__(CTA_WARPS * 32, 1) iq3s_grouped_k(Iq3sArgs p) 
 #pragma unroll
                 for (int m = 0; m < NMAT; ++m) {
                     const uint32_t s = drained % STAGES;
-                    if (!__all_sync(0xffffffffu, mbar_wait(bar0 + 8 * s, (drained / STAGES) & 1u))) { alive = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(bar0 + 8 * s, (drained / STAGES) & 1u))) { alive = false; *abort_flag = 1; break; }
                     TileRegs cur;
                     read_tile(cur, my_ring + s * TILE, lane);
                     ++drained;
@@ -319,9 +322,15 @@ __global__ void __launch_bounds__(CTA_WARPS * 32, 1) iq3s_grouped_k(Iq3sArgs p) 
         }
     }
     if (!alive) {                             // a wait ran out: report it and let the copies in flight land before leaving
+        *abort_flag = 1;
         if (lane == 0) atomicExch(p.plan + PLAN_STATUS, 1);
         for (; drained < filled; ++drained) mbar_wait(bar0 + 8 * (drained % STAGES), (drained / STAGES) & 1u);
     }
+    if (threadIdx.x == 0 && *abort_flag) {    // the last staging into each activation buffer (bounded waits; after a clean run they were consumed)
+        const uint32_t nb = uint32_t(p.nbuf);
+        for (uint32_t i = xissued > nb ? xissued - nb : 0; i < xissued; ++i) mbar_wait(xbar + 8 * (nb == 2 ? (i & 1u) : 0u), (nb == 2 ? i >> 1 : i) & 1u);
+    }
+    __syncthreads();                          // nobody leaves while a copy into the block's shared memory may be in flight
 }
 
 int sm_count() {
