@@ -206,17 +206,32 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
                 if (NMAT == 2) rs[NMAT - 1] = (a1 && row < p.rows) ? a1[ai] : 1.f;
             }
             const uint32_t taddr = tmem + (uint32_t(32 * q) << 16) + ab * (NMAT * G_NT);
-            for (int c = 0; c < im.nv; c += 16) {
-                uint32_t g[16], u[16];
-                tmem_ld16(taddr + c, g);
-                if (NMAT == 2) tmem_ld16(taddr + G_NT + c, u);
-                tmem_ld_wait();
-                if (row < p.rows) {
+            // the item's assignments and their activation scales, 32 per round in registers: the stores below may alias any
+            // global array as far as the compiler knows, so loads inside the token loop would each wait for the one before
+            int a_of[G_NT / 32];
+            float is_of[G_NT / 32];
+#pragma unroll
+            for (int i = 0; i < G_NT / 32; ++i) {
+                const int idx = 32 * i + lane;
+                a_of[i] = idx < im.nv ? perm[im.off + im.c0 + idx] : -1;
+                is_of[i] = a_of[i] >= 0 ? p.inv_scale[MODE == 0 ? (a_of[i] < p.A ? a_of[i] / p.topk : a_of[i] - p.A) : a_of[i]] : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < G_NT / 32; ++i) {
+                if (32 * i >= im.nv) break;
+#pragma unroll
+                for (int c2 = 0; c2 < 32; c2 += 16) {
+                    const int c = 32 * i + c2;
+                    if (c >= im.nv) break;
+                    uint32_t g[16], u[16];
+                    tmem_ld16(taddr + c, g);
+                    if (NMAT == 2) tmem_ld16(taddr + G_NT + c, u);
+                    tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        if (c + j < im.nv) {
-                            const int a = perm[im.off + im.c0 + c + j];
-                            const float is = p.inv_scale[MODE == 0 ? (a < p.A ? a / p.topk : a - p.A) : a];
+                        const int a = __shfl_sync(0xffffffffu, a_of[i], c2 + j);
+                        const float is = __shfl_sync(0xffffffffu, is_of[i], c2 + j);
+                        if (a >= 0 && row < p.rows) {
                             const float gv = __uint_as_float(g[j]) * (is * rs[0]);
                             p.out[size_t(a) * p.rows + row] = MODE == 0 ? (gv / (1.f + expf(-gv))) * (__uint_as_float(u[j]) * (is * rs[NMAT - 1])) : gv;
                         }
