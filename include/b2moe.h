@@ -231,6 +231,13 @@ B2MOE_API int32_t b2moe_combine(const float * y, const int32_t * ids, const floa
                       int32_t topk, int32_t hidden, int32_t shared_tokens, void * out, int32_t out_dtype,
                       b2moe_stream stream);
 
+/* The combine with the layer's skip connection fused (the residual add the engines do right after the MoE block,
+ * src/models/qwen/qwen35/qwen35_forward.cpp:1113 add_sumsq, src/models/qwen/qwen4exp/fn_prefill.cpp:279-285): out[t] =
+ * residual[t] + the weighted sum. residual is [n][hidden] of out_dtype and may be the out buffer itself. */
+B2MOE_API int32_t b2moe_combine_residual(const float * y, const int32_t * ids, const float * weights, const float * shared_weights,
+                               const void * residual, int32_t n, int32_t topk, int32_t hidden, int32_t shared_tokens, void * out,
+                               int32_t out_dtype, b2moe_stream stream);
+
 /* ---- expert parallelism --------------------------------------------------------------------------------------
  * Rank r of G owns the contiguous experts [first_expert, first_expert + local_experts); tokens are data-parallel and
  * router weights replicated. Per layer: all ranks exchange their activation rows and routed ids (NCCL, host-driven),
@@ -362,6 +369,9 @@ typedef struct b2moe_layer_ws {
 B2MOE_API int32_t b2moe_layer_workspace(const b2moe_layer * layer, int32_t n, b2moe_layer_ws * ws);
 B2MOE_API int32_t b2moe_layer_forward(const b2moe_layer * layer, const void * x, int32_t x_dtype, int32_t n, void * out,
                             int32_t out_dtype, void * workspace, size_t workspace_bytes, b2moe_stream stream);
+/* b2moe_layer_forward with the skip connection: out = residual + layer(x) (b2moe_combine_residual as its last launch). */
+B2MOE_API int32_t b2moe_layer_forward_residual(const b2moe_layer * layer, const void * x, int32_t x_dtype, int32_t n, const void * residual,
+                                     void * out, int32_t out_dtype, void * workspace, size_t workspace_bytes, b2moe_stream stream);
 
 #ifdef __cplusplus
 }

@@ -145,6 +145,24 @@ def test_layer_loaded_from_a_gguf_file_equals_the_layer_loaded_from_its_raw_rows
     assert torch.equal(half.gate.data, full.gate.data[4 * per:]) and torch.equal(half.router_w, full.router_w[4:])
 
 
+@pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16))
+def test_layer_with_fused_residual(dtype):
+    """out = residual + layer(x) in the combine's pass: equals the two steps done apart, also in place"""
+    from tqllm_b200 import moe
+    shape = synth.CONFIGS["c2"]
+    layer, x = layer_inputs(shape, 16, 9, 5)
+    dev = moe.MoeLayer.from_synth(layer, experts=16)
+    xd = x.cuda()
+    plain = dev.forward(xd, out_dtype=torch.float32)
+    res = torch.randn(9, shape.hidden, device="cuda").to(dtype)
+    want = (res.float() + plain).to(dtype)
+    got = dev.forward(xd, residual=res)
+    assert got.dtype == dtype and torch.equal(got, want)
+    buf = res.clone()
+    dev.forward(xd, out=buf, residual=buf)
+    assert torch.equal(buf, want)
+
+
 def test_step_by_step_equals_layer_forward(orc):
     """the separate entry points chained by hand give the bits of b2moe_layer_forward"""
     from tqllm_b200 import moe

@@ -90,6 +90,7 @@ SIGNATURES = {
     "b2moe_static_scratch_bytes": (_sz, []),
     "b2moe_expert_down_static": (_i32, [C.POINTER(Bank)] * 2 + [_vp, _vp, _i32, _i32, _i32, _vp, _vp]),
     "b2moe_combine": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _i32, _vp]),
+    "b2moe_combine_residual": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _i32, _vp]),
     "b2moe_gguf_open": (_i32, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "b2moe_gguf_close": (None, [_vp]),
     "b2moe_gguf_tensor_count": (_i32, [_vp]),
@@ -109,6 +110,7 @@ SIGNATURES = {
     "b2moe_harness_launches": (C.c_uint64, []),
     "b2moe_layer_workspace": (_i32, [C.POINTER(Layer), _i32, C.POINTER(LayerWs)]),
     "b2moe_layer_forward": (_i32, [C.POINTER(Layer), _vp, _i32, _i32, _vp, _i32, _vp, _sz, _vp]),
+    "b2moe_layer_forward_residual": (_i32, [C.POINTER(Layer), _vp, _i32, _i32, _vp, _vp, _i32, _vp, _sz, _vp]),
 }
 
 if not os.path.isfile(LIB_PATH):

@@ -211,8 +211,8 @@ extern "C" B2MOE_API int32_t b2moe_layer_workspace(const b2moe_layer * L, int32_
     return B2MOE_OK;
 }
 
-extern "C" B2MOE_API int32_t b2moe_layer_forward(const b2moe_layer * L, const void * x, int32_t x_dtype, int32_t n, void * out,
-                                       int32_t out_dtype, void * workspace, size_t workspace_bytes, b2moe_stream stream) {
+static int32_t layer_forward(const b2moe_layer * L, const void * x, int32_t x_dtype, int32_t n, const void * residual, void * out,
+                             int32_t out_dtype, void * workspace, size_t workspace_bytes, b2moe_stream stream) {
     b2moe_layer_ws ws;
     if (int32_t rc = b2moe_layer_workspace(L, n, &ws)) return rc;
     if (!x || !out || !workspace || !L->router_w) return B2MOE_ERR_NULL;
@@ -256,5 +256,17 @@ extern "C" B2MOE_API int32_t b2moe_layer_forward(const b2moe_layer * L, const vo
     if (int32_t rc = expert_gateup(&L->gate, &L->up, &L->sh_gate, &L->sh_up, x, x_dtype, plan, n, L->topk, sh, act, es, es_bytes, stream, x_staged))
         return rc;
     if (int32_t rc = b2moe_expert_down(&L->down, &L->sh_down, act, plan, n, L->topk, sh, y, es, es_bytes, stream)) return rc;
+    if (residual) return b2moe_combine_residual(y, nullptr, weights, gated_shared ? shw : nullptr, residual, n, L->topk, L->hidden, sh, out, out_dtype, stream);
     return b2moe_combine(y, nullptr, weights, gated_shared ? shw : nullptr, n, L->topk, L->hidden, sh, out, out_dtype, stream);
+}
+
+extern "C" B2MOE_API int32_t b2moe_layer_forward(const b2moe_layer * L, const void * x, int32_t x_dtype, int32_t n, void * out,
+                                       int32_t out_dtype, void * workspace, size_t workspace_bytes, b2moe_stream stream) {
+    return layer_forward(L, x, x_dtype, n, nullptr, out, out_dtype, workspace, workspace_bytes, stream);
+}
+// the layer with its skip connection: out = residual + MoE(x); residual [n][hidden] of out_dtype, may be the out buffer
+extern "C" B2MOE_API int32_t b2moe_layer_forward_residual(const b2moe_layer * L, const void * x, int32_t x_dtype, int32_t n, const void * residual,
+                                                void * out, int32_t out_dtype, void * workspace, size_t workspace_bytes, b2moe_stream stream) {
+    if (!residual) return B2MOE_ERR_NULL;
+    return layer_forward(L, x, x_dtype, n, residual, out, out_dtype, workspace, workspace_bytes, stream);
 }

@@ -270,13 +270,19 @@ class MoeLayer:
         self.ws = torch.zeros(v.total, dtype=torch.uint8, device=self.device)
         self.ws_view, self.ws_tokens = v, n
 
-    def forward(self, x: torch.Tensor, out: torch.Tensor | None = None, out_dtype=torch.float32) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, out: torch.Tensor | None = None, out_dtype=torch.float32, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """out = layer(x), or residual + layer(x) when a residual [n][hidden] of the output's dtype is given (it may be `out`)"""
         n = x.shape[0]
         self.reserve(n)
         if out is None:
-            out = torch.empty(n, self.shape.hidden, dtype=out_dtype, device=self.device)
-        check(lib.b2moe_layer_forward(C.byref(self.c), x.data_ptr(), _DT[x.dtype], n, out.data_ptr(), _DT[out.dtype],
-                                      self.ws.data_ptr(), self.ws.numel(), _stream()), "b2moe_layer_forward")
+            out = torch.empty(n, self.shape.hidden, dtype=out_dtype if residual is None else residual.dtype, device=self.device)
+        if residual is None:
+            check(lib.b2moe_layer_forward(C.byref(self.c), x.data_ptr(), _DT[x.dtype], n, out.data_ptr(), _DT[out.dtype],
+                                          self.ws.data_ptr(), self.ws.numel(), _stream()), "b2moe_layer_forward")
+        else:
+            assert residual.dtype == out.dtype and residual.shape == out.shape
+            check(lib.b2moe_layer_forward_residual(C.byref(self.c), x.data_ptr(), _DT[x.dtype], n, residual.data_ptr(), out.data_ptr(),
+                                                   _DT[out.dtype], self.ws.data_ptr(), self.ws.numel(), _stream()), "b2moe_layer_forward_residual")
         return out
 
     def artefacts(self) -> dict:
