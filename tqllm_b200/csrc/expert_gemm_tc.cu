@@ -20,6 +20,8 @@
 // gave 3e-2 of the output RMS as the largest error, fp16 stays below the layer tolerance). An activation row is
 // multiplied by 2^e so that its largest magnitude lies in [2^14, 2^15) and rounded to fp16: exact for bf16 inputs down
 // to 2^-29 of the row maximum; the epilogue multiplies the sums (fp32) by 2^-e.
+#include <type_traits>
+
 #include "common.cuh"
 #include "formats.cuh"
 #include "gemm_decode.cuh"
@@ -327,26 +329,28 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
 #pragma unroll
                     for (int m = 0; m < NMAT; ++m) pre[m] = gdec::Dec<T>::prep(my_raw + (slot * NMAT + m) * CB, lane, half);
                 }
-                for (int j = 0; j < steps; ++j, ++gk) {
+                // the (up to) four 64-column steps of the chunk, written out so that every step is straight-line code with its
+                // column offset a constant and the lane's row / table / scale addresses computed once per chunk
+                auto one_step = [&](auto J) {
+                    constexpr int j = decltype(J)::value;
+                    if (j >= steps || !ok) return;
                     const uint32_t sa = gk % A_STAGES;
-                    if (gk >= A_STAGES && !__all_sync(0xffffffffu, bar_wait(a_empty + 8 * sa, ((gk / A_STAGES) - 1) & 1u, DEC_BACKOFF))) { ok = false; break; }
+                    if (gk >= A_STAGES && !__all_sync(0xffffffffu, bar_wait(a_empty + 8 * sa, ((gk / A_STAGES) - 1) & 1u, DEC_BACKOFF))) { ok = false; return; }
                     if (live) {
 #pragma unroll
-                        for (int m = 0; m < NMAT; ++m) {
-                            const uint8_t * chunk = my_raw + (slot * NMAT + m) * CB;
-                            uint8_t * dst = a_st + (sa * NMAT + m) * A_MAT + 2 * tw * 128;
-                            switch (j) {
-                                case 0: gdec::Dec<T>::template step<0>(chunk, lane, dst, dec_tab, half, pre[m]); break;
-                                case 1: gdec::Dec<T>::template step<1>(chunk, lane, dst, dec_tab, half, pre[m]); break;
-                                case 2: gdec::Dec<T>::template step<2>(chunk, lane, dst, dec_tab, half, pre[m]); break;
-                                default: gdec::Dec<T>::template step<3>(chunk, lane, dst, dec_tab, half, pre[m]); break;
-                            }
-                        }
+                        for (int m = 0; m < NMAT; ++m)
+                            gdec::Dec<T>::template step<j>(my_raw + (slot * NMAT + m) * CB, lane, a_st + (sa * NMAT + m) * A_MAT + 2 * tw * 128, dec_tab, half, pre[m]);
                     }
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0) bar_arrive(a_full + 8 * sa);
-                }
+                    ++gk;
+                };
+                one_step(std::integral_constant<int, 0>{});
+                one_step(std::integral_constant<int, 1>{});
+                one_step(std::integral_constant<int, 2>{});
+                one_step(std::integral_constant<int, 3>{});
+                if (!ok) break;
                 __syncwarp();                                          // every lane is done with the slot
                 if (live && lane == 0) {
                     bar_arrive(my_empty + 8 * slot);
