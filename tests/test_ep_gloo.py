@@ -39,7 +39,15 @@ def gate_vector(name):
     return torch.randn(256, generator=g) * 0.1
 
 
-def worker(rank, world, port, name, out_dir, a2a=False):
+def skewed_order(E, world):
+    """a placement as b2moe_place_experts gives it for a histogram with one hot expert per contiguous block's start"""
+    from tqllm_b200 import moe
+    counts = np.array([1000 // (1 + (e * 7) % E) for e in range(E)], np.uint64)
+    order, _ = moe.place_experts(counts, world)
+    return order
+
+
+def worker(rank, world, port, name, out_dir, a2a=False, placed=False):
     import sys
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
     from ep_oracle_backend import OracleEpBackend
@@ -47,6 +55,8 @@ def worker(rank, world, port, name, out_dir, a2a=False):
                             timeout=datetime.timedelta(seconds=60))
     shape, E, T = case(name)
     layer = synth.make_layer(shape, 31, "cpu", experts=E)
+    if placed:                                      # the experts stacked in a load-aware order before the rank blocks are cut
+        layer = synth.permute_experts(layer, skewed_order(E, world))
     x = synth.make_tokens(shape, T * world, 31, "cpu")[rank * T:(rank + 1) * T]
     fwd = ep.ep_forward_a2a if a2a else ep.ep_forward
     out = fwd(OracleEpBackend(shape, layer, E, world, rank, gate_vector(name)), ep.TorchComm(), x)
@@ -70,6 +80,26 @@ def test_ep_matches_unsplit_oracle(orc, tmp_path, name, world, a2a):
     got = np.concatenate([np.load(tmp_path / f"out{r}.npy") for r in range(world)])
     rms = np.sqrt((want.astype(np.float64) ** 2).mean())
     assert np.abs(got - want).max() <= 1e-5 * rms        # only the order of the fp32 partial sums differs
+
+
+@pytest.mark.parametrize("a2a", (False, True), ids=("allgather", "alltoall"))
+def test_ep_with_a_load_aware_placement_matches_the_unplaced_layer(orc, tmp_path, a2a):
+    """experts stacked in the order b2moe_place_experts returns, then split over the ranks: the layer's output is that of
+    the layer in its original order (routing only renames the experts)"""
+    name, world = "softmax_shared", 2
+    port = free_port()
+    mp.spawn(worker, args=(world, port, name, str(tmp_path), a2a, True), nprocs=world, join=True)
+    shape, E, T = case(name)
+    assert sorted(skewed_order(E, world).tolist()) == list(range(E)) and not np.array_equal(skewed_order(E, world), np.arange(E))
+    layer = synth.make_layer(shape, 31, "cpu", experts=E)
+    x = synth.make_tokens(shape, T * world, 31, "cpu")
+    want = orc.moe_layer(x=x.float().numpy(), router_w=layer.router_w.numpy(), topk=shape.topk, ff=shape.ff, gating=shape.gating,
+                         norm=shape.norm, scale=shape.scale, types=shape.types, gate=layer.raw[0].numpy(), up=layer.raw[1].numpy(),
+                         down=layer.raw[2].numpy(), experts=E, sel_bias=None,
+                         shared=tuple(t.numpy() for t in layer.shared_raw), shared_gate_vec=None)["out"]
+    got = np.concatenate([np.load(tmp_path / f"out{r}.npy") for r in range(world)])
+    rms = np.sqrt((want.astype(np.float64) ** 2).mean())
+    assert np.abs(got - want).max() <= 1e-5 * rms
 
 
 def test_expert_ranges_partition():
