@@ -174,6 +174,18 @@ B2MOE_API int32_t b2moe_expert_gateup_swiglu(const b2moe_bank * gate, const b2mo
 B2MOE_API int32_t b2moe_expert_down(const b2moe_bank * down, const b2moe_bank * shared_down, const float * act, const int32_t * plan,
                           int32_t n, int32_t topk, int32_t shared_tokens, float * y, void * workspace, size_t workspace_bytes,
                           b2moe_stream stream);
+/* The two products for a caller that knows how many of the n * topk assignments are live (id >= 0). Under expert parallelism a
+ * rank sees every gathered token but owns 1 / G of the experts (the other ids are -1, src/experts/moe.cu:496-503
+ * ep_local_ids); the kernel family is chosen by live assignments per expert, which the plain entry points take as n * topk.
+ * live_assignments is an estimate used for that choice only (0 <= live_assignments <= n * topk); results do not depend on it
+ * beyond the family's rounding. */
+B2MOE_API int32_t b2moe_expert_gateup_swiglu_sparse(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_bank * shared_gate,
+                                          const b2moe_bank * shared_up, const void * x, int32_t x_dtype, const int32_t * plan, int32_t n,
+                                          int32_t topk, int32_t shared_tokens, int64_t live_assignments, float * act, void * workspace,
+                                          size_t workspace_bytes, b2moe_stream stream);
+B2MOE_API int32_t b2moe_expert_down_sparse(const b2moe_bank * down, const b2moe_bank * shared_down, const float * act, const int32_t * plan,
+                                 int32_t n, int32_t topk, int32_t shared_tokens, int64_t live_assignments, float * y, void * workspace,
+                                 size_t workspace_bytes, b2moe_stream stream);
 /* The down product without a workspace argument and without any allocation, for callers that cannot provide
  * scratch (an engine plugin that owns no device memory; code inside a stream capture or another region where
  * cudaMalloc is not allowed). It has no counterpart in the reference. The scratch b2moe_expert_down would take from

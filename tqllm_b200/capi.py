@@ -77,6 +77,8 @@ SIGNATURES = {
     "b2moe_expert_workspace_bytes": (_sz, [_u32, _i32, _i32, _i32]),
     "b2moe_expert_gateup_swiglu": (_i32, [C.POINTER(Bank)] * 4 + [_vp, _i32, _vp, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
     "b2moe_expert_down": (_i32, [C.POINTER(Bank)] * 2 + [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
+    "b2moe_expert_down_sparse": (_i32, [C.POINTER(Bank)] * 2 + [_vp, _vp, _i32, _i32, _i32, _i64, _vp, _vp, _sz, _vp]),
+    "b2moe_expert_gateup_swiglu_sparse": (_i32, [C.POINTER(Bank)] * 4 + [_vp, _i32, _vp, _i32, _i32, _i32, _i64, _vp, _vp, _sz, _vp]),
     "b2moe_expert_matvec_workspace_bytes": (_sz, [C.POINTER(Bank), _i32, _i32]),
     "b2moe_expert_gemm_gateup_workspace_bytes": (_sz, [C.POINTER(Bank), _i32, _i32, _i32]),
     "b2moe_plan_from_groups": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp, _vp]),

@@ -126,7 +126,7 @@ extern "C" B2MOE_API size_t b2moe_expert_workspace_bytes(uint32_t type, int32_t 
 // x_staged: the caller has already written the staged form of x where the 4-bit decode kernels expect it (b2moe_layer_forward)
 static int32_t expert_gateup(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_bank * shared_gate, const b2moe_bank * shared_up,
                              const void * x, int32_t x_dtype, const int32_t * plan, int32_t n, int32_t topk, int32_t shared_tokens, float * act,
-                             void * workspace, size_t workspace_bytes, b2moe_stream stream, bool x_staged) {
+                             void * workspace, size_t workspace_bytes, b2moe_stream stream, bool x_staged, long long live = -1) {
     if (int32_t rc = check_bank(gate)) return rc;
     if (int32_t rc = check_bank(up)) return rc;
     if (int32_t rc = same_shape(gate, up, true)) return rc;
@@ -139,7 +139,7 @@ static int32_t expert_gateup(const b2moe_bank * gate, const b2moe_bank * up, con
     }
     if (!x || !plan || !act) return B2MOE_ERR_NULL;
     if (!aligned16(x) || !aligned16(act)) return B2MOE_ERR_ALIGN;
-    const int path = expert_path(gate->type, gate->cols, x_dtype, 2, gate->experts, (long long)n * topk);
+    const int path = expert_path(gate->type, gate->cols, x_dtype, 2, gate->experts, live >= 0 ? live : (long long)n * topk);
     if (path != B2MOE_FAMILY_GENERIC) {
         const size_t need = b2moe_expert_workspace_bytes(gate->type, n, gate->cols, x_dtype);
         if (need && !workspace) return B2MOE_ERR_NULL;
@@ -162,9 +162,8 @@ extern "C" B2MOE_API int32_t b2moe_expert_gateup_swiglu(const b2moe_bank * gate,
     return expert_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, workspace, workspace_bytes, stream, false);
 }
 
-extern "C" B2MOE_API int32_t b2moe_expert_down(const b2moe_bank * down, const b2moe_bank * shared_down, const float * act, const int32_t * plan,
-                                     int32_t n, int32_t topk, int32_t shared_tokens, float * y, void * workspace,
-                                     size_t workspace_bytes, b2moe_stream stream) {
+static int32_t expert_down(const b2moe_bank * down, const b2moe_bank * shared_down, const float * act, const int32_t * plan, int32_t n, int32_t topk,
+                           int32_t shared_tokens, float * y, void * workspace, size_t workspace_bytes, b2moe_stream stream, long long live) {
     if (int32_t rc = check_bank(down)) return rc;
     if (n <= 0 || topk <= 0 || (shared_tokens != 0 && shared_tokens != n)) return B2MOE_ERR_SHAPE;
     if (shared_tokens) {
@@ -173,7 +172,7 @@ extern "C" B2MOE_API int32_t b2moe_expert_down(const b2moe_bank * down, const b2
     }
     if (!act || !plan || !y) return B2MOE_ERR_NULL;
     if (!aligned16(act) || !aligned16(y)) return B2MOE_ERR_ALIGN;
-    const int path = expert_path(down->type, down->cols, B2MOE_F32, 1, down->experts, (long long)n * topk);
+    const int path = expert_path(down->type, down->cols, B2MOE_F32, 1, down->experts, live >= 0 ? live : (long long)n * topk);
     if (path != B2MOE_FAMILY_GENERIC) {
         const int rows_x = n * topk + shared_tokens;
         if (!workspace) return B2MOE_ERR_NULL;
@@ -187,6 +186,28 @@ extern "C" B2MOE_API int32_t b2moe_expert_down(const b2moe_bank * down, const b2
         return iq3s_down(down, shared_down, act, plan, n, topk, shared_tokens, y, workspace, ma, as_stream(stream));
     }
     return generic_down(down, shared_down, act, plan, n, topk, shared_tokens, y, as_stream(stream));
+}
+
+extern "C" B2MOE_API int32_t b2moe_expert_down(const b2moe_bank * down, const b2moe_bank * shared_down, const float * act, const int32_t * plan,
+                                     int32_t n, int32_t topk, int32_t shared_tokens, float * y, void * workspace,
+                                     size_t workspace_bytes, b2moe_stream stream) {
+    return expert_down(down, shared_down, act, plan, n, topk, shared_tokens, y, workspace, workspace_bytes, stream, -1);
+}
+// The two products for a caller that knows how many of the n * topk assignments are live (id >= 0): under expert parallelism a
+// rank sees every token but owns 1 / G of the experts, and the kernel family is chosen by tokens per expert.
+extern "C" B2MOE_API int32_t b2moe_expert_gateup_swiglu_sparse(const b2moe_bank * gate, const b2moe_bank * up, const b2moe_bank * shared_gate,
+                                                     const b2moe_bank * shared_up, const void * x, int32_t x_dtype, const int32_t * plan, int32_t n,
+                                                     int32_t topk, int32_t shared_tokens, int64_t live_assignments, float * act, void * workspace,
+                                                     size_t workspace_bytes, b2moe_stream stream) {
+    if (live_assignments < 0 || live_assignments > (long long)n * topk) return B2MOE_ERR_SHAPE;
+    return expert_gateup(gate, up, shared_gate, shared_up, x, x_dtype, plan, n, topk, shared_tokens, act, workspace, workspace_bytes, stream, false,
+                         live_assignments);
+}
+extern "C" B2MOE_API int32_t b2moe_expert_down_sparse(const b2moe_bank * down, const b2moe_bank * shared_down, const float * act, const int32_t * plan,
+                                            int32_t n, int32_t topk, int32_t shared_tokens, int64_t live_assignments, float * y, void * workspace,
+                                            size_t workspace_bytes, b2moe_stream stream) {
+    if (live_assignments < 0 || live_assignments > (long long)n * topk) return B2MOE_ERR_SHAPE;
+    return expert_down(down, shared_down, act, plan, n, topk, shared_tokens, y, workspace, workspace_bytes, stream, live_assignments);
 }
 
 extern "C" B2MOE_API int32_t b2moe_layer_workspace(const b2moe_layer * L, int32_t n, b2moe_layer_ws * ws) {

@@ -235,6 +235,11 @@ class CudaEpLayer:
                                                     int(sh.norm), sh.scale, n, self._st()), "b2moe_route_sigmoid")
         return ids, w
 
+    def live_estimate(self, nominal: int) -> int:
+        """expected number of the nominal n * topk assignments whose expert lives on this rank (uniform routing): the kernel
+        family of the expert products is chosen from it (b2moe_expert_*_sparse)"""
+        return min(nominal, max(1, -(-nominal * self.count // self.E)))
+
     def partial_sums(self, x_all, ids_all, w_all):
         from . import moe
         lib, sh, L = self.lib, self.shape, self.layer
@@ -259,10 +264,11 @@ class CudaEpLayer:
         ews = self._b("ews", (max(eg, ed, 16),), torch.uint8)
         br = lambda b: C.byref(b.c)
         shg, shu, shd = (br(L.sh[0]), br(L.sh[1]), br(L.sh[2])) if has_sh else (None, None, None)
-        self.capi.check(lib.b2moe_expert_gateup_swiglu(br(L.gate), br(L.up), shg, shu, x_all.data_ptr(), dt, plan.data_ptr(), N, k,
-                                                       shared_n, act.data_ptr(), ews.data_ptr(), ews.numel(), self._st()), "gateup")
-        self.capi.check(lib.b2moe_expert_down(br(L.down), shd, act.data_ptr(), plan.data_ptr(), N, k, shared_n, y.data_ptr(),
-                                              ews.data_ptr(), ews.numel(), self._st()), "down")
+        live = self.live_estimate(N * k)                 # this rank owns count / experts_total of the experts: so many ids are not -1
+        self.capi.check(lib.b2moe_expert_gateup_swiglu_sparse(br(L.gate), br(L.up), shg, shu, x_all.data_ptr(), dt, plan.data_ptr(), N, k,
+                                                              shared_n, live, act.data_ptr(), ews.data_ptr(), ews.numel(), self._st()), "gateup")
+        self.capi.check(lib.b2moe_expert_down_sparse(br(L.down), shd, act.data_ptr(), plan.data_ptr(), N, k, shared_n, live, y.data_ptr(),
+                                                     ews.data_ptr(), ews.numel(), self._st()), "down")
         parts = self._b("parts", (N, sh.hidden), torch.float32)
         self.capi.check(lib.b2moe_combine(y.data_ptr(), local.data_ptr(), w_all.data_ptr(), None, N, k, sh.hidden, 0, parts.data_ptr(),
                                           self.capi.F32, self._st()), "b2moe_combine")
@@ -323,10 +329,11 @@ class CudaEpLayer:
         ews = torch.empty(max(eg, ed, 16), dtype=torch.uint8, device=recv.device)
         br = lambda b: C.byref(b.c)
         shg, shu, shd = (br(L.sh[0]), br(L.sh[1]), br(L.sh[2])) if has_sh else (None, None, None)
-        self.capi.check(lib.b2moe_expert_gateup_swiglu(br(L.gate), br(L.up), shg, shu, x.data_ptr(), dt, plan.data_ptr(), N, k, shared_n,
-                                                       act.data_ptr(), ews.data_ptr(), ews.numel(), self._st()), "gateup")
-        self.capi.check(lib.b2moe_expert_down(br(L.down), shd, act.data_ptr(), plan.data_ptr(), N, k, shared_n, y.data_ptr(), ews.data_ptr(),
-                                              ews.numel(), self._st()), "down")
+        live = self.live_estimate(N * k)
+        self.capi.check(lib.b2moe_expert_gateup_swiglu_sparse(br(L.gate), br(L.up), shg, shu, x.data_ptr(), dt, plan.data_ptr(), N, k, shared_n,
+                                                              live, act.data_ptr(), ews.data_ptr(), ews.numel(), self._st()), "gateup")
+        self.capi.check(lib.b2moe_expert_down_sparse(br(L.down), shd, act.data_ptr(), plan.data_ptr(), N, k, shared_n, live, y.data_ptr(),
+                                                     ews.data_ptr(), ews.numel(), self._st()), "down")
         parts = torch.empty(N, H, dtype=torch.float32, device=recv.device)
         self.capi.check(lib.b2moe_combine(y.data_ptr(), ids.data_ptr(), w.data_ptr(), None, N, k, H, 0, parts.data_ptr(), self.capi.F32,
                                           self._st()), "b2moe_combine")
