@@ -163,6 +163,29 @@ def test_layer_with_fused_residual(dtype):
     assert torch.equal(buf, want)
 
 
+def test_launch_chain_and_column_split_switches_do_not_change_results():
+    """harness switches of the decode path: plain stream order instead of dependent launches gives the same bits; one warp
+    per row job instead of the column split (few tokens) gives the same values up to the order of the partial sums"""
+    from tqllm_b200 import moe
+    from tqllm_b200.capi import lib
+    shape = synth.CONFIGS["c2"]
+    layer, x = layer_inputs(shape, 64, 2, 17)
+    dev = moe.MoeLayer.from_synth(layer, experts=64)
+    xd = x.cuda()
+    base = dev.forward(xd).clone()
+    try:
+        lib.b2moe_harness_overlap(0)
+        assert torch.equal(dev.forward(xd), base)
+        lib.b2moe_harness_overlap(1)
+        lib.b2moe_harness_column_split(1)
+        unsplit = dev.forward(xd).clone()
+    finally:
+        lib.b2moe_harness_overlap(1)
+        lib.b2moe_harness_column_split(4)
+    assert rel_err(unsplit.cpu().numpy(), base.cpu().numpy()) < 1e-4      # a changed last bit of an act value can move its 15-bit staging
+    assert dev.artefacts()["status"] == 0
+
+
 def test_step_by_step_equals_layer_forward(orc):
     """the separate entry points chained by hand give the bits of b2moe_layer_forward"""
     from tqllm_b200 import moe
