@@ -35,7 +35,9 @@ constexpr int G_ROWS = 128;                 // weight rows per item = M
 // tokens per item: template parameter NT = 128 (two accumulator sets, four B stages; the default) or 256 (one accumulator
 // set in the gate/up product, two B stages; opt-in)
 constexpr int G_KS = 64;                    // columns per pipeline step (four MMAs of K = 16 per matrix)
-constexpr int A_STAGES = 2, RAW_SLOTS = 2, MAX_B_STAGES = 4;
+constexpr int MAX_A_STAGES = 4, RAW_SLOTS = 2, MAX_B_STAGES = 4;
+// stages of decoded A operand: the down product (one matrix) has room for four, gate/up (two matrices per stage) for two
+template <int NMAT> constexpr int a_stages() { return NMAT == 1 ? 4 : 2; }
 constexpr uint32_t DEC_BACKOFF = 60;       // ns between tries of a decode warp's waits
 constexpr int A_LBO = gdec::A_LBO;          // bytes between k cores of A
 constexpr int A_MAT = 8 * A_LBO;            // one matrix of one A stage: 128 rows x 64 columns
@@ -44,7 +46,7 @@ constexpr int A_MAT = 8 * A_LBO;            // one matrix of one A stage: 128 ro
 #endif
 constexpr int MMA_WARP = 0, LOAD_WARP0 = 5, LOAD_WARPS = B2_LOAD_WARPS, LOAD_THREADS = 32 * LOAD_WARPS, DEC_WARP0 = LOAD_WARP0 + LOAD_WARPS, DEC_WARPS = 16;   // warps 1..4: epilogue
 constexpr int G_THREADS = (DEC_WARP0 + DEC_WARPS) * 32;
-constexpr int N_BARS = 2 * 8 * RAW_SLOTS + 2 * A_STAGES + 2 * MAX_B_STAGES + 4;
+constexpr int N_BARS = 2 * 8 * RAW_SLOTS + 2 * MAX_A_STAGES + 2 * MAX_B_STAGES + 4;
 
 struct GemmArgs {
     const uint8_t * w0, * w1;               // stacked banks (gate, up) or (down, -)
@@ -63,7 +65,7 @@ template <uint32_t T> constexpr int chunk_bytes() { return chunk_tiles<T>() * Fm
 
 template <uint32_t T, int NMAT, int NT>
 constexpr size_t gemm_smem(int experts) {
-    return size_t(A_STAGES) * NMAT * A_MAT + size_t(NT == 128 ? 4 : 2) * (8 * NT * 16) + size_t(8) * RAW_SLOTS * NMAT * chunk_bytes<T>() +
+    return size_t(a_stages<NMAT>()) * NMAT * A_MAT + size_t(NT == 128 ? 4 : 2) * (8 * NT * 16) + size_t(8) * RAW_SLOTS * NMAT * chunk_bytes<T>() +
            gdec::Dec<T>::TAB_BYTES + size_t(experts + 3) * 4 + 16 + size_t(N_BARS) * 8 + 16;
 }
 
@@ -90,7 +92,7 @@ template <uint32_t T, int MODE, int NT>
 __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
     constexpr int NMAT = MODE == 0 ? 2 : 1;
     constexpr int G_NT = NT, B_LBO = NT * 16, B_STAGE = 8 * B_LBO;      // B: bytes between k cores; NT tokens x 64 columns
-    constexpr int B_STAGES = NT == 128 ? 4 : 2, B_LAG = NT == 128 ? 2 : 1;
+    constexpr int B_STAGES = NT == 128 ? 4 : 2, B_LAG = NT == 128 ? 2 : 1, A_STAGES = a_stages<NMAT>();
     constexpr uint32_t ACC_SETS = NMAT * NT * 2 <= 512 ? 2 : 1;        // accumulator sets that fit the 512 tensor-memory columns
     constexpr int KT = Fmt<T>::KT, TILE = Fmt<T>::TILE, CT = chunk_tiles<T>(), CB = chunk_bytes<T>();
     constexpr uint32_t TMEM_COLS = 512;
@@ -103,8 +105,8 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
     uint64_t * bars = reinterpret_cast<uint64_t *>((reinterpret_cast<uintptr_t>(cum + p.experts + 3) + 15) & ~uintptr_t(15));
     uint32_t * tmem_slot = reinterpret_cast<uint32_t *>(bars + N_BARS);
     volatile int * abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-    const uint32_t raw_full = saddr(bars), raw_empty = raw_full + 8 * 8 * RAW_SLOTS, a_full = raw_empty + 8 * 8 * RAW_SLOTS, a_empty = a_full + 8 * A_STAGES,
-                   b_full = a_empty + 8 * A_STAGES, b_empty = b_full + 8 * MAX_B_STAGES, acc_full = b_empty + 8 * MAX_B_STAGES,
+    const uint32_t raw_full = saddr(bars), raw_empty = raw_full + 8 * 8 * RAW_SLOTS, a_full = raw_empty + 8 * 8 * RAW_SLOTS, a_empty = a_full + 8 * MAX_A_STAGES,
+                   b_full = a_empty + 8 * MAX_A_STAGES, b_empty = b_full + 8 * MAX_B_STAGES, acc_full = b_empty + 8 * MAX_B_STAGES,
                    acc_empty = acc_full + 16;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int e1 = p.experts + 1;
