@@ -23,36 +23,8 @@ __device__ __forceinline__ float stage_scale(float mx, int bits, float & inv) {
     inv = __uint_as_float(uint32_t(127 - (bits - 2) + ex) << 23);
     return __uint_as_float(uint32_t(127 + bits - 2 - ex) << 23);         // 2^(bits - 2 - ex)
 }
-// sub-block b of a row: one lane per column; every lane of the warp calls it. orow / recs: the row's staged bytes and records
-// (global or shared memory)
-__device__ __forceinline__ void stage_sub_block(const void * x, int dtype, size_t row_first, int b, float scale, uint8_t * orow, uint8_t * recs, int lane) {
-    const int t = (lane & 15) >> 2, j = lane & 3, h = lane >> 4;
-    const int v = __float2int_rn(load_act(x, dtype, row_first + 32 * b + lane) * scale);
-    uint8_t * sb = orow + size_t(b) * 64 + t * 16 + h * 4 + j;
-    sb[0] = uint8_t(v >> 8);
-    sb[8] = uint8_t(v & 255);
-    int sum = v;
-    for (int d = 16; d; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
-    if (lane == 0) {
-        const int bb = b & 7;
-        reinterpret_cast<__half2 *>(recs + size_t(b >> 3) * 32)[2 * (bb & 3) + (bb >> 2)] =
-            __floats2half2_rn(float((sum >> 10) * 16), float(sum & 1023) * 0.015625f);
-    }
-}
-// one whole row (elements [first, first + k) of x) by one warp into `orow`; returns the row's inverse scale
-__device__ inline float stage_row_to(const void * x, int dtype, size_t first, int k, int bits, uint8_t * orow, int lane) {
-    float mx = 0.f;
-    for (int j = lane; j < k; j += 32) mx = fmaxf(mx, fabsf(load_act(x, dtype, first + j)));
-    for (int d = 16; d; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
-    float inv;
-    const float scale = stage_scale(mx, bits, inv);
-    uint8_t * recs = orow + size_t(k) * 2;
-#pragma unroll 4
-    for (int b = 0; b < (k >> 5); ++b) stage_sub_block(x, dtype, first, b, scale, orow, recs, lane);
-    return inv;
-}
-// The same row with a lane per sub-block (32 consecutive columns each): no cross-lane step except the row maximum, so a warp
-// that shares its scheduler with busy warps still stages a row in about a microsecond. Rows must start on 16 bytes.
+// One row by one warp, a lane per sub-block (32 consecutive columns each): no cross-lane step except the row maximum, so a
+// warp that shares its scheduler with busy warps still stages a row in about a microsecond. Rows must start on 16 bytes.
 template <int DT> struct RowLoad;
 template <> struct RowLoad<B2MOE_F32> {      // eight columns from two 16-byte loads
     __device__ static void eight(const void * x, size_t first, int i, float (&v)[8]) {

@@ -77,27 +77,14 @@ __device__ __forceinline__ void mma_i8(int (&c)[4], uint32_t a0, uint32_t a1, ui
         asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
                      : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
-// Activation staging (layout and row code: dec4_stage.cuh): one block of four warps per row.
+// Activation staging (layout and row code: dec4_stage.cuh): a warp per row, four rows per block.
 constexpr int STAGE_WARPS = 4;
 __global__ void __launch_bounds__(STAGE_WARPS * 32) dec4_stage_k(const void * __restrict__ x, int dtype, int rows, int k, int bits,
                                                                  uint8_t * __restrict__ out, float * __restrict__ inv_scale) {
-    __shared__ float wmax[STAGE_WARPS];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, row = blockIdx.x;
+    const int lane = threadIdx.x & 31, row = blockIdx.x * STAGE_WARPS + (threadIdx.x >> 5);
     grid_release();
     grid_wait();
-    float mx = 0.f;
-    for (int j = threadIdx.x; j < k; j += STAGE_WARPS * 32) mx = fmaxf(mx, fabsf(load_act(x, dtype, size_t(row) * k + j)));
-    for (int d = 16; d; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
-    if (lane == 0) wmax[warp] = mx;
-    __syncthreads();
-#pragma unroll
-    for (int w = 0; w < STAGE_WARPS; ++w) mx = fmaxf(mx, wmax[w]);
-    float inv;
-    const float scale = stage_scale(mx, bits, inv);
-    if (threadIdx.x == 0) inv_scale[row] = inv;
-    uint8_t * orow = out + size_t(row) * staged_row_bytes(k);
-    uint8_t * recs = orow + size_t(k) * 2;
-    for (int b = warp; b < (k >> 5); b += STAGE_WARPS) stage_sub_block(x, dtype, size_t(row) * k, b, scale, orow, recs, lane);
+    if (row < rows) stage_row_warp(x, dtype, row, k, bits, out, inv_scale, lane);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -562,7 +549,7 @@ int32_t stage(Dec4Args & a, const void * x, int dtype, int rows_x, int k, void *
     a.x = w; a.inv_scale = inv;
     if (already) return B2MOE_OK;            // an earlier launch of the caller wrote the staged rows (route_plan_stage)
     if (g_skip_stage) return B2MOE_OK;       // the workspace still holds the staged rows of the previous call (benchmarks: the product alone)
-    launch_overlapped(dec4_stage_k, dim3(rows_x), dim3(STAGE_WARPS * 32), 0, s, x, dtype, rows_x, k, int(D4<T>::BITS), w, inv);
+    launch_overlapped(dec4_stage_k, dim3((rows_x + STAGE_WARPS - 1) / STAGE_WARPS), dim3(STAGE_WARPS * 32), 0, s, x, dtype, rows_x, k, int(D4<T>::BITS), w, inv);
     return launch_status();
 }
 
