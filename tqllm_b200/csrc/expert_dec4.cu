@@ -21,8 +21,13 @@
 // 16th row tile of a segment; lane w of the producer warp is its feeder: it streams the tiles warp w will read, in
 // order, over the whole share, through that warp's own ring of bulk copies (cp.async.bulk + mbarrier, no multicast;
 // a full and an empty barrier per slot), so the ring never drains between jobs or segments. Lanes 16 .. 23 of the
-// producer copy the staged activation rows of a segment's tokens into one of two shared buffers, one segment ahead;
-// the consumers hand a buffer back through a barrier of their own, so no block-wide barrier sits in the loop.
+// producer copy the staged activation rows of a segment's tokens into one of two shared buffers, one segment ahead, and
+// leave each token column's assignment index and inverse scale beside them (the consumers' loop touches no global
+// memory but its stores); the consumers hand a buffer back through a barrier of their own, so no block-wide barrier
+// sits in the loop.
+// Small launches (a few row jobs per block, known from the call's shape): 2 or 4 consumer warps share a row job, each
+// taking a part of its columns, and meet in shared memory where the first of them adds the parts in a fixed order; the
+// down product then also has one more warp that stages its fp32 activation rows itself (no staging launch).
 // Every wait is bounded; a wait that runs out sets the plan's status word and a block-wide flag, every warp stops at
 // its next wait or item, the producer lets the copies in flight land, and the block leaves.
 #include "common.cuh"
