@@ -582,7 +582,7 @@ def run_b200(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8+f32", "data": "synthetic",
         "config": {"workload": workload_name(shape, T, L), "tokens": T, "layers": L, "router_scale": rscale, "parallelism": "single GPU",
-                   "l2": "per-step expert weights (GBs) exceed the 126 MB L2; no flush needed", "cuda_graph": graphed, "dependent_launch_overlap": bool(args.overlap),
+                   "l2": "per-step expert weights (GBs) exceed the 126 MB L2; no flush needed", "cuda_graph": graphed, "e2e_leg": "pinned H2D copy, the same graph replay, one D2H copy of all layer outputs" if graphed else "pinned H2D copy, direct launches, one D2H copy", "dependent_launch_overlap": bool(args.overlap),
                    "activations": "bf16 in, bf16 out; expert products on integer tensor-core MMA over 15-bit fixed-point activations, fp32 sums",
                    "iq3s_bank_layout": args.iq3s_layout},
         "repeats": {"n": len(reg), "ms_per_step_median": ms_step, "ms_per_step_min": min(reg), "ms_per_step_max": max(reg),
