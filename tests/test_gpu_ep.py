@@ -37,6 +37,13 @@ def run_split(shape, E, T, world, seed, gate_vec=None):
     w_all = torch.cat([w for _, w in routed]).contiguous()
     assert np.array_equal(ids_all.cpu().numpy(), want_ids)
     parts = [rk.partial_sums(xd, ids_all, w_all) for rk in ranks]
+    # the packed-record form of the same exchange (one pack launch per rank, one unpack launch) gives the same partial sums
+    if ranks[0].can_pack(xd, ids_all.shape[1]):
+        rec_all = torch.cat([rk.pack_all(xd[r * T:(r + 1) * T].contiguous(), *routed[r]) for r, rk in enumerate(ranks)]).contiguous()
+        for r, rk in enumerate(ranks):
+            want_parts = parts[r][0].clone()
+            got_parts, _ = rk.partial_sums_packed(rec_all, ids_all.shape[1], xd.dtype)
+            assert torch.equal(got_parts, want_parts)
     outs = []
     for h, rk in enumerate(ranks):
         recv = torch.stack([parts[r][0][h * T:(h + 1) * T] for r in range(world)]).contiguous()

@@ -131,9 +131,13 @@ def unpack_tokens(rec: torch.Tensor, hidden: int, topk: int, x_dtype, x=None, id
 def ep_forward(backend, comm, x_local: torch.Tensor) -> torch.Tensor:
     """one expert-parallel layer forward for this rank's tokens; `backend` supplies the three compute phases"""
     ids, weights = backend.route_local(x_local)
-    rec_all = comm.all_gather(pack_tokens(x_local, ids, weights))
-    x_all, ids_all, w_all = unpack_tokens(rec_all, x_local.shape[1], ids.shape[1], x_local.dtype)
-    parts, shared = backend.partial_sums(x_all, ids_all, w_all)
+    if getattr(backend, "can_pack", None) and backend.can_pack(x_local, ids.shape[1]):      # one pack and one unpack launch
+        rec_all = comm.all_gather(backend.pack_all(x_local, ids, weights))
+        parts, shared = backend.partial_sums_packed(rec_all, ids.shape[1], x_local.dtype)
+    else:
+        rec_all = comm.all_gather(pack_tokens(x_local, ids, weights))
+        x_all, ids_all, w_all = unpack_tokens(rec_all, x_local.shape[1], ids.shape[1], x_local.dtype)
+        parts, shared = backend.partial_sums(x_all, ids_all, w_all)
     recv = comm.all_to_all(parts.view(comm.world, x_local.shape[0], -1))
     return backend.finish(recv, shared)
 
@@ -241,15 +245,43 @@ class CudaEpLayer:
         return min(nominal, max(1, -(-nominal * self.count // self.E)))
 
     def partial_sums(self, x_all, ids_all, w_all):
+        N, k = ids_all.shape
+        local = self._b("local", (N, k), torch.int32)
+        self.capi.check(self.lib.b2moe_ep_local_ids(ids_all.data_ptr(), local.data_ptr(), N * k, self.first, self.count, self._st()), "ep_local_ids")
+        return self._local_products(x_all, local, w_all)
+
+    # one launch each instead of three strided copies (and a fourth for the local ids): the packed token records of the all-gather
+    def can_pack(self, x, k):
+        return (x.shape[1] * x.element_size()) % 16 == 0 and (8 * k) % 16 == 0
+
+    def pack_all(self, x, ids, w, out=None):
+        n, k = ids.shape
+        xb = x.shape[1] * x.element_size()
+        if out is None:
+            out = torch.empty(n, xb + 8 * k, dtype=torch.uint8, device=x.device)
+        lst = self.buf.get("own_list")
+        if lst is None or lst.numel() != n:
+            lst = torch.arange(n, dtype=torch.int32, device=x.device)
+            self.buf["own_list"], self.buf["own_offsets"] = lst, torch.tensor([0, n], dtype=torch.int32, device=x.device)
+        self.capi.check(self.lib.b2moe_ep_pack(x.data_ptr(), xb, ids.data_ptr(), w.data_ptr(), k, n, lst.data_ptr(), self.buf["own_offsets"].data_ptr(),
+                                               1, n, out.data_ptr(), self._st()), "b2moe_ep_pack")
+        return out
+
+    def partial_sums_packed(self, rec_all, k, x_dtype):
+        N, H = rec_all.shape[0], self.shape.hidden
+        x_all, local, w_all = self._b("x_all", (N, H), x_dtype), self._b("local", (N, k), torch.int32), self._b("w_all", (N, k), torch.float32)
+        self.capi.check(self.lib.b2moe_ep_unpack(rec_all.data_ptr(), N, H * x_all.element_size(), k, self.first, self.count, x_all.data_ptr(),
+                                                 local.data_ptr(), w_all.data_ptr(), self._st()), "b2moe_ep_unpack")
+        return self._local_products(x_all, local, w_all)
+
+    def _local_products(self, x_all, local, w_all):
         from . import moe
         lib, sh, L = self.lib, self.shape, self.layer
-        N, k = ids_all.shape
+        N, k = local.shape
         T = N // self.world
         A = N * k
         has_sh = L.sh is not None
         shared_n = N if has_sh else 0                      # buffer rows for the shared expert (token-indexed)
-        local = self._b("local", (N, k), torch.int32)
-        self.capi.check(lib.b2moe_ep_local_ids(ids_all.data_ptr(), local.data_ptr(), A, self.first, self.count, self._st()), "ep_local_ids")
         pv = self.capi.PlanView()
         lib.b2moe_plan_view_of(self.count, A, T if has_sh else 0, C.byref(pv))
         plan = self._b("plan", (pv.total,), torch.int32)
@@ -376,14 +408,20 @@ class GraphedEpForward:
         # eager pass: allocates the backend's buffers and gives the exchange buffers their shapes
         ids, w = backend.route_local(x_local)
         k = ids.shape[1]
-        self.rec = pack_tokens(x_local, ids, w)
+        packed = bool(getattr(backend, "can_pack", None)) and backend.can_pack(x_local, k)
+        self.rec = backend.pack_all(x_local, ids, w) if packed else pack_tokens(x_local, ids, w)
         self.rec_all = torch.empty((G * T, self.rec.shape[1]), dtype=torch.uint8, device=dev)
         self.x_all = torch.empty((G * T,) + tuple(x_local.shape[1:]), dtype=x_local.dtype, device=dev)
         self.ids_all = torch.empty((G * T, k), dtype=ids.dtype, device=dev)
         self.w_all = torch.empty((G * T, k), dtype=w.dtype, device=dev)
         comm.all_gather(self.rec, self.rec_all)
-        unpack_tokens(self.rec_all, x_local.shape[1], k, x_local.dtype, self.x_all, self.ids_all, self.w_all)
-        parts, shared = backend.partial_sums(self.x_all, self.ids_all, self.w_all)
+
+        def local_phase():
+            if packed:
+                return backend.partial_sums_packed(self.rec_all, k, x_local.dtype)
+            unpack_tokens(self.rec_all, x_local.shape[1], k, x_local.dtype, self.x_all, self.ids_all, self.w_all)
+            return backend.partial_sums(self.x_all, self.ids_all, self.w_all)
+        parts, shared = local_phase()
         self.recv = torch.empty((G, T, parts.shape[1]), dtype=parts.dtype, device=dev)
         comm.all_to_all(parts.view(G, T, -1), self.recv)
         backend.finish(self.recv, shared)
@@ -391,10 +429,12 @@ class GraphedEpForward:
         self.g_route, self.g_part, self.g_fin = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.g_route, stream=stream):             # route + pack
             self.ids, self.w = backend.route_local(x_local)
-            pack_tokens(x_local, self.ids, self.w, self.rec)
+            if packed:
+                backend.pack_all(x_local, self.ids, self.w, self.rec)
+            else:
+                pack_tokens(x_local, self.ids, self.w, self.rec)
         with torch.cuda.graph(self.g_part, stream=stream):              # unpack + local experts + partial sums
-            unpack_tokens(self.rec_all, x_local.shape[1], k, x_local.dtype, self.x_all, self.ids_all, self.w_all)
-            self.parts, self.shared = backend.partial_sums(self.x_all, self.ids_all, self.w_all)
+            self.parts, self.shared = local_phase()
         with torch.cuda.graph(self.g_fin, stream=stream):
             self.out = backend.finish(self.recv, self.shared)
 
