@@ -171,10 +171,12 @@ def phase_times(backend, comm, x_local: torch.Tensor, reps: int = 20) -> dict:
         e[0].record()
         ids, weights = backend.route_local(x_local)
         e[1].record()
-        rec_all = comm.all_gather(pack_tokens(x_local, ids, weights))
-        x_all, ids_all, w_all = unpack_tokens(rec_all, x_local.shape[1], ids.shape[1], x_local.dtype)
+        packed = bool(getattr(backend, "can_pack", None)) and backend.can_pack(x_local, ids.shape[1])
+        rec_all = comm.all_gather(backend.pack_all(x_local, ids, weights) if packed else pack_tokens(x_local, ids, weights))
+        if not packed:
+            x_all, ids_all, w_all = unpack_tokens(rec_all, x_local.shape[1], ids.shape[1], x_local.dtype)
         e[2].record()
-        parts, shared = backend.partial_sums(x_all, ids_all, w_all)
+        parts, shared = backend.partial_sums_packed(rec_all, ids.shape[1], x_local.dtype) if packed else backend.partial_sums(x_all, ids_all, w_all)
         e[3].record()
         recv = comm.all_to_all(parts.view(comm.world, x_local.shape[0], -1))
         e[4].record()
