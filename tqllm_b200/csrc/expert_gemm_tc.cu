@@ -4,14 +4,16 @@
 // (src/formats/weight/quant_u4h.inc:609-774, src/formats/weight/quant.cu:286-405) with their fused SwiGLU epilogue
 // (quant_u4h.inc:756-759): per expert Y_e = W_e . X_e^T over the expert's gathered token rows.
 //
-// One persistent block per SM; an item is (expert, tile of <= 128 of its tokens, block of 128 weight rows):
+// One persistent block per SM; an item is (expert, tile of <= 128 of its tokens, two blocks of 128 weight rows): the same
+// 128 rows of the gate and of the up matrix, or two consecutive row blocks of the down matrix. Per row block
 //   D[128 rows][N tokens] (fp32, tensor memory) = sum over K of A[128][K] (fp16) . B[N][K] (fp16)
 //   A: the weight rows, decoded from the bank's block format to fp16 in shared memory by the CUDA cores, 64 columns per
 //      step (canonical K-major core-matrix layout, no swizzle); the raw blocks arrive through a per-warp ring of bulk
 //      copies (cp.async.bulk + mbarrier), 256 columns per copy;
 //   B: the tokens' activation rows (fp16, each row scaled by a power of two), gathered through the dispatch permutation with 16-byte cp.async;
-//   the gate and the up matrix share B and have an accumulator each; two accumulator sets alternate between items, so
-//   the epilogue of one item (SwiGLU, stores) overlaps the products of the next.
+//   the two row blocks of an item share B (one gathered copy of the token rows serves 256 weight rows) and have an
+//   accumulator each; two accumulator sets alternate between items, so the epilogue of one item (SwiGLU, stores) overlaps
+//   the products of the next.
 // Warps: 0 issues tcgen05.mma (one lane); 1..4 epilogue (tcgen05.ld, one TMEM lane quarter each); 5..6 load B;
 // 7..22 decode A (two warps per row tile of the block: rows g and rows g + 8 of the lane-major tile). Every wait is bounded; a wait that runs out sets the plan's
 // status word, and the block drains and leaves.
@@ -35,9 +37,9 @@ constexpr int G_ROWS = 128;                 // weight rows per item = M
 // tokens per item: template parameter NT = 128 (two accumulator sets, four B stages; the default) or 256 (one accumulator
 // set in the gate/up product, two B stages; opt-in)
 constexpr int G_KS = 64;                    // columns per pipeline step (four MMAs of K = 16 per matrix)
-constexpr int MAX_A_STAGES = 4, RAW_SLOTS = 2, MAX_B_STAGES = 4;
-// stages of decoded A operand: the down product (one matrix) has room for four, gate/up (two matrices per stage) for two
-template <int NMAT> constexpr int a_stages() { return NMAT == 1 ? 4 : 2; }
+constexpr int NMAT = 2;                     // row blocks per item: (gate, up) or two consecutive blocks of the down matrix
+constexpr int A_STAGES = 2;                 // stages of decoded A operand (two row blocks each)
+constexpr int MAX_A_STAGES = A_STAGES, RAW_SLOTS = 2, MAX_B_STAGES = 4;
 constexpr uint32_t DEC_BACKOFF = 60;       // ns between tries of a decode warp's waits
 constexpr int A_LBO = gdec::A_LBO;          // bytes between k cores of A
 constexpr int A_MAT = 8 * A_LBO;            // one matrix of one A stage: 128 rows x 64 columns
@@ -63,9 +65,9 @@ struct GemmArgs {
 template <uint32_t T> constexpr int chunk_tiles() { return 256 / Fmt<T>::KT; }
 template <uint32_t T> constexpr int chunk_bytes() { return chunk_tiles<T>() * Fmt<T>::TILE; }
 
-template <uint32_t T, int NMAT, int NT>
+template <uint32_t T, int NT>
 constexpr size_t gemm_smem(int experts) {
-    return size_t(a_stages<NMAT>()) * NMAT * A_MAT + size_t(NT == 128 ? 4 : 2) * (8 * NT * 16) + size_t(8) * RAW_SLOTS * NMAT * chunk_bytes<T>() +
+    return size_t(A_STAGES) * NMAT * A_MAT + size_t(NT == 128 ? 4 : 2) * (8 * NT * 16) + size_t(8) * RAW_SLOTS * NMAT * chunk_bytes<T>() +
            gdec::Dec<T>::TAB_BYTES + size_t(experts + 3) * 4 + 16 + size_t(N_BARS) * 8 + 16;
 }
 
@@ -90,9 +92,8 @@ __global__ void rows_to_f16_k(const void * __restrict__ x, int dtype, int rows, 
 // MODE 0: act[a][r] = silu(gate_r . x_tok(a)) * (up_r . x_tok(a));  MODE 1: y[a][r] = down_r . act[a]
 template <uint32_t T, int MODE, int NT>
 __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
-    constexpr int NMAT = MODE == 0 ? 2 : 1;
     constexpr int G_NT = NT, B_LBO = NT * 16, B_STAGE = 8 * B_LBO;      // B: bytes between k cores; NT tokens x 64 columns
-    constexpr int B_STAGES = NT == 128 ? 4 : 2, B_LAG = NT == 128 ? 2 : 1, A_STAGES = a_stages<NMAT>();
+    constexpr int B_STAGES = NT == 128 ? 4 : 2, B_LAG = NT == 128 ? 2 : 1;
     constexpr uint32_t ACC_SETS = NMAT * NT * 2 <= 512 ? 2 : 1;        // accumulator sets that fit the 512 tensor-memory columns
     constexpr int KT = Fmt<T>::KT, TILE = Fmt<T>::TILE, CT = chunk_tiles<T>(), CB = chunk_bytes<T>();
     constexpr uint32_t TMEM_COLS = 512;
@@ -111,7 +112,8 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int e1 = p.experts + 1;
     const int * counts = p.plan + PLAN_HDR, * offsets = counts + e1, * active = offsets + e1 + 1, * perm = active + e1;
-    const int na = p.plan[PLAN_NACTIVE], row_tiles = (p.rows + 15) >> 4, row_blocks = (row_tiles + 7) >> 3;
+    constexpr int ITEM_TILES = MODE == 0 ? 8 : 16;                     // row tiles of one matrix that an item covers
+    const int na = p.plan[PLAN_NACTIVE], row_tiles = (p.rows + 15) >> 4, row_blocks = (row_tiles + ITEM_TILES - 1) / ITEM_TILES;
     const int k_tiles = p.k / KT, ksteps = p.k / G_KS, nchunks = (k_tiles + CT - 1) / CT;
 
     gdec::Dec<T>::init(dec_tab, threadIdx.x, G_THREADS);
@@ -200,14 +202,15 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
             const uint32_t ab = ic % ACC_SETS;
             if (!__all_sync(0xffffffffu, bar_wait(acc_full + 8 * ab, (ic / ACC_SETS) & 1u, 1000))) { if (lane == 0) give_up(); break; }
             fence_after();
-            const int row = im.rb * G_ROWS + 32 * q + lane;
+            // this thread's weight row in accumulator 0 and in accumulator 1 (the up matrix's same row, or the next row block)
+            const int row = im.rb * (ITEM_TILES * 16) + 32 * q + lane, row1 = MODE == 0 ? row : row + G_ROWS;
             float rs[NMAT];                                            // fp32 row scales of the bank (NVFP4G), else 1
             {
                 const bool shared = im.e == p.experts;
-                const size_t ai = size_t(shared ? 0 : im.e) * row_tiles * 16 + row;
-                const float * a0 = shared ? p.saux0 : p.aux0, * a1 = shared ? p.saux1 : p.aux1;
-                rs[0] = (a0 && row < p.rows) ? a0[ai] : 1.f;
-                if (NMAT == 2) rs[NMAT - 1] = (a1 && row < p.rows) ? a1[ai] : 1.f;
+                const size_t ai = size_t(shared ? 0 : im.e) * row_tiles * 16;
+                const float * a0 = shared ? p.saux0 : p.aux0, * a1 = MODE == 0 ? (shared ? p.saux1 : p.aux1) : a0;
+                rs[0] = (a0 && row < p.rows) ? a0[ai + row] : 1.f;
+                rs[1] = (a1 && row1 < p.rows) ? a1[ai + row1] : 1.f;
             }
             const uint32_t taddr = tmem + (uint32_t(32 * q) << 16) + ab * (NMAT * G_NT);
             // the item's assignments and their activation scales, 32 per round in registers: the stores below may alias any
@@ -229,15 +232,16 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
                     if (c >= im.nv) break;
                     uint32_t g[16], u[16];
                     tmem_ld16(taddr + c, g);
-                    if (NMAT == 2) tmem_ld16(taddr + G_NT + c, u);
+                    tmem_ld16(taddr + G_NT + c, u);
                     tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int a = __shfl_sync(0xffffffffu, a_of[i], c2 + j);
                         const float is = __shfl_sync(0xffffffffu, is_of[i], c2 + j);
                         if (a >= 0 && row < p.rows) {
-                            const float gv = __uint_as_float(g[j]) * (is * rs[0]);
-                            p.out[size_t(a) * p.rows + row] = MODE == 0 ? (gv / (1.f + expf(-gv))) * (__uint_as_float(u[j]) * (is * rs[NMAT - 1])) : gv;
+                            const float gv = __uint_as_float(g[j]) * (is * rs[0]), uv = __uint_as_float(u[j]) * (is * rs[1]);
+                            p.out[size_t(a) * p.rows + row] = MODE == 0 ? (gv / (1.f + expf(-gv))) * uv : gv;
+                            if (MODE == 1 && row1 < p.rows) p.out[size_t(a) * p.rows + row1] = uv;
                         }
                     }
                 }
@@ -302,21 +306,21 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
         bool ok = true;
         for (int it = blockIdx.x; it < n_items && ok && !*abort_flag; it += gridDim.x) {
             const Item im = locate(it);
-            const int rt = im.rb * 8 + tw;
-            const bool live = rt < row_tiles, shared = im.e == p.experts;
-            const uint8_t * base[NMAT];
-            base[0] = (shared ? p.s0 : p.w0 + size_t(im.e) * p.bank_bytes) + size_t(rt) * k_tiles * TILE;
-            if (NMAT == 2) base[NMAT - 1] = (shared ? p.s1 : p.w1 + size_t(im.e) * p.bank_bytes) + size_t(rt) * k_tiles * TILE;
+            // row tile of accumulator 0 and of accumulator 1: the same tile of the gate and the up matrix, or tiles tw and tw + 8 of the item's 16
+            const int rt = im.rb * ITEM_TILES + tw, rt1 = MODE == 0 ? rt : rt + 8;
+            const bool live = rt < row_tiles, live1 = rt1 < row_tiles, shared = im.e == p.experts;      // live1 implies live
+            const uint8_t * bank0 = shared ? p.s0 : p.w0 + size_t(im.e) * p.bank_bytes;
+            const uint8_t * bank1 = MODE == 0 ? (shared ? p.s1 : p.w1 + size_t(im.e) * p.bank_bytes) : bank0;
+            const uint8_t * base[NMAT] = {bank0 + size_t(rt) * k_tiles * TILE, bank1 + size_t(rt1) * k_tiles * TILE};
             // chunk c of this row tile -> the ring slot of use number u (lane 0 of the pair's first warp); false = gave up
             auto issue = [&](int c, uint32_t u) {
                 const uint32_t slot = u % RAW_SLOTS;
                 if (u >= RAW_SLOTS && !bar_wait(my_empty + 8 * slot, ((u / RAW_SLOTS) - 1) & 1u)) return false;   // both warps are done with it
                 const int tiles = min(CT, k_tiles - c * CT);
                 const uint32_t bytes = uint32_t(tiles) * TILE, bar = my_full + 8 * slot;
-                bar_expect_tx(bar, bytes * NMAT);
-#pragma unroll
-                for (int m = 0; m < NMAT; ++m)
-                    bulk_copy(saddr(my_raw) + (slot * NMAT + m) * CB, base[m] + size_t(c) * CT * TILE, bytes, bar);
+                bar_expect_tx(bar, live1 ? 2 * bytes : bytes);
+                bulk_copy(saddr(my_raw) + (slot * NMAT + 0) * CB, base[0] + size_t(c) * CT * TILE, bytes, bar);
+                if (live1) bulk_copy(saddr(my_raw) + (slot * NMAT + 1) * CB, base[1] + size_t(c) * CT * TILE, bytes, bar);
                 return true;
             };
             if (live && half == 0 && lane == 0)
@@ -327,10 +331,8 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
                 if (live && !__all_sync(0xffffffffu, bar_wait(my_full + 8 * slot, (gc / RAW_SLOTS) & 1u, DEC_BACKOFF))) { ok = false; break; }
                 const int steps = min(4, ksteps - 4 * c);
                 typename gdec::Dec<T>::Pre pre[NMAT];                  // per-chunk constants of the decoder
-                if (live) {
-#pragma unroll
-                    for (int m = 0; m < NMAT; ++m) pre[m] = gdec::Dec<T>::prep(my_raw + (slot * NMAT + m) * CB, lane, half);
-                }
+                if (live) pre[0] = gdec::Dec<T>::prep(my_raw + (slot * NMAT + 0) * CB, lane, half);
+                if (live1) pre[1] = gdec::Dec<T>::prep(my_raw + (slot * NMAT + 1) * CB, lane, half);
                 // the (up to) four 64-column steps of the chunk, written out so that every step is straight-line code with its
                 // column offset a constant and the lane's row / table / scale addresses computed once per chunk
                 auto one_step = [&](auto J) {
@@ -338,11 +340,8 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
                     if (j >= steps || !ok) return;
                     const uint32_t sa = gk % A_STAGES;
                     if (gk >= A_STAGES && !__all_sync(0xffffffffu, bar_wait(a_empty + 8 * sa, ((gk / A_STAGES) - 1) & 1u, DEC_BACKOFF))) { ok = false; return; }
-                    if (live) {
-#pragma unroll
-                        for (int m = 0; m < NMAT; ++m)
-                            gdec::Dec<T>::template step<j>(my_raw + (slot * NMAT + m) * CB, lane, a_st + (sa * NMAT + m) * A_MAT + 2 * tw * 128, dec_tab, half, pre[m]);
-                    }
+                    if (live) gdec::Dec<T>::template step<j>(my_raw + (slot * NMAT + 0) * CB, lane, a_st + (sa * NMAT + 0) * A_MAT + 2 * tw * 128, dec_tab, half, pre[0]);
+                    if (live1) gdec::Dec<T>::template step<j>(my_raw + (slot * NMAT + 1) * CB, lane, a_st + (sa * NMAT + 1) * A_MAT + 2 * tw * 128, dec_tab, half, pre[1]);
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0) bar_arrive(a_full + 8 * sa);
@@ -377,7 +376,7 @@ constexpr size_t GEMM_SMEM_LIMIT = 232448 - 1024;
 
 template <uint32_t T, int MODE, int NT>
 int32_t gemm_launch_nt(const GemmArgs & a, int sms, cudaStream_t s) {
-    const size_t smem = gemm_smem<T, MODE == 0 ? 2 : 1, NT>(a.experts);
+    const size_t smem = gemm_smem<T, NT>(a.experts);
     if (smem > GEMM_SMEM_LIMIT) return B2MOE_ERR_SHAPE;
     if (cudaFuncSetAttribute(gemm_tc_k<T, MODE, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return B2MOE_ERR_CUDA;
     gemm_tc_k<T, MODE, NT><<<sms, G_THREADS, smem, s>>>(a);
@@ -392,7 +391,7 @@ int32_t gemm_launch_t(const GemmArgs & a, cudaStream_t s) {
     const int sms = gemm_sm_count();
     if (sms <= 0) return B2MOE_ERR_CUDA;
     const bool wide = g_item_tokens == 256;
-    if (wide && gemm_smem<T, MODE == 0 ? 2 : 1, 256>(a.experts) <= GEMM_SMEM_LIMIT) return gemm_launch_nt<T, MODE, 256>(a, sms, s);
+    if (wide && gemm_smem<T, 256>(a.experts) <= GEMM_SMEM_LIMIT) return gemm_launch_nt<T, MODE, 256>(a, sms, s);
     return gemm_launch_nt<T, MODE, 128>(a, sms, s);
 }
 template <int MODE>
@@ -407,14 +406,14 @@ int32_t gemm_launch(uint32_t type, const GemmArgs & a, cudaStream_t s) {
     }
     return B2MOE_ERR_FORMAT;
 }
-size_t gemm_smem_of(uint32_t type, int nmat, int experts) {
+size_t gemm_smem_of(uint32_t type, int experts) {
     switch (type) {
-        case T_Q4_K: return nmat == 2 ? gemm_smem<T_Q4_K, 2, 128>(experts) : gemm_smem<T_Q4_K, 1, 128>(experts);
-        case T_IQ3_S: return nmat == 2 ? gemm_smem<T_IQ3_S, 2, 128>(experts) : gemm_smem<T_IQ3_S, 1, 128>(experts);
-        case T_IQ3S4: return nmat == 2 ? gemm_smem<T_IQ3S4, 2, 128>(experts) : gemm_smem<T_IQ3S4, 1, 128>(experts);
-        case T_IQ4_XS: return nmat == 2 ? gemm_smem<T_IQ4_XS, 2, 128>(experts) : gemm_smem<T_IQ4_XS, 1, 128>(experts);
-        case T_IQ4_NL: return nmat == 2 ? gemm_smem<T_IQ4_NL, 2, 128>(experts) : gemm_smem<T_IQ4_NL, 1, 128>(experts);
-        case T_NVFP4G: return nmat == 2 ? gemm_smem<T_NVFP4G, 2, 128>(experts) : gemm_smem<T_NVFP4G, 1, 128>(experts);
+        case T_Q4_K: return gemm_smem<T_Q4_K, 128>(experts);
+        case T_IQ3_S: return gemm_smem<T_IQ3_S, 128>(experts);
+        case T_IQ3S4: return gemm_smem<T_IQ3S4, 128>(experts);
+        case T_IQ4_XS: return gemm_smem<T_IQ4_XS, 128>(experts);
+        case T_IQ4_NL: return gemm_smem<T_IQ4_NL, 128>(experts);
+        case T_NVFP4G: return gemm_smem<T_NVFP4G, 128>(experts);
     }
     return ~size_t(0);
 }
@@ -437,7 +436,8 @@ int32_t convert_rows(uint32_t type, const void * x, int dtype, int rows, int k, 
 void gemm_tc_item_tokens(int tokens) { g_item_tokens = tokens == 256 ? 256 : 128; }
 // true when the tensor-core GEMM takes banks of this type with rows of length k (nmat: 2 = gate/up, 1 = down)
 bool gemm_tc_supported(uint32_t type, int k, int nmat, int experts) {
-    return k >= G_KS && k % G_KS == 0 && gemm_smem_of(type, nmat, experts) <= GEMM_SMEM_LIMIT;
+    (void)nmat;                                                       // both products stage two row blocks per item
+    return k >= G_KS && k % G_KS == 0 && gemm_smem_of(type, experts) <= GEMM_SMEM_LIMIT;
 }
 // scratch: the scaled fp16 copy of `rows_x` activation rows of length k and one float per row
 size_t gemm_tc_workspace_bytes(int rows_x, int k) {
