@@ -240,7 +240,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
                         const float is = __shfl_sync(0xffffffffu, is_of[i], c2 + j);
                         if (a >= 0 && row < p.rows) {
                             const float gv = __uint_as_float(g[j]) * (is * rs[0]), uv = __uint_as_float(u[j]) * (is * rs[1]);
-                            p.out[size_t(a) * p.rows + row] = MODE == 0 ? (gv / (1.f + expf(-gv))) * uv : gv;
+                            p.out[size_t(a) * p.rows + row] = MODE == 0 ? __fdividef(gv, 1.f + __expf(-gv)) * uv : gv;      // fast exp and divide: relative error about 2^-21
                             if (MODE == 1 && row1 < p.rows) p.out[size_t(a) * p.rows + row1] = uv;
                         }
                     }

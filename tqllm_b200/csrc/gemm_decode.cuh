@@ -7,11 +7,13 @@
 // than shuffling values between lanes, the GEMM permutes the 64 columns of a step — colmap<T>(pos) is the column stored
 // at operand position pos — and the activation rows are written in the same order (the sum over K does not care).
 //
-// Values: the fp32 formula of the format's host decoder (dequantize_host, src/formats/weight/dequant.cpp:80-99,137-150,
-// 177-192,352-360,397-409) evaluated so that the fp16 result carries one rounding: Q4_K in fp32 (d sc q - dmin m);
-// IQ3_S (odd magnitude x (1 + 2 s)) exact in fp16, then x d; IQ4_NL kvalue x d; NVFP4 e2m1 x e4m3 exact (the fp32 row
-// scale is applied to the accumulator in the epilogue). IQ4_XS multiplies the kvalue by fp16(d (ls - 32)): that factor's
-// rounding (relative 2^-12, the same for the 32 weights of a sub-block) comes on top of the single rounding.
+// Values: the formula of the format's host decoder (dequantize_host, src/formats/weight/dequant.cpp:80-99,137-150,
+// 177-192,352-360,397-409) in fp16 arithmetic on two weights per instruction, arranged so that every intermediate but the
+// last is exact: IQ3_S (odd magnitude x (1 + 2 s)) exact, then x d; the 4-bit IQ3_S codes the same; IQ4_NL kvalue x d;
+// NVFP4 e2m1 x e4m3 exact (the fp32 row scale is applied to the accumulator in the epilogue): one rounding each. Q4_K:
+// sc q exact, x d - the leading fp16 term of dmin m (one rounding), + the rest of dmin m (a second rounding, which removes
+// the error the 32 weights of a sub-block would otherwise share). IQ4_XS multiplies the kvalue by
+// fp16(d (ls - 32)): that factor's rounding (relative 2^-12, the same for the 32 weights of a sub-block) comes on top.
 #pragma once
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
@@ -26,7 +28,8 @@ constexpr int A_LBO = 2048 + 32;            // bytes between the k cores of the 
 // column (0..63, inside the step) held at operand position pos (0..63)
 template <uint32_t T> __host__ __device__ inline int colmap(int pos) {
     const int c = pos >> 3, q = pos & 7;                               // core, position inside the 16-byte row
-    if (T == T_Q4_K || T == T_IQ3S4) return q < 4 ? 4 * c + q : 32 + 4 * c + (q - 4); // word c: low nibbles = sub-block 0, high = sub-block 1
+    // word c: low nibbles = sub-block 0, high nibbles = sub-block 1; inside each the decoder emits bytes 0, 2, 1, 3 (nibble pairs 16 bits apart)
+    if (T == T_Q4_K || T == T_IQ3S4) return (q < 4 ? 0 : 32) + 4 * c + ((q & 1) << 1) + ((q >> 1) & 1);
     if (T == T_IQ4_XS || T == T_IQ4_NL) return 32 * (c >> 2) + 4 * (c & 3) + (q >> 1) + 16 * (q & 1);   // byte i: columns i, i + 16
     return pos;                                                        // IQ3_S, NVFP4G: eight consecutive columns per word
 }
@@ -49,14 +52,8 @@ template <uint32_t T> __device__ inline void build_lut(uint32_t * lut, int tid, 
     for (int i = tid; i < 256 * LUT_COPIES; i += nthreads) {
         const int b = i / LUT_COPIES;
         float lo, hi;
-        if (T == T_NVFP4G) {
-            const float m[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
-            lo = (b & 8) ? -m[b & 7] : m[b & 7];
-            hi = (b & 128) ? -m[(b >> 4) & 7] : m[(b >> 4) & 7];
-        } else {
-            lo = float(c_kvalues_iq4nl[b & 15]);
-            hi = float(c_kvalues_iq4nl[b >> 4]);
-        }
+        lo = float(c_kvalues_iq4nl[b & 15]);
+        hi = float(c_kvalues_iq4nl[b >> 4]);
         lut[i] = pack_h2(lo, hi);
     }
 }
@@ -76,31 +73,42 @@ template <uint32_t T> struct Dec;
 template <> struct Dec<T_Q4_K> {
     static constexpr int TAB_BYTES = 0;
     __device__ static void init(void *, int, int) {}
-    // (1 + q / 16) as a float from the nibble at bit `pos` of w, then S (1 + q / 16) + C = d sc q - dmin m with S = 16 d sc,
-    // C = -(S + dmin m): one fp32 rounding, far below the fp16 rounding that follows
-    template <int POS> __device__ __forceinline__ static float val(uint32_t w, float S, float C) {
-        const uint32_t f = ((POS <= 19 ? w << (19 - POS) : w >> (POS - 19)) & 0x00780000u) | 0x3F800000u;
-        return fmaf(__uint_as_float(f), S, C);
+    // The nibbles at bits POS and POS + 16 of w as the half2 (1 + q / 16, 1 + q' / 16): one shift and one logic operation for
+    // two weights (the nibble lands in the top four mantissa bits under the exponent of 1.0).
+    template <int POS> __device__ __forceinline__ static __half2 pair(uint32_t w) {
+        const uint32_t s = POS <= 6 ? w << (6 - POS) : w >> (POS - 6);
+        return bits_h2((s & 0x03C003C0u) | 0x3C003C00u);
     }
-    __device__ __forceinline__ static uint4 word(uint32_t w, float S1, float C1, float S2, float C2) {
+    // d sc q - dmin m on two weights per instruction: t = (1 + q / 16) (16 sc) - 16 sc = sc q (an integer below 1024:
+    // exact), then t d + MH (exact product, one rounding of the weight) and + ML, where MH + ML = -dmin m split into two fp16
+    // terms. Rounding the sub-block's d sc or dmin m to one fp16 constant would be cheaper, but that error is shared by the
+    // 32 weights of the sub-block and adds up along a row, and rounding t d before the subtraction loses the bits that
+    // cancel (both measured: 2.5 to 3 times the output error of this form).
+    __device__ __forceinline__ static uint32_t two(__half2 pr, __half2 SC, __half2 NSC, __half2 MH, __half2 ML, __half2 D) {
+        return h2_bits(__hadd2(__hfma2(__hfma2(pr, SC, NSC), D, MH), ML));
+    }
+    struct Sub { __half2 SC, MH, ML; };                              // constants of one sub-block
+    __device__ __forceinline__ static uint4 word(uint32_t w, const Sub & s1, const Sub & s2, __half2 D) {
+        const __half2 NSC1 = __hneg2(s1.SC), NSC2 = __hneg2(s2.SC);
         uint4 o;
-        o.x = pack_h2(val<0>(w, S1, C1), val<8>(w, S1, C1));
-        o.y = pack_h2(val<16>(w, S1, C1), val<24>(w, S1, C1));
-        o.z = pack_h2(val<4>(w, S2, C2), val<12>(w, S2, C2));
-        o.w = pack_h2(val<20>(w, S2, C2), val<28>(w, S2, C2));
+        o.x = two(pair<0>(w), s1.SC, NSC1, s1.MH, s1.ML, D);            // bytes 0 and 2, low nibbles
+        o.y = two(pair<8>(w), s1.SC, NSC1, s1.MH, s1.ML, D);            // bytes 1 and 3, low nibbles
+        o.z = two(pair<4>(w), s2.SC, NSC2, s2.MH, s2.ML, D);            // bytes 0 and 2, high nibbles
+        o.w = two(pair<12>(w), s2.SC, NSC2, s2.MH, s2.ML, D);           // bytes 1 and 3, high nibbles
         return o;
     }
-    // Once per 256-column chunk: lane t of a row's four lanes turns the header into the constants of sub-blocks 2 t and
-    // 2 t + 1 (S = 16 d sc, C = -(S + dmin m)); a step fetches the pair it needs from lane J with shuffles.
-    struct Pre { float S[2], C[2]; };
+    // Once per 256-column chunk: every lane keeps its row's (d, d); lane t of a row's four lanes turns the header into 16 sc
+    // and the two terms of -dmin m of sub-blocks 2 t and 2 t + 1 (both halves of a half2); a step fetches the pair it needs
+    // from lane J with shuffles.
+    struct Pre { uint32_t SC[2], MH[2], ML[2], D; };
     __device__ __forceinline__ static Pre prep(const uint8_t * chunk, int lane, int r) {
         const int g = lane >> 2, t = lane & 3;
         const uint4 h = *reinterpret_cast<const uint4 *>(chunk + 2048 + 16 * (g + 8 * r));
-        const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
-        const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
         // bytes of the 12-byte scale field: s[i] = byte i of (h.y, h.z, h.w)
         const uint32_t hi = h.w;
+        const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
         Pre p;
+        p.D = (h.x & 0xffffu) * 0x10001u;
 #pragma unroll
         for (int b = 0; b < 2; ++b) {
             const int jj = 2 * t + b;
@@ -113,8 +121,11 @@ template <> struct Dec<T_Q4_K> {
                 sc = (q & 15u) | ((((h.y >> (8 * (jj - 4))) & 255u) >> 6) << 4);
                 mn = (q >> 4) | ((((h.z >> (8 * (jj - 4))) & 255u) >> 6) << 4);
             }
-            p.S[b] = 16.f * (d * float(sc));
-            p.C[b] = -(p.S[b] + dmin * float(mn));
+            p.SC[b] = h2_bits(__float2half2_rn(float(16u * sc)));
+            const float m = -(dmin * float(mn));                        // exact in fp32 (11 x 6 bits)
+            const __half mh = __float2half_rn(m);
+            p.MH[b] = h2_bits(__half2half2(mh));
+            p.ML[b] = h2_bits(__float2half2_rn(m - __half2float(mh)));
         }
         return p;
     }
@@ -122,34 +133,52 @@ template <> struct Dec<T_Q4_K> {
         const int g = lane >> 2, t = lane & 3, src = (lane & ~3) | J;
         const uint4 q4 = *reinterpret_cast<const uint4 *>(chunk + 512 * J + 16 * lane);
         const uint32_t wa = r ? q4.z : q4.x, wb = r ? q4.w : q4.y;      // this warp's row: g + 8 r
-        const float S1 = __shfl_sync(0xffffffffu, pre.S[0], src), C1 = __shfl_sync(0xffffffffu, pre.C[0], src);
-        const float S2 = __shfl_sync(0xffffffffu, pre.S[1], src), C2 = __shfl_sync(0xffffffffu, pre.C[1], src);
-        *core_row(dst, t, g + 8 * r) = word(wa, S1, C1, S2, C2);
-        *core_row(dst, t + 4, g + 8 * r) = word(wb, S1, C1, S2, C2);
+        Sub s1, s2;
+        s1.SC = bits_h2(__shfl_sync(0xffffffffu, pre.SC[0], src)); s2.SC = bits_h2(__shfl_sync(0xffffffffu, pre.SC[1], src));
+        s1.MH = bits_h2(__shfl_sync(0xffffffffu, pre.MH[0], src)); s2.MH = bits_h2(__shfl_sync(0xffffffffu, pre.MH[1], src));
+        s1.ML = bits_h2(__shfl_sync(0xffffffffu, pre.ML[0], src)); s2.ML = bits_h2(__shfl_sync(0xffffffffu, pre.ML[1], src));
+        *core_row(dst, t, g + 8 * r) = word(wa, s1, s2, bits_h2(pre.D));
+        *core_row(dst, t + 4, g + 8 * r) = word(wb, s1, s2, bits_h2(pre.D));
     }
 };
 
-// IQ3_S held as 4-bit codes (formats.cuh, Fmt<T_IQ3S4>): the tile has the Q4_K shape and a weight is db (2 n - 15), so the
-// Q4_K word decoder serves it with S = 32 db and C = -47 db (S (1 + n / 16) + C = db (2 n - 15), exact in fp32)
+// IQ3_S held as 4-bit codes (formats.cuh, Fmt<T_IQ3S4>): the tile has the Q4_K shape and a weight is d (1 + 2 s) (2 n - 15):
+// t = (1 + n / 16) (32 (1 + 2 s)) - 47 (1 + 2 s) = (1 + 2 s) (2 n - 15), an integer below 512 from exact constants, then t d
+// (one rounding)
 template <> struct Dec<T_IQ3S4> {
     static constexpr int TAB_BYTES = 0;
     __device__ static void init(void *, int, int) {}
-    using Pre = Dec<T_Q4_K>::Pre;
+    struct Pre { uint32_t SC[2], C[2], D; };
     __device__ __forceinline__ static Pre prep(const uint8_t * chunk, int lane, int r) {
         const int g = lane >> 2, t = lane & 3, row = g + 8 * r;
         const uint32_t sc = *reinterpret_cast<const uint32_t *>(chunk + 2048 + 4 * row);
-        const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(chunk + 2112 + 2 * row)));
         Pre p;
+        p.D = uint32_t(*reinterpret_cast<const unsigned short *>(chunk + 2112 + 2 * row)) * 0x10001u;
 #pragma unroll
         for (int b = 0; b < 2; ++b) {
-            const float db = d * float(1 + 2 * int((sc >> (4 * (2 * t + b))) & 15u));
-            p.S[b] = 32.f * db;
-            p.C[b] = -47.f * db;
+            const float s1 = float(1 + 2 * int((sc >> (4 * (2 * t + b))) & 15u));
+            p.SC[b] = h2_bits(__float2half2_rn(32.f * s1));
+            p.C[b] = h2_bits(__float2half2_rn(-47.f * s1));
         }
         return p;
     }
-    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void * tab, int r, const Pre & pre) {
-        Dec<T_Q4_K>::step<J>(chunk, lane, dst, tab, r, pre);
+    __device__ __forceinline__ static uint4 word(uint32_t w, __half2 SC1, __half2 C1, __half2 SC2, __half2 C2, __half2 D) {
+        using Q = Dec<T_Q4_K>;
+        uint4 o;
+        o.x = h2_bits(__hmul2(__hfma2(Q::pair<0>(w), SC1, C1), D));
+        o.y = h2_bits(__hmul2(__hfma2(Q::pair<8>(w), SC1, C1), D));
+        o.z = h2_bits(__hmul2(__hfma2(Q::pair<4>(w), SC2, C2), D));
+        o.w = h2_bits(__hmul2(__hfma2(Q::pair<12>(w), SC2, C2), D));
+        return o;
+    }
+    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void *, int r, const Pre & pre) {
+        const int g = lane >> 2, t = lane & 3, src = (lane & ~3) | J;
+        const uint4 q4 = *reinterpret_cast<const uint4 *>(chunk + 512 * J + 16 * lane);
+        const uint32_t wa = r ? q4.z : q4.x, wb = r ? q4.w : q4.y;      // this warp's row: g + 8 r
+        const __half2 SC1 = bits_h2(__shfl_sync(0xffffffffu, pre.SC[0], src)), C1 = bits_h2(__shfl_sync(0xffffffffu, pre.C[0], src));
+        const __half2 SC2 = bits_h2(__shfl_sync(0xffffffffu, pre.SC[1], src)), C2 = bits_h2(__shfl_sync(0xffffffffu, pre.C[1], src));
+        *core_row(dst, t, g + 8 * r) = word(wa, SC1, C1, SC2, C2, bits_h2(pre.D));
+        *core_row(dst, t + 4, g + 8 * r) = word(wb, SC1, C1, SC2, C2, bits_h2(pre.D));
     }
 };
 
@@ -207,11 +236,23 @@ template <> struct Dec<T_IQ4_NL> {
 template <> struct Dec<T_NVFP4G> {
     struct Pre {};
     __device__ __forceinline__ static Pre prep(const uint8_t *, int, int) { return Pre{}; }
-    static constexpr int TAB_BYTES = LUT_BYTES;
-    __device__ static void init(void * tab, int tid, int n) { build_lut<T_NVFP4G>(static_cast<uint32_t *>(tab), tid, n); }
-    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void * tab, int r, const Pre &) {
+    static constexpr int TAB_BYTES = 0;
+    __device__ static void init(void *, int, int) {}
+    // the eight e2m1 codes of a word -> eight fp16 values (the hardware conversion, two codes per instruction: low nibble
+    // first) times `scale`; every product of an e2m1 and an e4m3 value is exact in fp16
+    __device__ __forceinline__ static uint4 word(uint32_t w, __half2 scale) {
+        uint32_t v0, v1, v2, v3;
+        asm("{\n .reg .b8 b0, b1, b2, b3;\n mov.b32 {b0, b1, b2, b3}, %4;\n cvt.rn.f16x2.e2m1x2 %0, b0;\n cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+            " cvt.rn.f16x2.e2m1x2 %2, b2;\n cvt.rn.f16x2.e2m1x2 %3, b3;\n}" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(w));
+        uint4 o;
+        o.x = h2_bits(__hmul2(bits_h2(v0), scale));
+        o.y = h2_bits(__hmul2(bits_h2(v1), scale));
+        o.z = h2_bits(__hmul2(bits_h2(v2), scale));
+        o.w = h2_bits(__hmul2(bits_h2(v3), scale));
+        return o;
+    }
+    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void *, int r, const Pre &) {
         const int g = lane >> 2, t = lane & 3;
-        const uint32_t * lut = static_cast<const uint32_t *>(tab) + (lane & (LUT_COPIES - 1));
         const uint8_t * tile = chunk + (J >> 1) * Fmt<T_NVFP4G>::TILE;
         constexpr int P = J & 1;                                         // plane = sub-blocks 2 P, 2 P + 1 of the 128-column tile
         const uint4 q4 = *reinterpret_cast<const uint4 *>(tile + 512 * P + 16 * lane);
@@ -223,7 +264,7 @@ template <> struct Dec<T_NVFP4G> {
             for (int b = 0; b < 2; ++b) {
                 const uint32_t sbyte = (scw >> (16 * b + 8 * (t >> 1))) & 255u;       // the 16-weight group of word t
                 const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(sbyte | (sbyte << 8)), __NV_E4M3);
-                *core_row(dst, 4 * b + t, g + 8 * r) = lut_word(lut, wr[b], __half2(hr));
+                *core_row(dst, 4 * b + t, g + 8 * r) = word(wr[b], __half2(hr));
             }
         }
     }
