@@ -23,7 +23,8 @@ def cpu_keys(gating, logits, bias):
 
 
 @pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16, torch.float16))
-@pytest.mark.parametrize("n,h,e", ((1, 256, 8), (5, 1024, 32), (64, 2048, 512), (19, 512, 100)))
+# the last two sizes take the shared-memory tile kernel (bf16, 256 tokens or more): ragged token and row tiles, and the c3 prefill shape
+@pytest.mark.parametrize("n,h,e", ((1, 256, 8), (5, 1024, 32), (64, 2048, 512), (19, 512, 100), (300, 96, 70), (1024, 2048, 512)))
 def test_router_logits_vs_fp64(orc, dtype, n, h, e):
     from tqllm_b200 import moe
     g = torch.Generator()

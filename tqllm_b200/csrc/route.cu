@@ -144,6 +144,134 @@ __global__ void __launch_bounds__(RM_WARPS * 32) router_mma_k(const float * __re
     cluster.sync();                                                     // the other blocks' tiles stay alive until block 0 has read them
 }
 
+// ---- the same product for many tokens (prefill): shared-memory tiles ----
+// One block = 64 router rows x 128 tokens, 8 warps of 32 x 32 outputs, 32 columns per stage: the weights are split into
+// their three bf16 terms once per block and stage (not once per 64 tokens and warp as above) and both operands reach the
+// MMAs through ldmatrix, so a stage costs a warp 16 shared loads for its 48 MMAs. Every output is summed by one warp over
+// the whole hidden dimension in ascending column order (terms lo, mid, hi per 16 columns; 256 columns per partial sum): the
+// same bits every run.
+constexpr int RT_ROWS = 64, RT_TOK = 128, RT_K = 32, RT_THREADS = 256, RT_LD = RT_K + 8;   // row stride in shared memory: 80 bytes, conflict-free for ldmatrix
+constexpr int RT_W_STAGE = 3 * RT_ROWS * RT_LD * 2, RT_X_STAGE = RT_TOK * RT_LD * 2, RT_SMEM = 2 * (RT_W_STAGE + RT_X_STAGE);
+__device__ __forceinline__ void ldmatrix4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// (w.x, w.y) -> bf16x2 terms hi, mid, lo with hi + mid + lo = w exactly (24 significant bits); same values as split3
+__device__ __forceinline__ void split3_pair(float2 w, uint32_t & hi, uint32_t & mid, uint32_t & lo) {
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hi) : "f"(w.y), "f"(w.x));
+    const float r0 = w.x - __uint_as_float(hi << 16), r1 = w.y - __uint_as_float(hi & 0xffff0000u);
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(mid) : "f"(r1), "f"(r0));
+    const float q0 = r0 - __uint_as_float(mid << 16), q1 = r1 - __uint_as_float(mid & 0xffff0000u);
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"(q1), "f"(q0));
+}
+__global__ void __launch_bounds__(RT_THREADS) router_tile_k(const float * __restrict__ w, const float * __restrict__ shared,
+                                                             const __nv_bfloat16 * __restrict__ x, float * __restrict__ logits, int ld, int h,
+                                                             int e, int rows, int n) {
+    extern __shared__ __align__(128) uint8_t rt_smem[];
+    uint8_t * w_sm = rt_smem;                                          // [2 stages][3 terms][64 rows][RT_LD] bf16
+    uint8_t * x_sm = rt_smem + 2 * RT_W_STAGE;                         // [2 stages][128 tokens][RT_LD] bf16
+    grid_release();
+    grid_wait();                                                       // x may be the output of the launch before this one
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const int r0 = blockIdx.x * RT_ROWS, t0 = blockIdx.y * RT_TOK;
+    const int wr = warp >> 2, wc = warp & 3;                            // the warp's 32 rows x 32 tokens
+    // this thread's four float2 of a weight stage: row f / 16, columns 2 (f % 16), f = tid + 256 j
+    const float * wsrc[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int f = tid + RT_THREADS * j, row = min(r0 + (f >> 4), rows - 1);
+        wsrc[j] = (row == e ? shared : w + size_t(row) * h) + 2 * (f & 15);
+    }
+    // this thread's two 16-byte pieces of an activation stage: token p / 4, piece p % 4, p = tid + 256 j
+    const __nv_bfloat16 * xsrc[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int p = tid + RT_THREADS * j;
+        xsrc[j] = x + size_t(min(t0 + (p >> 2), n - 1)) * h + 8 * (p & 3);
+    }
+    auto load_x = [&](int stage, int k0) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int p = tid + RT_THREADS * j;
+            const uint32_t dst = uint32_t(__cvta_generic_to_shared(x_sm + stage * RT_X_STAGE + ((p >> 2) * RT_LD + 8 * (p & 3)) * 2));
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(__cvta_generic_to_global(xsrc[j] + k0)) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float2 wreg[4];
+    auto load_w = [&](int k0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) wreg[j] = *reinterpret_cast<const float2 *>(wsrc[j] + k0);
+    };
+    auto store_w = [&](int stage) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int f = tid + RT_THREADS * j;
+            uint32_t hi, mid, lo;
+            split3_pair(wreg[j], hi, mid, lo);
+            uint32_t * dst = reinterpret_cast<uint32_t *>(w_sm + stage * RT_W_STAGE + ((f >> 4) * RT_LD + 2 * (f & 15)) * 2);
+            dst[0] = hi;
+            dst[RT_ROWS * RT_LD / 2] = mid;
+            dst[2 * RT_ROWS * RT_LD / 2] = lo;
+        }
+    };
+    // acc sums 256 columns at a time and is then added to tot: the rounding error of a long fp32 chain grows with its
+    // length, and the router's tolerance against an fp64 dot (3e-6) leaves no room for a 2048-term chain
+    float acc[2][4][4], tot[2][4][4];
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[a][b][c] = tot[a][b][c] = 0.f;
+    // ldmatrix addresses of this lane inside a stage: A rows 32 wr + 16 rt + (lane % 16), columns 8 (lane / 16);
+    // B tokens 32 wc + 16 pr + (lane % 8) + 8 (lane / 16), columns 8 ((lane / 8) % 2)
+    const uint32_t w_base = uint32_t(__cvta_generic_to_shared(w_sm)) + ((32 * wr + (lane & 15)) * RT_LD + 8 * (lane >> 4)) * 2;
+    const uint32_t x_base = uint32_t(__cvta_generic_to_shared(x_sm)) + ((32 * wc + (lane & 7) + 8 * (lane >> 4)) * RT_LD + 8 * ((lane >> 3) & 1)) * 2;
+    const int stages = h / RT_K;
+    load_x(0, 0);
+    load_w(0);
+    for (int s = 0; s < stages; ++s) {
+        const int buf = s & 1;
+        store_w(buf);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                               // stage s is complete; every warp is done with stage s - 1
+        if (s + 1 < stages) { load_x(buf ^ 1, (s + 1) * RT_K); load_w((s + 1) * RT_K); }
+#pragma unroll
+        for (int kk = 0; kk < RT_K / 16; ++kk) {
+            uint32_t b[2][4];                                          // token tiles (0, 1) and (2, 3): b0, b1 of each
+#pragma unroll
+            for (int pr = 0; pr < 2; ++pr) ldmatrix4(b[pr], x_base + buf * RT_X_STAGE + (16 * pr * RT_LD + 16 * kk) * 2);
+#pragma unroll
+            for (int term = 2; term >= 0; --term) {                    // smallest terms first
+#pragma unroll
+                for (int rt = 0; rt < 2; ++rt) {
+                    uint32_t a[4];
+                    ldmatrix4(a, w_base + buf * RT_W_STAGE + ((term * RT_ROWS + 16 * rt) * RT_LD + 16 * kk) * 2);
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt) mma_bf16_acc(acc[rt][nt], a, b[nt >> 1][2 * (nt & 1)], b[nt >> 1][2 * (nt & 1) + 1]);
+                }
+            }
+        }
+        if ((s & 7) == 7 || s + 1 == stages) {
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) { tot[a][b][c] += acc[a][b][c]; acc[a][b][c] = 0.f; }
+        }
+    }
+#pragma unroll
+    for (int rt = 0; rt < 2; ++rt)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int row = r0 + 32 * wr + 16 * rt + g + 8 * (c >> 1), tok = t0 + 32 * wc + 8 * nt + 2 * t + (c & 1);
+                if (row < rows && tok < n) logits[size_t(tok) * ld + row] = tot[rt][nt][c];
+            }
+}
+
 __device__ __forceinline__ void argmax_merge(float & v, int & i, float ov, int oi) {
     if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
 }
@@ -417,6 +545,11 @@ extern "C" B2MOE_API int32_t b2moe_router(const float * router_w, const float * 
     cudaStream_t s = as_stream(stream);
     if (x_dtype == B2MOE_F32)
         router_k<B2MOE_F32><<<grid, 256, 0, s>>>(router_w, shared_gate, static_cast<const float *>(x), logits, ld, hidden, experts, rows, n);
+    else if (x_dtype == B2MOE_BF16 && hidden % RT_K == 0 && n >= 2 * RT_TOK) {
+        if (cudaFuncSetAttribute(router_tile_k, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM) != cudaSuccess) return B2MOE_ERR_CUDA;
+        launch_overlapped(router_tile_k, dim3(ceil_div(rows, RT_ROWS), ceil_div(n, RT_TOK)), dim3(RT_THREADS), size_t(RT_SMEM), s, router_w, shared_gate,
+                          static_cast<const __nv_bfloat16 *>(x), logits, ld, hidden, experts, rows, n);
+    }
     else if (x_dtype == B2MOE_BF16 && hidden % 16 == 0)
     {
         // split the hidden dimension over a cluster of up to 4 blocks while every block keeps at least 256 columns
