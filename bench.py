@@ -10,7 +10,8 @@ One JSON line on stdout (rank 0):
   value      layer-tokens per second = tokens * layers / step time, inputs resident in HBM, CUDA-event timed: the K-step
              region is timed `--repeats` times and the median taken (min / max under "repeats")
   e2e        the same through host buffers: pinned-host -> device copy of the activations and device -> host copy of
-             the layer outputs inside the timed region
+             the layer outputs of every step inside the timed region; two buffer sets, the copies on their own streams
+             (they overlap the neighbouring steps' layer calls); serial_ms_per_step = everything on one stream
   roofline   the dominant kernel (the grouped gate/up + SwiGLU product, timed alone): GGUF block bytes of the gate and
              up matrices of the experts it touched / its CUDA-event duration, against the measured HBM copy bandwidth
   sweep, workloads   extra records, not the headline: the decode batch sweep (1 / 4 / 16 tokens) of the same layers and
@@ -272,6 +273,42 @@ def graph_of(torch, stream, fn):
     return g
 
 
+def pipelined_e2e_ms(torch, stream, x_host, xs, outs_dev, outs_host, runs, n):
+    """ms per step of n end-to-end steps with the copies on their own streams: step i's host -> device copy, its layer calls
+    and its device -> host copy run in that order, but the copies of one step overlap the layer calls of its neighbours (two
+    sets of device and host buffers, taken in turn). Every copy lies between the two events on the launching stream."""
+    s_in, s_out = torch.cuda.Stream(stream.device), torch.cuda.Stream(stream.device)
+    ev = lambda: [torch.cuda.Event(), torch.cuda.Event()]
+    in_done, comp_done, out_done = ev(), ev(), ev()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for st in (stream, s_in, s_out):
+        st.synchronize()
+    e0.record(stream)
+    s_in.wait_event(e0)
+    for i in range(n):
+        b = i & 1
+        with torch.cuda.stream(s_in):
+            if i >= 2:
+                s_in.wait_event(comp_done[b])                          # step i - 2 has read this input buffer
+            xs[b].copy_(x_host, non_blocking=True)
+            in_done[b].record(s_in)
+        stream.wait_event(in_done[b])
+        if i >= 2:
+            stream.wait_event(out_done[b])                             # step i - 2's outputs have left this output buffer
+        with torch.cuda.stream(stream):
+            runs[b]()
+            comp_done[b].record(stream)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(comp_done[b])
+            outs_host[b].copy_(outs_dev[b], non_blocking=True)
+            out_done[b].record(s_out)
+    for b in range(min(n, 2)):
+        stream.wait_event(out_done[b])
+    e1.record(stream)
+    stream.synchronize()
+    return e0.elapsed_time(e1) / n
+
+
 def event_ms(torch, stream, fn, n):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     stream.synchronize()
@@ -442,7 +479,25 @@ def run_b200(args):
         for _ in range(min(args.warmup, 3)):
             step_e2e()
         reg_e2e = [event_ms(torch, stream, step_e2e, args.steps) for _ in range(max(1, min(R, 10)))]
-        ms_step, ms_e2e = statistics.median(reg), statistics.median(reg_e2e)
+        ms_step, ms_e2e_serial = statistics.median(reg), statistics.median(reg_e2e)
+        # the same with a second set of buffers and the copies on their own streams (the figure that is reported)
+        x_b, out_all_b = torch.empty_like(x), torch.empty_like(out_all)
+        out_host_b = torch.empty_like(out_host).pin_memory()
+
+        def step_b():
+            for l, lay in enumerate(layers):
+                lay.forward(x_b, out=out_all_b[l])
+
+        x_b.copy_(x)
+        step_b()
+        stream.synchronize()
+        run_b = graph_of(torch, stream, step_b).replay if args.graph else step_b
+        pipe = (torch, stream, x_host, [x, x_b], [out_all, out_all_b], [out_host, out_host_b], [run, run_b])
+        pipelined_e2e_ms(*pipe, max(args.steps, 4))
+        reg_e2e = [pipelined_e2e_ms(*pipe, args.steps) for _ in range(max(1, min(R, 10)))]
+        ms_e2e = statistics.median(reg_e2e)
+        if not torch.equal(out_host, out_host_b):
+            raise SystemExit("bench.py: the two buffer sets of the end-to-end leg disagree")
 
         # stage timings: every stage of a layer alone (CUDA events on the launching stream around graph replays), averaged over the layers
         prods = [expert_products(torch, moe, lib, C, lay, x, shape, stream) for lay in layers]
@@ -582,12 +637,12 @@ def run_b200(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8+f32", "data": "synthetic",
         "config": {"workload": workload_name(shape, T, L), "tokens": T, "layers": L, "router_scale": rscale, "parallelism": "single GPU",
-                   "l2": "per-step expert weights (GBs) exceed the 126 MB L2; no flush needed", "cuda_graph": graphed, "e2e_leg": "pinned H2D copy, the same graph replay, one D2H copy of all layer outputs" if graphed else "pinned H2D copy, direct launches, one D2H copy", "dependent_launch_overlap": bool(args.overlap),
+                   "l2": "per-step expert weights (GBs) exceed the 126 MB L2; no flush needed", "cuda_graph": graphed, "e2e_leg": ("every step: pinned H2D copy of its tokens, " + ("the same graph replay" if graphed else "direct launches") + ", one D2H copy of all layer outputs; two buffer sets taken in turn, copies on their own streams so that they overlap the neighbouring steps' layer calls; e2e.serial_ms_per_step = the same on one stream"), "dependent_launch_overlap": bool(args.overlap),
                    "activations": "bf16 in, bf16 out; expert products on integer tensor-core MMA over 15-bit fixed-point activations, fp32 sums",
                    "iq3s_bank_layout": args.iq3s_layout},
         "repeats": {"n": len(reg), "ms_per_step_median": ms_step, "ms_per_step_min": min(reg), "ms_per_step_max": max(reg),
                     "e2e_n": len(reg_e2e), "e2e_min": min(reg_e2e), "e2e_max": max(reg_e2e)},
-        "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": x_host.numel() * 2,
+        "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e, "serial_ms_per_step": ms_e2e_serial, "h2d_bytes_per_step": x_host.numel() * 2,
                 "d2h_bytes_per_step": out_host.numel() * 2},
         "gpu_launches": args.steps * launches_per_step, "launches_per_step": launches_per_step,
         "roofline": {"bound": bound, "kernel": "grouped gate/up + SwiGLU product (its launch alone)", "achieved": achieved, "peak": peak, "unit": roof_unit,
