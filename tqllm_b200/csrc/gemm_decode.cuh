@@ -45,9 +45,9 @@ __device__ __forceinline__ uint4 * core_row(uint8_t * base, int core, int r16) {
     return reinterpret_cast<uint4 *>(base + core * A_LBO + (r16 >> 3) * 128 + (r16 & 7) * 16);
 }
 
-// 256-entry table byte -> half2(value of the low nibble, value of the high nibble), eight interleaved copies
-// (entry b of copy c at word 8 b + c) so that the lanes of a warp spread over the banks
-constexpr int LUT_COPIES = 8, LUT_BYTES = 256 * LUT_COPIES * 4;
+// 256-entry table byte -> half2(value of the low nibble, value of the high nibble), sixteen interleaved copies
+// (entry b of copy c at word 16 b + c) so that the lanes of a warp spread over the banks
+constexpr int LUT_COPIES = 16, LUT_BYTES = 256 * LUT_COPIES * 4;      // 16 KB: two lanes share a copy (8 copies: c5 gate/up 3.65 ms, 16: 3.47)
 template <uint32_t T> __device__ inline void build_lut(uint32_t * lut, int tid, int nthreads) {
     for (int i = tid; i < 256 * LUT_COPIES; i += nthreads) {
         const int b = i / LUT_COPIES;
