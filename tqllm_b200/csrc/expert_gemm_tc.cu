@@ -331,8 +331,10 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
                 if (live && !__all_sync(0xffffffffu, bar_wait(my_full + 8 * slot, (gc / RAW_SLOTS) & 1u, DEC_BACKOFF))) { ok = false; break; }
                 const int steps = min(4, ksteps - 4 * c);
                 typename gdec::Dec<T>::Pre pre[NMAT];                  // per-chunk constants of the decoder
-                if (live) pre[0] = gdec::Dec<T>::prep(my_raw + (slot * NMAT + 0) * CB, lane, half);
-                if (live1) pre[1] = gdec::Dec<T>::prep(my_raw + (slot * NMAT + 1) * CB, lane, half);
+                const uint8_t * chunk0 = my_raw + (slot * NMAT + 0) * CB, * chunk1 = my_raw + (slot * NMAT + 1) * CB;
+                typename gdec::Dec<T>::Raw rw[NMAT];                   // the raw words of the step that comes next
+                if (live) { pre[0] = gdec::Dec<T>::prep(chunk0, lane, half); rw[0] = gdec::Dec<T>::template load<0>(chunk0, lane, half); }
+                if (live1) { pre[1] = gdec::Dec<T>::prep(chunk1, lane, half); rw[1] = gdec::Dec<T>::template load<0>(chunk1, lane, half); }
                 // the (up to) four 64-column steps of the chunk, written out so that every step is straight-line code with its
                 // column offset a constant and the lane's row / table / scale addresses computed once per chunk
                 auto one_step = [&](auto J) {
@@ -340,8 +342,25 @@ __global__ void __launch_bounds__(G_THREADS, 1) gemm_tc_k(const GemmArgs p) {
                     if (j >= steps || !ok) return;
                     const uint32_t sa = gk % A_STAGES;
                     if (gk >= A_STAGES && !__all_sync(0xffffffffu, bar_wait(a_empty + 8 * sa, ((gk / A_STAGES) - 1) & 1u, DEC_BACKOFF))) { ok = false; return; }
-                    if (live) gdec::Dec<T>::template step<j>(my_raw + (slot * NMAT + 0) * CB, lane, a_st + (sa * NMAT + 0) * A_MAT + 2 * tw * 128, dec_tab, half, pre[0]);
-                    if (live1) gdec::Dec<T>::template step<j>(my_raw + (slot * NMAT + 1) * CB, lane, a_st + (sa * NMAT + 1) * A_MAT + 2 * tw * 128, dec_tab, half, pre[1]);
+                    const int row16 = (lane >> 2) + 8 * half, tq = lane & 3;
+                    if (live) {
+                        uint4 o[2];
+                        gdec::Dec<T>::template compute<j>(rw[0], chunk0, lane, dec_tab, half, pre[0], o);
+                        uint8_t * dst = a_st + (sa * NMAT + 0) * A_MAT + 2 * tw * 128;
+                        *gdec::core_row(dst, tq, row16) = o[0];
+                        *gdec::core_row(dst, tq + 4, row16) = o[1];
+                    }
+                    if (live1) {
+                        uint4 o[2];
+                        gdec::Dec<T>::template compute<j>(rw[1], chunk1, lane, dec_tab, half, pre[1], o);
+                        uint8_t * dst = a_st + (sa * NMAT + 1) * A_MAT + 2 * tw * 128;
+                        *gdec::core_row(dst, tq, row16) = o[0];
+                        *gdec::core_row(dst, tq + 4, row16) = o[1];
+                    }
+                    if (j + 1 < 4 && j + 1 < steps) {                  // the next step's raw words, in flight across the hand-off and the next wait
+                        if (live) rw[0] = gdec::Dec<T>::template load<(j + 1) & 3>(chunk0, lane, half);
+                        if (live1) rw[1] = gdec::Dec<T>::template load<(j + 1) & 3>(chunk1, lane, half);
+                    }
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0) bar_arrive(a_full + 8 * sa);

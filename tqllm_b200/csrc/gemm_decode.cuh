@@ -2,7 +2,11 @@
 //
 // Two warps own a row tile (warp half r decodes rows g + 8 r); lane L = 4 g + t holds, in the bank's lane-major
 // layout, the code words of rows g and g + 8 (formats.cuh). Every code word (or pair of IQ3_S grid entries) decodes to eight fp16 values = one 16-byte row of one
-// core matrix, so a lane writes whole core-matrix rows with 16-byte stores. Which eight columns a word covers depends
+// core matrix, so a lane writes whole core-matrix rows with 16-byte stores: per step the rows of cores t and t + 4.
+// A decoder is two halves: load<J> reads the lane's raw words of step J into registers, compute<J> turns them into the
+// two 16-byte rows; the kernel issues the loads of the next step before it hands the current one over, so that their
+// latency passes during the hand-off and the next wait (the compiler cannot move them itself: it cannot prove that the
+// operand stores and the raw loads do not alias, and the waits are barriers to it). Which eight columns a word covers depends
 // on the format (a Q4_K byte holds column c of two different sub-blocks, an IQ4 byte columns c and c + 16, ...): rather
 // than shuffling values between lanes, the GEMM permutes the 64 columns of a step — colmap<T>(pos) is the column stored
 // at operand position pos — and the activation rows are written in the same order (the sum over K does not care).
@@ -129,16 +133,18 @@ template <> struct Dec<T_Q4_K> {
         }
         return p;
     }
-    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void *, int r, const Pre & pre) {
-        const int g = lane >> 2, t = lane & 3, src = (lane & ~3) | J;
-        const uint4 q4 = *reinterpret_cast<const uint4 *>(chunk + 512 * J + 16 * lane);
-        const uint32_t wa = r ? q4.z : q4.x, wb = r ? q4.w : q4.y;      // this warp's row: g + 8 r
+    struct Raw { uint2 w; };                                          // the code words of cores t and t + 4 of this warp's row (g + 8 r)
+    template <int J> __device__ __forceinline__ static Raw load(const uint8_t * chunk, int lane, int r) {
+        return Raw{*reinterpret_cast<const uint2 *>(chunk + 512 * J + 16 * lane + 8 * r)};
+    }
+    template <int J> __device__ __forceinline__ static void compute(const Raw & raw, const uint8_t *, int lane, const void *, int, const Pre & pre, uint4 (&o)[2]) {
+        const int src = (lane & ~3) | J;
         Sub s1, s2;
         s1.SC = bits_h2(__shfl_sync(0xffffffffu, pre.SC[0], src)); s2.SC = bits_h2(__shfl_sync(0xffffffffu, pre.SC[1], src));
         s1.MH = bits_h2(__shfl_sync(0xffffffffu, pre.MH[0], src)); s2.MH = bits_h2(__shfl_sync(0xffffffffu, pre.MH[1], src));
         s1.ML = bits_h2(__shfl_sync(0xffffffffu, pre.ML[0], src)); s2.ML = bits_h2(__shfl_sync(0xffffffffu, pre.ML[1], src));
-        *core_row(dst, t, g + 8 * r) = word(wa, s1, s2, bits_h2(pre.D));
-        *core_row(dst, t + 4, g + 8 * r) = word(wb, s1, s2, bits_h2(pre.D));
+        o[0] = word(raw.w.x, s1, s2, bits_h2(pre.D));
+        o[1] = word(raw.w.y, s1, s2, bits_h2(pre.D));
     }
 };
 
@@ -171,14 +177,14 @@ template <> struct Dec<T_IQ3S4> {
         o.w = h2_bits(__hmul2(__hfma2(Q::pair<12>(w), SC2, C2), D));
         return o;
     }
-    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void *, int r, const Pre & pre) {
-        const int g = lane >> 2, t = lane & 3, src = (lane & ~3) | J;
-        const uint4 q4 = *reinterpret_cast<const uint4 *>(chunk + 512 * J + 16 * lane);
-        const uint32_t wa = r ? q4.z : q4.x, wb = r ? q4.w : q4.y;      // this warp's row: g + 8 r
+    using Raw = Dec<T_Q4_K>::Raw;
+    template <int J> __device__ __forceinline__ static Raw load(const uint8_t * chunk, int lane, int r) { return Dec<T_Q4_K>::load<J>(chunk, lane, r); }
+    template <int J> __device__ __forceinline__ static void compute(const Raw & raw, const uint8_t *, int lane, const void *, int, const Pre & pre, uint4 (&o)[2]) {
+        const int src = (lane & ~3) | J;
         const __half2 SC1 = bits_h2(__shfl_sync(0xffffffffu, pre.SC[0], src)), C1 = bits_h2(__shfl_sync(0xffffffffu, pre.C[0], src));
         const __half2 SC2 = bits_h2(__shfl_sync(0xffffffffu, pre.SC[1], src)), C2 = bits_h2(__shfl_sync(0xffffffffu, pre.C[1], src));
-        *core_row(dst, t, g + 8 * r) = word(wa, SC1, C1, SC2, C2, bits_h2(pre.D));
-        *core_row(dst, t + 4, g + 8 * r) = word(wb, SC1, C1, SC2, C2, bits_h2(pre.D));
+        o[0] = word(raw.w.x, SC1, C1, SC2, C2, bits_h2(pre.D));
+        o[1] = word(raw.w.y, SC1, C1, SC2, C2, bits_h2(pre.D));
     }
 };
 
@@ -202,13 +208,14 @@ template <> struct Dec<T_IQ4_XS> {
         }
         return p;
     }
-    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void * tab, int r, const Pre & pre) {
-        const int g = lane >> 2, t = lane & 3, src = (lane & ~3) | J;
+    using Raw = Dec<T_Q4_K>::Raw;
+    template <int J> __device__ __forceinline__ static Raw load(const uint8_t * chunk, int lane, int r) { return Dec<T_Q4_K>::load<J>(chunk, lane, r); }
+    template <int J> __device__ __forceinline__ static void compute(const Raw & raw, const uint8_t *, int lane, const void * tab, int, const Pre & pre, uint4 (&o)[2]) {
+        const int src = (lane & ~3) | J;
         const uint32_t * lut = static_cast<const uint32_t *>(tab) + (lane & (LUT_COPIES - 1));
-        const uint4 q4 = *reinterpret_cast<const uint4 *>(chunk + 512 * J + 16 * lane);
         const uint32_t d0 = __shfl_sync(0xffffffffu, pre.dl[0], src), d1 = __shfl_sync(0xffffffffu, pre.dl[1], src);
-        *core_row(dst, t, g + 8 * r) = lut_word(lut, r ? q4.z : q4.x, bits_h2(d0));
-        *core_row(dst, 4 + t, g + 8 * r) = lut_word(lut, r ? q4.w : q4.y, bits_h2(d1));
+        o[0] = lut_word(lut, raw.w.x, bits_h2(d0));
+        o[1] = lut_word(lut, raw.w.y, bits_h2(d1));
     }
 };
 
@@ -217,18 +224,22 @@ template <> struct Dec<T_IQ4_NL> {
     __device__ __forceinline__ static Pre prep(const uint8_t *, int, int) { return Pre{}; }
     static constexpr int TAB_BYTES = LUT_BYTES;
     __device__ static void init(void * tab, int tid, int n) { build_lut<T_IQ4_NL>(static_cast<uint32_t *>(tab), tid, n); }
-    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void * tab, int r, const Pre &) {
-        const int g = lane >> 2, t = lane & 3;
-        const uint32_t * lut = static_cast<const uint32_t *>(tab) + (lane & (LUT_COPIES - 1));
+    struct Raw { uint32_t w[2]; unsigned short d[2]; };                // per 32-column tile of the step: the row's code word and its fp16 scale
+    template <int J> __device__ __forceinline__ static Raw load(const uint8_t * chunk, int lane, int r) {
+        const int g = lane >> 2;
+        Raw raw;
 #pragma unroll
         for (int b = 0; b < 2; ++b) {                                   // the step's two 32-column tiles
             const uint8_t * tile = chunk + (2 * J + b) * Fmt<T_IQ4_NL>::TILE;
-            const uint2 w = *reinterpret_cast<const uint2 *>(tile + 8 * lane);
-            {
-                const __half dh = __ushort_as_half(*reinterpret_cast<const unsigned short *>(tile + 256 + 2 * (g + 8 * r)));
-                *core_row(dst, 4 * b + t, g + 8 * r) = lut_word(lut, r ? w.y : w.x, __half2half2(dh));
-            }
+            raw.w[b] = *reinterpret_cast<const uint32_t *>(tile + 8 * lane + 4 * r);
+            raw.d[b] = *reinterpret_cast<const unsigned short *>(tile + 256 + 2 * (g + 8 * r));
         }
+        return raw;
+    }
+    template <int J> __device__ __forceinline__ static void compute(const Raw & raw, const uint8_t *, int lane, const void * tab, int, const Pre &, uint4 (&o)[2]) {
+        const uint32_t * lut = static_cast<const uint32_t *>(tab) + (lane & (LUT_COPIES - 1));
+#pragma unroll
+        for (int b = 0; b < 2; ++b) o[b] = lut_word(lut, raw.w[b], __half2half2(__ushort_as_half(raw.d[b])));
     }
 };
 
@@ -251,21 +262,24 @@ template <> struct Dec<T_NVFP4G> {
         o.w = h2_bits(__hmul2(bits_h2(v3), scale));
         return o;
     }
-    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void *, int r, const Pre &) {
-        const int g = lane >> 2, t = lane & 3;
+    struct Raw { uint2 w; uint32_t scw; };                            // the row's two code words of the step and its four E4M3 group scales
+    template <int J> __device__ __forceinline__ static Raw load(const uint8_t * chunk, int lane, int r) {
+        const int g = lane >> 2;
         const uint8_t * tile = chunk + (J >> 1) * Fmt<T_NVFP4G>::TILE;
         constexpr int P = J & 1;                                         // plane = sub-blocks 2 P, 2 P + 1 of the 128-column tile
-        const uint4 q4 = *reinterpret_cast<const uint4 *>(tile + 512 * P + 16 * lane);
-        const uint32_t wr[2] = {r ? q4.z : q4.x, r ? q4.w : q4.y};             // this warp's row: g + 8 r
-        {
-            const uint2 sc8 = *reinterpret_cast<const uint2 *>(tile + 1024 + 8 * (g + 8 * r));     // eight E4M3 group scales
-            const uint32_t scw = P ? sc8.y : sc8.x;                      // scales of sub-blocks 2 P (bytes 0, 1), 2 P + 1 (bytes 2, 3)
+        Raw raw;
+        raw.w = *reinterpret_cast<const uint2 *>(tile + 512 * P + 16 * lane + 8 * r);           // this warp's row: g + 8 r
+        raw.scw = *reinterpret_cast<const uint32_t *>(tile + 1024 + 8 * (g + 8 * r) + 4 * P);   // scales of sub-blocks 2 P (bytes 0, 1), 2 P + 1 (bytes 2, 3)
+        return raw;
+    }
+    template <int J> __device__ __forceinline__ static void compute(const Raw & raw, const uint8_t *, int lane, const void *, int, const Pre &, uint4 (&o)[2]) {
+        const int t = lane & 3;
+        const uint32_t wr[2] = {raw.w.x, raw.w.y};
 #pragma unroll
-            for (int b = 0; b < 2; ++b) {
-                const uint32_t sbyte = (scw >> (16 * b + 8 * (t >> 1))) & 255u;       // the 16-weight group of word t
-                const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(sbyte | (sbyte << 8)), __NV_E4M3);
-                *core_row(dst, 4 * b + t, g + 8 * r) = word(wr[b], __half2(hr));
-            }
+        for (int b = 0; b < 2; ++b) {
+            const uint32_t sbyte = (raw.scw >> (16 * b + 8 * (t >> 1))) & 255u;       // the 16-weight group of word t
+            const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(sbyte | (sbyte << 8)), __NV_E4M3);
+            o[b] = word(wr[b], __half2(hr));
         }
     }
 };
@@ -283,8 +297,10 @@ template <> struct Dec<T_IQ3_S> {
             t2[i] = make_uint2(pack_h2(float(m & 255u), float((m >> 8) & 255u)), pack_h2(float((m >> 16) & 255u), float(m >> 24)));
         }
     }
-    template <int J> __device__ __forceinline__ static void step(const uint8_t * chunk, int lane, uint8_t * dst, const void * tab, int r, const Pre &) {
-        const int g = lane >> 2, t = lane & 3;
+    struct Raw {};                                                     // 13 words a lane: read inside compute
+    template <int J> __device__ __forceinline__ static Raw load(const uint8_t *, int, int) { return Raw{}; }
+    template <int J> __device__ __forceinline__ static void compute(const Raw &, const uint8_t * chunk, int lane, const void * tab, int r, const Pre &, uint4 (&out)[2]) {
+        const int g = lane >> 2;
         const uint2 * mags = static_cast<const uint2 *>(tab);
         uint32_t w[13];
         {
@@ -319,7 +335,7 @@ template <> struct Dec<T_IQ3_S> {
                     o[2 * jj] = h2_bits(__hmul2(__hmul2(bits_h2(m.x), s2), d2)) ^ ((sg << (15 - R)) & 0x80008000u);
                     o[2 * jj + 1] = h2_bits(__hmul2(__hmul2(bits_h2(m.y), s2), d2)) ^ ((R <= 7 ? sg << (7 - R) : sg >> (R - 7)) & 0x80008000u);
                 }
-                *core_row(dst, 4 * b + t, row) = make_uint4(o[0], o[1], o[2], o[3]);
+                out[b] = make_uint4(o[0], o[1], o[2], o[3]);
             }
         }
     }
