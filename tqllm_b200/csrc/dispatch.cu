@@ -42,7 +42,16 @@ __global__ void dispatch_scan_k(int * __restrict__ hist, int chunks, int e, int 
     int * counts = plan + PLAN_HDR, * offsets = counts + e1, * active = offsets + e1 + 1;
     for (int x = threadIdx.x; x < e; x += blockDim.x) {
         int run = 0;
-        for (int c = 0; c < chunks; ++c) { const int v = hist[size_t(c) * e + x]; hist[size_t(c) * e + x] = run; run += v; }
+        // eight chunk counters at a time: the loads of a batch are independent of its stores (one load per store would wait
+        // for the store before it, since both go to the same array)
+        for (int c0 = 0; c0 < chunks; c0 += 8) {
+            int v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = c0 + i < chunks ? hist[size_t(c0 + i) * e + x] : 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (c0 + i < chunks) { hist[size_t(c0 + i) * e + x] = run; run += v[i]; }
+        }
         counts[x] = run;
     }
     if (threadIdx.x == 0) counts[e] = shared_tokens;
