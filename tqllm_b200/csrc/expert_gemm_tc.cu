@@ -72,22 +72,39 @@ constexpr size_t gemm_smem(int experts) {
 }
 
 // any activation dtype -> fp16 rows scaled by a power of two per row (one warp per row) + the inverse scales; inside every
-// 64-column step the columns are stored in the order of the format's A operand (gdec::colmap)
-template <uint32_t T>
-__global__ void rows_to_f16_k(const void * __restrict__ x, int dtype, int rows, int k, __half * __restrict__ out, float * __restrict__ inv_scale) {
+// 64-column step the columns are stored in the order of the format's A operand (gdec::colmap). Two passes over the row:
+// its largest magnitude with 16-byte loads, then (from the cache) two source columns per lane and step into one half2
+template <uint32_t T, int DT>
+__global__ void rows_to_f16_k(const typename Elem<DT>::type * __restrict__ x, int rows, int k, bool wide_loads, __half * __restrict__ out,
+                              float * __restrict__ inv_scale) {
+    using E = typename Elem<DT>::type;
+    constexpr int V = 16 / int(sizeof(E));                              // elements per 16-byte load
     const int lane = threadIdx.x & 31, row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
+    const E * xr = x + size_t(row) * k;
     float mx = 0.f;
-    for (int j = lane; j < k; j += 32) mx = fmaxf(mx, fabsf(load_act(x, dtype, size_t(row) * k + j)));
+    if (wide_loads) {                                                  // rows start on 16-byte boundaries (k is a multiple of 64)
+#pragma unroll 4
+        for (int j = lane * V; j < k; j += 32 * V) {
+            const uint4 q = *reinterpret_cast<const uint4 *>(xr + j);
+            const E * e = reinterpret_cast<const E *>(&q);
+#pragma unroll
+            for (int i = 0; i < V; ++i) mx = fmaxf(mx, fabsf(Elem<DT>::to_f(e[i])));
+        }
+    } else {
+        for (int j = lane; j < k; j += 32) mx = fmaxf(mx, fabsf(Elem<DT>::to_f(xr[j])));
+    }
     for (int d = 16; d; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
     int ex = int((__float_as_uint(mx) >> 23) & 255u) - 127;              // floor(log2(mx)) for a normal mx
     ex = (mx > 0.f && mx < 3e38f) ? max(-100, min(100, ex)) : 14;
     const float scale = __uint_as_float(uint32_t(127 + 14 - ex) << 23);  // 2^(14 - ex)
     if (lane == 0) inv_scale[row] = __uint_as_float(uint32_t(127 - 14 + ex) << 23);
-    for (int j = lane; j < k; j += 32)
-        out[size_t(row) * k + j] = __float2half_rn(load_act(x, dtype, size_t(row) * k + (j & ~63) + gdec::colmap<T>(j & 63)) * scale);
+    const int c0 = gdec::colmap<T>(2 * lane), c1 = gdec::colmap<T>(2 * lane + 1);       // source columns of this lane's two positions
+    __half2 * orow = reinterpret_cast<__half2 *>(out + size_t(row) * k) + lane;
+#pragma unroll 4
+    for (int gb = 0; gb < k; gb += 64)
+        orow[gb >> 1] = __floats2half2_rn(Elem<DT>::to_f(xr[gb + c0]) * scale, Elem<DT>::to_f(xr[gb + c1]) * scale);
 }
-
 
 // MODE 0: act[a][r] = silu(gate_r . x_tok(a)) * (up_r . x_tok(a));  MODE 1: y[a][r] = down_r . act[a]
 template <uint32_t T, int MODE, int NT>
@@ -436,18 +453,28 @@ size_t gemm_smem_of(uint32_t type, int experts) {
     }
     return ~size_t(0);
 }
-int32_t convert_rows(uint32_t type, const void * x, int dtype, int rows, int k, __half * out, float * inv, cudaStream_t s) {
+template <uint32_t T>
+int32_t convert_rows_t(const void * x, int dtype, int rows, int k, __half * out, float * inv, cudaStream_t s) {
     const int blocks = ceil_div(rows, 8);
-    switch (type) {
-        case T_Q4_K: rows_to_f16_k<T_Q4_K><<<blocks, 256, 0, s>>>(x, dtype, rows, k, out, inv); break;
-        case T_IQ3_S: rows_to_f16_k<T_IQ3_S><<<blocks, 256, 0, s>>>(x, dtype, rows, k, out, inv); break;
-        case T_IQ3S4: rows_to_f16_k<T_IQ3S4><<<blocks, 256, 0, s>>>(x, dtype, rows, k, out, inv); break;
-        case T_IQ4_XS: rows_to_f16_k<T_IQ4_XS><<<blocks, 256, 0, s>>>(x, dtype, rows, k, out, inv); break;
-        case T_IQ4_NL: rows_to_f16_k<T_IQ4_NL><<<blocks, 256, 0, s>>>(x, dtype, rows, k, out, inv); break;
-        case T_NVFP4G: rows_to_f16_k<T_NVFP4G><<<blocks, 256, 0, s>>>(x, dtype, rows, k, out, inv); break;
-        default: return B2MOE_ERR_FORMAT;
+    const bool wide = aligned16(x);
+    switch (dtype) {
+        case B2MOE_F32: rows_to_f16_k<T, B2MOE_F32><<<blocks, 256, 0, s>>>(static_cast<const float *>(x), rows, k, wide, out, inv); break;
+        case B2MOE_F16: rows_to_f16_k<T, B2MOE_F16><<<blocks, 256, 0, s>>>(static_cast<const __half *>(x), rows, k, wide, out, inv); break;
+        case B2MOE_BF16: rows_to_f16_k<T, B2MOE_BF16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16 *>(x), rows, k, wide, out, inv); break;
+        default: return B2MOE_ERR_SHAPE;
     }
     return launch_status();
+}
+int32_t convert_rows(uint32_t type, const void * x, int dtype, int rows, int k, __half * out, float * inv, cudaStream_t s) {
+    switch (type) {
+        case T_Q4_K: return convert_rows_t<T_Q4_K>(x, dtype, rows, k, out, inv, s);
+        case T_IQ3_S: return convert_rows_t<T_IQ3_S>(x, dtype, rows, k, out, inv, s);
+        case T_IQ3S4: return convert_rows_t<T_IQ3S4>(x, dtype, rows, k, out, inv, s);
+        case T_IQ4_XS: return convert_rows_t<T_IQ4_XS>(x, dtype, rows, k, out, inv, s);
+        case T_IQ4_NL: return convert_rows_t<T_IQ4_NL>(x, dtype, rows, k, out, inv, s);
+        case T_NVFP4G: return convert_rows_t<T_NVFP4G>(x, dtype, rows, k, out, inv, s);
+    }
+    return B2MOE_ERR_FORMAT;
 }
 
 }  // namespace
