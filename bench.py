@@ -62,6 +62,8 @@ def parse():
     p.add_argument("--iq3s-layout", default="codes", choices=("codes", "gguf"), help="bank layout of IQ3_S experts")
     p.add_argument("--ring", default="", help="nbuf,stages,slot_tiles: force the decode kernels' shared-memory configuration (A/B timing)")
     p.add_argument("--column-split", type=int, default=0, help="1 / 2 / 4: most warps of the decode kernels that share a row job (0: the library's default)")
+    p.add_argument("--peer-exchange", type=int, default=1, help="expert parallel: 1 = the two fixed-size exchanges of a layer over peer memory "
+                   "(the library's own put / wait kernels), 0 = NCCL collectives")
     p.add_argument("--overlap", type=int, default=1, help="0: plain stream order between the launches of a layer instead of programmatic dependent launch")
     return p.parse_args()
 
@@ -786,12 +788,29 @@ def run_ep(args, torch, dist, capi, moe, synth, rank, world, local, dev):
     eps, _ = ep_layers(torch, moe, synth, ep, shape, L, rank, world, dev, args.iq3s_layout, rscale)
     layers = [e.layer for e in eps]
     x = synth.make_tokens(shape, T, SEED + rank, dev)
-    comm = ep.TorchComm()
+    comm = ep.TorchComm()                   # NCCL: the variable-size all-to-all records, and the fallback
+    hc, exchange = comm, "NCCL all-gather dispatch + all-to-all combine"
+    if args.peer_exchange:
+        try:
+            hc = ep.PeerComm()
+            hc.all_gather(torch.zeros(4, 16, dtype=torch.uint8, device=dev))       # set-up and one exchange; every rank fails or none does
+            torch.cuda.synchronize()
+            hc.check()
+            exchange = "dispatch and combine exchanges over peer memory (put + bounded wait kernels, plain NVLink stores)"
+        except Exception as e:
+            hc, exchange = comm, exchange + f" (peer memory unavailable: {type(e).__name__}: {e})"[:200]
+    if hc is not comm:                      # the two transports must give the same bits
+        for e in eps:
+            want = ep.ep_forward(e, comm, x).clone()
+            got = ep.ep_forward(e, hc, x)
+            torch.cuda.synchronize()
+            if not torch.equal(got, want):
+                raise SystemExit("bench.py: the peer-memory exchange and the NCCL exchange disagree")
     outs = [None] * L
 
     def step_direct():
         for l, e in enumerate(eps):
-            outs[l] = ep.ep_forward(e, comm, x)
+            outs[l] = ep.ep_forward(e, hc, x)
     step = step_direct
 
     x_host = x.cpu().pin_memory()
@@ -806,7 +825,7 @@ def run_ep(args, torch, dist, capi, moe, synth, rank, world, local, dev):
         launches_per_step = int(lib.b2moe_harness_launches() - n0)
         stream.synchronize()
         if args.graph:                   # only the compute phases are captured, no collective is
-            graphed = [ep.GraphedEpForward(e, comm, x) for e in eps]
+            graphed = [ep.GraphedEpForward(e, hc, x) for e in eps]
 
             def step_graphed():
                 for l, gf in enumerate(graphed):
@@ -843,18 +862,18 @@ def run_ep(args, torch, dist, capi, moe, synth, rank, world, local, dev):
         reg_e2e = [timed(step_e2e, args.steps) for _ in range(max(1, min(R, 5)))]
         ms_step, ms_e2e = statistics.median(reg), statistics.median(reg_e2e)
         # where a layer's time goes on this rank: every phase bracketed by events (direct launches, not the graphed ones)
-        phase_us = ep.phase_times(eps[0], comm, x, reps=20)
+        phase_us = ep.phase_times(eps[0], hc, x, reps=20)
         torch.cuda.synchronize()
         n_active = sum(int(e.buf["plan"][0]) for e in eps) / L      # this rank's active experts per layer (with the shared one)
         # a fixed total batch beside the weak-scaling value: 512 tokens over all ranks, the same 4 layers
         fixed = None
         if not args.no_extras and args.workload == "c2" and 512 % world == 0:
             xf = synth.make_tokens(shape, 512 // world, SEED + 100 + rank, dev)
-            gf = [ep.GraphedEpForward(e, comm, xf) for e in eps] if args.graph else None
+            gf = [ep.GraphedEpForward(e, hc, xf) for e in eps] if args.graph else None
 
             def step_fixed():
                 for l, e in enumerate(eps):
-                    gf[l]() if gf is not None else ep.ep_forward(e, comm, xf)
+                    gf[l]() if gf is not None else ep.ep_forward(e, hc, xf)
             for _ in range(3):
                 step_fixed()
             ms_f = statistics.median([timed(step_fixed, args.steps) for _ in range(3)])
@@ -868,9 +887,11 @@ def run_ep(args, torch, dist, capi, moe, synth, rank, world, local, dev):
         workloads = {}
         for key, cfg, toks, a2a in (("c4_decode_16", "c4", 16, False), ("c4_prefill_2048", "c4", 2048, True), ("c5_prefill_8192", "c5", 8192, True)):
             try:
-                workloads[key] = ep_record(torch, dist, moe, synth, ep, comm, stream, dev, rank, world, cfg, toks, a2a, args.iq3s_layout)
+                workloads[key] = ep_record(torch, dist, moe, synth, ep, comm if a2a else hc, stream, dev, rank, world, cfg, toks, a2a, args.iq3s_layout)
             except Exception as e:                                  # every rank fails or none does: the shapes are the same everywhere
                 workloads[key] = {"error": f"{type(e).__name__}: {e}"[:300]}
+    if hc is not comm:
+        hc.check()                          # a wait that ran out would have left stale inbox contents behind
     peak, peak_kind = peaks()
     weight_bytes_step = n_active * L * shape.expert_bytes()
     achieved = weight_bytes_step / (ms_step * 1e-3) / 1e9
@@ -881,7 +902,7 @@ def run_ep(args, torch, dist, capi, moe, synth, rank, world, local, dev):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8+f32", "data": "synthetic",
             "config": {"workload": workload_name(shape, T, L), "tokens": T, "layers": L, "router_scale": rscale,
-                       "parallelism": f"ep{world}: {shape.experts // world} experts per GPU, {T} tokens per GPU, NCCL all-gather dispatch + all-to-all combine",
+                       "parallelism": f"ep{world}: {shape.experts // world} experts per GPU, {T} tokens per GPU, {exchange}",
                        "l2": "per-step expert weights exceed the 126 MB L2; no flush needed",
                        "cuda_graph": "compute phases only" if args.graph else False, "iq3s_bank_layout": args.iq3s_layout},
             "repeats": {"n": len(reg), "ms_per_step_median": ms_step, "ms_per_step_min": min(reg), "ms_per_step_max": max(reg)},

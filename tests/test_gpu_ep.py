@@ -159,6 +159,9 @@ class OneRankComm:
     """world of one: the exchanges are copies (the graphed forward must give the bits of the direct one)"""
     world, rank = 1, 0
 
+    def buffer(self, shape, dtype, device=None):
+        return torch.empty(shape, dtype=dtype, device=device)
+
     def all_gather(self, t, out=None):
         if out is None:
             return t.clone()
@@ -190,3 +193,51 @@ def test_graphed_compute_phases_equal_direct_launches():
     side.synchronize()
     assert torch.equal(got1, want)
     assert torch.equal(got2, torch.flip(want, dims=(0,)))
+
+
+def test_peer_memory_exchange_world_of_one_equals_copies():
+    """the put / wait kernels through the rank's own inbox: the same bits as plain copies, direct and graphed, and the
+    sequence numbers keep step over repeated exchanges"""
+    from tqllm_b200 import ep, moe
+    shape = synth.LayerShape("ep-peer", 512, 16, 4, 256, shared=True, types=(21, 21, 21))
+    layer, x = layer_inputs(shape, 16, 24, 5)
+    loc = moe.MoeLayer.from_synth(layer, experts=16)
+    rk = ep.CudaEpLayer(loc, layer.router_w.cuda(), 16, 1, 0, out_dtype=torch.float32)
+    xd = x.cuda()
+    want = ep.ep_forward(rk, OneRankComm(), xd).clone()
+    pc = ep.PeerComm()
+    try:
+        for _ in range(3):
+            got = ep.ep_forward(rk, pc, xd).clone()
+            assert torch.equal(got, want)
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            gf = ep.GraphedEpForward(rk, pc, xd)
+            g1 = gf().clone()
+            g2 = gf().clone()
+        side.synchronize()
+        assert torch.equal(g1, want) and torch.equal(g2, want)
+        pc.check()
+    finally:
+        pc.close()
+
+
+def test_peer_wait_runs_out_and_reports_the_sender():
+    """a counter that nobody raises: the wait returns within its bound and names the sender in the status word (no trap, the
+    context stays usable)"""
+    from tqllm_b200 import capi
+    lib = capi.lib
+    counters = torch.zeros(4, dtype=torch.int32, device="cuda")
+    counters[0] = 7
+    counters[1] = 7
+    counters[3] = 9
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    capi.check(lib.b2moe_peer_wait(counters.data_ptr(), 4, 7, status.data_ptr(), st), "b2moe_peer_wait")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 1 + 2                      # sender 2 never arrived; 0, 1 and 3 (already past 7) did
+    status.zero_()
+    counters[2] = 7
+    capi.check(lib.b2moe_peer_wait(counters.data_ptr(), 4, 7, status.data_ptr(), st), "b2moe_peer_wait")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0

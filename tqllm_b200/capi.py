@@ -72,6 +72,12 @@ SIGNATURES = {
     "b2moe_ep_pack": (_i32, [_vp, _i32, _vp, _vp, _i32, _i32, _vp, _vp, _i32, _i32, _vp, _vp]),
     "b2moe_ep_unpack": (_i32, [_vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp]),
     "b2moe_ep_return_reduce": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _i32, _i32, _vp, _i32, _vp]),
+    "b2moe_peer_alloc": (_i32, [_sz, C.POINTER(_vp), _vp]),
+    "b2moe_peer_open": (_i32, [_vp, C.POINTER(_vp)]),
+    "b2moe_peer_close": (_i32, [_vp]),
+    "b2moe_peer_free": (_i32, [_vp]),
+    "b2moe_peer_put": (_i32, [_vp, _sz, _sz, _vp, _vp, _vp, _i32, _i32, _vp]),
+    "b2moe_peer_wait": (_i32, [_vp, _i32, _i32, _vp, _vp]),
     "b2moe_route_dispatch": (_i32, [_i32, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _f32, _i32, _i32, _i32, _vp, _vp, _sz, _vp]),
     "b2moe_plan_to_groups": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp, _vp]),
     "b2moe_expert_workspace_bytes": (_sz, [_u32, _i32, _i32, _i32]),

@@ -48,6 +48,10 @@ class TorchComm:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
 
+    def buffer(self, shape, dtype, device=None) -> torch.Tensor:
+        """a result buffer for all_gather / all_to_all (PeerComm hands out its inboxes here)"""
+        return torch.empty(shape, dtype=dtype, device=device)
+
     def all_gather(self, t: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """[n, ...] per rank -> [world * n, ...] in rank order"""
         if out is None:
@@ -100,6 +104,120 @@ class TorchComm:
             for q in reqs:
                 q.wait()
         return out
+
+
+class _LibraryMemory:
+    """device memory owned by the library, handed to torch through the CUDA array interface (uint8)"""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerComm:
+    """The two fixed-size exchanges of the all-gather path over peer memory instead of library collectives: every rank owns
+    an inbox with one slot per sender; a sender stores its block into every receiver's inbox and raises a counter there
+    (b2moe_peer_put), a receiver waits, bounded, for all counters (b2moe_peer_wait). One process per GPU on one node. The
+    process group is used for set-up only (the 64-byte memory handles). all_gather / all_to_all write into a tensor obtained
+    from buffer() (or into an inbox of their own when none is given) and return it; the result stays valid until the next
+    exchange into the same buffer."""
+
+    def __init__(self, group=None):
+        from . import capi
+        self.capi, self.lib = capi, capi.lib
+        self.group = group
+        # without a process group: a world of one (the exchanges then run through the rank's own inbox)
+        self.world, self.rank = (dist.get_world_size(group), dist.get_rank(group)) if dist.is_initialized() else (1, 0)
+        self.dev = torch.device("cuda", torch.cuda.current_device())
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self.inboxes, self.own, self.opened = {}, [], []
+
+    def _symmetric(self, nbytes: int):
+        """a zeroed allocation of nbytes on every rank -> (own pointer, [every rank's pointer as seen from here])"""
+        ptr, handle = C.c_void_p(), (C.c_uint8 * 64)()
+        self.capi.check(self.lib.b2moe_peer_alloc(nbytes, C.byref(ptr), handle), "b2moe_peer_alloc")
+        self.own.append(ptr.value)
+        if self.world == 1:
+            return ptr.value, [ptr.value]
+        mine = torch.tensor(list(handle), dtype=torch.uint8, device=self.dev)
+        every = torch.empty(self.world * 64, dtype=torch.uint8, device=self.dev)
+        dist.all_gather_into_tensor(every, mine, group=self.group)
+        every = every.cpu().view(self.world, 64)
+        ptrs, failed = [], 0
+        for p in range(self.world):
+            if p == self.rank:
+                ptrs.append(ptr.value)
+                continue
+            q, h = C.c_void_p(), (C.c_uint8 * 64)(*every[p].tolist())
+            if self.lib.b2moe_peer_open(h, C.byref(q)) != 0:
+                failed = 1
+                ptrs.append(0)
+            else:
+                self.opened.append(q.value)
+                ptrs.append(q.value)
+        bad = torch.tensor([failed], dtype=torch.int32, device=self.dev)
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX, group=self.group)      # every rank learns of a failure: they give up together
+        if int(bad):
+            raise self.capi.B2moeError(self.capi.ERR_CUDA, "a peer's memory handle could not be opened")
+        return ptr.value, ptrs
+
+    def buffer(self, shape, dtype, device=None) -> torch.Tensor:
+        """an exchange result buffer: world slots of numel / world elements each (collective: every rank, same order)"""
+        nbytes = int(torch.Size(shape).numel()) * torch.empty(0, dtype=dtype).element_size()
+        assert nbytes % (16 * self.world) == 0
+        slot = nbytes // self.world
+        box, boxes = self._symmetric(nbytes)
+        cnt, cnts = self._symmetric(max(256, 4 * self.world))
+        t = torch.as_tensor(_LibraryMemory(box, nbytes), device=self.dev).view(dtype).view(shape)
+        self.inboxes[t.data_ptr()] = {
+            "tensor": t, "slot": slot, "counters": cnt, "seq": 0,
+            "dst": torch.tensor([boxes[p] + self.rank * slot for p in range(self.world)], dtype=torch.int64, device=self.dev),
+            "flags": torch.tensor([cnts[p] + 4 * self.rank for p in range(self.world)], dtype=torch.int64, device=self.dev),
+            "tickets": torch.zeros(self.world, dtype=torch.int32, device=self.dev)}
+        return t
+
+    def _exchange(self, t: torch.Tensor, stride: int, nbytes: int, out: torch.Tensor) -> torch.Tensor:
+        b = self.inboxes[out.data_ptr()]
+        assert nbytes == b["slot"] and t.is_contiguous()
+        b["seq"] += 1
+        st = torch.cuda.current_stream().cuda_stream
+        self.capi.check(self.lib.b2moe_peer_put(t.data_ptr(), stride, nbytes, b["dst"].data_ptr(), b["flags"].data_ptr(), b["tickets"].data_ptr(),
+                                                self.world, b["seq"], st), "b2moe_peer_put")
+        self.capi.check(self.lib.b2moe_peer_wait(b["counters"], self.world, b["seq"], self.status.data_ptr(), st), "b2moe_peer_wait")
+        return out
+
+    def _own_buffer(self, kind, shape, dtype):
+        key = (kind, tuple(shape), dtype)
+        if key not in self.inboxes:
+            self.inboxes[key] = self.buffer(shape, dtype)
+        return self.inboxes[key]
+
+    def all_gather(self, t: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """every rank's t (same shape everywhere) stacked along dim 0 in rank order"""
+        if out is None:
+            out = self._own_buffer("ag", (self.world * t.shape[0],) + tuple(t.shape[1:]), t.dtype)
+        return self._exchange(t, 0, t.numel() * t.element_size(), out)
+
+    def all_to_all(self, t: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """t[p] goes to rank p; out[q] = what rank q sent here"""
+        if out is None:
+            out = self._own_buffer("a2a", tuple(t.shape), t.dtype)
+        n = t[0].numel() * t.element_size()
+        return self._exchange(t, n, n, out)
+
+    def check(self):
+        """raises if a wait ran out (reads one int from the device: call it outside timed regions)"""
+        v = int(self.status.item())
+        if v:
+            raise self.capi.B2moeError(self.capi.ERR_CUDA, f"the exchange with rank {v - 1} did not arrive within the wait's bound")
+
+    def close(self):
+        torch.cuda.synchronize()
+        for q in self.opened:
+            self.lib.b2moe_peer_close(q)
+        self.inboxes.clear()
+        for q in self.own:
+            self.lib.b2moe_peer_free(q)
+        self.opened, self.own = [], []
 
 
 def pack_tokens(x: torch.Tensor, ids: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -412,7 +530,7 @@ class GraphedEpForward:
         k = ids.shape[1]
         packed = bool(getattr(backend, "can_pack", None)) and backend.can_pack(x_local, k)
         self.rec = backend.pack_all(x_local, ids, w) if packed else pack_tokens(x_local, ids, w)
-        self.rec_all = torch.empty((G * T, self.rec.shape[1]), dtype=torch.uint8, device=dev)
+        self.rec_all = comm.buffer((G * T, self.rec.shape[1]), torch.uint8, dev)
         self.x_all = torch.empty((G * T,) + tuple(x_local.shape[1:]), dtype=x_local.dtype, device=dev)
         self.ids_all = torch.empty((G * T, k), dtype=ids.dtype, device=dev)
         self.w_all = torch.empty((G * T, k), dtype=w.dtype, device=dev)
@@ -424,7 +542,7 @@ class GraphedEpForward:
             unpack_tokens(self.rec_all, x_local.shape[1], k, x_local.dtype, self.x_all, self.ids_all, self.w_all)
             return backend.partial_sums(self.x_all, self.ids_all, self.w_all)
         parts, shared = local_phase()
-        self.recv = torch.empty((G, T, parts.shape[1]), dtype=parts.dtype, device=dev)
+        self.recv = comm.buffer((G, T, parts.shape[1]), parts.dtype, dev)
         comm.all_to_all(parts.view(G, T, -1), self.recv)
         backend.finish(self.recv, shared)
         stream.synchronize()
