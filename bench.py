@@ -824,13 +824,23 @@ def run_ep(args, torch, dist, capi, moe, synth, rank, world, local, dev):
         step()
         launches_per_step = int(lib.b2moe_harness_launches() - n0)
         stream.synchronize()
-        if args.graph:                   # only the compute phases are captured, no collective is
+        graph_note, whole = False, None
+        if args.graph and getattr(hc, "capturable", False):
+            # the peer-memory exchanges are the library's own kernels (bounded waits, device-side sequence numbers): the whole
+            # step, exchanges included, is one graph
+            whole = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(whole, stream=stream):
+                step_direct()
+            step = whole.replay
+            graph_note = "whole step, peer-memory exchanges included"
+        elif args.graph:                 # only the compute phases are captured, no collective is
             graphed = [ep.GraphedEpForward(e, hc, x) for e in eps]
 
             def step_graphed():
                 for l, gf in enumerate(graphed):
                     outs[l] = gf()
             step = step_graphed
+            graph_note = "compute phases only"
 
         def step_e2e():
             x.copy_(x_host, non_blocking=True)
@@ -882,7 +892,7 @@ def run_ep(args, torch, dist, capi, moe, synth, rank, world, local, dev):
     workloads = None
     if not args.no_extras and args.workload == "c2":
         del eps, layers
-        graphed = None
+        graphed = whole = step = None
         torch.cuda.empty_cache()
         workloads = {}
         for key, cfg, toks, a2a in (("c4_decode_16", "c4", 16, False), ("c4_prefill_2048", "c4", 2048, True), ("c5_prefill_8192", "c5", 8192, True)):
@@ -904,7 +914,7 @@ def run_ep(args, torch, dist, capi, moe, synth, rank, world, local, dev):
             "config": {"workload": workload_name(shape, T, L), "tokens": T, "layers": L, "router_scale": rscale,
                        "parallelism": f"ep{world}: {shape.experts // world} experts per GPU, {T} tokens per GPU, {exchange}",
                        "l2": "per-step expert weights exceed the 126 MB L2; no flush needed",
-                       "cuda_graph": "compute phases only" if args.graph else False, "iq3s_bank_layout": args.iq3s_layout},
+                       "cuda_graph": graph_note, "iq3s_bank_layout": args.iq3s_layout},
             "repeats": {"n": len(reg), "ms_per_step_median": ms_step, "ms_per_step_min": min(reg), "ms_per_step_max": max(reg)},
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": x_host.numel() * 2,
                     "d2h_bytes_per_step": out_host.numel() * 2},

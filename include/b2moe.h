@@ -296,8 +296,11 @@ B2MOE_API int32_t b2moe_ep_return_reduce(const float * back, const int32_t * pos
  *   b2moe_peer_free undo them. An inbox is an allocation with one slot per sender; a counter row is one int32 per sender.
  * b2moe_peer_put: for every peer p, `bytes` (a multiple of 16) from src + p * src_stride (stride 0: the same block to
  *   everyone) are stored to dst[p] (this sender's slot in p's inbox; device array of `peers` pointers) and then, after a
- *   system-wide fence, `seq` is stored to flags[p] (this sender's counter at p). tickets: `peers` zeroed int32 of local scratch.
- * b2moe_peer_wait: returns (on the stream) once each of the `peers` local counters has reached `seq`; a counter that has
+ *   system-wide fence, `seq` is stored to flags[p] (this sender's counter at p). tickets: `peers` + 2 zeroed int32 of local
+ *   scratch. seq <= 0: the launch numbers the exchange itself (one more than the last, kept in tickets[peers + 1]), so
+ *   that the same launch can be replayed from a CUDA graph.
+ * b2moe_peer_wait: returns (on the stream) once each of the `peers` local counters has reached `seq` (seq <= 0: one more
+ *   than at the last wait, kept in counters[peers]: the row needs peers + 1 words); a counter that has
  *   not after about half a second sets *status (device int32, 0 before) to 1 + its index and the kernel returns: it never
  *   spins without a bound. A slot may be written again only after its reader has finished with it; the order of an
  *   expert-parallel layer gives that (a rank sends exchange s + 1 only after it has received all of exchange s). */
@@ -307,7 +310,7 @@ B2MOE_API int32_t b2moe_peer_close(void * ptr);
 B2MOE_API int32_t b2moe_peer_free(void * ptr);
 B2MOE_API int32_t b2moe_peer_put(const void * src, size_t src_stride, size_t bytes, void * const * dst, int32_t * const * flags,
                        int32_t * tickets, int32_t peers, int32_t seq, b2moe_stream stream);
-B2MOE_API int32_t b2moe_peer_wait(const int32_t * counters, int32_t peers, int32_t seq, int32_t * status, b2moe_stream stream);
+B2MOE_API int32_t b2moe_peer_wait(int32_t * counters, int32_t peers, int32_t seq, int32_t * status, b2moe_stream stream);
 
 /* ---- GGUF expert reader and bank packer (host code, host pointers; no CUDA call) ------------------------------------
  * Replaces the expert-serving part of the reference's reader: gguf_expert_count / gguf_expert_slice

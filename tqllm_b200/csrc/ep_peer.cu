@@ -26,13 +26,15 @@ struct PutArgs {
     size_t bytes;               // bytes per peer, a multiple of 16
     void * const * dst;         // [peers] device array: this sender's slot in every peer's inbox
     int * const * flag;         // [peers] device array: this sender's counter in every peer's counter row
-    int * tickets;              // [peers] local scratch, zero between launches
-    int peers, blocks_per_peer, seq;
+    int * tickets;              // [peers + 2] local scratch: a ticket per peer and one for the launch (zero between launches), the sequence counter
+    int peers, blocks_per_peer, seq;   // seq <= 0: the number of this exchange is tickets[peers + 1] + 1, and the launch advances it
 };
 
 // grid = peers x blocks_per_peer; the last block of a peer's group to finish raises that peer's counter
 __global__ void __launch_bounds__(PUT_THREADS) peer_put_k(const PutArgs a) {
     const int peer = blockIdx.x / a.blocks_per_peer, part = blockIdx.x % a.blocks_per_peer;
+    // the counter is advanced by the last block of the launch to finish, after every block has read it (below)
+    const int seq = a.seq > 0 ? a.seq : *reinterpret_cast<volatile int *>(a.tickets + a.peers + 1) + 1;
     const uint4 * src = reinterpret_cast<const uint4 *>(a.src + size_t(peer) * a.src_stride);
     uint4 * dst = static_cast<uint4 *>(a.dst[peer]);
     const size_t n16 = a.bytes >> 4;
@@ -44,14 +46,22 @@ __global__ void __launch_bounds__(PUT_THREADS) peer_put_k(const PutArgs a) {
         if (ticket == a.blocks_per_peer - 1) {
             a.tickets[peer] = 0;                                        // ready for the next launch (stream order)
             __threadfence_system();
-            *reinterpret_cast<volatile int *>(a.flag[peer]) = a.seq;
+            *reinterpret_cast<volatile int *>(a.flag[peer]) = seq;
+        }
+        if (a.seq <= 0 && atomicAdd(a.tickets + a.peers, 1) == int(gridDim.x) - 1) {       // every block has its seq by now
+            a.tickets[a.peers] = 0;
+            a.tickets[a.peers + 1] = seq;
         }
     }
 }
 
-// one block; thread p waits for sender p's counter. status: 0 = all arrived, otherwise 1 + the first sender that did not
-__global__ void peer_wait_k(const int * counters, int peers, int seq, int * status) {
+// one block; thread p waits for sender p's counter. status: 0 = all arrived, otherwise 1 + the first sender that did not.
+// seq_in <= 0: the number of this exchange is counters[peers] + 1 (a word of the row that no sender writes), advanced here
+__global__ void peer_wait_k(int * counters, int peers, int seq_in, int * status) {
     const int p = threadIdx.x;
+    const int seq = seq_in > 0 ? seq_in : *reinterpret_cast<volatile int *>(counters + peers) + 1;
+    __syncthreads();                                                   // everyone has read the number before thread 0 advances it
+    if (seq_in <= 0 && p == 0) counters[peers] = seq;
     bool ok = true;
     if (p < peers) {
         const volatile int * c = counters + p;
@@ -110,7 +120,7 @@ extern "C" B2MOE_API int32_t b2moe_peer_put(const void * src, size_t src_stride,
     peer_put_k<<<peers * a.blocks_per_peer, PUT_THREADS, 0, as_stream(stream)>>>(a);
     return launch_status();
 }
-extern "C" B2MOE_API int32_t b2moe_peer_wait(const int32_t * counters, int32_t peers, int32_t seq, int32_t * status, b2moe_stream stream) {
+extern "C" B2MOE_API int32_t b2moe_peer_wait(int32_t * counters, int32_t peers, int32_t seq, int32_t * status, b2moe_stream stream) {
     if (!counters || !status) return B2MOE_ERR_NULL;
     if (peers <= 0 || peers > 1024) return B2MOE_ERR_SHAPE;
     peer_wait_k<<<1, (peers + 31) / 32 * 32, 0, as_stream(stream)>>>(counters, peers, seq, status);

@@ -119,7 +119,9 @@ class PeerComm:
     (b2moe_peer_put), a receiver waits, bounded, for all counters (b2moe_peer_wait). One process per GPU on one node. The
     process group is used for set-up only (the 64-byte memory handles). all_gather / all_to_all write into a tensor obtained
     from buffer() (or into an inbox of their own when none is given) and return it; the result stays valid until the next
-    exchange into the same buffer."""
+    exchange into the same buffer. The kernels number the exchanges themselves (device counters), so a sequence of layer
+    calls with their exchanges can be captured into a CUDA graph and replayed (`capturable`)."""
+    capturable = True
 
     def __init__(self, group=None):
         from . import capi
@@ -166,23 +168,22 @@ class PeerComm:
         assert nbytes % (16 * self.world) == 0
         slot = nbytes // self.world
         box, boxes = self._symmetric(nbytes)
-        cnt, cnts = self._symmetric(max(256, 4 * self.world))
+        cnt, cnts = self._symmetric(max(256, 4 * (self.world + 1)))
         t = torch.as_tensor(_LibraryMemory(box, nbytes), device=self.dev).view(dtype).view(shape)
         self.inboxes[t.data_ptr()] = {
-            "tensor": t, "slot": slot, "counters": cnt, "seq": 0,
+            "tensor": t, "slot": slot, "counters": cnt,
             "dst": torch.tensor([boxes[p] + self.rank * slot for p in range(self.world)], dtype=torch.int64, device=self.dev),
             "flags": torch.tensor([cnts[p] + 4 * self.rank for p in range(self.world)], dtype=torch.int64, device=self.dev),
-            "tickets": torch.zeros(self.world, dtype=torch.int32, device=self.dev)}
+            "tickets": torch.zeros(self.world + 2, dtype=torch.int32, device=self.dev)}
         return t
 
     def _exchange(self, t: torch.Tensor, stride: int, nbytes: int, out: torch.Tensor) -> torch.Tensor:
         b = self.inboxes[out.data_ptr()]
         assert nbytes == b["slot"] and t.is_contiguous()
-        b["seq"] += 1
         st = torch.cuda.current_stream().cuda_stream
         self.capi.check(self.lib.b2moe_peer_put(t.data_ptr(), stride, nbytes, b["dst"].data_ptr(), b["flags"].data_ptr(), b["tickets"].data_ptr(),
-                                                self.world, b["seq"], st), "b2moe_peer_put")
-        self.capi.check(self.lib.b2moe_peer_wait(b["counters"], self.world, b["seq"], self.status.data_ptr(), st), "b2moe_peer_wait")
+                                                self.world, 0, st), "b2moe_peer_put")
+        self.capi.check(self.lib.b2moe_peer_wait(b["counters"], self.world, 0, self.status.data_ptr(), st), "b2moe_peer_wait")
         return out
 
     def _own_buffer(self, kind, shape, dtype):
