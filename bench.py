@@ -742,6 +742,7 @@ def ep_record(torch, dist, moe, synth, ep, comm, stream, dev, rank, world, cfg, 
     def timed(order_of):
         eps, note = ep_layers(torch, moe, synth, ep, shape, 1, rank, world, dev, layout, zipf_tokens=zx, order_of=order_of)
         with torch.cuda.stream(stream):
+            dist.barrier()                                               # the ranks finish building their layers at different times
             for _ in range(2):
                 fwd(eps[0], comm, x)
             dist.barrier()
@@ -828,11 +829,21 @@ def run_ep(args, torch, dist, capi, moe, synth, rank, world, local, dev):
         if args.graph and getattr(hc, "capturable", False):
             # the peer-memory exchanges are the library's own kernels (bounded waits, device-side sequence numbers): the whole
             # step, exchanges included, is one graph
-            whole = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(whole, stream=stream):
-                step_direct()
-            step = whole.replay
-            graph_note = "whole step, peer-memory exchanges included"
+            captured = 1
+            try:
+                whole = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(whole, stream=stream):
+                    step_direct()
+            except Exception:
+                captured, whole = 0, None
+            flag = torch.tensor([captured], dtype=torch.int32, device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)                 # every rank replays a graph or none does; also: nobody replays
+            torch.cuda.synchronize()                                     # (and waits on a peer) while a peer is still capturing
+            if int(flag):
+                step = whole.replay
+                graph_note = "whole step, peer-memory exchanges included"
+            else:
+                whole = None
         elif args.graph:                 # only the compute phases are captured, no collective is
             graphed = [ep.GraphedEpForward(e, hc, x) for e in eps]
 

@@ -301,7 +301,7 @@ B2MOE_API int32_t b2moe_ep_return_reduce(const float * back, const int32_t * pos
  *   that the same launch can be replayed from a CUDA graph.
  * b2moe_peer_wait: returns (on the stream) once each of the `peers` local counters has reached `seq` (seq <= 0: one more
  *   than at the last wait, kept in counters[peers]: the row needs peers + 1 words); a counter that has
- *   not after about half a second sets *status (device int32, 0 before) to 1 + its index and the kernel returns: it never
+ *   not after two to three seconds sets *status (device int32, 0 before) to 1 + its index and the kernel returns: it never
  *   spins without a bound. A slot may be written again only after its reader has finished with it; the order of an
  *   expert-parallel layer gives that (a rank sends exchange s + 1 only after it has received all of exchange s). */
 B2MOE_API int32_t b2moe_peer_alloc(size_t bytes, void ** ptr, uint8_t handle[64]);

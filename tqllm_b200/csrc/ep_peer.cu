@@ -18,7 +18,7 @@ namespace b2 {
 namespace {
 
 constexpr int PUT_THREADS = 256;
-constexpr uint32_t PEER_WAIT_TRIES = 1u << 22;     // polls of about 100 ns: the wait gives up after roughly half a second
+constexpr uint32_t PEER_WAIT_TRIES = 1u << 24;     // polls of 100 to 200 ns: the wait gives up after two to three seconds
 
 struct PutArgs {
     const uint8_t * src;        // the sender's data

@@ -136,16 +136,20 @@ class PeerComm:
     def _symmetric(self, nbytes: int):
         """a zeroed allocation of nbytes on every rank -> (own pointer, [every rank's pointer as seen from here])"""
         ptr, handle = C.c_void_p(), (C.c_uint8 * 64)()
-        self.capi.check(self.lib.b2moe_peer_alloc(nbytes, C.byref(ptr), handle), "b2moe_peer_alloc")
-        self.own.append(ptr.value)
+        failed = int(self.lib.b2moe_peer_alloc(nbytes, C.byref(ptr), handle) != 0)
+        if not failed:
+            self.own.append(ptr.value)
         if self.world == 1:
+            if failed:
+                raise self.capi.B2moeError(self.capi.ERR_CUDA, "b2moe_peer_alloc failed")
             return ptr.value, [ptr.value]
+        # a rank that failed still takes part in the two collectives below, so that all ranks give up together
         mine = torch.tensor(list(handle), dtype=torch.uint8, device=self.dev)
         every = torch.empty(self.world * 64, dtype=torch.uint8, device=self.dev)
         dist.all_gather_into_tensor(every, mine, group=self.group)
         every = every.cpu().view(self.world, 64)
-        ptrs, failed = [], 0
-        for p in range(self.world):
+        ptrs = []
+        for p in range(self.world if not failed else 0):
             if p == self.rank:
                 ptrs.append(ptr.value)
                 continue
@@ -159,7 +163,7 @@ class PeerComm:
         bad = torch.tensor([failed], dtype=torch.int32, device=self.dev)
         dist.all_reduce(bad, op=dist.ReduceOp.MAX, group=self.group)      # every rank learns of a failure: they give up together
         if int(bad):
-            raise self.capi.B2moeError(self.capi.ERR_CUDA, "a peer's memory handle could not be opened")
+            raise self.capi.B2moeError(self.capi.ERR_CUDA, "an inbox could not be allocated or a peer's memory handle could not be opened")
         return ptr.value, ptrs
 
     def buffer(self, shape, dtype, device=None) -> torch.Tensor:
