@@ -87,7 +87,12 @@ extern "C" B2MOE_API int32_t b2moe_peer_alloc(size_t bytes, void ** ptr, uint8_t
     void * p = nullptr;
     if (cudaMalloc(&p, bytes) != cudaSuccess) return B2MOE_ERR_CUDA;
     cudaIpcMemHandle_t h;
-    if (cudaMemset(p, 0, bytes) != cudaSuccess || cudaIpcGetMemHandle(&h, p) != cudaSuccess) { cudaFree(p); cudaGetLastError(); return B2MOE_ERR_CUDA; }
+    // the zeroing must have finished before any peer can write here: wait for it (set-up time, never inside a capture)
+    if (cudaMemset(p, 0, bytes) != cudaSuccess || cudaStreamSynchronize(nullptr) != cudaSuccess || cudaIpcGetMemHandle(&h, p) != cudaSuccess) {
+        cudaFree(p);
+        cudaGetLastError();
+        return B2MOE_ERR_CUDA;
+    }
     std::memcpy(handle, &h, 64);
     *ptr = p;
     return B2MOE_OK;
