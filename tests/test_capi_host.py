@@ -97,6 +97,17 @@ def test_arguments_are_rejected_before_any_launch():
     assert lib.b2moe_expert_down(C.byref(iq), None, 16, 16, 2, 2, 0, 16, None, 0, None) == capi.ERR_NULL        # needs scratch
     assert lib.b2moe_expert_down(C.byref(iq), None, 16, 16, 2, 2, 0, 16, 32, 64, None) == capi.ERR_WORKSPACE
     assert lib.b2moe_combine(16, None, 16, None, 2, 2, 30, 0, 16, capi.F32, None) == capi.ERR_SHAPE
+    # the peer-memory exchange: pointer, size and alignment checks come before any CUDA call
+    assert lib.b2moe_peer_put(None, 0, 64, 16, 16, 16, 2, 1, None) == capi.ERR_NULL
+    assert lib.b2moe_peer_put(16, 0, 60, 16, 16, 16, 2, 1, None) == capi.ERR_SHAPE         # bytes: a multiple of 16
+    assert lib.b2moe_peer_put(16, 8, 64, 16, 16, 16, 2, 1, None) == capi.ERR_SHAPE         # stride: a multiple of 16
+    assert lib.b2moe_peer_put(24, 0, 64, 16, 16, 16, 2, 1, None) == capi.ERR_ALIGN
+    assert lib.b2moe_peer_put(16, 0, 64, 16, 16, 16, 0, 1, None) == capi.ERR_SHAPE
+    assert lib.b2moe_peer_wait(None, 2, 1, 16, None) == capi.ERR_NULL
+    assert lib.b2moe_peer_wait(16, 0, 1, 16, None) == capi.ERR_SHAPE
+    assert lib.b2moe_peer_alloc(0, C.byref(C.c_void_p()), (C.c_uint8 * 64)()) == capi.ERR_SHAPE
+    assert lib.b2moe_peer_open(None, C.byref(C.c_void_p())) == capi.ERR_NULL
+    assert lib.b2moe_peer_close(None) == capi.ERR_NULL and lib.b2moe_peer_free(None) == capi.ERR_NULL
     with pytest.raises(capi.B2moeError):
         capi.check(capi.ERR_WORKSPACE, "x")
 
