@@ -12,8 +12,10 @@
  *   - assignment a = token * topk + slot; per-assignment outputs are [n * topk][rows];
  *   - every entry point is stream-ordered, does no host synchronisation and allocates nothing: scratch comes from a
  *     caller-provided workspace, and the library keeps no mutable state between calls (re-entrant across streams).
- *     Two exceptions, both stated where they are declared: b2moe_expert_down_static keeps its scratch in one array
- *     inside the library, and the b2moe_harness_* hooks set process-wide switches for tests and benchmarks;
+ *     Exceptions, each stated where it is declared: b2moe_expert_down_static keeps its scratch in one array inside the
+ *     library; the b2moe_harness_* hooks set process-wide switches for tests and benchmarks; b2moe_peer_alloc /
+ *     b2moe_peer_open (set-up of the multi-GPU exchange, called once, outside any step) allocate and map device memory
+ *     and synchronise with the device, and b2moe_gguf_* is host code that maps a file;
  *   - return value: 0 = ok, otherwise a b2moe_status code (b2moe_status_string gives the text). Nothing is launched
  *     when the arguments are rejected. There is no CPU fallback: without a CUDA device every compute entry point
  *     returns B2MOE_ERR_CUDA.
